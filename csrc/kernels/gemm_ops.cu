@@ -1,0 +1,643 @@
+// GEMM kernels of iris_b200 for sm_100a: the local GEMM and the fused compute+collective ops
+//   all_gather_matmul      (reference iris/ops/all_gather_matmul.py:27-159, examples/14 push variant)
+//   matmul_all_gather      (iris/ops/matmul_all_gather.py:28-105; examples/07 all-scatter layout)
+//   matmul_reduce_scatter  (iris/ops/matmul_reduce_scatter.py:26-118; examples/22 row-chunk ownership)
+//   matmul_all_reduce      (iris/ops/matmul_all_reduce.py:26-144)
+// all built on include/iris/gemm/sm100_mainloop.cuh (TMA -> smem ring -> tcgen05.mma -> TMEM).
+// The collective half of each op runs inside the same kernel: peer stores / NVLS multimem stores
+// issued from the epilogue warps or from dedicated communication CTAs, per-tile flags on the
+// symmetric heap, bounded waits.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <string.h>
+#include <stdio.h>
+
+#include "iris/host_api.h"
+#include "iris/context.cuh"
+#include "iris/rma.cuh"
+#include "iris/sync.cuh"
+#include "iris/multimem.cuh"
+#include "iris/gemm/sm100_mainloop.cuh"
+
+using namespace iris;
+using namespace iris::gemm;
+
+static_assert(sizeof(IrisCtx) == sizeof(DeviceContext), "IrisCtx must mirror iris::DeviceContext");
+
+namespace {
+
+struct Common {
+  CUtensorMap tmA;
+  CUtensorMap tmB;
+  Shape sh;
+  int tiles_m, tiles_n, group_m;
+  int n_gemm_ctas;
+  int bf16;
+  int bn;
+  const float* bias_row;
+  const float* bias_col;
+  int32_t* status;
+
+  IRIS_D Shape shape() const { return sh; }
+  IRIS_D int gemm_ctas() const { return n_gemm_ctas; }
+  IRIS_D int num_tiles() const { return tiles_m * tiles_n; }
+  IRIS_D const CUtensorMap* b_map() const { return &tmB; }
+  IRIS_D bool is_bf16() const { return bf16 != 0; }
+  IRIS_D bool has_bias() const { return bias_row != nullptr || bias_col != nullptr; }
+  IRIS_D float row_bias(int row) const { return (bias_row && row < sh.M) ? bias_row[row] : 0.f; }
+  IRIS_D float col_bias(int col) const { return (bias_col && col < sh.N) ? bias_col[col] : 0.f; }
+  IRIS_D void fail(int code) const {
+    if (status) atomicCAS(status, 0, code);
+  }
+};
+
+// ------------------------------------------------------------------------------------ local GEMM
+struct LocalGemm : Common {
+  uint8_t* C;
+  int64_t ldc;
+  struct State {};
+  IRIS_D void tile(int t, int& tm, int& tn) const { swizzled_tile(t, tiles_m, tiles_n, group_m, tm, tn); }
+  IRIS_D bool a_source(State&, int tm, int kb, ASource& s) const {
+    s.map = &tmA; s.x = kb * kBK; s.y = tm * kBM; s.bk = kb * kBK;
+    return true;
+  }
+  IRIS_D void begin_tile(State&, int, int) const {}
+  IRIS_D void store16(State&, int row, int col, uint4 v) const {
+    if (row < sh.M && col < sh.N) *(uint4*)(C + ((int64_t)row * ldc + col) * 2) = v;
+  }
+  IRIS_D void tile_done(State&, int, int) const {}
+  IRIS_D void comm_main() const {}
+  IRIS_D void post_main() const {}
+};
+
+// ------------------------------------------------------------------------------------ AG + GEMM
+// A is sharded over ranks (rows: mode 0, K: mode 1). Communication CTAs push this rank's shard
+// into every peer's inbox (one multimem.st through the switch when NVLS is on, else one store per
+// peer) and bump a per-(source, 128-row chunk) arrival counter with release semantics. The TMA
+// producer of a GEMM CTA polls the counter of the chunk it is about to read (acquire) and then
+// loads from its OWN memory: a remote tile crosses NVLink once, whatever the number of N tiles.
+// The inbox and the counters are double-buffered by call parity; waiting for every source's
+// counters in call k proves every rank left call k-1, so buffer reuse needs no extra barrier.
+struct AllGatherGemm : Common {
+  CUtensorMap tmInbox;     // rows = 2 * W * rows_per_src, cols = cols_per_src
+  DeviceContext ctx;
+  SyncBlock* sb;
+  const uint8_t* A_local;  // this rank's shard, row pitch lda (elements)
+  int64_t lda;
+  uint8_t* inbox;          // heap, buffer 0 of [2][W][rows_per_src][cols_per_src]
+  int32_t* flags;          // heap, [2][W][chunks]
+  uint8_t* C;
+  int64_t ldc;
+  int mode;                // 0: rows sharded, 1: K sharded
+  int rows_per_src;        // mode 0: M_local, mode 1: M
+  int cols_per_src;        // mode 0: K, mode 1: K_local
+  int chunks;              // 128-row chunks per source
+  int n_comm_ctas;
+  int use_mc;
+
+  struct State {
+    int key = -1;
+    int epoch = -1;
+  };
+  IRIS_D int src_of_group(int g) const {  // own shard first, then the order the pushes arrive in
+    int s = ctx.rank - g;
+    return s < 0 ? s + ctx.world : s;
+  }
+  IRIS_D void tile(int t, int& tm, int& tn) const {
+    if (mode == 0) {
+      const int per_src = chunks * tiles_n;
+      const int g = t / per_src;
+      int lm, ln;
+      swizzled_tile(t - g * per_src, chunks, tiles_n, group_m, lm, ln);
+      tm = src_of_group(g) * chunks + lm;
+      tn = ln;
+    } else {
+      swizzled_tile(t, tiles_m, tiles_n, group_m, tm, tn);
+    }
+  }
+  IRIS_D bool a_source(State& st, int tm, int kb, ASource& s) const {
+    if (st.epoch < 0) st.epoch = read_epoch(sb);
+    const int buf = st.epoch & 1;
+    const int target = ((st.epoch >> 1) + 1) * n_comm_ctas;
+    int src, chunk, x;
+    if (mode == 0) {
+      src = tm / chunks; chunk = tm - src * chunks; x = kb * kBK; s.bk = x;
+    } else {
+      const int kb_per_src = cols_per_src / kBK;
+      const int g = kb / kb_per_src;
+      src = src_of_group(g); chunk = tm; x = (kb - g * kb_per_src) * kBK; s.bk = src * cols_per_src + x;
+    }
+    if (src == ctx.rank && !use_mc) {
+      s.map = &tmA; s.x = x; s.y = chunk * kBM;
+      return true;
+    }
+    const int key = src * chunks + chunk;
+    if (key != st.key) {
+      if (!wait_flag_ge(ctx, flags + ((size_t)buf * ctx.world + src) * chunks + chunk, target)) return false;
+      st.key = key;
+      // The data was written by another GPU (generic proxy, remote); order the TMA (async proxy)
+      // reads after the acquire.
+      ptx::fence_proxy_async();
+    }
+    s.map = &tmInbox; s.x = x; s.y = ((buf * ctx.world + src) * rows_per_src) + chunk * kBM;
+    return true;
+  }
+  IRIS_D void begin_tile(State&, int, int) const {}
+  IRIS_D void store16(State&, int row, int col, uint4 v) const {
+    if (row < sh.M && col < sh.N) *(uint4*)(C + ((int64_t)row * ldc + col) * 2) = v;
+  }
+  IRIS_D void tile_done(State&, int, int) const {}
+
+  // Communication CTAs: CTA j moves slice j (of n_comm_ctas) of every 128-row chunk, chunk by
+  // chunk, so chunk 0 is complete everywhere first.
+  IRIS_D void comm_main() const {
+    const int j = blockIdx.x - n_gemm_ctas;
+    const int epoch = read_epoch(sb);
+    const int buf = epoch & 1;
+    const size_t row_bytes = (size_t)cols_per_src * 2;
+    const size_t vec_per_row = row_bytes / 16;
+    for (int c = 0; c < chunks; ++c) {
+      const int r0 = c * kBM;
+      const int nrows = min(kBM, rows_per_src - r0);
+      // slice the chunk by rows
+      const int rows_lo = (int)((int64_t)nrows * j / n_comm_ctas), rows_hi = (int)((int64_t)nrows * (j + 1) / n_comm_ctas);
+      const size_t nvec = (size_t)(rows_hi - rows_lo) * vec_per_row;
+      uint8_t* dst_local = inbox + (((size_t)buf * ctx.world + ctx.rank) * rows_per_src + r0 + rows_lo) * row_bytes;
+      int32_t* flag_local = flags + ((size_t)buf * ctx.world + ctx.rank) * chunks + c;
+      if (use_mc) {
+        uint8_t* dst = ctx.mc(dst_local);
+        for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+          const size_t rr = i / vec_per_row, cc = i - rr * vec_per_row;
+          const multimem::V4 v = *(const multimem::V4*)(A_local + ((size_t)(r0 + rows_lo + rr) * lda) * 2 + cc * 16);
+          multimem::st_v4(dst + rr * row_bytes + cc * 16, v);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          fence_sys();
+          multimem::red_release_add_u32(ctx.mc(flag_local), 1);
+        }
+      } else {
+        for (int p = 1; p < ctx.world; ++p) {
+          int dst_rank = ctx.rank + p;
+          if (dst_rank >= ctx.world) dst_rank -= ctx.world;
+          uint8_t* dst = ctx.remote(dst_local, dst_rank);
+          // 8 independent 16-byte loads in flight per thread, then the 8 peer stores
+          const uint8_t* src0 = A_local + ((size_t)(r0 + rows_lo) * lda) * 2;
+          const size_t src_pitch = (size_t)lda * 2;
+          size_t i = threadIdx.x;
+          for (; i + 7 * (size_t)blockDim.x < nvec; i += 8 * (size_t)blockDim.x) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const size_t k = i + u * (size_t)blockDim.x, rr = k / vec_per_row, cc = k - rr * vec_per_row;
+              v[u] = *(const uint4*)(src0 + rr * src_pitch + cc * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const size_t k = i + u * (size_t)blockDim.x, rr = k / vec_per_row, cc = k - rr * vec_per_row;
+              *(uint4*)(dst + rr * row_bytes + cc * 16) = v[u];
+            }
+          }
+          for (; i < nvec; i += blockDim.x) {
+            const size_t rr = i / vec_per_row, cc = i - rr * vec_per_row;
+            *(uint4*)(dst + rr * row_bytes + cc * 16) = *(const uint4*)(src0 + rr * src_pitch + cc * 16);
+          }
+          __syncthreads();
+          if (threadIdx.x == 0) {
+            fence_sys();
+            red_release_sys_add(ctx.remote(flag_local, dst_rank), 1);
+          }
+        }
+      }
+    }
+    finish();
+  }
+  IRIS_D void post_main() const { finish(); }
+  // Count finished CTAs; the last one advances the call counter (no cross-rank round needed).
+  IRIS_D void finish() const {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int e = read_epoch(sb);
+      __threadfence();
+      if (atomicAdd(&sb->done, 1) == (int)gridDim.x - 1) {
+        sb->done = 0;
+        sb->epoch = e + 1;
+        __threadfence();
+      }
+    }
+  }
+};
+
+// ------------------------------------------------------------------------- GEMM + push epilogues
+// mode ALL_GATHER / ALL_SCATTER: the epilogue stores each 16-byte output fragment to every rank
+// (multimem.st, or one store per peer). The last CTA runs one cross-rank round before the kernel
+// ends, so every rank's output is complete when its kernel completes.
+// mode REDUCE_SCATTER / ALL_REDUCE / RS_TILES: each output tile has an owner rank. Every rank
+// stores its partial tile (16-bit) into the owner's staging slot for (source, tile) and adds 1 to
+// the owner's arrival counter for that tile (release, system scope). After its own GEMM tiles a
+// CTA turns reducer: it waits (acquire) until a tile it owns has W arrivals, sums the W partials
+// in fp32 and writes the result: to its own output (reduce-scatter) or to all ranks (all-reduce).
+// Staging and counters are double-buffered by call parity, as in AllGatherGemm.
+struct ScatterGemm : Common {
+  DeviceContext ctx;
+  SyncBlock* sb;
+  int mode;               // IrisGemmOp
+  uint8_t* out;           // final output; heap pointer when peers write it (AG / AR / ALL_SCATTER)
+  int64_t ld_out;
+  uint8_t* staging;       // heap: [2][W][max_owned][128*bn] 16-bit
+  int32_t* flags;         // heap: [2][max_owned]
+  int max_owned;          // owned tiles per rank (upper bound used for addressing)
+  int tiles_m_per_rank;   // REDUCE_SCATTER: row tiles per owner
+  int tiles_per_rank;     // RS_TILES: contiguous tile block per owner
+  int use_mc;
+
+  struct State {
+    int buf = -1;
+    int row0 = 0, col0 = 0;
+    int owner = 0, lt = 0;
+    uint8_t* slot = nullptr;   // owner's staging slot for (me, tile), already translated
+  };
+  // owner rank and the tile's index among the owner's tiles
+  IRIS_D void owner_of(int tm, int tn, int& owner, int& lt) const {
+    if (mode == IRIS_GEMM_REDUCE_SCATTER) {
+      owner = tm / tiles_m_per_rank;
+      lt = (tm - owner * tiles_m_per_rank) * tiles_n + tn;
+    } else if (mode == IRIS_GEMM_ALL_REDUCE) {
+      const int t = tm * tiles_n + tn;
+      owner = t % ctx.world;
+      lt = t / ctx.world;
+    } else {  // RS_TILES: contiguous blocks, last rank takes the remainder
+      const int t = tm * tiles_n + tn;
+      owner = min(t / tiles_per_rank, ctx.world - 1);
+      lt = t - owner * tiles_per_rank;
+    }
+  }
+  IRIS_D void tile(int t, int& tm, int& tn) const {
+    if (mode == IRIS_GEMM_REDUCE_SCATTER) {
+      // other owners' rows first (next rank first), my own rows last
+      const int per_owner = tiles_m_per_rank * tiles_n;
+      const int g = t / per_owner;
+      int owner = ctx.rank + 1 + g;
+      if (owner >= ctx.world) owner -= ctx.world;
+      int lm, ln;
+      swizzled_tile(t - g * per_owner, tiles_m_per_rank, tiles_n, group_m, lm, ln);
+      tm = owner * tiles_m_per_rank + lm;
+      tn = ln;
+    } else {
+      swizzled_tile(t, tiles_m, tiles_n, group_m, tm, tn);
+    }
+  }
+  IRIS_D bool a_source(State&, int tm, int kb, ASource& s) const {
+    s.map = &tmA; s.x = kb * kBK; s.y = tm * kBM; s.bk = kb * kBK;
+    return true;
+  }
+  IRIS_D void begin_tile(State& st, int tm, int tn) const {
+    if (!reducing()) return;
+    if (st.buf < 0) st.buf = read_epoch(sb) & 1;
+    owner_of(tm, tn, st.owner, st.lt);
+    st.row0 = tm * kBM; st.col0 = tn * bn;
+    uint8_t* slot = staging + ((((size_t)st.buf * ctx.world + ctx.rank) * max_owned + st.lt) * (size_t)(kBM * bn)) * 2;
+    st.slot = ctx.remote(slot, st.owner);
+  }
+  IRIS_D bool reducing() const {
+    return mode == IRIS_GEMM_REDUCE_SCATTER || mode == IRIS_GEMM_ALL_REDUCE || mode == IRIS_GEMM_RS_TILES;
+  }
+  IRIS_D void store_everywhere(uint8_t* local_ptr, uint4 v) const {
+    if (use_mc) {
+      multimem::V4 m{v.x, v.y, v.z, v.w};
+      multimem::st_v4(ctx.mc(local_ptr), m);
+    } else {
+      *(uint4*)local_ptr = v;
+      for (int p = 1; p < ctx.world; ++p) {
+        int r = ctx.rank + p;
+        if (r >= ctx.world) r -= ctx.world;
+        *(uint4*)ctx.remote(local_ptr, r) = v;
+      }
+    }
+  }
+  IRIS_D void store16(State& st, int row, int col, uint4 v) const {
+    if (row >= sh.M || col >= sh.N) return;
+    if (mode == IRIS_GEMM_ALL_GATHER) {
+      store_everywhere(out + (((int64_t)ctx.rank * sh.M + row) * ld_out + col) * 2, v);
+    } else if (mode == IRIS_GEMM_ALL_SCATTER) {
+      store_everywhere(out + ((int64_t)row * ld_out + (int64_t)ctx.rank * sh.N + col) * 2, v);
+    } else {
+      *(uint4*)(st.slot + ((size_t)(row - st.row0) * bn + (col - st.col0)) * 2) = v;
+    }
+  }
+  IRIS_D void tile_done(State& st, int, int) const {
+    if (!reducing()) return;
+    fence_sys();
+    red_release_sys_add(ctx.remote(flags + (size_t)st.buf * max_owned + st.lt, st.owner), 1);
+  }
+  IRIS_D void comm_main() const {}
+
+  IRIS_D int owned_tiles() const {
+    const int total = tiles_m * tiles_n;
+    if (mode == IRIS_GEMM_REDUCE_SCATTER) return tiles_m_per_rank * tiles_n;
+    if (mode == IRIS_GEMM_ALL_REDUCE) return (total - ctx.rank + ctx.world - 1) / ctx.world;
+    if (ctx.rank == ctx.world - 1) return total - tiles_per_rank * (ctx.world - 1);
+    return tiles_per_rank;
+  }
+  // global (tm, tn) of my owned tile `lt`
+  IRIS_D void owned_tile(int lt, int& tm, int& tn) const {
+    int t;
+    if (mode == IRIS_GEMM_REDUCE_SCATTER) {
+      tm = ctx.rank * tiles_m_per_rank + lt / tiles_n;
+      tn = lt % tiles_n;
+      return;
+    } else if (mode == IRIS_GEMM_ALL_REDUCE) {
+      t = lt * ctx.world + ctx.rank;
+    } else {
+      t = ctx.rank * tiles_per_rank + lt;
+    }
+    tm = t / tiles_n;
+    tn = t % tiles_n;
+  }
+  IRIS_D void post_main() const {
+    const int epoch = read_epoch(sb);
+    if (reducing()) {
+      __shared__ int s_ok;
+      const int buf = epoch & 1;
+      const int target = ((epoch >> 1) + 1) * ctx.world;
+      const int n_owned = owned_tiles();
+      const int vec_per_row = bn / 8;
+      for (int lt = blockIdx.x; lt < n_owned; lt += n_gemm_ctas) {
+        if (threadIdx.x == 0) s_ok = wait_flag_ge(ctx, flags + (size_t)buf * max_owned + lt, target) ? 1 : 0;
+        __syncthreads();
+        const bool ok = s_ok != 0;
+        __syncthreads();
+        if (!ok) break;
+        int tm, tn;
+        owned_tile(lt, tm, tn);
+        const int rows = min(kBM, sh.M - tm * kBM);
+        const int cols = min(bn, sh.N - tn * bn);
+        for (int i = threadIdx.x; i < rows * vec_per_row; i += blockDim.x) {
+          const int rr = i / vec_per_row, cv = i - rr * vec_per_row;
+          if (cv * 8 >= cols) continue;
+          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int s = 0; s < ctx.world; ++s) {
+            const uint8_t* slot = staging + ((((size_t)buf * ctx.world + s) * max_owned + lt) * (size_t)(kBM * bn)) * 2;
+            const uint4 v = *(const uint4*)(slot + ((size_t)rr * bn + cv * 8) * 2);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float2 f = bf16 ? __bfloat1622float2(*(const __nv_bfloat162*)&w[q]) : __half22float2(*(const __half2*)&w[q]);
+              acc[2 * q] += f.x; acc[2 * q + 1] += f.y;
+            }
+          }
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (bf16) { __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]); o[q] = *(uint32_t*)&h; }
+            else { __half2 h = __floats2half2_rn(acc[2 * q], acc[2 * q + 1]); o[q] = *(uint32_t*)&h; }
+          }
+          const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+          const int grow = tm * kBM + rr, gcol = tn * bn + cv * 8;
+          if (mode == IRIS_GEMM_REDUCE_SCATTER) {
+            *(uint4*)(out + ((int64_t)(grow - ctx.rank * tiles_m_per_rank * kBM) * ld_out + gcol) * 2) = ov;
+          } else if (mode == IRIS_GEMM_RS_TILES) {
+            *(uint4*)(out + ((int64_t)grow * ld_out + gcol) * 2) = ov;
+          } else {
+            store_everywhere(out + ((int64_t)grow * ld_out + gcol) * 2, ov);
+          }
+        }
+      }
+    }
+    const bool peers_write_out = mode == IRIS_GEMM_ALL_GATHER || mode == IRIS_GEMM_ALL_SCATTER || mode == IRIS_GEMM_ALL_REDUCE;
+    if (peers_write_out) {
+      grid_exit_barrier(ctx, sb, epoch, 0);
+    } else {
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&sb->done, 1) == (int)gridDim.x - 1) {
+          sb->done = 0;
+          sb->epoch = epoch + 1;
+          __threadfence();
+        }
+      }
+    }
+  }
+};
+
+// ------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess) fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+// 2-D map over a row-major [rows, cols] 16-bit matrix with pitch `ld` elements; box = box_cols x box_rows.
+int make_map(CUtensorMap* m, const void* base, int dtype, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+             uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -10;
+  if (((uint64_t)base & 15) || ((ld * 2) & 15)) return -11;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = dtype == IRIS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(m, dt, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Tile width: fewest waves over `ctas` persistent CTAs, weighted by tile cost; ties to the wider.
+int choose_bn(int M, int N, int ctas, bool mn_major) {
+  const int cand[3] = {256, 224, 128};
+  double best = 1e30;
+  int best_bn = 256;
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cand[i];
+    const int tiles = ceil_div(M, kBM) * ceil_div(N, bn);
+    const int waves = ceil_div(tiles, ctas);
+    // cost of a tile ~ its MMA time; a 128-wide tile runs at lower efficiency (more smem traffic per flop)
+    const double cost = waves * (double)bn * (bn == 128 ? 1.12 : 1.0);
+    if (cost < best - 1e-9) { best = cost; best_bn = bn; }
+  }
+  (void)mn_major;
+  return best_bn;
+}
+
+template <class Cfg, class Policy>
+int launch(const Policy& pol, int grid, cudaStream_t stream) {
+  auto kern = gemm_kernel<Cfg, Policy>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return -20;
+    attr_set = true;
+  }
+  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(pol);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+template <class Policy>
+int dispatch(const Policy& pol, int bn, bool kmajor, int grid, cudaStream_t stream) {
+  if (kmajor) {
+    if (bn == 256) return launch<Config<256, true, 4>>(pol, grid, stream);
+    if (bn == 224) return launch<Config<224, true, 4>>(pol, grid, stream);
+    if (bn == 128) return launch<Config<128, true, 6>>(pol, grid, stream);
+  } else {
+    if (bn == 256) return launch<Config<256, false, 4>>(pol, grid, stream);
+    if (bn == 224) return launch<Config<224, false, 4>>(pol, grid, stream);
+    if (bn == 128) return launch<Config<128, false, 6>>(pol, grid, stream);
+  }
+  return -30;
+}
+
+int fill_common(Common& c, const IrisGemmDesc* d, int bn, int gemm_ctas, const void* A, uint64_t a_rows, uint64_t a_cols,
+                int64_t lda) {
+  if (d->dtype != IRIS_BF16 && d->dtype != IRIS_F16) return -2;
+  if (d->N % 8 || d->K % 8) return -3;
+  int r = make_map(&c.tmA, A, d->dtype, a_rows, a_cols, lda, kBK, kBM);
+  if (r) return r;
+  if (d->b_kmajor) r = make_map(&c.tmB, d->B, d->dtype, d->N, d->K, d->ldb, kBK, bn);
+  else r = make_map(&c.tmB, d->B, d->dtype, d->K, d->N, d->ldb, 64, 64);
+  if (r) return r;
+  c.sh = Shape{d->M, d->N, d->K};
+  c.tiles_m = ceil_div(d->M, kBM);
+  c.tiles_n = ceil_div(d->N, bn);
+  c.group_m = d->group_m > 0 ? d->group_m : 8;
+  c.n_gemm_ctas = gemm_ctas;
+  c.bf16 = d->dtype == IRIS_BF16;
+  c.bn = bn;
+  c.bias_row = d->bias_row;
+  c.bias_col = d->bias_col;
+  c.status = d->ctx.status;
+  return 0;
+}
+
+struct Plan {
+  int bn, gemm_ctas, comm_ctas;
+  int chunks, rows_per_src, cols_per_src;
+  int max_owned, tiles_m_per_rank, tiles_per_rank;
+  uint64_t inbox_bytes, flags_bytes, staging_bytes;
+};
+
+int make_plan(const IrisGemmDesc* d, Plan& p) {
+  memset(&p, 0, sizeof(p));
+  const int W = d->ctx.world > 0 ? d->ctx.world : 1;
+  const int sms = sm_count();
+  const bool ag = d->op == IRIS_GEMM_AG_M || d->op == IRIS_GEMM_AG_K;
+  p.comm_ctas = ag && W > 1 ? (d->comm_ctas > 0 ? d->comm_ctas : (d->use_mc && d->ctx.mc_base ? 4 : 16)) : 0;
+  p.gemm_ctas = d->gemm_ctas > 0 ? d->gemm_ctas : sms - p.comm_ctas;
+  if (p.gemm_ctas + p.comm_ctas > sms) return -4;  // every CTA must be resident: consumers wait on producers
+  p.bn = d->bn > 0 ? d->bn : choose_bn(d->M, d->N, p.gemm_ctas, !d->b_kmajor);
+  if (p.bn != 256 && p.bn != 224 && p.bn != 128) return -5;
+  const int tiles_m = ceil_div(d->M, kBM), tiles_n = ceil_div(d->N, p.bn);
+  if (d->op == IRIS_GEMM_AG_M) {
+    if (d->M_local % kBM || d->M != d->M_local * W) return -6;
+    p.rows_per_src = d->M_local; p.cols_per_src = d->K; p.chunks = d->M_local / kBM;
+  } else if (d->op == IRIS_GEMM_AG_K) {
+    if (d->K_local % kBK || d->K != d->K_local * W) return -6;
+    p.rows_per_src = d->M; p.cols_per_src = d->K_local; p.chunks = tiles_m;
+  }
+  if (ag) {
+    p.inbox_bytes = 2ull * W * p.rows_per_src * p.cols_per_src * 2;
+    p.flags_bytes = 2ull * W * p.chunks * 4;
+  }
+  if (d->op == IRIS_GEMM_REDUCE_SCATTER) {
+    if (tiles_m % W || d->M % (W * kBM)) return -7;
+    p.tiles_m_per_rank = tiles_m / W;
+    p.max_owned = p.tiles_m_per_rank * tiles_n;
+  } else if (d->op == IRIS_GEMM_ALL_REDUCE) {
+    p.max_owned = ceil_div(tiles_m * tiles_n, W);
+  } else if (d->op == IRIS_GEMM_RS_TILES) {
+    p.tiles_per_rank = (tiles_m * tiles_n) / W;
+    if (p.tiles_per_rank == 0) p.tiles_per_rank = 1;
+    p.max_owned = tiles_m * tiles_n - p.tiles_per_rank * (W - 1);
+    if (p.max_owned < p.tiles_per_rank) p.max_owned = p.tiles_per_rank;
+  }
+  if (p.max_owned) {
+    p.staging_bytes = 2ull * W * p.max_owned * kBM * p.bn * 2;
+    p.flags_bytes = 2ull * p.max_owned * 4;
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int iris_gemm_workspace(const IrisGemmDesc* d, uint64_t* inbox_bytes, uint64_t* flags_bytes,
+                                   uint64_t* staging_bytes, int32_t* bn_out) {
+  Plan p;
+  int r = make_plan(d, p);
+  if (r) return r;
+  if (inbox_bytes) *inbox_bytes = p.inbox_bytes;
+  if (flags_bytes) *flags_bytes = p.flags_bytes;
+  if (staging_bytes) *staging_bytes = p.staging_bytes;
+  if (bn_out) *bn_out = p.bn;
+  return 0;
+}
+
+extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  Plan p;
+  int r = make_plan(d, p);
+  if (r) return r;
+  const int grid = p.gemm_ctas + p.comm_ctas;
+  const bool use_mc = d->use_mc && d->ctx.mc_base != 0 && d->ctx.world > 1;
+  DeviceContext ctx;
+  memcpy(&ctx, &d->ctx, sizeof(ctx));
+
+  if (d->op == IRIS_GEMM_LOCAL) {
+    LocalGemm pol;
+    r = fill_common(pol, d, p.bn, p.gemm_ctas, d->A, d->M, d->K, d->lda);
+    if (r) return r;
+    pol.C = (uint8_t*)d->C; pol.ldc = d->ldc;
+    const int tiles = pol.tiles_m * pol.tiles_n;
+    return dispatch(pol, p.bn, d->b_kmajor != 0, tiles < grid ? tiles : grid, stream);
+  }
+  if (d->op == IRIS_GEMM_AG_M || d->op == IRIS_GEMM_AG_K) {
+    AllGatherGemm pol;
+    // tmA covers this rank's shard only
+    r = fill_common(pol, d, p.bn, p.gemm_ctas, d->A, p.rows_per_src, p.cols_per_src, d->lda);
+    if (r) return r;
+    if (ctx.world > 1) {
+      r = make_map(&pol.tmInbox, d->inbox, d->dtype, 2ull * ctx.world * p.rows_per_src, p.cols_per_src, p.cols_per_src,
+                   kBK, kBM);
+      if (r) return r;
+    } else {
+      pol.tmInbox = pol.tmA;
+    }
+    pol.ctx = ctx; pol.sb = (SyncBlock*)d->sync_block;
+    pol.A_local = (const uint8_t*)d->A; pol.lda = d->lda;
+    pol.inbox = (uint8_t*)d->inbox; pol.flags = d->flags;
+    pol.C = (uint8_t*)d->C; pol.ldc = d->ldc;
+    pol.mode = d->op == IRIS_GEMM_AG_M ? 0 : 1;
+    pol.rows_per_src = p.rows_per_src; pol.cols_per_src = p.cols_per_src; pol.chunks = p.chunks;
+    pol.n_comm_ctas = p.comm_ctas; pol.use_mc = use_mc;
+    if ((p.cols_per_src * 2) % 16) return -8;
+    return dispatch(pol, p.bn, d->b_kmajor != 0, grid, stream);
+  }
+  ScatterGemm pol;
+  r = fill_common(pol, d, p.bn, p.gemm_ctas, d->A, d->M, d->K, d->lda);
+  if (r) return r;
+  pol.ctx = ctx; pol.sb = (SyncBlock*)d->sync_block; pol.mode = d->op;
+  pol.out = (uint8_t*)d->C; pol.ld_out = d->ldc;
+  pol.staging = (uint8_t*)d->staging; pol.flags = d->flags;
+  pol.max_owned = p.max_owned; pol.tiles_m_per_rank = p.tiles_m_per_rank; pol.tiles_per_rank = p.tiles_per_rank;
+  pol.use_mc = use_mc;
+  // reducers stride over all GEMM CTAs, so launch the full grid even for few tiles
+  return dispatch(pol, p.bn, d->b_kmajor != 0, grid, stream);
+}

@@ -1,0 +1,301 @@
+// Persistent, warp-specialised GEMM main loop for sm_100a:
+//   warp 0      TMA producer: cp.async.bulk.tensor (no multicast) into a ring of swizzled smem stages
+//   warp 1      MMA issuer: tcgen05.mma, fp32 accumulators in TMEM, two accumulator buffers so the
+//               epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2..5  epilogue: tcgen05.ld TMEM -> registers -> 16-bit -> smem transpose -> 16-byte stores
+//
+// What differs between a local GEMM and the fused compute+collective kernels is injected through
+// a Policy object (tile order, where an A tile comes from and which flag guards it, where an
+// output fragment goes and who is told about it, what extra "communication CTAs" do). It stands in
+// for the reference's use of tritonblas' GemmContext/ScheduleContext (iris/ops/matmul_all_reduce.py:
+// 95-105) plus the tile collectives of iris/mem/triton/context.py:687-997 used as GEMM epilogues.
+//
+// Operand layouts: A is [M, K] row-major ("K-major"). B is either [N, K] row-major (K-major, the
+// nn.Linear weight layout, passed as a transposed view) or [K, N] row-major ("MN-major").
+// 16-bit inputs (bf16 or fp16), fp32 accumulation, 16-bit output.
+#pragma once
+#include "../common.cuh"
+#include "../ptx.cuh"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace iris {
+namespace gemm {
+
+constexpr int kBM = 128;         // rows of an output tile = TMEM lanes
+constexpr int kBK = 64;          // K per stage: 64 x 2 B = one 128-byte swizzle row
+constexpr int kUmmaK = 16;       // K of one tcgen05.mma for 16-bit inputs
+constexpr int kThreads = 192;    // 6 warps
+constexpr int kEpiWarps = 4;
+constexpr uint64_t kPipeTimeoutNs = 4000000000ull;
+
+template <int BN_, bool kBKMajor_, int kStages_>
+struct Config {
+  static constexpr int BN = BN_;
+  static constexpr bool kBKMajor = kBKMajor_;
+  static constexpr int kStages = kStages_;
+  static constexpr int kABytes = kBM * kBK * 2;                         // 16 KB
+  static constexpr int kBBoxes = kBKMajor_ ? 1 : (BN_ + 63) / 64;       // MN-major: 64(n) x 64(k) boxes
+  static constexpr int kBBytes = kBKMajor_ ? BN_ * kBK * 2 : kBBoxes * 8192;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kAccCols = 256;                                  // column pitch of an accumulator buffer
+  static constexpr int kTmemCols = 512;
+  static constexpr int kEpiBytes = kEpiWarps * 32 * 64;                 // 32 rows x 32 cols x 2 B per warp
+  static constexpr int kSmemBytes = 1024 + kStages_ * kStageBytes + kEpiBytes + 256;
+  static_assert(BN_ % 32 == 0 && BN_ >= 32 && BN_ <= 256, "BN must be a multiple of 32 up to 256");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+// K-major tile [rows][64] of 16-bit: 8-row groups are 1024 B apart (SBO); LBO unused.
+IRIS_D uint64_t desc_kmajor(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand stored as 64(k) x 64(n) boxes of 8 KB: k groups of 8 rows are 1024 B apart
+// (SBO), the next 64 columns of n are one box = 8192 B further (LBO).
+IRIS_D uint64_t desc_mnmajor(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(8192 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: fp32 accumulate, A K-major, M = 128.
+IRIS_HD uint32_t make_idesc(int n, bool bf16, bool b_mn_major) {
+  uint32_t fmt = bf16 ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(kBM >> 4) << 24);
+}
+
+struct Shape {
+  int M, N, K;
+};
+
+// Where the producer gets the A tile of (m_tile, k_block) from.
+struct ASource {
+  const CUtensorMap* map;
+  int x, y;   // coordinates of the A box in `map`
+  int bk;     // K offset of the matching B rows/columns (differs from x when A is gathered along K)
+};
+
+// GROUP_M swizzled tile order (same idea as the reference's GROUP_SIZE_M, all_reduce.py:182-187).
+IRIS_D void swizzled_tile(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  int per_group = group_m * tiles_n;
+  int g = t / per_group;
+  int first_m = g * group_m;
+  int gsz = min(tiles_m - first_m, group_m);
+  int r = t - g * per_group;
+  tm = first_m + r % gsz;
+  tn = r / gsz;
+}
+
+struct Pipeline {
+  uint64_t* full;        // [stages]  TMA bytes landed
+  uint64_t* empty;       // [stages]  MMAs that read the stage retired
+  uint64_t* tmem_full;   // [2]       accumulator complete
+  uint64_t* tmem_empty;  // [2]       accumulator drained by the epilogue
+};
+
+// The kernel body. `Policy` must provide:
+//   Shape shape() const;  int gemm_ctas() const;  int num_tiles() const;
+//   void tile(int t, int& m_tile, int& n_tile) const;
+//   struct State;                                          (mutable per-thread scratch of the hooks)
+//   bool a_source(State&, int m_tile, int kb, ASource& s) const;   (producer warp, all lanes; false = abort)
+//   const CUtensorMap* b_map() const;  bool is_bf16() const;
+//   void begin_tile(State&, int m_tile, int n_tile) const; (every epilogue thread, before a tile's stores)
+//   void store16(State&, int row, int col, uint4 v) const; (8 consecutive outputs of one row)
+//   float row_bias(int row) const;  float col_bias(int col) const;  bool has_bias() const;
+//   void tile_done(State&, int m_tile, int n_tile) const;  (one thread, after the tile's stores)
+//   void comm_main() const;                                 (CTAs with blockIdx.x >= gemm_ctas())
+//   void post_main() const;                                 (GEMM CTAs, all threads, after their tiles)
+//   void fail(int code) const;
+// The policy is a __grid_constant__ kernel parameter (its tensor maps are used in place), so every
+// hook is const.
+template <class Cfg, class Policy>
+IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const Shape sh = pol.shape();
+
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint8_t* epi_base = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* bars = (uint64_t*)(epi_base + Cfg::kEpiBytes);
+  Pipeline pipe{bars, bars + Cfg::kStages, bars + 2 * Cfg::kStages, bars + 2 * Cfg::kStages + 2};
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * Cfg::kStages + 4);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      ptx::mbar_init(&pipe.full[s], 1);
+      ptx::mbar_init(&pipe.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&pipe.tmem_full[b], 1);
+      ptx::mbar_init(&pipe.tmem_empty[b], kEpiWarps);
+    }
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+
+  const int num_tiles = pol.num_tiles();
+  const int k_blocks = (sh.K + kBK - 1) / kBK;
+  const int first = blockIdx.x, step = pol.gemm_ctas();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) ptx::prefetch_tmap(pol.b_map());
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    typename Policy::State st;
+    for (int t = first; t < num_tiles && ok; t += step) {
+      int tm, tn;
+      pol.tile(t, tm, tn);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        ASource as;
+        if (!pol.a_source(st, tm, kb, as)) { ok = false; break; }
+        if (!ptx::mbar_wait(&pipe.empty[s], ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
+        if (lane == 0) {
+          uint8_t* sa = stage_base + s * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          ptx::mbar_expect_tx(&pipe.full[s], Cfg::kStageBytes);
+          ptx::tma_load_2d(sa, as.map, &pipe.full[s], as.x, as.y);
+          if constexpr (Cfg::kBKMajor) {
+            ptx::tma_load_2d(sb, pol.b_map(), &pipe.full[s], as.bk, tn * Cfg::BN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < Cfg::kBBoxes; ++j)
+              ptx::tma_load_2d(sb + j * 8192, pol.b_map(), &pipe.full[s], tn * Cfg::BN + j * 64, as.bk);
+          }
+        }
+        __syncwarp();
+        if (++s == Cfg::kStages) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = make_idesc(Cfg::BN, pol.is_bf16(), !Cfg::kBKMajor);
+    int s = 0;
+    uint32_t ph = 0;
+    int it = 0;
+    bool ok = true;
+    for (int t = first; t < num_tiles && ok; t += step, ++it) {
+      const int buf = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      if (!ptx::mbar_wait(&pipe.tmem_empty[buf], acc_ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); break; }
+      ptx::tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * Cfg::kAccCols;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!ptx::mbar_wait(&pipe.full[s], ph, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
+        ptx::tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = ptx::smem_u32(stage_base + s * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            uint64_t ad = desc_kmajor(sa + k * (kUmmaK * 2));
+            uint64_t bd = Cfg::kBKMajor ? desc_kmajor(sb + k * (kUmmaK * 2)) : desc_mnmajor(sb + k * (kUmmaK * 128));
+            ptx::mma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+          }
+          ptx::mma_commit(&pipe.empty[s]);
+          if (kb == k_blocks - 1) ptx::mma_commit(&pipe.tmem_full[buf]);
+        }
+        __syncwarp();
+        if (++s == Cfg::kStages) { s = 0; ph ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    uint8_t* my_epi = epi_base + (warp - 2) * (32 * 64);
+    const bool bf16 = pol.is_bf16();
+    const bool has_bias = pol.has_bias();
+    typename Policy::State est;
+    int it = 0;
+    for (int t = first; t < num_tiles; t += step, ++it) {
+      const int buf = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      int tm, tn;
+      pol.tile(t, tm, tn);
+      // A wait that runs out still goes through this tile's named barrier (the other epilogue
+      // warps may have got through) and leaves afterwards.
+      const bool live = ptx::mbar_wait(&pipe.tmem_full[buf], acc_ph, kPipeTimeoutNs);
+      if (!live) {
+        pol.fail(kTimeoutPipeline);
+        ptx::named_barrier(1, kEpiWarps * 32);
+        break;
+      }
+      ptx::tc_fence_after();
+      pol.begin_tile(est, tm, tn);
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * Cfg::kAccCols;
+      const int row0 = tm * kBM + quarter * 32;
+      const float rb = has_bias ? pol.row_bias(row0 + lane) : 0.f;
+#pragma unroll 1
+      for (int c = 0; c < Cfg::BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(t_addr + c * 32, r);
+        ptx::tmem_ld_wait();
+        if (c == Cfg::BN / 32 - 1) {
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&pipe.tmem_empty[buf]);
+        }
+        const int col0 = tn * Cfg::BN + c * 32;
+        // fp32 -> 16-bit pairs, staged so that a row's 64 bytes leave as 4 x 16-byte pieces
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float a = __uint_as_float(r[2 * j]) + rb, b = __uint_as_float(r[2 * j + 1]) + rb;
+          if (has_bias) { a += pol.col_bias(col0 + 2 * j); b += pol.col_bias(col0 + 2 * j + 1); }
+          if (bf16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+            packed[j] = *(uint32_t*)&h;
+          } else {
+            __half2 h = __floats2half2_rn(a, b);
+            packed[j] = *(uint32_t*)&h;
+          }
+        }
+        const int sw = (lane >> 1) & 3;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 v = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          *(uint4*)(my_epi + lane * 64 + ((j ^ sw) * 16)) = v;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int rr = i * 8 + (lane >> 2), cc = lane & 3;
+          uint4 v = *(uint4*)(my_epi + rr * 64 + ((cc ^ ((rr >> 1) & 3)) * 16));
+          pol.store16(est, row0 + rr, col0 + cc * 8, v);
+        }
+        __syncwarp();
+      }
+      ptx::named_barrier(1, kEpiWarps * 32);
+      if (warp == 2 && lane == 0) pol.tile_done(est, tm, tn);
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  pol.post_main();
+}
+
+template <class Cfg, class Policy>
+__global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ Policy pol_in) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x >= pol_in.gemm_ctas()) {
+    pol_in.comm_main();
+    return;
+  }
+  gemm_cta_main<Cfg, Policy>(pol_in, smem_raw);
+}
+
+}  // namespace gemm
+}  // namespace iris

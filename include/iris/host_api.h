@@ -1,0 +1,75 @@
+// C ABI shared by the kernel library (libiris_b200_kernels.so) and its Python loader
+// (iris_b200/_lib.py mirrors these structs with ctypes). Every entry point returns 0 or a
+// negative error code, launches on the given stream and never synchronises or allocates unless
+// its comment says so.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IRIS_MAX_RANKS 72
+
+// Host copy of iris::DeviceContext (same field order).
+typedef struct IrisCtx {
+  int32_t rank;
+  int32_t world;
+  uint64_t heap_size;
+  uint64_t mc_base;
+  int32_t* status;
+  uint64_t timeout_ns;
+  // trace block (see include/iris/context.cuh TraceBuffers)
+  int32_t trace_enabled;
+  int32_t trace_max_events;
+  void* trace_ptrs[15];
+  uint64_t bases[IRIS_MAX_RANKS];
+} IrisCtx;
+
+enum IrisDType { IRIS_F16 = 0, IRIS_BF16 = 1, IRIS_F32 = 2, IRIS_I32 = 3, IRIS_I8 = 4, IRIS_F8E4M3 = 5, IRIS_I64 = 6 };
+
+enum IrisGemmOp {
+  IRIS_GEMM_LOCAL = 0,          // C = A @ B (+ bias)
+  IRIS_GEMM_AG_M = 1,           // all-gather A (sharded by rows) then GEMM
+  IRIS_GEMM_AG_K = 2,           // all-gather A (sharded along K) then GEMM
+  IRIS_GEMM_ALL_GATHER = 3,     // GEMM then all-gather of C rows (rank r's rows at r*M)
+  IRIS_GEMM_REDUCE_SCATTER = 4, // GEMM then sum over ranks, rank r keeps rows [r*M/W, (r+1)*M/W)
+  IRIS_GEMM_ALL_REDUCE = 5,     // GEMM then sum over ranks, everyone gets [M, N]
+  IRIS_GEMM_ALL_SCATTER = 6,    // GEMM then all-gather of C columns (rank r's columns at r*N)
+  IRIS_GEMM_RS_TILES = 7,       // GEMM then sum over ranks; output [M, N], rank r writes only the
+                                // tiles it owns (contiguous tile blocks, last rank takes the remainder)
+};
+
+typedef struct IrisGemmDesc {
+  int32_t op;
+  int32_t M, N, K;        // problem of the MMA loop on this rank (gathered sizes for AG_*)
+  int32_t dtype;          // IRIS_F16 or IRIS_BF16 (inputs and output)
+  int32_t b_kmajor;       // 1: B given as [N, K] row-major, 0: B given as [K, N] row-major
+  int32_t bn;             // tile width: 128, 224 or 256; 0 = choose
+  int32_t group_m;        // tile-order swizzle, 0 = default
+  int32_t gemm_ctas;      // 0 = all SMs minus comm_ctas
+  int32_t comm_ctas;      // CTAs that only move data (AG_M / AG_K), 0 = default
+  int32_t use_mc;         // use the NVLS multicast window when the context has one
+  int32_t reserved;
+  const void* A; int64_t lda;
+  const void* B; int64_t ldb;
+  void* C; int64_t ldc;
+  const float* bias_row;  // [M] or null
+  const float* bias_col;  // [N] or null
+  IrisCtx ctx;
+  void* sync_block;       // iris::SyncBlock on the heap
+  void* inbox;            // AG_*: [2][W][rows][cols] staging of gathered A (heap)
+  int32_t* flags;         // AG_*: [2][W][chunks]; RS/AR: [2][tiles] arrival counters (heap)
+  void* staging;          // RS/AR: [2][W][owned tiles][128*bn] partial tiles (heap)
+  int32_t M_local;        // AG_M: rows per rank; ALL_GATHER: rows per rank (= M)
+  int32_t K_local;        // AG_K: K per rank
+} IrisGemmDesc;
+
+// Bytes of workspace the op needs for this shape (inbox / flags / staging). Pure arithmetic.
+int iris_gemm_workspace(const IrisGemmDesc* d, uint64_t* inbox_bytes, uint64_t* flags_bytes, uint64_t* staging_bytes,
+                        int32_t* bn_out);
+int iris_gemm_launch(const IrisGemmDesc* d, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
