@@ -38,13 +38,13 @@ IRIS_HD To bit_cast(const From& f) {
 
 #if defined(__CUDACC__)
 // ---- raw loads ------------------------------------------------------------------------------
-#define IRIS_LD_BODY(SUFFIX, OUTS, ...)                                                              \
-  if constexpr (V) asm volatile("ld.volatile.global" SUFFIX : OUTS : "l"(p) : "memory");              \
-  else if constexpr (C == CacheOp::ca) asm volatile("ld.global.ca" SUFFIX : OUTS : "l"(p) : "memory"); \
-  else if constexpr (C == CacheOp::cg) asm volatile("ld.global.cg" SUFFIX : OUTS : "l"(p) : "memory"); \
-  else if constexpr (C == CacheOp::cs) asm volatile("ld.global.cs" SUFFIX : OUTS : "l"(p) : "memory"); \
-  else if constexpr (C == CacheOp::cv) asm volatile("ld.global.cv" SUFFIX : OUTS : "l"(p) : "memory"); \
-  else asm volatile("ld.global" SUFFIX : OUTS : "l"(p) : "memory");
+#define IRIS_LD_BODY(SUFFIX, ...)                                                                       \
+  if constexpr (V) asm volatile("ld.volatile.global" SUFFIX : __VA_ARGS__ : "l"(p) : "memory");              \
+  else if constexpr (C == CacheOp::ca) asm volatile("ld.global.ca" SUFFIX : __VA_ARGS__ : "l"(p) : "memory"); \
+  else if constexpr (C == CacheOp::cg) asm volatile("ld.global.cg" SUFFIX : __VA_ARGS__ : "l"(p) : "memory"); \
+  else if constexpr (C == CacheOp::cs) asm volatile("ld.global.cs" SUFFIX : __VA_ARGS__ : "l"(p) : "memory"); \
+  else if constexpr (C == CacheOp::cv) asm volatile("ld.global.cv" SUFFIX : __VA_ARGS__ : "l"(p) : "memory"); \
+  else asm volatile("ld.global" SUFFIX : __VA_ARGS__ : "l"(p) : "memory");
 
 template <CacheOp C, bool V> IRIS_D uint8_t ld_raw(const uint8_t* p) {
   uint32_t v; IRIS_LD_BODY(".u8 %0, [%1];", "=r"(v)) return (uint8_t)v;

@@ -1,0 +1,376 @@
+"""Fused GEMM + collective operations (reference: iris/ops/__init__.py:37-178).
+
+Each op is ONE sm_100a kernel (``csrc/kernels/gemm_ops.cu``): tcgen05/TMEM tiles fed by TMA, with
+the collective carried out by the same kernel through peer stores, NVLS multimem stores and
+per-tile flags on the symmetric heap.
+
+=========================  =====================================================================
+``all_gather_matmul``      ``C = gather(A_sharded) @ B``; A sharded along K (reference layout,
+                           ``shard_dim=1``) or along rows (``shard_dim=0``, tensor-parallel MLP)
+``matmul_all_gather``      ``C[r*M:(r+1)*M] = A_r @ B`` gathered on every rank
+``matmul_all_reduce``      ``C = sum_r A_r @ B_r`` on every rank
+``matmul_reduce_scatter``  ``sum_r A_r @ B_r`` with each rank keeping its tiles (reference layout:
+                           full-shape output, owned tiles only) or its row block (``scatter_rows``)
+=========================  =====================================================================
+
+Module-level functions take the context first (``iris_b200.ops.matmul_all_reduce(ctx, C, A, B)``);
+``ctx.ops.<op>(C, A, B, ...)`` binds it. Every op returns its ``FusedWorkspace``; pass it back to
+skip the (collective) allocation of buffers on later calls. Inputs that the tensor-core kernel
+cannot take (fp32, shapes that do not tile) go through the unfused path: GEMM, then the
+collective of ``ctx.ccl``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _lib
+from .config import FusedConfig
+from .gemm import fill_desc, matmul
+from .workspace import FusedWorkspace
+
+__all__ = [
+    "FusedConfig", "FusedWorkspace", "OpsNamespace", "matmul",
+    "matmul_all_reduce", "matmul_all_reduce_preamble", "all_gather_matmul", "all_gather_matmul_preamble",
+    "matmul_all_gather", "matmul_all_gather_preamble", "matmul_reduce_scatter", "matmul_reduce_scatter_preamble",
+]
+
+_FUSED_DTYPES = (torch.bfloat16, torch.float16)
+
+
+def _fusable(ctx, *tensors) -> bool:
+    return (not ctx.is_cpu) and all(t.dtype in _FUSED_DTYPES for t in tensors) and all(t.dim() == 2 for t in tensors)
+
+
+def _base_desc(ctx, op, M, N, K, A, B, out, config, bias_row=None, bias_col=None) -> tuple:
+    d = _lib.IrisGemmDesc()
+    d.op = op
+    d.M, d.N, d.K = M, N, K
+    keep = fill_desc(d, A, B, out, bias_row=bias_row, bias_col=bias_col, bn=config.tile_n())
+    d.group_m = config.group_size_m
+    d.comm_ctas = config.comm_sms
+    d.use_mc = 1 if (config.use_multicast and ctx.has_multicast()) else 0
+    d.ctx = ctx.ctx_struct()
+    return d, keep
+
+
+def _plan(d) -> tuple:
+    inbox, flags, staging, bn = C.c_uint64(0), C.c_uint64(0), C.c_uint64(0), C.c_int32(0)
+    rc = _lib.kernels().iris_gemm_workspace(C.byref(d), C.byref(inbox), C.byref(flags), C.byref(staging), C.byref(bn))
+    return rc, inbox.value, flags.value, staging.value, bn.value
+
+
+def _make_workspace(ctx, operation, shape, dtype, variant, d) -> FusedWorkspace | None:
+    """Allocate the op's heap buffers (collective). None when the kernel cannot take the shape."""
+    rc, inbox, flags, staging, bn = _plan(d)
+    if rc != 0:
+        return None
+    ws = FusedWorkspace(operation=operation, shape=tuple(shape), dtype=dtype, world_size=ctx.num_ranks, variant=variant, bn=bn)
+    ws.sync_block = ctx.zeros(80, dtype=torch.int32)
+    if inbox:
+        ws.inbox = ctx.heap.allocate(inbox, torch.uint8)
+    if flags:
+        ws.flags = ctx.zeros(flags // 4, dtype=torch.int32)
+        ws.locks = ws.flags
+    if staging:
+        ws.staging = ctx.heap.allocate(staging, torch.uint8)
+        ws.aux_buffer = ws.staging
+    ws.prepared = True
+    ctx.barrier()
+    return ws
+
+
+def _launch(ctx, d, ws) -> None:
+    d.sync_block = ws.sync_block.data_ptr()
+    d.inbox = ws.inbox.data_ptr() if ws.inbox is not None else None
+    d.flags = ws.flags.data_ptr() if ws.flags is not None else None
+    d.staging = ws.staging.data_ptr() if ws.staging is not None else None
+    d.bn = ws.bn
+    _lib.check(_lib.kernels().iris_gemm_launch(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), f"{ws.operation} launch")
+
+
+def _local_matmul(A, B, bias=None, bias_dim=1):
+    if A.is_cuda and A.dtype in _FUSED_DTYPES and A.stride(-1) == 1:
+        return matmul(A, B, bias=bias, bias_dim=bias_dim)
+    out = A @ B
+    if bias is not None:
+        out = out + (bias[:, None] if bias_dim == 0 else bias[None, :])
+    return out
+
+
+def _bias32(bias):
+    return bias.float().contiguous() if bias is not None else None
+
+
+def _finish(ctx, async_op):
+    if not async_op:
+        ctx.barrier()
+
+
+# ----------------------------------------------------------------------------- all_gather_matmul
+def _agm_desc(ctx, out, A_sharded, B, bias, config, shard_dim):
+    W = ctx.num_ranks
+    if shard_dim == 1:
+        M, K_local = A_sharded.shape
+        K, N = B.shape
+        if K != K_local * W:
+            raise ValueError(f"all_gather_matmul: B has K={K} but A_sharded supplies {K_local} x {W} ranks")
+        if tuple(out.shape) != (M, N):
+            raise ValueError(f"all_gather_matmul: output must be {(M, N)}, got {tuple(out.shape)}")
+        d, keep = _base_desc(ctx, _lib.GEMM_AG_K, M, N, K, A_sharded, B, out, config, bias_row=bias)
+        d.K_local = K_local
+    else:
+        M_local, K = A_sharded.shape
+        K2, N = B.shape
+        if K != K2:
+            raise ValueError(f"all_gather_matmul: A has K={K}, B has K={K2}")
+        if tuple(out.shape) != (M_local * W, N):
+            raise ValueError(f"all_gather_matmul: output must be {(M_local * W, N)}, got {tuple(out.shape)}")
+        d, keep = _base_desc(ctx, _lib.GEMM_AG_M, M_local * W, N, K, A_sharded, B, out, config, bias_row=bias)
+        d.M_local = M_local
+    return d, keep
+
+
+def all_gather_matmul_preamble(shmem, A_sharded, B, config=None, shard_dim=1):
+    """Allocate the workspace of ``all_gather_matmul`` (collective)."""
+    config = config or FusedConfig()
+    if not _fusable(shmem, A_sharded, B):
+        return FusedWorkspace(operation="all_gather_matmul", variant="unfused", world_size=shmem.num_ranks, prepared=True)
+    W = shmem.num_ranks
+    shape = (A_sharded.shape[0], B.shape[1]) if shard_dim == 1 else (A_sharded.shape[0] * W, B.shape[1])
+    out = torch.empty(shape, dtype=A_sharded.dtype, device=A_sharded.device)
+    d, _ = _agm_desc(shmem, out, A_sharded, B, None, config, shard_dim)
+    key = tuple(A_sharded.shape) + tuple(B.shape) + (shard_dim,)
+    ws = _make_workspace(shmem, "all_gather_matmul", key, A_sharded.dtype, "fused", d)
+    if ws is None:
+        return FusedWorkspace(operation="all_gather_matmul", variant="unfused", world_size=W, prepared=True)
+    return ws
+
+
+def all_gather_matmul(shmem, output_tensor, A_sharded, B, bias=None, async_op=False, config=None, workspace=None,
+                      shard_dim=1):
+    """``output = gather(A_sharded) @ B (+ bias[:, None])``.
+
+    ``shard_dim=1`` (reference layout, iris/ops/all_gather_matmul.py:202-204): ``A_sharded`` is
+    ``(M, K/W)``, rank r holding columns ``[r*K/W, (r+1)*K/W)``. ``shard_dim=0``: ``A_sharded`` is
+    ``(M/W, K)``, rank r holding rows ``[r*M/W, (r+1)*M/W)`` and the output is ``(M, N)``.
+    """
+    config = config or FusedConfig()
+    W = shmem.num_ranks
+    key = tuple(A_sharded.shape) + tuple(B.shape) + (shard_dim,)
+    ws = workspace
+    if ws is None or not (ws.variant == "unfused" or ws.matches("all_gather_matmul", key, A_sharded.dtype, W, "fused")):
+        ws = all_gather_matmul_preamble(shmem, A_sharded, B, config, shard_dim)
+    if ws.variant == "unfused":
+        gathered = _unfused_gather(shmem, A_sharded, shard_dim)
+        output_tensor.copy_(_local_matmul(gathered, B, bias, bias_dim=0))
+    else:
+        d, keep = _agm_desc(shmem, output_tensor, A_sharded, B, _bias32(bias), config, shard_dim)
+        _launch(shmem, d, ws)
+        del keep
+    _finish(shmem, async_op)
+    return ws
+
+
+def _unfused_gather(ctx, A_sharded, shard_dim):
+    W = ctx.num_ranks
+    src = ctx.as_symmetric(A_sharded.contiguous())
+    if shard_dim == 0:
+        dst = ctx.empty((A_sharded.shape[0] * W, A_sharded.shape[1]), dtype=A_sharded.dtype)
+        ctx.ccl.all_gather(dst, src, async_op=False)
+        return dst
+    dst = ctx.empty((W * A_sharded.shape[0], A_sharded.shape[1]), dtype=A_sharded.dtype)
+    ctx.ccl.all_gather(dst, src, async_op=False)
+    M, Kl = A_sharded.shape
+    return dst.view(W, M, Kl).permute(1, 0, 2).reshape(M, W * Kl)
+
+
+# ----------------------------------------------------------------------------- matmul_all_gather
+def matmul_all_gather_preamble(shmem, A, B, config=None, scatter_cols=False):
+    config = config or FusedConfig()
+    if not _fusable(shmem, A, B):
+        return FusedWorkspace(operation="matmul_all_gather", variant="unfused", world_size=shmem.num_ranks, prepared=True)
+    W = shmem.num_ranks
+    M, K = A.shape
+    N = B.shape[1]
+    out = torch.empty((M * W, N) if not scatter_cols else (M, N * W), dtype=A.dtype, device=A.device)
+    op = _lib.GEMM_ALL_SCATTER if scatter_cols else _lib.GEMM_ALL_GATHER
+    d, _ = _base_desc(shmem, op, M, N, K, A, B, out, config)
+    ws = _make_workspace(shmem, "matmul_all_gather", tuple(A.shape) + tuple(B.shape) + (scatter_cols,), A.dtype, "fused", d)
+    return ws or FusedWorkspace(operation="matmul_all_gather", variant="unfused", world_size=W, prepared=True)
+
+
+def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, config=None, workspace=None,
+                      scatter_cols=False):
+    """``output[r*M:(r+1)*M] = A_r @ B`` on every rank (reference: iris/ops/matmul_all_gather.py:173-196).
+
+    With ``scatter_cols`` the local result is ``(M, N_local)`` and lands in columns
+    ``[r*N_local, (r+1)*N_local)`` of every rank's ``(M, W*N_local)`` output: the "GEMM +
+    all-scatter" layout of the reference's examples/07_gemm_all_scatter.
+    """
+    config = config or FusedConfig()
+    W = shmem.num_ranks
+    M, K = A.shape
+    N = B.shape[1]
+    want = (M, N * W) if scatter_cols else (M * W, N)
+    if tuple(output_tensor.shape) != want:
+        raise ValueError(f"matmul_all_gather: output must be {want}, got {tuple(output_tensor.shape)}")
+    key = tuple(A.shape) + tuple(B.shape) + (scatter_cols,)
+    ws = workspace
+    if ws is None or not (ws.variant == "unfused" or ws.matches("matmul_all_gather", key, A.dtype, W, "fused")):
+        ws = matmul_all_gather_preamble(shmem, A, B, config, scatter_cols)
+    if ws.variant == "unfused" or not shmem.is_symmetric(output_tensor):
+        local = _local_matmul(A, B, bias, bias_dim=0)
+        if scatter_cols:
+            tmp = shmem.empty((W * M, N), dtype=A.dtype)
+            shmem.ccl.all_gather(tmp, shmem.as_symmetric(local.contiguous()))
+            output_tensor.copy_(tmp.view(W, M, N).permute(1, 0, 2).reshape(M, W * N))
+        else:
+            dst = output_tensor if shmem.is_symmetric(output_tensor) else shmem.empty(want, dtype=A.dtype)
+            shmem.ccl.all_gather(dst, shmem.as_symmetric(local.contiguous()))
+            if dst is not output_tensor:
+                output_tensor.copy_(dst)
+    else:
+        op = _lib.GEMM_ALL_SCATTER if scatter_cols else _lib.GEMM_ALL_GATHER
+        d, keep = _base_desc(shmem, op, M, N, K, A, B, output_tensor, config, bias_row=_bias32(bias))
+        _launch(shmem, d, ws)
+        del keep
+    _finish(shmem, async_op)
+    return ws
+
+
+# ----------------------------------------------------------------------------- matmul_all_reduce
+def matmul_all_reduce_preamble(shmem, C_out, A, B, config=None):
+    config = config or FusedConfig()
+    if not _fusable(shmem, A, B) or not shmem.is_symmetric(C_out):
+        return FusedWorkspace(operation="matmul_all_reduce", variant="unfused", world_size=shmem.num_ranks, prepared=True)
+    M, K = A.shape
+    N = B.shape[1]
+    d, _ = _base_desc(shmem, _lib.GEMM_ALL_REDUCE, M, N, K, A, B, C_out, config)
+    ws = _make_workspace(shmem, "matmul_all_reduce", tuple(A.shape) + tuple(B.shape), A.dtype, "fused", d)
+    return ws or FusedWorkspace(operation="matmul_all_reduce", variant="unfused", world_size=shmem.num_ranks, prepared=True)
+
+
+def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, config=None, workspace=None):
+    """``output = sum over ranks of (A_r @ B_r)`` (+ bias) on every rank
+    (reference: iris/ops/matmul_all_reduce.py:222-372). The bias, if any, is added once."""
+    config = config or FusedConfig()
+    W = shmem.num_ranks
+    M, K = A.shape
+    N = B.shape[1]
+    if tuple(output_tensor.shape) != (M, N):
+        raise ValueError(f"matmul_all_reduce: output must be {(M, N)}, got {tuple(output_tensor.shape)}")
+    key = tuple(A.shape) + tuple(B.shape)
+    ws = workspace
+    if ws is None or not (ws.variant == "unfused" or ws.matches("matmul_all_reduce", key, A.dtype, W, "fused")):
+        ws = matmul_all_reduce_preamble(shmem, output_tensor, A, B, config)
+    # a bias must enter the sum exactly once: rank 0 adds it to its partial product
+    b = bias if (bias is not None and shmem.cur_rank == 0) else None
+    if ws.variant == "unfused":
+        part = shmem.as_symmetric(_local_matmul(A, B, b, bias_dim=0).contiguous())
+        dst = output_tensor if shmem.is_symmetric(output_tensor) else shmem.empty((M, N), dtype=A.dtype)
+        shmem.ccl.all_reduce(dst, part)
+        if dst is not output_tensor:
+            output_tensor.copy_(dst)
+    else:
+        d, keep = _base_desc(shmem, _lib.GEMM_ALL_REDUCE, M, N, K, A, B, output_tensor, config, bias_row=_bias32(b))
+        _launch(shmem, d, ws)
+        del keep
+    _finish(shmem, async_op)
+    return ws
+
+
+# ----------------------------------------------------------------------------- matmul_reduce_scatter
+def matmul_reduce_scatter_preamble(shmem, C_out, A, B, config=None, scatter_rows=False):
+    config = config or FusedConfig()
+    if not _fusable(shmem, A, B):
+        return FusedWorkspace(operation="matmul_reduce_scatter", variant="unfused", world_size=shmem.num_ranks, prepared=True)
+    M, K = A.shape
+    N = B.shape[1]
+    op = _lib.GEMM_REDUCE_SCATTER if scatter_rows else _lib.GEMM_RS_TILES
+    d, _ = _base_desc(shmem, op, M, N, K, A, B, C_out, config)
+    ws = _make_workspace(shmem, "matmul_reduce_scatter", tuple(A.shape) + tuple(B.shape) + (scatter_rows,), A.dtype, "fused", d)
+    return ws or FusedWorkspace(operation="matmul_reduce_scatter", variant="unfused", world_size=shmem.num_ranks, prepared=True)
+
+
+def owned_tile_range(num_tiles: int, world: int, rank: int) -> range:
+    """Tiles (row-major ids) owned by ``rank`` in the reference layout of matmul_reduce_scatter:
+    contiguous blocks of ``num_tiles // world``, the last rank also taking the remainder
+    (iris/mem/triton/context.py:967-979)."""
+    per = max(num_tiles // world, 1)
+    lo = min(rank * per, num_tiles)
+    hi = num_tiles if rank == world - 1 else min(lo + per, num_tiles)
+    return range(lo, hi)
+
+
+def matmul_reduce_scatter(shmem, output_tensor, A, B, bias=None, async_op=False, config=None, workspace=None,
+                          scatter_rows=False):
+    """``sum over ranks of (A_r @ B_r)``, scattered.
+
+    Default (reference layout, iris/ops/matmul_reduce_scatter.py:191-294): ``output`` is ``(M, N)``
+    and this rank writes only the 128 x ``ws.bn`` tiles in ``owned_tile_range``; the rest of
+    ``output`` is left untouched. ``scatter_rows=True``: ``output`` is ``(M/W, N)``, this rank's row
+    block of the sum (the tensor-parallel layout).
+    """
+    config = config or FusedConfig()
+    W = shmem.num_ranks
+    M, K = A.shape
+    N = B.shape[1]
+    want = (M // W, N) if scatter_rows else (M, N)
+    if tuple(output_tensor.shape) != want:
+        raise ValueError(f"matmul_reduce_scatter: output must be {want}, got {tuple(output_tensor.shape)}")
+    key = tuple(A.shape) + tuple(B.shape) + (scatter_rows,)
+    ws = workspace
+    if ws is None or not (ws.variant == "unfused" or ws.matches("matmul_reduce_scatter", key, A.dtype, W, "fused")):
+        ws = matmul_reduce_scatter_preamble(shmem, output_tensor, A, B, config, scatter_rows)
+    b = bias if (bias is not None and shmem.cur_rank == 0) else None
+    if ws.variant == "unfused":
+        from ..ccl import Config
+
+        part = shmem.as_symmetric(_local_matmul(A, B, b, bias_dim=0).contiguous())
+        if scatter_rows:
+            dst = shmem.empty(want, dtype=A.dtype)
+            shmem.ccl.reduce_scatter(dst, part, config=Config(reduce_scatter_rows=True))
+            output_tensor.copy_(dst)
+        else:
+            full = shmem.empty((M, N), dtype=A.dtype)
+            shmem.ccl.all_reduce(full, part)
+            bn = ws.bn or 256
+            tiles_n = -(-N // bn)
+            for t in owned_tile_range(-(-M // 128) * tiles_n, W, shmem.cur_rank):
+                tm, tn = divmod(t, tiles_n)
+                output_tensor[tm * 128:(tm + 1) * 128, tn * bn:(tn + 1) * bn] = full[tm * 128:(tm + 1) * 128, tn * bn:(tn + 1) * bn]
+            ws.bn = bn
+    else:
+        op = _lib.GEMM_REDUCE_SCATTER if scatter_rows else _lib.GEMM_RS_TILES
+        d, keep = _base_desc(shmem, op, M, N, K, A, B, output_tensor, config, bias_row=_bias32(b))
+        _launch(shmem, d, ws)
+        del keep
+    _finish(shmem, async_op)
+    return ws
+
+
+class OpsNamespace:
+    """``ctx.ops``: the module-level functions with the context bound."""
+
+    def __init__(self, ctx):
+        self._ctx = ctx
+
+    def matmul(self, A, B, bias=None, out=None):
+        return matmul(A, B, bias=bias, out=out)
+
+    def matmul_all_reduce(self, output_tensor, A, B, bias=None, async_op=False, config=None, workspace=None):
+        return matmul_all_reduce(self._ctx, output_tensor, A, B, bias, async_op, config, workspace)
+
+    def all_gather_matmul(self, output_tensor, A_sharded, B, bias=None, async_op=False, config=None, workspace=None,
+                          shard_dim=1):
+        return all_gather_matmul(self._ctx, output_tensor, A_sharded, B, bias, async_op, config, workspace, shard_dim)
+
+    def matmul_all_gather(self, output_tensor, A, B, bias=None, async_op=False, config=None, workspace=None,
+                          scatter_cols=False):
+        return matmul_all_gather(self._ctx, output_tensor, A, B, bias, async_op, config, workspace, scatter_cols)
+
+    def matmul_reduce_scatter(self, output_tensor, A, B, bias=None, async_op=False, config=None, workspace=None,
+                              scatter_rows=False):
+        return matmul_reduce_scatter(self._ctx, output_tensor, A, B, bias, async_op, config, workspace, scatter_rows)

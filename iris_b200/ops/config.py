@@ -1,0 +1,41 @@
+"""Configuration of the fused GEMM + collective ops (reference: iris/ops/config.py:13-104).
+
+The reference's tile sizes drive a Triton kernel; here the GEMM tile is fixed at 128 rows by the
+tcgen05 instruction shape and ``block_size_n`` selects the tile width (128, 224 or 256; anything
+else means "choose by wave count"). ``block_size_m`` / ``block_size_k`` are validated and kept for
+API compatibility.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass
+class FusedConfig:
+    block_size_m: int = 128
+    block_size_n: int = 0
+    block_size_k: int = 64
+    group_size_m: int = 8
+    num_sms: int | None = None
+    num_xcds: int = 1
+    chunk_size: int = 1
+    all_reduce_variant: str = "two_shot"
+    all_reduce_num_rings: int = 1
+    comm_sms: int = 0
+    use_multicast: bool = True
+    allow_tf32: bool = True
+
+    def __post_init__(self):
+        if self.block_size_m <= 0 or self.block_size_k <= 0 or self.block_size_n < 0:
+            raise ValueError("block sizes must be positive")
+        if self.group_size_m <= 0:
+            raise ValueError("group_size_m must be positive")
+        if self.all_reduce_variant not in ("atomic", "ring", "one_shot", "two_shot", "spinlock", "auto"):
+            raise ValueError(f"unknown all_reduce_variant {self.all_reduce_variant!r}")
+
+    def validate(self, world_size: int | None = None) -> None:
+        if world_size is not None and world_size <= 0:
+            raise ValueError("world_size must be positive")
+
+    def tile_n(self) -> int:
+        return self.block_size_n if self.block_size_n in (128, 224, 256) else 0

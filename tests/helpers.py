@@ -1,0 +1,83 @@
+"""Launch helpers for multi-process tests.
+
+CPU tests run `world` gloo ranks as child processes of the test (spawn); GPU tests run one child
+per GPU with the nccl backend. The child entry point is a module-level function
+``fn(rank, world, *args)``; an exception in any rank fails the test with that rank's traceback.
+"""
+from __future__ import annotations
+
+import os
+import socket
+import sys
+import traceback
+
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, world, port, backend, fn, args, errq, env):
+    try:
+        os.environ.update(env)
+        os.environ.update({"RANK": str(rank), "LOCAL_RANK": str(rank), "WORLD_SIZE": str(world),
+                           "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+        if ROOT not in sys.path:
+            sys.path.insert(0, ROOT)
+        import torch.distributed as dist
+
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+        try:
+            fn(rank, world, *args)
+        finally:
+            try:
+                dist.destroy_process_group()
+            except Exception:
+                pass
+    except BaseException:
+        errq.put((rank, traceback.format_exc()))
+        raise
+
+
+def run_ranks(fn, world: int, args=(), backend: str = "gloo", timeout: float = 300.0, env: dict | None = None,
+              expect_failures: bool = False):
+    """Run ``fn(rank, world, *args)`` on ``world`` ranks; raise with the first failing traceback."""
+    ctx = mp.get_context("spawn")
+    errq = ctx.Queue()
+    port = free_port()
+    env = dict(env or {})
+    if backend == "gloo":
+        env.setdefault("IRIS_BACKEND", "cpu")
+    procs = [ctx.Process(target=_entry, args=(r, world, port, backend, fn, args, errq, env)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.kill()  # the exact child processes started above
+        p.join()
+    errors = []
+    while not errq.empty():
+        errors.append(errq.get())
+    codes = [p.exitcode for p in procs]
+    if expect_failures:
+        return codes, errors
+    if hung:
+        raise AssertionError(f"{len(hung)} rank(s) still running after {timeout}s")
+    if errors:
+        rank, tb = errors[0]
+        raise AssertionError(f"rank {rank} failed:\n{tb}")
+    if any(c != 0 for c in codes):
+        raise AssertionError(f"rank exit codes {codes}")
+    return codes, errors
