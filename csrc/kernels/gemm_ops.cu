@@ -37,7 +37,11 @@ struct Common {
   const float* bias_row;
   const float* bias_col;
   int32_t* status;
+  int64_t* timeline;   // optional [tiles + chunks][4] nanosecond stamps (globaltimer)
 
+  IRIS_D void stamp(int slot, int what) const {
+    if (timeline) timeline[(size_t)slot * 4 + what] = (int64_t)now_ns();
+  }
   IRIS_D Shape shape() const { return sh; }
   IRIS_D int gemm_ctas() const { return n_gemm_ctas; }
   IRIS_D int num_tiles() const { return tiles_m * tiles_n; }
@@ -65,8 +69,10 @@ struct LocalGemm : Common {
   IRIS_D void store16(State&, int row, int col, uint4 v) const {
     if (row < sh.M && col < sh.N) *(uint4*)(C + ((int64_t)row * ldc + col) * 2) = v;
   }
+  static constexpr bool kBulkEpilogue = false;
+  IRIS_D void store_chunk(State&, int, int, int, const uint8_t*) const {}
   IRIS_D void tile_done(State&, int, int) const {}
-  IRIS_D void comm_main() const {}
+  IRIS_D void comm_main(uint8_t*, int) const {}
   IRIS_D void post_main() const {}
 };
 
@@ -96,8 +102,12 @@ struct AllGatherGemm : Common {
   int use_mc;
 
   struct State {
-    int key = -1;
+    int key = -1;        // (source, chunk) whose arrival has been confirmed
     int epoch = -1;
+    int tm = -1;         // tile row the cached values below belong to
+    int src = 0, chunk = 0, g = 0, kb_next_src = 0, kb0 = 0;
+    const CUtensorMap* map = nullptr;
+    int y = 0;
   };
   IRIS_D int src_of_group(int g) const {  // own shard first, then the order the pushes arrive in
     int s = ctx.rank - g;
@@ -115,100 +125,205 @@ struct AllGatherGemm : Common {
       swizzled_tile(t, tiles_m, tiles_n, group_m, tm, tn);
     }
   }
-  IRIS_D bool a_source(State& st, int tm, int kb, ASource& s) const {
-    if (st.epoch < 0) st.epoch = read_epoch(sb);
-    const int buf = st.epoch & 1;
-    const int target = ((st.epoch >> 1) + 1) * n_comm_ctas;
-    int src, chunk, x;
-    if (mode == 0) {
-      src = tm / chunks; chunk = tm - src * chunks; x = kb * kBK; s.bk = x;
-    } else {
-      const int kb_per_src = cols_per_src / kBK;
-      const int g = kb / kb_per_src;
-      src = src_of_group(g); chunk = tm; x = (kb - g * kb_per_src) * kBK; s.bk = src * cols_per_src + x;
-    }
-    if (src == ctx.rank && !use_mc) {
-      s.map = &tmA; s.x = x; s.y = chunk * kBM;
+  // Select the map / row of (source, chunk) and make sure the chunk has arrived. The divisions
+  // and the flag poll happen once per (tile, source), not per K block.
+  IRIS_D bool select(State& st, int src, int chunk) const {
+    st.src = src; st.chunk = chunk;
+    if (src == ctx.rank) {       // own shard: read in place, nothing to wait for
+      st.map = &tmA; st.y = chunk * kBM;
       return true;
     }
+    const int buf = st.epoch & 1;
     const int key = src * chunks + chunk;
     if (key != st.key) {
+      const int target = ((st.epoch >> 1) + 1) * n_comm_ctas;
       if (!wait_flag_ge(ctx, flags + ((size_t)buf * ctx.world + src) * chunks + chunk, target)) return false;
       st.key = key;
       // The data was written by another GPU (generic proxy, remote); order the TMA (async proxy)
       // reads after the acquire.
       ptx::fence_proxy_async();
     }
-    s.map = &tmInbox; s.x = x; s.y = ((buf * ctx.world + src) * rows_per_src) + chunk * kBM;
+    st.map = &tmInbox; st.y = ((buf * ctx.world + src) * rows_per_src) + chunk * kBM;
+    return true;
+  }
+  IRIS_D bool a_source(State& st, int tm, int kb, ASource& s) const {
+    if (st.epoch < 0) st.epoch = read_epoch(sb);
+    if (mode == 0) {
+      if (tm != st.tm) {
+        st.tm = tm;
+        const int src = tm / chunks;
+        if (!select(st, src, tm - src * chunks)) return false;
+      }
+      s.map = st.map; s.x = kb * kBK; s.y = st.y; s.bk = s.x;
+      return true;
+    }
+    // K-sharded: walk the sources along K, own shard first
+    if (kb == 0 || kb == st.kb_next_src) {
+      const int kb_per_src = cols_per_src / kBK;
+      st.g = kb == 0 ? 0 : st.g + 1;
+      st.kb0 = st.g * kb_per_src;
+      st.kb_next_src = st.kb0 + kb_per_src;
+      if (!select(st, src_of_group(st.g), tm)) return false;
+    }
+    s.map = st.map; s.x = (kb - st.kb0) * kBK; s.y = st.y; s.bk = st.src * cols_per_src + s.x;
     return true;
   }
   IRIS_D void begin_tile(State&, int, int) const {}
   IRIS_D void store16(State&, int row, int col, uint4 v) const {
     if (row < sh.M && col < sh.N) *(uint4*)(C + ((int64_t)row * ldc + col) * 2) = v;
   }
+  static constexpr bool kBulkEpilogue = false;
+  IRIS_D void store_chunk(State&, int, int, int, const uint8_t*) const {}
   IRIS_D void tile_done(State&, int, int) const {}
 
   // Communication CTAs: CTA j moves slice j (of n_comm_ctas) of every 128-row chunk, chunk by
-  // chunk, so chunk 0 is complete everywhere first.
-  IRIS_D void comm_main() const {
+  // chunk, so chunk 0 is complete everywhere first. The slice streams through a ring of shared
+  // memory buffers filled by bulk async copies (cp.async.bulk, local HBM read once); from there it
+  // goes either to each peer with bulk async stores issued by one thread (unicast), or to all
+  // ranks at once with multimem.st issued by every thread (NVLS). After the last piece of a chunk
+  // the stores are drained and the chunk's arrival counter is raised on the receivers.
+  static constexpr int kPiece = 32 * 1024;
+  // wait until at most `n` of the most recent bulk groups are still pending
+  IRIS_D static void bulk_wait_upto(int n) {
+    switch (n) {
+      case 0: ptx::bulk_wait<0>(); break;
+      case 1: ptx::bulk_wait<1>(); break;
+      case 2: ptx::bulk_wait<2>(); break;
+      case 3: ptx::bulk_wait<3>(); break;
+      case 4: ptx::bulk_wait<4>(); break;
+      case 5: ptx::bulk_wait<5>(); break;
+      case 6: ptx::bulk_wait<6>(); break;
+      case 7: ptx::bulk_wait<7>(); break;
+      case 8: ptx::bulk_wait<8>(); break;
+      default: ptx::bulk_wait<0>(); break;   // more groups than cases: drain everything
+    }
+  }
+  IRIS_D void signal_chunk(int buf, int c) const {
+    int32_t* flag_local = flags + ((size_t)buf * ctx.world + ctx.rank) * chunks + c;
+    ptx::fence_proxy_async();
+    fence_sys();
+    for (int p = 1; p < ctx.world; ++p) {
+      int dst_rank = ctx.rank + p;
+      if (dst_rank >= ctx.world) dst_rank -= ctx.world;
+      red_release_sys_add(ctx.remote(flag_local, dst_rank), 1);
+    }
+  }
+  IRIS_D void comm_main(uint8_t* smem_raw, int smem_bytes) const {
     const int j = blockIdx.x - n_gemm_ctas;
     const int epoch = read_epoch(sb);
     const int buf = epoch & 1;
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    int nb = (smem_bytes - 1024) / kPiece;
+    if (nb > 6) nb = 6;
+    uint64_t* bars = (uint64_t*)(smem + (size_t)nb * kPiece);
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < nb; ++i) ptx::mbar_init(&bars[i], 1);
+      ptx::fence_mbar_init();
+      ptx::fence_proxy_async();
+    }
+    __syncthreads();
     const size_t row_bytes = (size_t)cols_per_src * 2;
-    const size_t vec_per_row = row_bytes / 16;
+    const size_t src_pitch = (size_t)lda * 2;
+    const bool flat = src_pitch == row_bytes;
+    const int pieces_per_row = (int)((row_bytes + kPiece - 1) / kPiece);
+    // piece i of a slice of `nrows` rows starting at byte offsets (src0, dst0): (src, dst, bytes)
+    auto piece = [&](int i, size_t slice_bytes, size_t& soff, size_t& doff, uint32_t& bytes) {
+      if (flat) {
+        soff = doff = (size_t)i * kPiece;
+        bytes = (uint32_t)min((size_t)kPiece, slice_bytes - soff);
+      } else {
+        const int r = i / pieces_per_row, k = i - r * pieces_per_row;
+        soff = (size_t)r * src_pitch + (size_t)k * kPiece;
+        doff = (size_t)r * row_bytes + (size_t)k * kPiece;
+        bytes = (uint32_t)min((size_t)kPiece, row_bytes - (size_t)k * kPiece);
+      }
+    };
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
+    int it_global = 0;   // pieces issued so far by this CTA (selects ring slot and barrier parity)
     for (int c = 0; c < chunks; ++c) {
       const int r0 = c * kBM;
-      const int nrows = min(kBM, rows_per_src - r0);
-      // slice the chunk by rows
-      const int rows_lo = (int)((int64_t)nrows * j / n_comm_ctas), rows_hi = (int)((int64_t)nrows * (j + 1) / n_comm_ctas);
-      const size_t nvec = (size_t)(rows_hi - rows_lo) * vec_per_row;
+      const int nrows_c = min(kBM, rows_per_src - r0);
+      const int rows_lo = (int)((int64_t)nrows_c * j / n_comm_ctas), rows_hi = (int)((int64_t)nrows_c * (j + 1) / n_comm_ctas);
+      const int nrows = rows_hi - rows_lo;
+      const size_t slice_bytes = (size_t)nrows * row_bytes;
+      const int n = nrows == 0 ? 0 : (flat ? (int)((slice_bytes + kPiece - 1) / kPiece) : nrows * pieces_per_row);
+      const uint8_t* src0 = A_local + (size_t)(r0 + rows_lo) * src_pitch;
       uint8_t* dst_local = inbox + (((size_t)buf * ctx.world + ctx.rank) * rows_per_src + r0 + rows_lo) * row_bytes;
       int32_t* flag_local = flags + ((size_t)buf * ctx.world + ctx.rank) * chunks + c;
+      const int base = it_global;
+      auto issue_load = [&](int i) {   // thread 0 only
+        size_t so, d_o; uint32_t by;
+        piece(i, slice_bytes, so, d_o, by);
+        const int slot = (base + i) % nb;
+        ptx::mbar_expect_tx(&bars[slot], by);
+        ptx::bulk_load(smem + (size_t)slot * kPiece, src0 + so, by, &bars[slot]);
+      };
       if (use_mc) {
-        uint8_t* dst = ctx.mc(dst_local);
-        for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-          const size_t rr = i / vec_per_row, cc = i - rr * vec_per_row;
-          const multimem::V4 v = *(const multimem::V4*)(A_local + ((size_t)(r0 + rows_lo + rr) * lda) * 2 + cc * 16);
-          multimem::st_v4(dst + rr * row_bytes + cc * 16, v);
+        uint8_t* dst_mc = ctx.mc(dst_local);
+        if (threadIdx.x == 0)
+          for (int i = 0; i < min(nb, n); ++i) issue_load(i);
+        for (int i = 0; i < n; ++i) {
+          const int slot = (base + i) % nb;
+          const uint32_t parity = (uint32_t)(((base + i) / nb) & 1);
+          if (!ptx::mbar_wait(&bars[slot], parity, kPipeTimeoutNs)) { fail(kTimeoutPipeline); s_abort = 1; }
+          __syncthreads();
+          if (s_abort) break;
+          size_t so, d_o; uint32_t by;
+          piece(i, slice_bytes, so, d_o, by);
+          const uint8_t* sp = smem + (size_t)slot * kPiece;
+          for (uint32_t u = threadIdx.x * 16; u < by; u += blockDim.x * 16) {
+            const multimem::V4 v = *(const multimem::V4*)(sp + u);
+            multimem::st_v4(dst_mc + d_o + u, v);
+          }
+          __syncthreads();
+          if (threadIdx.x == 0 && i + nb < n) {
+            ptx::fence_proxy_async();   // generic reads of the slot precede the async refill
+            issue_load(i + nb);
+          }
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
+        if (threadIdx.x == 0 && !s_abort) {
           fence_sys();
           multimem::red_release_add_u32(ctx.mc(flag_local), 1);
         }
-      } else {
-        for (int p = 1; p < ctx.world; ++p) {
-          int dst_rank = ctx.rank + p;
-          if (dst_rank >= ctx.world) dst_rank -= ctx.world;
-          uint8_t* dst = ctx.remote(dst_local, dst_rank);
-          // 8 independent 16-byte loads in flight per thread, then the 8 peer stores
-          const uint8_t* src0 = A_local + ((size_t)(r0 + rows_lo) * lda) * 2;
-          const size_t src_pitch = (size_t)lda * 2;
-          size_t i = threadIdx.x;
-          for (; i + 7 * (size_t)blockDim.x < nvec; i += 8 * (size_t)blockDim.x) {
-            uint4 v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const size_t k = i + u * (size_t)blockDim.x, rr = k / vec_per_row, cc = k - rr * vec_per_row;
-              v[u] = *(const uint4*)(src0 + rr * src_pitch + cc * 16);
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const size_t k = i + u * (size_t)blockDim.x, rr = k / vec_per_row, cc = k - rr * vec_per_row;
-              *(uint4*)(dst + rr * row_bytes + cc * 16) = v[u];
-            }
+      } else if (threadIdx.x == 0) {
+        int next_load = min(nb, n);
+        for (int i = 0; i < next_load; ++i) issue_load(i);
+        bool ok = true;
+        for (int i = 0; i < n && ok; ++i) {
+          const int slot = (base + i) % nb;
+          const uint32_t parity = (uint32_t)(((base + i) / nb) & 1);
+          if (!ptx::mbar_wait(&bars[slot], parity, kPipeTimeoutNs)) { fail(kTimeoutPipeline); ok = false; break; }
+          size_t so, d_o; uint32_t by;
+          piece(i, slice_bytes, so, d_o, by);
+          for (int p = 1; p < ctx.world; ++p) {
+            int dst_rank = ctx.rank + p;
+            if (dst_rank >= ctx.world) dst_rank -= ctx.world;
+            ptx::bulk_store(ctx.remote(dst_local, dst_rank) + d_o, smem + (size_t)slot * kPiece, by);
           }
-          for (; i < nvec; i += blockDim.x) {
-            const size_t rr = i / vec_per_row, cc = i - rr * vec_per_row;
-            *(uint4*)(dst + rr * row_bytes + cc * 16) = *(const uint4*)(src0 + rr * src_pitch + cc * 16);
+          ptx::bulk_commit();
+          ptx::bulk_wait_read<1>();
+          while (next_load <= i - 1 + nb && next_load < n) issue_load(next_load++);
+        }
+        if (!ok) { s_abort = 1; }
+        // The stores of chunk c are only known complete once all but the groups committed after
+        // them have drained: raise chunk c-1's counter now (its groups are older than the n just
+        // committed), and the last chunk's after a full drain. Keeps the pipe busy across chunks.
+        if (!s_abort) {
+          if (c > 0) {
+            bulk_wait_upto(n);
+            signal_chunk(buf, c - 1);
           }
-          __syncthreads();
-          if (threadIdx.x == 0) {
-            fence_sys();
-            red_release_sys_add(ctx.remote(flag_local, dst_rank), 1);
+          if (c == chunks - 1) {
+            ptx::bulk_wait<0>();
+            signal_chunk(buf, c);
           }
         }
       }
+      it_global += n;
+      if (threadIdx.x == 0 && j == 0) stamp(tiles_m * tiles_n + c, 3);
     }
     finish();
   }
@@ -238,7 +353,9 @@ struct AllGatherGemm : Common {
 // CTA turns reducer: it waits (acquire) until a tile it owns has W arrivals, sums the W partials
 // in fp32 and writes the result: to its own output (reduce-scatter) or to all ranks (all-reduce).
 // Staging and counters are double-buffered by call parity, as in AllGatherGemm.
-struct ScatterGemm : Common {
+template <bool kReduce>
+struct ScatterGemmT : Common {
+  static constexpr bool kBulkEpilogue = kReduce;
   DeviceContext ctx;
   SyncBlock* sb;
   int mode;               // IrisGemmOp
@@ -321,16 +438,21 @@ struct ScatterGemm : Common {
       store_everywhere(out + (((int64_t)ctx.rank * sh.M + row) * ld_out + col) * 2, v);
     } else if (mode == IRIS_GEMM_ALL_SCATTER) {
       store_everywhere(out + ((int64_t)row * ld_out + (int64_t)ctx.rank * sh.N + col) * 2, v);
-    } else {
-      *(uint4*)(st.slot + ((size_t)(row - st.row0) * bn + (col - st.col0)) * 2) = v;
     }
+  }
+  // Reducing modes: rows [32*quarter, +32) x columns [64*chunk, +width) of the current tile go to
+  // the owner's staging slot as one contiguous piece. Slot layout (private to this kernel):
+  // [chunk][quarter][32 rows][width columns], 16-byte groups XOR-swizzled as staged in smem.
+  IRIS_D void store_chunk(State& st, int quarter, int chunk, int width, const uint8_t* smem) const {
+    uint8_t* dst = st.slot + (size_t)chunk * (kBM * 64 * 2) + (size_t)quarter * (32 * width * 2);
+    ptx::bulk_store(dst, smem, 32 * width * 2);
   }
   IRIS_D void tile_done(State& st, int, int) const {
     if (!reducing()) return;
     fence_sys();
     red_release_sys_add(ctx.remote(flags + (size_t)st.buf * max_owned + st.lt, st.owner), 1);
   }
-  IRIS_D void comm_main() const {}
+  IRIS_D void comm_main(uint8_t*, int) const {}
 
   IRIS_D int owned_tiles() const {
     const int total = tiles_m * tiles_n;
@@ -378,7 +500,12 @@ struct ScatterGemm : Common {
           float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
           for (int s = 0; s < ctx.world; ++s) {
             const uint8_t* slot = staging + ((((size_t)buf * ctx.world + s) * max_owned + lt) * (size_t)(kBM * bn)) * 2;
-            const uint4 v = *(const uint4*)(slot + ((size_t)rr * bn + cv * 8) * 2);
+            const int chunk = cv >> 3, c16 = cv & 7;
+            const int width = (bn - chunk * 64) >= 64 ? 64 : 32;
+            const int r32 = rr & 31;
+            const int pos = width == 64 ? (c16 ^ (r32 & 7)) : (c16 ^ ((r32 >> 1) & 3));
+            const uint4 v = *(const uint4*)(slot + (size_t)chunk * (kBM * 64 * 2) + (size_t)(rr >> 5) * (32 * width * 2) +
+                                            (size_t)r32 * (width * 2) + pos * 16);
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -525,6 +652,7 @@ int fill_common(Common& c, const IrisGemmDesc* d, int bn, int gemm_ctas, const v
   c.bias_row = d->bias_row;
   c.bias_col = d->bias_col;
   c.status = d->ctx.status;
+  c.timeline = (int64_t*)d->timeline;
   return 0;
 }
 
@@ -540,7 +668,7 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
   const int W = d->ctx.world > 0 ? d->ctx.world : 1;
   const int sms = sm_count();
   const bool ag = d->op == IRIS_GEMM_AG_M || d->op == IRIS_GEMM_AG_K;
-  p.comm_ctas = ag && W > 1 ? (d->comm_ctas > 0 ? d->comm_ctas : (d->use_mc && d->ctx.mc_base ? 4 : 16)) : 0;
+  p.comm_ctas = ag && W > 1 ? (d->comm_ctas > 0 ? d->comm_ctas : 8) : 0;
   p.gemm_ctas = d->gemm_ctas > 0 ? d->gemm_ctas : sms - p.comm_ctas;
   if (p.gemm_ctas + p.comm_ctas > sms) return -4;  // every CTA must be resident: consumers wait on producers
   p.bn = d->bn > 0 ? d->bn : choose_bn(d->M, d->N, p.gemm_ctas, !d->b_kmajor);
@@ -630,14 +758,25 @@ extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
     if ((p.cols_per_src * 2) % 16) return -8;
     return dispatch(pol, p.bn, d->b_kmajor != 0, grid, stream);
   }
-  ScatterGemm pol;
-  r = fill_common(pol, d, p.bn, p.gemm_ctas, d->A, d->M, d->K, d->lda);
-  if (r) return r;
-  pol.ctx = ctx; pol.sb = (SyncBlock*)d->sync_block; pol.mode = d->op;
-  pol.out = (uint8_t*)d->C; pol.ld_out = d->ldc;
-  pol.staging = (uint8_t*)d->staging; pol.flags = d->flags;
-  pol.max_owned = p.max_owned; pol.tiles_m_per_rank = p.tiles_m_per_rank; pol.tiles_per_rank = p.tiles_per_rank;
-  pol.use_mc = use_mc;
+  auto fill = [&](auto& pol) -> int {
+    int rr = fill_common(pol, d, p.bn, p.gemm_ctas, d->A, d->M, d->K, d->lda);
+    if (rr) return rr;
+    pol.ctx = ctx; pol.sb = (SyncBlock*)d->sync_block; pol.mode = d->op;
+    pol.out = (uint8_t*)d->C; pol.ld_out = d->ldc;
+    pol.staging = (uint8_t*)d->staging; pol.flags = d->flags;
+    pol.max_owned = p.max_owned; pol.tiles_m_per_rank = p.tiles_m_per_rank; pol.tiles_per_rank = p.tiles_per_rank;
+    pol.use_mc = use_mc;
+    return 0;
+  };
   // reducers stride over all GEMM CTAs, so launch the full grid even for few tiles
+  if (d->op == IRIS_GEMM_ALL_GATHER || d->op == IRIS_GEMM_ALL_SCATTER) {
+    ScatterGemmT<false> pol;
+    r = fill(pol);
+    if (r) return r;
+    return dispatch(pol, p.bn, d->b_kmajor != 0, grid, stream);
+  }
+  ScatterGemmT<true> pol;
+  r = fill(pol);
+  if (r) return r;
   return dispatch(pol, p.bn, d->b_kmajor != 0, grid, stream);
 }

@@ -40,7 +40,7 @@ struct Config {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kAccCols = 256;                                  // column pitch of an accumulator buffer
   static constexpr int kTmemCols = 512;
-  static constexpr int kEpiBytes = kEpiWarps * 32 * 64;                 // 32 rows x 32 cols x 2 B per warp
+  static constexpr int kEpiBytes = kEpiWarps * 2 * 4096;                // per warp: two 32-row x 64-col staging chunks
   static constexpr int kSmemBytes = 1024 + kStages_ * kStageBytes + kEpiBytes + 256;
   static_assert(BN_ % 32 == 0 && BN_ >= 32 && BN_ <= 256, "BN must be a multiple of 32 up to 256");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
@@ -103,10 +103,17 @@ struct Pipeline {
 //   void begin_tile(State&, int m_tile, int n_tile) const; (every epilogue thread, before a tile's stores)
 //   void store16(State&, int row, int col, uint4 v) const; (8 consecutive outputs of one row)
 //   float row_bias(int row) const;  float col_bias(int col) const;  bool has_bias() const;
+//   static constexpr bool kBulkEpilogue;                   (true: chunks leave through store_chunk)
+//   void store_chunk(State&, int quarter, int chunk, int width, const uint8_t* smem) const;
+//        (lane 0 of an epilogue warp: issue the bulk store(s) of rows [32*quarter, +32) x columns
+//         [64*chunk, +width) of the current tile, staged in `smem` in the swizzled chunk layout)
 //   void tile_done(State&, int m_tile, int n_tile) const;  (one thread, after the tile's stores)
-//   void comm_main() const;                                 (CTAs with blockIdx.x >= gemm_ctas())
+//   void comm_main(uint8_t* smem, int smem_bytes) const;    (CTAs with blockIdx.x >= gemm_ctas())
 //   void post_main() const;                                 (GEMM CTAs, all threads, after their tiles)
 //   void fail(int code) const;
+//   void stamp(int tile_seq, int what) const;              (optional per-tile timestamps: 0 tile
+//        start, 1 first A tile available, 2 tile stored; reference examples collect the same with
+//        COLLECT_TIMESTAMPS, examples/07_gemm_all_scatter/gemm_all_scatter.py:64-66)
 // The policy is a __grid_constant__ kernel parameter (its tensor maps are used in place), so every
 // hook is const.
 template <class Cfg, class Policy>
@@ -157,9 +164,11 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
     for (int t = first; t < num_tiles && ok; t += step) {
       int tm, tn;
       pol.tile(t, tm, tn);
+      if (lane == 0) pol.stamp(t, 0);
       for (int kb = 0; kb < k_blocks; ++kb) {
         ASource as;
         if (!pol.a_source(st, tm, kb, as)) { ok = false; break; }
+        if (kb == 0 && lane == 0) pol.stamp(t, 1);
         if (!ptx::mbar_wait(&pipe.empty[s], ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
         if (lane == 0) {
           uint8_t* sa = stage_base + s * Cfg::kStageBytes;
@@ -213,7 +222,8 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    uint8_t* my_epi = epi_base + (warp - 2) * (32 * 64);
+    uint8_t* my_epi = epi_base + (warp - 2) * (2 * 4096);
+    uint32_t chunk_seq = 0;   // bulk epilogue: chunks issued by this warp (selects the staging half)
     const bool bf16 = pol.is_bf16();
     const bool has_bias = pol.has_bias();
     typename Policy::State est;
@@ -236,6 +246,64 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * Cfg::kAccCols;
       const int row0 = tm * kBM + quarter * 32;
       const float rb = has_bias ? pol.row_bias(row0 + lane) : 0.f;
+      if constexpr (Policy::kBulkEpilogue) {
+        // The tile leaves in 64-column chunks: TMEM -> registers -> swizzled shared memory, then
+        // ONE bulk async store per chunk (4 KB, or 2 KB for a 32-column tail) issued by lane 0
+        // through the policy. Two staging halves per warp: a half is rewritten only after the
+        // store that read it has finished reading (wait_group.read).
+        constexpr int kChunks = (Cfg::BN + 63) / 64;
+#pragma unroll 1
+        for (int cc = 0; cc < kChunks; ++cc) {
+          const int w = (Cfg::BN - cc * 64) >= 64 ? 64 : 32;   // columns in this chunk
+          uint8_t* stage = my_epi + (chunk_seq & 1) * 4096;
+          if (lane == 0) ptx::bulk_wait_read<1>();
+          __syncwarp();
+#pragma unroll 1
+          for (int hlf = 0; hlf < w / 32; ++hlf) {
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(t_addr + cc * 64 + hlf * 32, r);
+            ptx::tmem_ld_wait();
+            if (cc == kChunks - 1 && hlf == w / 32 - 1) {
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(&pipe.tmem_empty[buf]);
+            }
+            const int col0 = tn * Cfg::BN + cc * 64 + hlf * 32;
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float a = __uint_as_float(r[2 * j]) + rb, b = __uint_as_float(r[2 * j + 1]) + rb;
+              if (has_bias) { a += pol.col_bias(col0 + 2 * j); b += pol.col_bias(col0 + 2 * j + 1); }
+              if (bf16) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                packed[j] = *(uint32_t*)&h;
+              } else {
+                __half2 h = __floats2half2_rn(a, b);
+                packed[j] = *(uint32_t*)&h;
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+              const int c16 = hlf * 4 + j;   // 16-byte column group inside the chunk
+              const int pos = w == 64 ? (c16 ^ (lane & 7)) : (c16 ^ ((lane >> 1) & 3));
+              *(uint4*)(stage + lane * (w * 2) + pos * 16) = v;
+            }
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            pol.store_chunk(est, quarter, cc, w, stage);
+            ptx::bulk_commit();
+          }
+          ++chunk_seq;
+        }
+        if (lane == 0) {
+          ptx::bulk_wait<0>();          // this warp's stores of the tile are complete
+          ptx::fence_proxy_async();
+        }
+        __syncwarp();
+      } else {
 #pragma unroll 1
       for (int c = 0; c < Cfg::BN / 32; ++c) {
         uint32_t r[32];
@@ -276,8 +344,12 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         }
         __syncwarp();
       }
+      }
       ptx::named_barrier(1, kEpiWarps * 32);
-      if (warp == 2 && lane == 0) pol.tile_done(est, tm, tn);
+      if (warp == 2 && lane == 0) {
+        pol.tile_done(est, tm, tn);
+        pol.stamp(t, 2);
+      }
     }
   }
   ptx::tc_fence_before();
@@ -291,7 +363,7 @@ template <class Cfg, class Policy>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ Policy pol_in) {
   extern __shared__ uint8_t smem_raw[];
   if ((int)blockIdx.x >= pol_in.gemm_ctas()) {
-    pol_in.comm_main();
+    pol_in.comm_main(smem_raw, Cfg::kSmemBytes);
     return;
   }
   gemm_cta_main<Cfg, Policy>(pol_in, smem_raw);

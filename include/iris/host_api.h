@@ -63,6 +63,8 @@ typedef struct IrisGemmDesc {
   void* staging;          // RS/AR: [2][W][owned tiles][128*bn] partial tiles (heap)
   int32_t M_local;        // AG_M: rows per rank; ALL_GATHER: rows per rank (= M)
   int32_t K_local;        // AG_K: K per rank
+  void* timeline;         // optional int64 [tiles + chunks][4]: per-tile timestamps in ns (0 start,
+                          // 1 operands available, 2 stored; comm CTA 0 stamps slot tiles+c, col 3)
 } IrisGemmDesc;
 
 // Bytes of workspace the op needs for this shape (inbox / flags / staging). Pure arithmetic.

@@ -63,6 +63,7 @@ class IrisGemmDesc(C.Structure):
         ("staging", C.c_void_p),
         ("M_local", C.c_int32),
         ("K_local", C.c_int32),
+        ("timeline", C.c_void_p),
     ]
 
 

@@ -1,0 +1,162 @@
+"""Distributed flash-decode layer: one query token per sequence, KV cache sharded along the
+sequence across ranks (reference: examples/13_flash_decode/flash_decode_fused_layer.py:38-148).
+
+``FlashDecodeLayer.forward(q, k_cache, v_cache, global_kv_lens, block_table)``
+
+* ``q``             ``[B, Hq, D]`` (replicated on every rank)
+* ``k_cache``/``v_cache``  this rank's paged shard ``[num_blocks, page, Hkv, D]``
+* ``global_kv_lens`` ``int32 [W, B]``: KV length held by every rank for every sequence
+* ``block_table``   ``int32 [B, max_blocks]``: page ids of this rank's shard
+
+Two kernel launches on the current stream (``csrc/kernels/flash_decode.cu``): the split-K pass
+over the local shard, then combine + exchange of the partial ``(o, lse)`` by remote stores with
+per-(source, batch, head) flags + final merge. No host synchronisation, no flag reset between
+calls. ``reference_decode`` is the plain fp32 PyTorch statement of the same computation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from .. import _lib
+
+
+class IrisDecodeDesc(C.Structure):
+    _fields_ = [
+        ("ctx", _lib.IrisCtx),
+        ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("block_table", C.c_void_p), ("kv_lens", C.c_void_p),
+        ("partial", C.c_void_p),
+        ("gathered", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p),
+        ("out", C.c_void_p), ("out_lse", C.c_void_p),
+        ("B", C.c_int32), ("Bmax", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32),
+        ("page", C.c_int32), ("max_blocks", C.c_int32), ("splits", C.c_int32),
+        ("sm_scale", C.c_float), ("soft_cap", C.c_float),
+        ("dtype", C.c_int32),
+        ("exchange", C.c_int32),
+    ]
+
+
+def reference_decode(q, k_cache, v_cache, kv_lens, block_table, sm_scale=None, soft_cap=0.0):
+    """fp32 paged GQA decode over ONE shard: returns ``(o [B,Hq,D] fp32, lse [B,Hq] natural log)``."""
+    B, Hq, D = q.shape
+    _, page, Hkv, _ = k_cache.shape
+    group = Hq // Hkv
+    sm_scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(D)
+    o = torch.zeros(B, Hq, D, dtype=torch.float32, device=q.device)
+    lse = torch.full((B, Hq), float("-inf"), dtype=torch.float32, device=q.device)
+    for b in range(B):
+        n = int(kv_lens[b])
+        if n == 0:
+            continue
+        nblk = -(-n // page)
+        blocks = block_table[b, :nblk].long()
+        k = k_cache[blocks].reshape(-1, Hkv, D)[:n].float()
+        v = v_cache[blocks].reshape(-1, Hkv, D)[:n].float()
+        qb = q[b].float().view(Hkv, group, D)
+        s = torch.einsum("hgd,nhd->hgn", qb, k) * sm_scale
+        if soft_cap > 0:
+            s = soft_cap * torch.tanh(s / soft_cap)
+        lse_b = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - lse_b[..., None])
+        o[b] = torch.einsum("hgn,nhd->hgd", p, v).reshape(Hq, D)
+        lse[b] = lse_b.reshape(Hq)
+    return o, lse
+
+
+def merge_partials(o_parts, lse_parts):
+    """Merge per-shard ``(o, lse)`` (leading dim = shard) into the attention over all shards."""
+    m = torch.max(lse_parts, dim=0).values
+    m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    w = torch.exp(lse_parts - m)
+    w = torch.where(torch.isnan(w), torch.zeros_like(w), w)
+    den = w.sum(0).clamp_min(1e-38)
+    return (w[..., None] * o_parts).sum(0) / den[..., None]
+
+
+class FlashDecodeLayer:
+    def __init__(self, ctx, num_q_heads: int, num_kv_heads: int, head_dim: int = 128, max_batch: int = 64,
+                 sm_scale: float | None = None, soft_cap: float = 0.0, max_splits: int = 64, dtype=torch.bfloat16):
+        if head_dim != 128:
+            raise ValueError("the decode kernel is specialised for head_dim 128")
+        if num_q_heads % num_kv_heads:
+            raise ValueError("num_q_heads must be a multiple of num_kv_heads")
+        self.ctx = ctx
+        self.Hq, self.Hkv, self.D = num_q_heads, num_kv_heads, head_dim
+        self.max_batch, self.max_splits = max_batch, max_splits
+        self.sm_scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(head_dim)
+        self.soft_cap = float(soft_cap)
+        self.dtype = dtype
+        W = ctx.get_num_ranks()
+        dev = ctx.get_device()
+        # exchange buffers on the heap: [2][W][Bmax][Hq][D+1] fp32 and [2][W][Bmax][Hq] int32
+        self.gathered = ctx.zeros((2, W, max_batch, num_q_heads, head_dim + 1), dtype=torch.float32)
+        self.signal_flags = ctx.zeros((2, W, max_batch, num_q_heads), dtype=torch.int32)
+        self.state = ctx.zeros(2, dtype=torch.int32)
+        self.partial = torch.empty((max_batch, num_q_heads, max_splits, head_dim + 1), dtype=torch.float32, device=dev)
+        ctx.barrier()
+
+    def _lib(self):
+        lib = _lib.kernels()
+        if not getattr(lib, "_iris_decode_typed", False):
+            lib.iris_flash_decode.argtypes = [C.POINTER(IrisDecodeDesc), C.c_void_p]
+            lib.iris_flash_decode.restype = C.c_int
+            lib._iris_decode_typed = True
+        return lib
+
+    def num_splits(self, batch: int, max_len: int) -> int:
+        sms = max(self.ctx.get_cu_count(), 1)
+        per_seq = self.Hkv * -(-(self.Hq // self.Hkv) // 16)
+        want = -(-4 * sms // max(batch * per_seq, 1))          # ~2 waves of 2 CTAs per SM
+        by_len = max(1, -(-max_len // 256))                     # at least 256 positions per split
+        return max(1, min(self.max_splits, want, by_len))
+
+    def forward(self, q, k_cache, v_cache, global_kv_lens, block_table, out=None, return_lse: bool = False):
+        ctx = self.ctx
+        B = q.shape[0]
+        if B > self.max_batch:
+            raise ValueError(f"batch {B} exceeds max_batch {self.max_batch}")
+        kv_lens = global_kv_lens[ctx.get_rank()].contiguous()
+        page = k_cache.shape[1]
+        if ctx.is_cpu:
+            return self._forward_cpu(q, k_cache, v_cache, kv_lens, block_table)
+        if out is None:
+            out = torch.empty((B, self.Hq, self.D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, self.Hq), dtype=torch.float32, device=q.device) if return_lse else None
+        d = IrisDecodeDesc()
+        d.ctx = ctx.ctx_struct()
+        d.q, d.k_cache, d.v_cache = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+        d.block_table, d.kv_lens = block_table.data_ptr(), kv_lens.data_ptr()
+        d.partial = self.partial.data_ptr()
+        d.gathered, d.flags, d.state = self.gathered.data_ptr(), self.signal_flags.data_ptr(), self.state.data_ptr()
+        d.out = out.data_ptr()
+        d.out_lse = lse.data_ptr() if lse is not None else None
+        d.B, d.Bmax, d.Hq, d.Hkv, d.D = B, self.max_batch, self.Hq, self.Hkv, self.D
+        d.page, d.max_blocks = page, block_table.shape[1]
+        d.splits = self.num_splits(B, block_table.shape[1] * page)
+        d.sm_scale, d.soft_cap = self.sm_scale, self.soft_cap
+        d.dtype = _lib.DTYPE_CODE[q.dtype]
+        d.exchange = 1
+        if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous() and block_table.is_contiguous()):
+            raise ValueError("flash decode takes contiguous q, caches and block table")
+        _lib.check(self._lib().iris_flash_decode(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "flash decode launch")
+        return (out, lse) if return_lse else out
+
+    __call__ = forward
+
+    def _forward_cpu(self, q, k_cache, v_cache, kv_lens, block_table):
+        """CPU backend: same exchange layout through the shared-memory heap, math in PyTorch."""
+        ctx = self.ctx
+        W, me = ctx.get_num_ranks(), ctx.get_rank()
+        B = q.shape[0]
+        o, lse = reference_decode(q, k_cache, v_cache, kv_lens, block_table, self.sm_scale, self.soft_cap)
+        ctx.device_barrier()
+        for r in range(W):
+            slot = ctx.heap.peer_view(self.gathered, r)[0, me, :B]
+            slot[..., : self.D] = o
+            slot[..., self.D] = lse
+        ctx.device_barrier()
+        parts = self.gathered[0, :, :B]
+        return merge_partials(parts[..., : self.D], parts[..., self.D]).to(q.dtype)

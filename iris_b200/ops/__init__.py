@@ -87,6 +87,8 @@ def _launch(ctx, d, ws) -> None:
     d.flags = ws.flags.data_ptr() if ws.flags is not None else None
     d.staging = ws.staging.data_ptr() if ws.staging is not None else None
     d.bn = ws.bn
+    tl = ws.extra.get("timeline")
+    d.timeline = tl.data_ptr() if tl is not None else None
     _lib.check(_lib.kernels().iris_gemm_launch(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), f"{ws.operation} launch")
 
 

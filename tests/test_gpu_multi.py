@@ -1,0 +1,277 @@
+"""Multi-GPU tests: one child process per GPU (nccl), world = min(#GPUs, 4).
+
+Oracles are torch.distributed collectives and fp32/fp64 host arithmetic, as in the reference's
+tests/ccl and tests/ops. Skipped on a machine with fewer than two GPUs.
+"""
+import pytest
+import torch
+
+from helpers import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _world():
+    return min(torch.cuda.device_count(), 4)
+
+
+def _maxerr(a, b):
+    return (a.double() - b.double()).abs().max().item()
+
+
+def _rma(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+
+    ctx = iris.iris(1 << 30)
+    buf = ctx.zeros(4096, dtype=torch.float32)
+    cnt = ctx.zeros(1, dtype=torch.int32)
+    ctx.barrier()
+    if rank == 0:
+        for b in range(4):
+            ctx.rma.store(buf[b * 1024:(b + 1) * 1024], 1.0, to_rank=1)
+    for p in range(world):
+        ctx.rma.atomic_add(cnt, 1, to_rank=p, sem="acq_rel", scope="sys")
+    ctx.barrier()
+    assert torch.all(buf == (1.0 if rank == 1 else 0.0))
+    assert int(cnt.item()) == world
+    peer = (rank + 1) % world
+    a = ctx.arange(0, 512, dtype=torch.int32)
+    a += 1000 * rank
+    b = ctx.zeros(512, dtype=torch.int32)
+    ctx.barrier()
+    for cm in (None, ".cg", ".cv"):
+        assert torch.equal(ctx.rma.load(a, from_rank=peer, cache_modifier=cm).cpu(), torch.arange(512, dtype=torch.int32) + 1000 * peer)
+    ctx.rma.get(a, b, from_rank=peer)
+    assert torch.equal(b.cpu(), torch.arange(512, dtype=torch.int32) + 1000 * peer)
+    ctx.barrier()
+    b.zero_()
+    ctx.barrier()
+    ctx.rma.put(a, b, to_rank=peer)
+    ctx.barrier()
+    assert torch.equal(b.cpu(), torch.arange(512, dtype=torch.int32) + 1000 * ((rank - 1) % world))
+    # device barrier orders a remote store before the peer's read, with no host sync in between
+    x = ctx.zeros(64, dtype=torch.float32)
+    ctx.barrier()
+    ctx.rma.store(x, float(rank + 1), to_rank=peer)
+    ctx.device_barrier()
+    got = x.clone()
+    torch.cuda.synchronize()
+    assert torch.all(got == float(((rank - 1) % world) + 1))
+    ctx.check()
+    ctx.barrier()
+
+
+def test_rma_between_gpus():
+    run_ranks(_rma, _world(), backend="nccl")
+
+
+def _ccl(rank, world, nvls):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.ccl import Config, owned_tiles
+
+    ctx = iris.iris(2 << 30)
+    assert ctx.has_multicast() or not nvls or True
+    for dtype, M, N in ((torch.bfloat16, 256, 512), (torch.float32, 128, 192), (torch.float16, 100, 72), (torch.float32, 1024, 2048)):
+        g = torch.Generator(device="cuda")
+        g.manual_seed(1234 + rank)
+        inp = ctx.empty((M, N), dtype=dtype)
+        inp.copy_((torch.rand(M, N, device="cuda", generator=g) * 2 - 1).to(dtype))
+        gathered = [torch.empty_like(inp) for _ in range(world)]
+        dist.all_gather(gathered, inp)
+        total = torch.stack([x.double() for x in gathered]).sum(0)
+        tol = 1e-5 * world if dtype == torch.float32 else 0.03 * world
+        out = ctx.zeros((world * M, N), dtype=dtype)
+        for v in ("persistent", "partitioned"):
+            out.zero_()
+            ctx.barrier()
+            ctx.ccl.all_gather(out, inp, config=Config(all_gather_variant=v))
+            assert torch.equal(out, torch.cat(gathered, 0)), v
+        if N % world == 0:
+            o2 = ctx.zeros((M, N), dtype=dtype)
+            ctx.barrier()
+            ctx.ccl.all_to_all(o2, inp)
+            n = N // world
+            exp = torch.cat([gathered[s][:, rank * n:(rank + 1) * n] for s in range(world)], 1)
+            assert torch.equal(o2, exp)
+        for v in ("one_shot", "two_shot", "atomic", "ring", "spinlock", "auto", "nvls"):
+            o3 = ctx.zeros((M, N), dtype=dtype)
+            ctx.barrier()
+            ws = None
+            for _ in range(3):
+                ws = ctx.ccl.all_reduce(o3, inp, config=Config(all_reduce_variant=v), workspace=ws)
+            assert _maxerr(o3, total) <= tol, (v, ws.variant, str(dtype))
+        for dmode in (0, 1):
+            o4 = ctx.zeros((M, N), dtype=dtype)
+            ctx.barrier()
+            cfg = Config(all_reduce_distribution=dmode)
+            ctx.ccl.reduce_scatter(o4, inp, config=cfg)
+            exp = torch.zeros(M, N, dtype=torch.float64, device="cuda")
+            for (r0, r1, c0, c1) in owned_tiles(M, N, cfg.block_size_m, cfg.block_size_n, world, rank, dmode):
+                exp[r0:r1, c0:c1] = total[r0:r1, c0:c1]
+            assert _maxerr(o4, exp) <= tol
+        if M % world == 0:
+            o5 = ctx.zeros((M // world, N), dtype=dtype)
+            ctx.barrier()
+            ctx.ccl.reduce_scatter(o5, inp, config=Config(reduce_scatter_rows=True))
+            assert _maxerr(o5, total[rank * (M // world):(rank + 1) * (M // world)]) <= tol
+    ctx.check()
+    ctx.barrier()
+
+
+@pytest.mark.parametrize("nvls", [False, True])
+def test_collectives_match_nccl(nvls):
+    run_ranks(_ccl, _world(), args=(nvls,), backend="nccl", env={"IRIS_NVLS": "1" if nvls else "0"})
+
+
+def _groups(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+
+    ctx = iris.iris(1 << 30)
+    # consecutive pairs and strided pairs, every collective restricted to the group
+    layouts = [[[0, 1], [2, 3]], [[0, 2], [1, 3]]]
+    for layout in layouts:
+        groups = [dist.new_group(r) for r in layout]
+        mine = next(g for g, r in zip(groups, layout) if rank in r)
+        members = next(r for r in layout if rank in r)
+        inp = ctx.full((64, 128), float(rank + 1), dtype=torch.float32)
+        out = ctx.zeros((64, 128), dtype=torch.float32)
+        ctx.barrier()
+        ctx.ccl.all_reduce(out, inp, group=mine)
+        assert torch.all(out == float(sum(m + 1 for m in members)))
+        ag = ctx.zeros((128, 128), dtype=torch.float32)
+        ctx.barrier()
+        ctx.ccl.all_gather(ag, inp, group=mine)
+        assert torch.all(ag[:64] == float(members[0] + 1)) and torch.all(ag[64:] == float(members[1] + 1))
+        ctx.barrier()
+    ctx.check()
+
+
+def test_process_groups():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    run_ranks(_groups, 4, backend="nccl")
+
+
+def _ops(rank, world, nvls):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.ops import owned_tile_range
+
+    ctx = iris.iris(4 << 30)
+    W = world
+    for dtype, Ml, N, K, kmajor in ((torch.bfloat16, 256, 512, 512, False), (torch.float16, 128, 768, 1024, True),
+                                    (torch.bfloat16, 512, 3584, 1024, False)):
+        torch.manual_seed(7 + rank)
+
+        def mkB(k, n):
+            return (torch.randn(n, k, device="cuda", dtype=dtype) * 0.05).t() if kmajor else torch.randn(k, n, device="cuda", dtype=dtype) * 0.05
+
+        A = torch.randn(Ml, K, device="cuda", dtype=dtype)
+        B = mkB(K, N)
+        Aall = torch.empty(W * Ml, K, device="cuda", dtype=dtype)
+        dist.all_gather_into_tensor(Aall, A)
+        ref = Aall.float() @ B.float()
+        C = ctx.zeros((W * Ml, N), dtype=dtype)
+        ws = None
+        for _ in range(3):
+            ws = ctx.ops.all_gather_matmul(C, A, B, shard_dim=0, workspace=ws)
+        assert ws.variant == "fused"
+        assert _maxerr(C, ref) <= 0.02 * ref.abs().max().item()
+        if K % (64 * W) == 0:
+            A2 = torch.randn(W * Ml, K // W, device="cuda", dtype=dtype)
+            bias = torch.randn(W * Ml, device="cuda", dtype=dtype)
+            parts = [torch.empty_like(A2) for _ in range(W)]
+            dist.all_gather(parts, A2)
+            ref2 = torch.cat(parts, 1).float() @ B.float() + bias.float()[:, None]
+            C2 = ctx.zeros((W * Ml, N), dtype=dtype)
+            ws2 = None
+            for _ in range(2):
+                ws2 = ctx.ops.all_gather_matmul(C2, A2, B, bias=bias, workspace=ws2)
+            assert _maxerr(C2, ref2) <= 0.02 * ref2.abs().max().item()
+        loc = (A.float() @ B.float()).to(dtype)
+        ref_ag = torch.empty(W * Ml, N, device="cuda", dtype=dtype)
+        dist.all_gather_into_tensor(ref_ag, loc)
+        C3 = ctx.zeros((W * Ml, N), dtype=dtype)
+        ws3 = None
+        for _ in range(2):
+            ws3 = ctx.ops.matmul_all_gather(C3, A, B, workspace=ws3)
+        assert _maxerr(C3, ref_ag) <= 0.02 * ref.abs().max().item()
+        M = W * Ml
+        A4 = torch.randn(M, K, device="cuda", dtype=dtype)
+        B4 = mkB(K, N)
+        tot = A4.float() @ B4.float()
+        dist.all_reduce(tot)
+        tol = 0.03 * tot.abs().max().item()
+        C4 = ctx.zeros((M, N), dtype=dtype)
+        ws4 = None
+        for _ in range(3):
+            ws4 = ctx.ops.matmul_all_reduce(C4, A4, B4, workspace=ws4)
+        assert _maxerr(C4, tot) <= tol
+        C5 = ctx.zeros((Ml, N), dtype=dtype)
+        ws5 = None
+        for _ in range(3):
+            ws5 = ctx.ops.matmul_reduce_scatter(C5, A4, B4, scatter_rows=True, workspace=ws5)
+        assert _maxerr(C5, tot[rank * Ml:(rank + 1) * Ml]) <= tol
+        C6 = ctx.zeros((M, N), dtype=dtype)
+        ws6 = None
+        for _ in range(2):
+            ws6 = ctx.ops.matmul_reduce_scatter(C6, A4, B4, workspace=ws6)
+        bn = ws6.bn
+        tiles_n = -(-N // bn)
+        exp = torch.zeros(M, N, device="cuda")
+        for t in owned_tile_range(-(-M // 128) * tiles_n, W, rank):
+            tm, tn = divmod(t, tiles_n)
+            exp[tm * 128:(tm + 1) * 128, tn * bn:(tn + 1) * bn] = tot[tm * 128:(tm + 1) * 128, tn * bn:(tn + 1) * bn]
+        assert _maxerr(C6, exp) <= tol
+    ctx.check()
+    ctx.barrier()
+
+
+@pytest.mark.parametrize("nvls", [False, True])
+def test_fused_ops_match_reference(nvls):
+    run_ranks(_ops, _world(), args=(nvls,), backend="nccl", env={"IRIS_NVLS": "1" if nvls else "0"}, timeout=600)
+
+
+def _decode(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.models import FlashDecodeLayer, merge_partials, reference_decode
+
+    ctx = iris.iris(1 << 30)
+    Hq, Hkv, D, page, B = 32, 4, 128, 64, 3
+    dt = torch.bfloat16
+    torch.manual_seed(5)
+    q = torch.randn(B, Hq, D, device="cuda", dtype=dt)           # replicated (same seed)
+    torch.manual_seed(100 + rank)
+    lens = [300 + 37 * rank, 64 * (rank + 1), 1 + rank]
+    max_blocks = -(-max(lens) // page)
+    kc = torch.randn(B * max_blocks, page, Hkv, D, device="cuda", dtype=dt)
+    vc = torch.randn(B * max_blocks, page, Hkv, D, device="cuda", dtype=dt)
+    table = torch.arange(B * max_blocks, device="cuda", dtype=torch.int32).view(B, max_blocks)
+    my_lens = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    all_lens = torch.empty(world, B, device="cuda", dtype=torch.int32)
+    dist.all_gather_into_tensor(all_lens, my_lens)
+    layer = FlashDecodeLayer(ctx, Hq, Hkv, D, max_batch=4)
+    for _ in range(3):
+        out = layer(q, kc, vc, all_lens, table)
+    o, lse = reference_decode(q, kc, vc, my_lens, table)
+    os_ = [torch.empty_like(o) for _ in range(world)]
+    ls_ = [torch.empty_like(lse) for _ in range(world)]
+    dist.all_gather(os_, o)
+    dist.all_gather(ls_, lse)
+    ref = merge_partials(torch.stack(os_), torch.stack(ls_))
+    assert (out.float() - ref).abs().max().item() < 2e-2
+    ctx.check()
+    ctx.barrier()
+
+
+def test_distributed_flash_decode():
+    run_ranks(_decode, _world(), backend="nccl")

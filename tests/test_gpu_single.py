@@ -1,0 +1,244 @@
+"""Single-GPU tests of the sm_100a kernels against plain PyTorch fp32 references.
+
+One process, world size 1: the heap, the device context, the collectives and the fused ops all run
+their real kernels (peer loops degenerate to the local rank), so every CUDA path is exercised on
+one B200. Multi-rank behaviour is covered by test_gpu_multi.py.
+"""
+import math
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import torch.distributed as dist
+
+    from helpers import free_port
+
+    torch.cuda.set_device(0)
+    if not dist.is_initialized():
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(free_port())
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    import iris_b200 as iris
+
+    c = iris.iris(2 << 30)
+    yield c
+    c.barrier()
+
+
+def _rel_err(a, ref):
+    return (a.float() - ref.float()).abs().max().item() / max(ref.float().abs().max().item(), 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kmajor", [True, False])
+@pytest.mark.parametrize("shape,bn", [((128, 256, 64), 256), ((256, 512, 512), 128), ((256, 448, 512), 224),
+                                      ((200, 264, 328), 0), ((1024, 3584, 1024), 0)])
+def test_gemm_matches_fp32_reference(dtype, kmajor, shape, bn):
+    from iris_b200.ops.gemm import matmul
+
+    M, N, K = shape
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device="cuda", dtype=dtype)
+    B = (torch.randn(N, K, device="cuda", dtype=dtype) * 0.05).t() if kmajor else torch.randn(K, N, device="cuda", dtype=dtype) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=dtype)
+    C = matmul(A, B, bias=bias, bn=bn)
+    ref = A.float() @ B.float() + bias.float()
+    assert _rel_err(C, ref) < 1e-2
+    rows = torch.randn(M, device="cuda", dtype=dtype)
+    C2 = matmul(A, B, bias=rows, bias_dim=0, bn=bn)
+    assert _rel_err(C2, A.float() @ B.float() + rows.float()[:, None]) < 1e-2
+
+
+def test_context_basics(ctx):
+    assert ctx.get_rank() == 0 and ctx.get_num_ranks() == 1
+    assert ctx.get_cu_count() >= 100
+    bases = ctx.get_heap_bases()
+    assert bases.dtype == torch.int64 and bases.numel() == 1 and int(bases[0]) == ctx.heap.base
+    dc = ctx.get_device_context()
+    assert dc.dtype == torch.int64 and dc.numel() == 2 + 1 + 17
+    assert int(dc[0]) == 0 and int(dc[1]) == 1 and int(dc[2]) == ctx.heap.base
+    t = ctx.zeros(3, 5, dtype=torch.float16)
+    assert ctx.is_symmetric(t) and t.shape == (3, 5) and torch.all(t == 0)
+    assert not ctx.is_symmetric(torch.zeros(4, device="cuda"))
+    s = ctx.as_symmetric(torch.arange(10, device="cuda"))
+    assert ctx.is_symmetric(s) and torch.equal(s, torch.arange(10, device="cuda"))
+    assert t.data_ptr() % 1024 == 0
+
+
+def test_heap_out_of_memory(ctx):
+    with pytest.raises(MemoryError):
+        ctx.empty(1 << 40, dtype=torch.uint8)
+
+
+def test_device_barrier_and_graph_capture(ctx):
+    for _ in range(3):
+        ctx.device_barrier()
+    torch.cuda.synchronize()
+    # the barrier keeps its round counter on the device, so a captured launch can be replayed
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        ctx.device_barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            ctx.device_barrier()
+        for _ in range(3):
+            g.replay()
+    torch.cuda.synchronize()
+    ctx.check()
+
+
+def test_wait_flag_times_out_without_hanging(ctx):
+    flag = ctx.zeros(1, dtype=torch.int32)
+    assert ctx.wait_flag(flag, 1, timeout_ms=50) is False      # nothing sets the flag: bounded wait gives up
+    flag.fill_(3)
+    assert ctx.wait_flag(flag, 2, timeout_ms=50) is True
+    x = torch.ones(8, device="cuda") * 2                         # the context is still usable
+    assert float(x.sum()) == 16.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.int32, torch.bfloat16, torch.int64, torch.int8])
+def test_rma_data_movement(ctx, dtype):
+    n = 1000
+    src = ctx.zeros(n, dtype=dtype)
+    src.copy_(torch.arange(n, device="cuda").to(dtype))
+    dst = ctx.zeros(n, dtype=dtype)
+    for cm in (None, ".ca", ".cg", ".cv", ".cs"):
+        got = ctx.rma.load(src, from_rank=0, cache_modifier=cm)
+        assert torch.equal(got, src)
+    assert torch.equal(ctx.rma.load(src, from_rank=0, volatile=True), src)
+    assert torch.equal(ctx.rma.load(src, from_rank=0, oo=True), src)
+    for cm in (None, ".wb", ".cg", ".cs", ".wt"):
+        dst.zero_()
+        ctx.rma.store(dst, src, to_rank=0, cache_modifier=cm)
+        assert torch.equal(dst, src)
+    dst.zero_()
+    ctx.rma.put(src, dst, to_rank=0)
+    assert torch.equal(dst, src)
+    dst.zero_()
+    ctx.rma.get(src, dst, from_rank=0, oo=True)
+    assert torch.equal(dst, src)
+    dst.zero_()
+    ctx.rma.copy(src, dst, from_rank=0, to_rank=0)
+    assert torch.equal(dst, src)
+    if dtype != torch.int8:
+        ctx.rma.store(dst, 7, to_rank=0)
+        assert torch.all(dst == 7)
+
+
+@pytest.mark.parametrize("sem", ["relaxed", "acquire", "release", "acq_rel"])
+@pytest.mark.parametrize("scope", ["cta", "gpu", "sys"])
+def test_rma_atomics(ctx, sem, scope):
+    t = ctx.full((257,), 5, dtype=torch.int32)
+    old = ctx.rma.atomic_add(t, 3, to_rank=0, sem=sem, scope=scope)
+    assert torch.all(old == 5) and torch.all(t == 8)
+    ctx.rma.atomic_sub(t, 1, to_rank=0, sem=sem, scope=scope)
+    assert torch.all(t == 7)
+    ctx.rma.atomic_max(t, 9, to_rank=0, sem=sem, scope=scope)
+    ctx.rma.atomic_min(t, 8, to_rank=0, sem=sem, scope=scope)
+    assert torch.all(t == 8)
+    old = ctx.rma.atomic_cas(t, 8, 1, to_rank=0, sem=sem, scope=scope)
+    assert torch.all(old == 8) and torch.all(t == 1)
+    old = ctx.rma.atomic_cas(t, 5, 2, to_rank=0, sem=sem, scope=scope)
+    assert torch.all(old == 1) and torch.all(t == 1)
+    old = ctx.rma.atomic_xchg(t, 6, to_rank=0, sem=sem, scope=scope)
+    assert torch.all(old == 1) and torch.all(t == 6)
+    f = ctx.full((64,), 1.5, dtype=torch.float32)
+    ctx.rma.atomic_add(f, 2.25, to_rank=0, sem=sem, scope=scope)
+    assert torch.all(f == 3.75)
+    h = ctx.full((64,), 1.5, dtype=torch.bfloat16)
+    ctx.rma.atomic_add(h, 0.5, to_rank=0, scope="sys" if scope == "sys" else "gpu")
+    assert torch.all(h == 2.0)
+
+
+def test_tracing_records_events(ctx, tmp_path):
+    ctx.tracing.enable(max_events=4096)
+    try:
+        assert int(ctx.get_device_context()[3]) == 1
+        t = ctx.zeros(100, dtype=torch.float32)
+        ctx.rma.store(t, 1.0, to_rank=0)
+        ctx.rma.load(t, from_rank=0)
+        torch.cuda.synchronize()
+        assert ctx.tracing.num_events() == 200
+        ctx.tracing.export(str(tmp_path / "trace.json"), merge=True)
+        import json
+
+        doc = json.load(open(tmp_path / "trace.json"))
+        names = {e["name"] for e in doc["traceEvents"]}
+        assert names == {"store", "load"}
+        assert all(e["ph"] in ("X", "i") for e in doc["traceEvents"])
+        assert min(e["ts"] for e in doc["traceEvents"]) == 0
+    finally:
+        ctx.tracing.enabled = False
+        ctx._build_device_context()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+def test_collectives_world1(ctx, dtype):
+    from iris_b200.ccl import Config
+
+    M, N = 96, 200
+    inp = ctx.empty((M, N), dtype=dtype)
+    inp.copy_(torch.rand(M, N, device="cuda") * 2 - 1)
+    out = ctx.zeros((M, N), dtype=dtype)
+    for v in ("one_shot", "two_shot", "atomic", "ring", "spinlock", "auto"):
+        out.zero_()
+        ctx.ccl.all_reduce(out, inp, config=Config(all_reduce_variant=v))
+        assert torch.equal(out, inp), v
+    out.zero_()
+    ctx.ccl.all_gather(out, inp)
+    assert torch.equal(out, inp)
+    out.zero_()
+    ctx.ccl.all_to_all(out, inp)
+    assert torch.equal(out, inp)
+    out.zero_()
+    ctx.ccl.reduce_scatter(out, inp)
+    assert torch.equal(out, inp)
+    ctx.check()
+
+
+def test_fused_ops_world1(ctx):
+    dt = torch.bfloat16
+    torch.manual_seed(1)
+    A = torch.randn(384, 512, device="cuda", dtype=dt)
+    B = torch.randn(512, 640, device="cuda", dtype=dt) * 0.05
+    ref = A.float() @ B.float()
+    for op, kw in (("all_gather_matmul", {"shard_dim": 0}), ("all_gather_matmul", {"shard_dim": 1}), ("matmul_all_gather", {}),
+                   ("matmul_all_reduce", {}), ("matmul_reduce_scatter", {"scatter_rows": True}), ("matmul_reduce_scatter", {})):
+        C = ctx.zeros((384, 640), dtype=dt)
+        ws = None
+        for _ in range(3):                       # repeated calls reuse the double-buffered workspace
+            ws = getattr(ctx.ops, op)(C, A, B, workspace=ws, **kw)
+        assert ws.variant == "fused", op
+        assert _rel_err(C, ref) < 1e-2, op
+    ctx.check()
+
+
+@pytest.mark.parametrize("batch,lens,page", [(1, [700], 16), (3, [1, 300, 1025], 64), (2, [4096, 77], 128)])
+@pytest.mark.parametrize("heads", [(16, 2), (64, 8), (8, 8)])
+def test_flash_decode_matches_reference(ctx, batch, lens, page, heads):
+    from iris_b200.models import FlashDecodeLayer, reference_decode
+
+    Hq, Hkv = heads
+    dt = torch.bfloat16
+    torch.manual_seed(3)
+    max_blocks = -(-max(lens) // page)
+    nblocks = batch * max_blocks + 3
+    kc = torch.randn(nblocks, page, Hkv, 128, device="cuda", dtype=dt)
+    vc = torch.randn(nblocks, page, Hkv, 128, device="cuda", dtype=dt)
+    perm = torch.randperm(nblocks, device="cuda")[: batch * max_blocks].to(torch.int32).view(batch, max_blocks)
+    q = torch.randn(batch, Hq, 128, device="cuda", dtype=dt)
+    kv_lens = torch.tensor([lens], device="cuda", dtype=torch.int32)
+    layer = FlashDecodeLayer(ctx, Hq, Hkv, 128, max_batch=4)
+    for _ in range(2):
+        out, lse = layer(q, kc, vc, kv_lens, perm, return_lse=True)
+    ro, rlse = reference_decode(q, kc, vc, kv_lens[0], perm)
+    assert (out.float() - ro).abs().max().item() < 2e-2
+    assert (lse - rlse).abs().max().item() < 2e-2
+    ctx.check()
