@@ -71,6 +71,8 @@ struct LocalGemm : Common {
   }
   static constexpr bool kBulkEpilogue = false;
   IRIS_D void store_chunk(State&, int, int, int, const uint8_t*) const {}
+  IRIS_D bool reduce_here(State&) const { return false; }
+  IRIS_D void add_partials(State&, int, int, int, uint32_t (&)[32]) const {}
   IRIS_D void tile_done(State&, int, int) const {}
   IRIS_D void comm_main(uint8_t*, int) const {}
   IRIS_D void post_main() const {}
@@ -174,6 +176,8 @@ struct AllGatherGemm : Common {
   }
   static constexpr bool kBulkEpilogue = false;
   IRIS_D void store_chunk(State&, int, int, int, const uint8_t*) const {}
+  IRIS_D bool reduce_here(State&) const { return false; }
+  IRIS_D void add_partials(State&, int, int, int, uint32_t (&)[32]) const {}
   IRIS_D void tile_done(State&, int, int) const {}
 
   // Communication CTAs: CTA j moves slice j (of n_comm_ctas) of every 128-row chunk, chunk by
@@ -370,10 +374,23 @@ struct ScatterGemmT : Common {
 
   struct State {
     int buf = -1;
-    int row0 = 0, col0 = 0;
+    int32_t target = 0;
     int owner = 0, lt = 0;
-    uint8_t* slot = nullptr;   // owner's staging slot for (me, tile), already translated
+    bool mine = false;         // this rank finishes the tile (adds the peers' partials)
+    bool have = true;          // the peers' partials arrived in time
+    uint8_t* slot = nullptr;   // not mine: owner's staging slot for (me, tile), translated
+    const uint8_t* part0 = nullptr;  // mine: staging slot of source 0 for this tile (local)
   };
+  IRIS_D size_t slot_bytes() const { return (size_t)kBM * bn * 2; }
+  IRIS_D int total_tiles() const { return tiles_m * tiles_n; }
+  // tiles owned by rank o
+  IRIS_D int owned_count(int o) const {
+    const int T = total_tiles();
+    if (mode == IRIS_GEMM_REDUCE_SCATTER) return tiles_m_per_rank * tiles_n;
+    if (mode == IRIS_GEMM_ALL_REDUCE) return (T - o + ctx.world - 1) / ctx.world;
+    if (o == ctx.world - 1) return max(0, T - tiles_per_rank * (ctx.world - 1));
+    return min(tiles_per_rank, max(0, T - tiles_per_rank * o));
+  }
   // owner rank and the tile's index among the owner's tiles
   IRIS_D void owner_of(int tm, int tn, int& owner, int& lt) const {
     if (mode == IRIS_GEMM_REDUCE_SCATTER) {
@@ -389,35 +406,107 @@ struct ScatterGemmT : Common {
       lt = t - owner * tiles_per_rank;
     }
   }
+  // Reducing modes visit the tiles owner by owner: the next rank's tiles first, this rank's own
+  // tiles last, so that by the time a rank finishes its own tiles every peer's partial for them
+  // has long been delivered.
   IRIS_D void tile(int t, int& tm, int& tn) const {
+    if (!reducing()) {
+      swizzled_tile(t, tiles_m, tiles_n, group_m, tm, tn);
+      return;
+    }
+    int o = ctx.rank, k = t;
+    for (int g = 0; g < ctx.world; ++g) {
+      o = ctx.rank + 1 + g;
+      if (o >= ctx.world) o -= ctx.world;
+      const int cnt = owned_count(o);
+      if (k < cnt) break;
+      k -= cnt;
+    }
     if (mode == IRIS_GEMM_REDUCE_SCATTER) {
-      // other owners' rows first (next rank first), my own rows last
-      const int per_owner = tiles_m_per_rank * tiles_n;
-      const int g = t / per_owner;
-      int owner = ctx.rank + 1 + g;
-      if (owner >= ctx.world) owner -= ctx.world;
       int lm, ln;
-      swizzled_tile(t - g * per_owner, tiles_m_per_rank, tiles_n, group_m, lm, ln);
-      tm = owner * tiles_m_per_rank + lm;
+      swizzled_tile(k, tiles_m_per_rank, tiles_n, group_m, lm, ln);
+      tm = o * tiles_m_per_rank + lm;
       tn = ln;
     } else {
-      swizzled_tile(t, tiles_m, tiles_n, group_m, tm, tn);
+      const int id = mode == IRIS_GEMM_ALL_REDUCE ? o + k * ctx.world : o * tiles_per_rank + k;
+      tm = id / tiles_n;
+      tn = id - tm * tiles_n;
     }
   }
   IRIS_D bool a_source(State&, int tm, int kb, ASource& s) const {
     s.map = &tmA; s.x = kb * kBK; s.y = tm * kBM; s.bk = kb * kBK;
     return true;
   }
-  IRIS_D void begin_tile(State& st, int tm, int tn) const {
-    if (!reducing()) return;
-    if (st.buf < 0) st.buf = read_epoch(sb) & 1;
-    owner_of(tm, tn, st.owner, st.lt);
-    st.row0 = tm * kBM; st.col0 = tn * bn;
-    uint8_t* slot = staging + ((((size_t)st.buf * ctx.world + ctx.rank) * max_owned + st.lt) * (size_t)(kBM * bn)) * 2;
-    st.slot = ctx.remote(slot, st.owner);
-  }
   IRIS_D bool reducing() const {
     return mode == IRIS_GEMM_REDUCE_SCATTER || mode == IRIS_GEMM_ALL_REDUCE || mode == IRIS_GEMM_RS_TILES;
+  }
+  IRIS_D void begin_tile(State& st, int tm, int tn) const {
+    if (!reducing()) return;
+    if (st.buf < 0) {
+      const int e = read_epoch(sb);
+      st.buf = e & 1;
+      st.target = ((e >> 1) + 1) * (ctx.world - 1);
+    }
+    owner_of(tm, tn, st.owner, st.lt);
+    st.mine = st.owner == ctx.rank;
+    uint8_t* slot0 = staging + (((size_t)st.buf * ctx.world) * max_owned + st.lt) * slot_bytes();
+    if (st.mine) {
+      st.part0 = slot0;
+      st.have = true;
+      if (ctx.world > 1) {
+        int ok = 1;
+        if ((threadIdx.x & 31) == 0) ok = wait_flag_ge(ctx, flags + (size_t)st.buf * max_owned + st.lt, st.target) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        st.have = ok != 0;
+      }
+    } else {
+      st.slot = ctx.remote(slot0 + (size_t)ctx.rank * max_owned * slot_bytes(), st.owner);
+    }
+  }
+  IRIS_D bool reduce_here(State& st) const { return st.mine; }
+  // Staging slot layout (private to this kernel): [64-col chunk][quarter][32 rows][width cols],
+  // 16-byte groups XOR-swizzled by row exactly as staged in shared memory by the epilogue.
+  IRIS_D void add_partials(State& st, int quarter, int c32, int lane, uint32_t (&acc)[32]) const {
+    if (!st.have || ctx.world == 1) return;
+    const int chunk = c32 >> 1, hlf = c32 & 1;
+    const int width = (bn - chunk * 64) >= 64 ? 64 : 32;
+    const size_t off = (size_t)chunk * (kBM * 64 * 2) + (size_t)quarter * (32 * width * 2) + (size_t)lane * (width * 2);
+    const size_t src_stride = (size_t)max_owned * slot_bytes();
+    const int g0 = width == 64 ? hlf * 4 : 0;
+    const int swz = width == 64 ? (lane & 7) : ((lane >> 1) & 3);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {        // 16 columns = two 16-byte groups per source
+#pragma unroll 1
+      for (int s0 = 0; s0 < ctx.world; s0 += 8) {
+        uint4 v[8][2];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int src = s0 + k;
+          if (src < ctx.world && src != ctx.rank) {
+            const uint8_t* p = st.part0 + (size_t)src * src_stride + off;
+            v[k][0] = __ldcg((const uint4*)(p + (((g0 + half * 2 + 0) ^ swz) << 4)));
+            v[k][1] = __ldcg((const uint4*)(p + (((g0 + half * 2 + 1) ^ swz) << 4)));
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int src = s0 + k;
+          if (src < ctx.world && src != ctx.rank) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const uint32_t w4[4] = {v[k][q].x, v[k][q].y, v[k][q].z, v[k][q].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = bf16 ? __bfloat1622float2(*(const __nv_bfloat162*)&w4[e]) : __half22float2(*(const __half2*)&w4[e]);
+                const int idx = half * 16 + q * 8 + e * 2;
+                acc[idx] = __float_as_uint(__uint_as_float(acc[idx]) + f.x);
+                acc[idx + 1] = __float_as_uint(__uint_as_float(acc[idx + 1]) + f.y);
+              }
+            }
+          }
+        }
+      }
+    }
   }
   IRIS_D void store_everywhere(uint8_t* local_ptr, uint4 v) const {
     if (use_mc) {
@@ -432,107 +521,45 @@ struct ScatterGemmT : Common {
       }
     }
   }
-  IRIS_D void store16(State& st, int row, int col, uint4 v) const {
+  IRIS_D void store16(State&, int row, int col, uint4 v) const {
     if (row >= sh.M || col >= sh.N) return;
-    if (mode == IRIS_GEMM_ALL_GATHER) {
-      store_everywhere(out + (((int64_t)ctx.rank * sh.M + row) * ld_out + col) * 2, v);
-    } else if (mode == IRIS_GEMM_ALL_SCATTER) {
-      store_everywhere(out + ((int64_t)row * ld_out + (int64_t)ctx.rank * sh.N + col) * 2, v);
+    switch (mode) {
+      case IRIS_GEMM_ALL_GATHER:
+        store_everywhere(out + (((int64_t)ctx.rank * sh.M + row) * ld_out + col) * 2, v);
+        break;
+      case IRIS_GEMM_ALL_SCATTER:
+        store_everywhere(out + ((int64_t)row * ld_out + (int64_t)ctx.rank * sh.N + col) * 2, v);
+        break;
+      case IRIS_GEMM_REDUCE_SCATTER:   // finished tile of my row block
+        *(uint4*)(out + ((int64_t)(row - ctx.rank * tiles_m_per_rank * kBM) * ld_out + col) * 2) = v;
+        break;
+      case IRIS_GEMM_RS_TILES:
+        *(uint4*)(out + ((int64_t)row * ld_out + col) * 2) = v;
+        break;
+      default:                         // ALL_REDUCE: the finished tile goes to every rank
+        store_everywhere(out + ((int64_t)row * ld_out + col) * 2, v);
+        break;
     }
   }
-  // Reducing modes: rows [32*quarter, +32) x columns [64*chunk, +width) of the current tile go to
-  // the owner's staging slot as one contiguous piece. Slot layout (private to this kernel):
-  // [chunk][quarter][32 rows][width columns], 16-byte groups XOR-swizzled as staged in smem.
+  // A tile finished elsewhere: rows [32*quarter, +32) x columns [64*chunk, +width) go to the
+  // owner's staging slot as one contiguous piece.
   IRIS_D void store_chunk(State& st, int quarter, int chunk, int width, const uint8_t* smem) const {
     uint8_t* dst = st.slot + (size_t)chunk * (kBM * 64 * 2) + (size_t)quarter * (32 * width * 2);
     ptx::bulk_store(dst, smem, 32 * width * 2);
   }
   IRIS_D void tile_done(State& st, int, int) const {
-    if (!reducing()) return;
+    if (!reducing() || st.mine) return;
     fence_sys();
     red_release_sys_add(ctx.remote(flags + (size_t)st.buf * max_owned + st.lt, st.owner), 1);
   }
   IRIS_D void comm_main(uint8_t*, int) const {}
-
-  IRIS_D int owned_tiles() const {
-    const int total = tiles_m * tiles_n;
-    if (mode == IRIS_GEMM_REDUCE_SCATTER) return tiles_m_per_rank * tiles_n;
-    if (mode == IRIS_GEMM_ALL_REDUCE) return (total - ctx.rank + ctx.world - 1) / ctx.world;
-    if (ctx.rank == ctx.world - 1) return total - tiles_per_rank * (ctx.world - 1);
-    return tiles_per_rank;
-  }
-  // global (tm, tn) of my owned tile `lt`
-  IRIS_D void owned_tile(int lt, int& tm, int& tn) const {
-    int t;
-    if (mode == IRIS_GEMM_REDUCE_SCATTER) {
-      tm = ctx.rank * tiles_m_per_rank + lt / tiles_n;
-      tn = lt % tiles_n;
-      return;
-    } else if (mode == IRIS_GEMM_ALL_REDUCE) {
-      t = lt * ctx.world + ctx.rank;
-    } else {
-      t = ctx.rank * tiles_per_rank + lt;
-    }
-    tm = t / tiles_n;
-    tn = t % tiles_n;
-  }
   IRIS_D void post_main() const {
     const int epoch = read_epoch(sb);
-    if (reducing()) {
-      __shared__ int s_ok;
-      const int buf = epoch & 1;
-      const int target = ((epoch >> 1) + 1) * ctx.world;
-      const int n_owned = owned_tiles();
-      const int vec_per_row = bn / 8;
-      for (int lt = blockIdx.x; lt < n_owned; lt += n_gemm_ctas) {
-        if (threadIdx.x == 0) s_ok = wait_flag_ge(ctx, flags + (size_t)buf * max_owned + lt, target) ? 1 : 0;
-        __syncthreads();
-        const bool ok = s_ok != 0;
-        __syncthreads();
-        if (!ok) break;
-        int tm, tn;
-        owned_tile(lt, tm, tn);
-        const int rows = min(kBM, sh.M - tm * kBM);
-        const int cols = min(bn, sh.N - tn * bn);
-        for (int i = threadIdx.x; i < rows * vec_per_row; i += blockDim.x) {
-          const int rr = i / vec_per_row, cv = i - rr * vec_per_row;
-          if (cv * 8 >= cols) continue;
-          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          for (int s = 0; s < ctx.world; ++s) {
-            const uint8_t* slot = staging + ((((size_t)buf * ctx.world + s) * max_owned + lt) * (size_t)(kBM * bn)) * 2;
-            const int chunk = cv >> 3, c16 = cv & 7;
-            const int width = (bn - chunk * 64) >= 64 ? 64 : 32;
-            const int r32 = rr & 31;
-            const int pos = width == 64 ? (c16 ^ (r32 & 7)) : (c16 ^ ((r32 >> 1) & 3));
-            const uint4 v = *(const uint4*)(slot + (size_t)chunk * (kBM * 64 * 2) + (size_t)(rr >> 5) * (32 * width * 2) +
-                                            (size_t)r32 * (width * 2) + pos * 16);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              float2 f = bf16 ? __bfloat1622float2(*(const __nv_bfloat162*)&w[q]) : __half22float2(*(const __half2*)&w[q]);
-              acc[2 * q] += f.x; acc[2 * q + 1] += f.y;
-            }
-          }
-          uint32_t o[4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (bf16) { __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]); o[q] = *(uint32_t*)&h; }
-            else { __half2 h = __floats2half2_rn(acc[2 * q], acc[2 * q + 1]); o[q] = *(uint32_t*)&h; }
-          }
-          const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
-          const int grow = tm * kBM + rr, gcol = tn * bn + cv * 8;
-          if (mode == IRIS_GEMM_REDUCE_SCATTER) {
-            *(uint4*)(out + ((int64_t)(grow - ctx.rank * tiles_m_per_rank * kBM) * ld_out + gcol) * 2) = ov;
-          } else if (mode == IRIS_GEMM_RS_TILES) {
-            *(uint4*)(out + ((int64_t)grow * ld_out + gcol) * 2) = ov;
-          } else {
-            store_everywhere(out + ((int64_t)grow * ld_out + gcol) * 2, ov);
-          }
-        }
-      }
-    }
-    const bool peers_write_out = mode == IRIS_GEMM_ALL_GATHER || mode == IRIS_GEMM_ALL_SCATTER || mode == IRIS_GEMM_ALL_REDUCE;
-    if (peers_write_out) {
+    // Outputs written by peers (AG, all-scatter, AR) need the cross-rank round; RS_TILES takes it
+    // too because a rank that owns no tile would otherwise never learn that its peers moved on.
+    // Row reduce-scatter needs none: waiting for every peer's partials in call k proves that all
+    // ranks left call k-1, which is what makes the double-buffered staging safe to reuse.
+    if (mode != IRIS_GEMM_REDUCE_SCATTER) {
       grid_exit_barrier(ctx, sb, epoch, 0);
     } else {
       __syncthreads();
@@ -669,6 +696,17 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
   const int sms = sm_count();
   const bool ag = d->op == IRIS_GEMM_AG_M || d->op == IRIS_GEMM_AG_K;
   p.comm_ctas = ag && W > 1 ? (d->comm_ctas > 0 ? d->comm_ctas : 8) : 0;
+  if (ag && W > 1 && d->comm_ctas <= 0 && d->gemm_ctas <= 0) {
+    // Communication CTAs are free as long as the GEMM keeps its number of waves: give them every
+    // SM the last wave would leave idle (between 8 and 32).
+    const int bn0 = d->bn > 0 ? d->bn : 256;
+    const int tiles = ceil_div(d->M, kBM) * ceil_div(d->N, bn0);
+    const int waves = ceil_div(tiles, sms - 8);
+    int spare = sms - ceil_div(tiles, waves);
+    if (spare > 32) spare = 32;
+    if (spare < 8) spare = 8;
+    p.comm_ctas = spare;
+  }
   p.gemm_ctas = d->gemm_ctas > 0 ? d->gemm_ctas : sms - p.comm_ctas;
   if (p.gemm_ctas + p.comm_ctas > sms) return -4;  // every CTA must be resident: consumers wait on producers
   p.bn = d->bn > 0 ? d->bn : choose_bn(d->M, d->N, p.gemm_ctas, !d->b_kmajor);

@@ -107,6 +107,10 @@ struct Pipeline {
 //   void store_chunk(State&, int quarter, int chunk, int width, const uint8_t* smem) const;
 //        (lane 0 of an epilogue warp: issue the bulk store(s) of rows [32*quarter, +32) x columns
 //         [64*chunk, +width) of the current tile, staged in `smem` in the swizzled chunk layout)
+//   bool reduce_here(State&) const;                        (bulk policies: this tile is finished on
+//        this rank: take the row-major path and add the other ranks' partials first)
+//   void add_partials(State&, int quarter, int c32, int lane, uint32_t (&acc)[32]) const;
+//        (add to the fp32 accumulators of row `lane` of the quarter, columns [32*c32, +32))
 //   void tile_done(State&, int m_tile, int n_tile) const;  (one thread, after the tile's stores)
 //   void comm_main(uint8_t* smem, int smem_bytes) const;    (CTAs with blockIdx.x >= gemm_ctas())
 //   void post_main() const;                                 (GEMM CTAs, all threads, after their tiles)
@@ -246,7 +250,24 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * Cfg::kAccCols;
       const int row0 = tm * kBM + quarter * 32;
       const float rb = has_bias ? pol.row_bias(row0 + lane) : 0.f;
-      if constexpr (Policy::kBulkEpilogue) {
+      // fp32 accumulators of 32 columns -> 16-bit pairs (bias added)
+      auto pack32 = [&](const uint32_t (&r)[32], int col0, uint32_t (&packed)[16]) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float a = __uint_as_float(r[2 * j]) + rb, b = __uint_as_float(r[2 * j + 1]) + rb;
+          if (has_bias) { a += pol.col_bias(col0 + 2 * j); b += pol.col_bias(col0 + 2 * j + 1); }
+          if (bf16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+            packed[j] = *(uint32_t*)&h;
+          } else {
+            __half2 h = __floats2half2_rn(a, b);
+            packed[j] = *(uint32_t*)&h;
+          }
+        }
+      };
+      bool bulk = false;
+      if constexpr (Policy::kBulkEpilogue) bulk = !pol.reduce_here(est);
+      if (bulk) {
         // The tile leaves in 64-column chunks: TMEM -> registers -> swizzled shared memory, then
         // ONE bulk async store per chunk (4 KB, or 2 KB for a 32-column tail) issued by lane 0
         // through the policy. Two staging halves per warp: a half is rewritten only after the
@@ -268,20 +289,8 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
               __syncwarp();
               if (lane == 0) ptx::mbar_arrive(&pipe.tmem_empty[buf]);
             }
-            const int col0 = tn * Cfg::BN + cc * 64 + hlf * 32;
             uint32_t packed[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float a = __uint_as_float(r[2 * j]) + rb, b = __uint_as_float(r[2 * j + 1]) + rb;
-              if (has_bias) { a += pol.col_bias(col0 + 2 * j); b += pol.col_bias(col0 + 2 * j + 1); }
-              if (bf16) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-                packed[j] = *(uint32_t*)&h;
-              } else {
-                __half2 h = __floats2half2_rn(a, b);
-                packed[j] = *(uint32_t*)&h;
-              }
-            }
+            pack32(r, tn * Cfg::BN + cc * 64 + hlf * 32, packed);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 v = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
@@ -304,46 +313,42 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         }
         __syncwarp();
       } else {
-#pragma unroll 1
-      for (int c = 0; c < Cfg::BN / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(t_addr + c * 32, r);
-        ptx::tmem_ld_wait();
-        if (c == Cfg::BN / 32 - 1) {
-          ptx::tc_fence_before();
+        // 32 columns at a time: TMEM -> registers (-> plus the other ranks' partials when this
+        // rank reduces the tile) -> 16-bit -> shared-memory transpose -> 16-byte row-major stores.
+        uint8_t* stage = my_epi;
+        if constexpr (Policy::kBulkEpilogue) {
+          if (lane == 0) ptx::bulk_wait_read<0>();   // earlier bulk stores may still read the staging
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&pipe.tmem_empty[buf]);
         }
-        const int col0 = tn * Cfg::BN + c * 32;
-        // fp32 -> 16-bit pairs, staged so that a row's 64 bytes leave as 4 x 16-byte pieces
-        uint32_t packed[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float a = __uint_as_float(r[2 * j]) + rb, b = __uint_as_float(r[2 * j + 1]) + rb;
-          if (has_bias) { a += pol.col_bias(col0 + 2 * j); b += pol.col_bias(col0 + 2 * j + 1); }
-          if (bf16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-            packed[j] = *(uint32_t*)&h;
-          } else {
-            __half2 h = __floats2half2_rn(a, b);
-            packed[j] = *(uint32_t*)&h;
+#pragma unroll 1
+        for (int c = 0; c < Cfg::BN / 32; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(t_addr + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (c == Cfg::BN / 32 - 1) {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&pipe.tmem_empty[buf]);
           }
-        }
-        const int sw = (lane >> 1) & 3;
+          if constexpr (Policy::kBulkEpilogue) pol.add_partials(est, quarter, c, lane, r);
+          const int col0 = tn * Cfg::BN + c * 32;
+          uint32_t packed[16];
+          pack32(r, col0, packed);
+          const int sw = (lane >> 1) & 3;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 v = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-          *(uint4*)(my_epi + lane * 64 + ((j ^ sw) * 16)) = v;
-        }
-        __syncwarp();
+          for (int j = 0; j < 4; ++j) {
+            uint4 v = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+            *(uint4*)(stage + lane * 64 + ((j ^ sw) * 16)) = v;
+          }
+          __syncwarp();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int rr = i * 8 + (lane >> 2), cc = lane & 3;
-          uint4 v = *(uint4*)(my_epi + rr * 64 + ((cc ^ ((rr >> 1) & 3)) * 16));
-          pol.store16(est, row0 + rr, col0 + cc * 8, v);
+          for (int i = 0; i < 4; ++i) {
+            const int rr = i * 8 + (lane >> 2), cc = lane & 3;
+            uint4 v = *(uint4*)(stage + rr * 64 + ((cc ^ ((rr >> 1) & 3)) * 16));
+            pol.store16(est, row0 + rr, col0 + cc * 8, v);
+          }
+          __syncwarp();
         }
-        __syncwarp();
-      }
       }
       ptx::named_barrier(1, kEpiWarps * 32);
       if (warp == 2 && lane == 0) {

@@ -20,6 +20,7 @@
 #if defined(__CUDACC__)
 #include "multimem.cuh"
 #include "ptx.cuh"
+#include "tile_collectives.cuh"
 #endif
 
 namespace iris {

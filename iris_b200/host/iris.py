@@ -137,6 +137,14 @@ class Iris:
         _lib.check(self._klib().iris_device_barrier(C.byref(ctx), C.c_void_p(sb.data_ptr()), C.c_void_p(_lib.current_stream_ptr())),
                    "device barrier launch")
 
+    def verify_symmetry(self) -> None:
+        """Raise if the ranks' heaps have diverged (different allocation sequences): symmetric
+        addressing is only valid when every rank allocated the same sizes in the same order."""
+        offs = D.distributed_allgather(np.array([self.heap.get_offset()], dtype=np.int64)).flatten().tolist()
+        if len(set(offs)) != 1:
+            raise RuntimeError(f"symmetric heap offsets differ across ranks: {offs}; every rank must allocate the same "
+                               f"tensors in the same order")
+
     def check(self) -> None:
         """Raise IrisTimeoutError if a kernel recorded a failed wait since the last check."""
         if not self.is_cpu:

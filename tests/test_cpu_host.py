@@ -1,0 +1,293 @@
+"""Host-layer tests that need no GPU: tensor factories, configs, bench harness parsing, logging,
+collectives / fused ops / flash decode on the CPU backend (gloo ranks sharing memfd heaps)."""
+import logging
+import math
+
+import pytest
+import torch
+
+from helpers import run_ranks
+
+
+# ------------------------------------------------------------------ pure python
+def test_ccl_config_validation():
+    from iris_b200.ccl import Config, ReduceOp
+
+    c = Config()
+    assert (c.block_size_m, c.block_size_n, c.comm_sms, c.swizzle_size) == (32, 64, 64, 4)
+    assert ReduceOp.SUM == 0
+    for bad in (dict(block_size_m=0), dict(comm_sms=-1), dict(all_reduce_variant="nope"), dict(all_gather_variant="x"),
+                dict(all_reduce_distribution=2), dict(threads_per_warp=48), dict(swizzle_size=0)):
+        with pytest.raises(ValueError):
+            Config(**bad)
+    # AMD-only knobs are accepted
+    Config(num_xcds=8, waves_per_eu=2, threads_per_warp=64, num_warps=8)
+
+
+def test_fused_config():
+    from iris_b200.ops import FusedConfig
+
+    c = FusedConfig()
+    assert c.tile_n() == 0 and FusedConfig(block_size_n=224).tile_n() == 224
+    with pytest.raises(ValueError):
+        FusedConfig(all_reduce_variant="bogus")
+    c.validate(8)
+    with pytest.raises(ValueError):
+        c.validate(0)
+
+
+def test_bench_axis_parsing_and_registry():
+    from iris_b200.bench import State, axis, linear_range, power_of_two, register, registry
+    from iris_b200.bench._core import SkipCombination, combinations
+    from iris_b200.bench._runner import format_console, format_csv, format_json, parse_axis_values
+    from iris_b200.bench import Result
+
+    assert power_of_two(2, 4) == [4, 8, 16] and linear_range(0, 6, 3) == [0, 3, 6]
+    assert parse_axis_values("pow2:10:12") == [1024, 2048, 4096]
+    assert parse_axis_values("lin:0:64:32") == [0, 32, 64]
+    assert parse_axis_values("bf16,fp32") == [torch.bfloat16, torch.float32]
+    assert parse_axis_values("1, 2,x") == [1, 2, "x"]
+    before = len(registry)
+
+    @register
+    @axis("M", [1, 2])
+    @axis("N", [3])
+    def demo(state, ctx):
+        state.set_bytes(10)
+
+    assert len(registry) == before + 1 and [a.name for a in registry[-1].axes] == ["M", "N"]
+    combos = list(combinations(registry[-1].axes, {"M": [7, 8, 9]}, {"M": [8]}))
+    assert combos == [{"M": 7, "N": 3}, {"M": 9, "N": 3}]
+    registry.pop()
+    s = State({"M": 4})
+    assert s["M"] == 4 and s.get("Q", 1) == 1
+    with pytest.raises(SkipCombination):
+        s.skip("why")
+    r = [Result("b", {"M": 4, "dtype": torch.float16}, 0.5, [], bandwidth_gbps=3.0, tflops=None, roofline_frac=0.5)]
+    assert "b" in format_console(r) and "float16" in format_json(r) and "gpu_time_ms" in format_csv(r)
+
+
+def test_logging_format(capsys):
+    import iris_b200 as iris
+    from iris_b200.host.logging import IrisFormatter, log_rank, logger
+
+    rec = logging.LogRecord("iris", logging.INFO, "f.py", 1, "hello", None, None)
+    rec.iris_rank, rec.iris_num_ranks, rec.iris_module = 1, 4, "mod"
+    out = IrisFormatter().format(rec)
+    assert "[Iris]" in out and "[1/4]" in out and "[mod]" in out and out.endswith("hello")
+    iris.set_logger_level(iris.DEBUG)
+    assert logger.level == logging.DEBUG
+    iris.set_logger_level(iris.WARNING)
+    log_rank(iris.WARNING, "w", 0, 2)
+
+
+def test_device_symbols_point_to_headers():
+    import os
+
+    import iris_b200 as iris
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(iris.__file__)))
+    for sym in (iris.load, iris.store, iris.atomic_cas, iris.DeviceContext, iris.TensorView):
+        assert os.path.exists(os.path.join(root, sym.header))
+        src = open(os.path.join(root, sym.header)).read()
+        assert sym.name in src
+    with pytest.raises(RuntimeError):
+        iris.load()
+
+
+def test_owned_tiles_partition():
+    from iris_b200.ccl import owned_tiles
+    from iris_b200.ops import owned_tile_range
+
+    for dist_mode in (0, 1):
+        seen = set()
+        for r in range(3):
+            for t in owned_tiles(100, 130, 32, 64, 3, r, dist_mode):
+                assert t not in seen
+                seen.add(t)
+        assert len(seen) == 4 * 3
+    for total, W in ((10, 4), (3, 8), (16, 8)):
+        got = [t for r in range(W) for t in owned_tile_range(total, W, r)]
+        assert sorted(got) == list(range(total))
+
+
+# ------------------------------------------------------------------ CPU backend, world 2 / 3
+def _factories(rank, world):
+    import iris_b200 as iris
+
+    ctx = iris.iris(1 << 26)
+    z = ctx.zeros(2, 3, dtype=torch.float32)
+    assert z.shape == (2, 3) and torch.all(z == 0) and ctx.is_symmetric(z)
+    assert ctx.zeros((4, 5)).shape == (4, 5) and ctx.zeros([2, 2]).shape == (2, 2)
+    o = ctx.ones(7, dtype=torch.int32)
+    assert torch.all(o == 1) and o.dtype == torch.int32
+    f = ctx.full((2, 2), 3.5)
+    assert torch.all(f == 3.5) and f.dtype == torch.get_default_dtype()
+    assert ctx.full((2,), 3).dtype == torch.int64
+    e = ctx.empty(5, 5, dtype=torch.bfloat16)
+    assert e.shape == (5, 5) and e.dtype == torch.bfloat16
+    zl = ctx.zeros_like(torch.ones(3, 4, dtype=torch.float16))
+    assert zl.shape == (3, 4) and zl.dtype == torch.float16 and ctx.is_symmetric(zl)
+    r = ctx.rand(100)
+    assert 0 <= float(r.min()) and float(r.max()) <= 1
+    assert ctx.randn(10, 10).shape == (10, 10)
+    ri = ctx.randint(0, 5, (50,))
+    assert ri.dtype == torch.int64 and int(ri.min()) >= 0 and int(ri.max()) < 5
+    assert ctx.randint(7, (4,)).shape == (4,)
+    u = ctx.uniform((20,), -2.0, -1.0)
+    assert float(u.max()) <= -1.0 and float(u.min()) >= -2.0
+    assert torch.equal(ctx.arange(5), torch.arange(5))
+    assert torch.equal(ctx.arange(1, 10, 3), torch.arange(1, 10, 3))
+    assert torch.allclose(ctx.arange(0.0, 1.0, 0.25), torch.arange(0.0, 1.0, 0.25))
+    assert torch.allclose(ctx.linspace(0, 1, 5), torch.linspace(0, 1, 5))
+    # out= must be a heap tensor of the right size and dtype
+    out = ctx.empty(6, dtype=torch.float32)
+    got = ctx.zeros(2, 3, out=out)
+    assert got.data_ptr() == out.data_ptr() and got.shape == (2, 3)
+    with pytest.raises(RuntimeError):
+        ctx.zeros(2, 3, out=torch.empty(6))
+    with pytest.raises(RuntimeError):
+        ctx.zeros(2, 2, out=out)
+    with pytest.raises(RuntimeError):
+        ctx.zeros(2, 3, out=out, dtype=torch.float16)
+    with pytest.raises(RuntimeError):
+        ctx.zeros(2, device="cuda:0")
+    with pytest.raises(ValueError):
+        ctx.zeros(2, layout=torch.sparse_coo)
+    cl = ctx.zeros(2, 3, 4, 5, memory_format=torch.channels_last)
+    assert cl.stride() == torch.zeros(2, 3, 4, 5).to(memory_format=torch.channels_last).stride() and ctx.is_symmetric(cl)
+    g = ctx.ones(3, requires_grad=True)
+    assert g.requires_grad
+    # alignment and exhaustion
+    assert ctx.zeros(1).data_ptr() % 1024 == 0
+    with pytest.raises(MemoryError):
+        ctx.empty(1 << 30, dtype=torch.uint8)
+    # broadcast
+    assert ctx.broadcast(rank * 10 + 5, src=1) == 15
+    t = ctx.broadcast(torch.full((3,), float(rank)), src=0)
+    assert torch.all(torch.as_tensor(t) == 0)
+    s = ctx.as_symmetric(torch.arange(6))
+    assert ctx.is_symmetric(s) and torch.equal(s, torch.arange(6))
+    dc = ctx.get_device_context()
+    assert int(dc[0]) == rank and int(dc[1]) == world and dc.numel() == 2 + world + 17
+    ctx.barrier()
+
+
+def test_factories_world2():
+    run_ranks(_factories, 2)
+
+
+def _ccl_cpu(rank, world):
+    import iris_b200 as iris
+    from iris_b200.ccl import Config, owned_tiles
+
+    ctx = iris.iris(1 << 26)
+    M, N = 8, 6 * world
+    inp = ctx.zeros((M, N), dtype=torch.float32)
+    inp.copy_(torch.arange(M * N, dtype=torch.float32).view(M, N) + 1000 * rank)
+    out = ctx.zeros((M, N), dtype=torch.float32)
+    ctx.barrier()
+    ctx.ccl.all_reduce(out, inp)
+    exp = sum(torch.arange(M * N, dtype=torch.float32).view(M, N) + 1000 * r for r in range(world))
+    assert torch.equal(out, exp)
+    ag = ctx.zeros((world * M, N), dtype=torch.float32)
+    ctx.ccl.all_gather(ag, inp)
+    for r in range(world):
+        assert torch.equal(ag[r * M:(r + 1) * M], torch.arange(M * N, dtype=torch.float32).view(M, N) + 1000 * r)
+    a2a = ctx.zeros((M, N), dtype=torch.float32)
+    ctx.ccl.all_to_all(a2a, inp)
+    n = N // world
+    for s in range(world):
+        src = torch.arange(M * N, dtype=torch.float32).view(M, N) + 1000 * s
+        assert torch.equal(a2a[:, s * n:(s + 1) * n], src[:, rank * n:(rank + 1) * n])
+    rs = ctx.zeros((M, N), dtype=torch.float32)
+    cfg = Config(block_size_m=4, block_size_n=4, all_reduce_distribution=0)
+    ctx.ccl.reduce_scatter(rs, inp, config=cfg)
+    mask = torch.zeros(M, N, dtype=torch.bool)
+    for (r0, r1, c0, c1) in owned_tiles(M, N, 4, 4, world, rank, 0):
+        mask[r0:r1, c0:c1] = True
+    assert torch.equal(rs[mask], exp[mask]) and torch.all(rs[~mask] == 0)
+    with pytest.raises(ValueError):
+        ctx.ccl.all_reduce(out, torch.zeros(M, N))
+    with pytest.raises(ValueError):
+        ctx.ccl.all_gather(out, inp)
+    # fused ops fall back to GEMM + collective on this backend, same results
+    A = torch.randn(4, 8)
+    B = torch.randn(8, 5)
+    C = ctx.zeros((4 * world, 5), dtype=torch.float32)
+    ctx.ops.all_gather_matmul(C, A, B, shard_dim=0)
+    import torch.distributed as dist
+
+    parts = [torch.empty_like(A) for _ in range(world)]
+    dist.all_gather(parts, A)
+    assert torch.allclose(C, torch.cat(parts, 0) @ B, atol=1e-5)
+    C2 = ctx.zeros((4, 5), dtype=torch.float32)
+    ctx.ops.matmul_all_reduce(C2, A, B)
+    tot = A @ B
+    dist.all_reduce(tot)
+    assert torch.allclose(C2, tot, atol=1e-4)
+    ctx.barrier()
+
+
+def test_collectives_cpu_world2():
+    run_ranks(_ccl_cpu, 2)
+
+
+def test_collectives_cpu_world3():
+    run_ranks(_ccl_cpu, 3)
+
+
+def _decode_cpu(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.models import FlashDecodeLayer, merge_partials, reference_decode
+
+    ctx = iris.iris(1 << 26)
+    Hq, Hkv, D, page, B = 8, 2, 128, 16, 2
+    torch.manual_seed(0)
+    q = torch.randn(B, Hq, D)
+    torch.manual_seed(10 + rank)
+    lens = torch.tensor([20 + rank, 5], dtype=torch.int32)
+    kc, vc = torch.randn(8, page, Hkv, D), torch.randn(8, page, Hkv, D)
+    table = torch.arange(8, dtype=torch.int32).view(2, 4)
+    all_lens = [torch.empty_like(lens) for _ in range(world)]
+    dist.all_gather(all_lens, lens)
+    layer = FlashDecodeLayer(ctx, Hq, Hkv, D, max_batch=2, dtype=torch.float32)
+    out = layer(q, kc, vc, torch.stack(all_lens), table)
+    # oracle: attention over the concatenation of all shards
+    o, lse = reference_decode(q, kc, vc, lens, table)
+    os_, ls_ = [torch.empty_like(o) for _ in range(world)], [torch.empty_like(lse) for _ in range(world)]
+    dist.all_gather(os_, o)
+    dist.all_gather(ls_, lse)
+    assert torch.allclose(out, merge_partials(torch.stack(os_), torch.stack(ls_)), atol=1e-5)
+    ctx.barrier()
+
+
+def test_flash_decode_cpu_world2():
+    run_ranks(_decode_cpu, 2)
+
+
+def test_reference_decode_equals_dense_attention():
+    from iris_b200.models import merge_partials, reference_decode
+
+    torch.manual_seed(1)
+    B, Hq, Hkv, D, page = 2, 4, 2, 128, 8
+    kc, vc = torch.randn(6, page, Hkv, D), torch.randn(6, page, Hkv, D)
+    q = torch.randn(B, Hq, D)
+    table = torch.tensor([[0, 1, 2], [3, 4, 5]], dtype=torch.int32)
+    lens = torch.tensor([20, 9], dtype=torch.int32)
+    o, lse = reference_decode(q, kc, vc, lens, table)
+    for b in range(B):
+        k = kc[table[b].long()].reshape(-1, Hkv, D)[: lens[b]]
+        v = vc[table[b].long()].reshape(-1, Hkv, D)[: lens[b]]
+        for h in range(Hq):
+            s = (k[:, h // 2] @ q[b, h]) / math.sqrt(D)
+            p = torch.softmax(s, 0)
+            assert torch.allclose(o[b, h], p @ v[:, h // 2], atol=1e-5)
+            assert abs(float(lse[b, h]) - float(torch.logsumexp(s, 0))) < 1e-5
+    # splitting a sequence in two shards and merging gives the same answer
+    o1, l1 = reference_decode(q, kc, vc, torch.tensor([8, 8], dtype=torch.int32), table)
+    o2, l2 = reference_decode(q, kc[:, :, :, :], vc, torch.tensor([0, 0], dtype=torch.int32), table)
+    m = merge_partials(torch.stack([o1, o2]), torch.stack([l1, l2]))
+    assert torch.allclose(m, o1, atol=1e-6)
