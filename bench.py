@@ -156,10 +156,12 @@ def main() -> int:
     sampler = ClockSampler(local)
 
     # ---------------- device-timed region: exactly `steps` steps between barriers
+    # (the clock sampler runs from the warm-up to the end of the end-to-end loop, all of it the
+    # same load, so that a short timed region still yields samples)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     ctx.barrier()
-    sampler.start()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dist.barrier()
     torch.cuda.synchronize()

@@ -579,8 +579,9 @@ int iris_ccl_launch(int op, const IrisCclDesc* d, void* stream) {
                    (d->ld_out * es) % 16 == 0 && (op == 2 || d->rows_mode || (d->block_n * es) % 16 == 0);
   if (!vec) a.use_mc = 0;
   if (op == 2 && d->variant == kArNvls && !a.use_mc) a.variant = kArTwoShot;
+  if (op == 2 && W == 1) a.variant = kArOneShot;   // a single rank: every variant is a local copy
   int grid = grid_for(d, (size_t)d->M * d->N * es);
-  if (op == 2 && d->variant == kArRing) {
+  if (op == 2 && a.variant == kArRing) {
     grid = d->comm_sms > 0 ? d->comm_sms : 32;  // must match the flag layout chosen by the host
   }
   switch (d->dtype) {

@@ -65,7 +65,9 @@ struct LocalGemm : Common {
     s.map = &tmA; s.x = kb * kBK; s.y = tm * kBM; s.bk = kb * kBK;
     return true;
   }
-  IRIS_D void begin_tile(State&, int, int) const {}
+  IRIS_D void begin_tile(State&, int, int, uint8_t*) const {}
+  IRIS_D int row_origin(State&, int tm) const { return tm * kBM; }
+  static constexpr bool kSwiGLU = false;
   IRIS_D void store16(State&, int row, int col, uint4 v) const {
     if (row < sh.M && col < sh.N) *(uint4*)(C + ((int64_t)row * ldc + col) * 2) = v;
   }
@@ -170,7 +172,9 @@ struct AllGatherGemm : Common {
     s.map = st.map; s.x = (kb - st.kb0) * kBK; s.y = st.y; s.bk = st.src * cols_per_src + s.x;
     return true;
   }
-  IRIS_D void begin_tile(State&, int, int) const {}
+  IRIS_D void begin_tile(State&, int, int, uint8_t*) const {}
+  IRIS_D int row_origin(State&, int tm) const { return tm * kBM; }
+  static constexpr bool kSwiGLU = false;
   IRIS_D void store16(State&, int row, int col, uint4 v) const {
     if (row < sh.M && col < sh.N) *(uint4*)(C + ((int64_t)row * ldc + col) * 2) = v;
   }
@@ -440,7 +444,9 @@ struct ScatterGemmT : Common {
   IRIS_D bool reducing() const {
     return mode == IRIS_GEMM_REDUCE_SCATTER || mode == IRIS_GEMM_ALL_REDUCE || mode == IRIS_GEMM_RS_TILES;
   }
-  IRIS_D void begin_tile(State& st, int tm, int tn) const {
+  static constexpr bool kSwiGLU = false;
+  IRIS_D int row_origin(State&, int tm) const { return tm * kBM; }
+  IRIS_D void begin_tile(State& st, int tm, int tn, uint8_t*) const {
     if (!reducing()) return;
     if (st.buf < 0) {
       const int e = read_epoch(sb);

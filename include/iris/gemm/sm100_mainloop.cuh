@@ -74,6 +74,7 @@ struct ASource {
   const CUtensorMap* map;
   int x, y;   // coordinates of the A box in `map`
   int bk;     // K offset of the matching B rows/columns (differs from x when A is gathered along K)
+  int bn0;    // first output column of the tile inside B's N dimension (grouped GEMMs offset it per group)
 };
 
 // GROUP_M swizzled tile order (same idea as the reference's GROUP_SIZE_M, all_reduce.py:182-187).
@@ -100,7 +101,13 @@ struct Pipeline {
 //   struct State;                                          (mutable per-thread scratch of the hooks)
 //   bool a_source(State&, int m_tile, int kb, ASource& s) const;   (producer warp, all lanes; false = abort)
 //   const CUtensorMap* b_map() const;  bool is_bf16() const;
-//   void begin_tile(State&, int m_tile, int n_tile) const; (every epilogue thread, before a tile's stores)
+//   void begin_tile(State&, int m_tile, int n_tile, uint8_t* warp_scratch) const;
+//        (every epilogue thread, before a tile's stores; warp_scratch: 4 KB of shared memory private
+//         to the warp, free on the row-major path)
+//   int row_origin(State&, int m_tile) const;              (first output row of the tile: m_tile*128
+//        for a plain GEMM, the group's row offset for a grouped one)
+//   static constexpr bool kSwiGLU;                         (row-major path: the tile's columns are
+//        [gate 128 | up 128]; emit silu(gate) * up, 128 columns per 256-wide tile)
 //   void store16(State&, int row, int col, uint4 v) const; (8 consecutive outputs of one row)
 //   float row_bias(int row) const;  float col_bias(int col) const;  bool has_bias() const;
 //   static constexpr bool kBulkEpilogue;                   (true: chunks leave through store_chunk)
@@ -171,6 +178,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
       if (lane == 0) pol.stamp(t, 0);
       for (int kb = 0; kb < k_blocks; ++kb) {
         ASource as;
+        as.bn0 = tn * Cfg::BN;
         if (!pol.a_source(st, tm, kb, as)) { ok = false; break; }
         if (kb == 0 && lane == 0) pol.stamp(t, 1);
         if (!ptx::mbar_wait(&pipe.empty[s], ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
@@ -180,11 +188,11 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
           ptx::mbar_expect_tx(&pipe.full[s], Cfg::kStageBytes);
           ptx::tma_load_2d(sa, as.map, &pipe.full[s], as.x, as.y);
           if constexpr (Cfg::kBKMajor) {
-            ptx::tma_load_2d(sb, pol.b_map(), &pipe.full[s], as.bk, tn * Cfg::BN);
+            ptx::tma_load_2d(sb, pol.b_map(), &pipe.full[s], as.bk, as.bn0);
           } else {
 #pragma unroll
             for (int j = 0; j < Cfg::kBBoxes; ++j)
-              ptx::tma_load_2d(sb + j * 8192, pol.b_map(), &pipe.full[s], tn * Cfg::BN + j * 64, as.bk);
+              ptx::tma_load_2d(sb + j * 8192, pol.b_map(), &pipe.full[s], as.bn0 + j * 64, as.bk);
           }
         }
         __syncwarp();
@@ -246,9 +254,9 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         break;
       }
       ptx::tc_fence_after();
-      pol.begin_tile(est, tm, tn);
+      pol.begin_tile(est, tm, tn, my_epi + 4096);
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * Cfg::kAccCols;
-      const int row0 = tm * kBM + quarter * 32;
+      const int row0 = pol.row_origin(est, tm) + quarter * 32;
       const float rb = has_bias ? pol.row_bias(row0 + lane) : 0.f;
       // fp32 accumulators of 32 columns -> 16-bit pairs (bias added)
       auto pack32 = [&](const uint32_t (&r)[32], int col0, uint32_t (&packed)[16]) {
@@ -320,6 +328,44 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
           if (lane == 0) ptx::bulk_wait_read<0>();   // earlier bulk stores may still read the staging
           __syncwarp();
         }
+        if constexpr (Policy::kSwiGLU) {
+          static_assert(!Policy::kSwiGLU || Cfg::BN == 256, "the SwiGLU epilogue pairs columns c and c + 128 of a 256-wide tile");
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t g[32], u[32];
+            ptx::tmem_ld_32x32(t_addr + c * 32, g);
+            ptx::tmem_ld_32x32(t_addr + 128 + c * 32, u);
+            ptx::tmem_ld_wait();
+            if (c == 3) {
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(&pipe.tmem_empty[buf]);
+            }
+            uint32_t r[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+              r[j] = __float_as_uint(gv / (1.f + __expf(-gv)) * uv);
+            }
+            const int col0 = tn * 128 + c * 32;
+            uint32_t packed[16];
+            pack32(r, col0, packed);
+            const int sw = (lane >> 1) & 3;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+              *(uint4*)(stage + lane * 64 + ((j ^ sw) * 16)) = v;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int rr = i * 8 + (lane >> 2), cc = lane & 3;
+              uint4 v = *(uint4*)(stage + rr * 64 + ((cc ^ ((rr >> 1) & 3)) * 16));
+              pol.store16(est, row0 + rr, col0 + cc * 8, v);
+            }
+            __syncwarp();
+          }
+        } else
 #pragma unroll 1
         for (int c = 0; c < Cfg::BN / 32; ++c) {
           uint32_t r[32];

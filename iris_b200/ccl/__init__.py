@@ -162,6 +162,8 @@ class CCL:
     # ------------------------------------------------------------------ all_reduce
     def _pick_all_reduce(self, config: Config, nbytes: int, group, dtype) -> str:
         v = config.all_reduce_variant
+        if self.ctx.ctx_struct(group).world == 1:
+            return "one_shot"       # nothing to exchange: every variant is a copy
         nvls_ok = config.use_multicast and group is None and self.ctx.has_multicast() and dtype != torch.int32
         if v == "nvls" and not nvls_ok:
             return "two_shot"
