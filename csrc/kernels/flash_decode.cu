@@ -24,6 +24,8 @@
 
 #include "iris/host_api.h"
 #include "iris/iris.cuh"
+#include "flash_decode_static.h"
+#include <stdio.h>
 
 using namespace iris;
 
@@ -410,3 +412,114 @@ int iris_flash_decode(const IrisDecodeDesc* d, void* stream) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ entry point that allocates nothing
+// See flash_decode_static.h. The split-K kernel above is launched unchanged with its partial
+// results directed into the file-scope array below; a small kernel then folds the splits into
+// the output. Host code never uses `g_decode_static_scratch` as an address: the name is only a
+// handle on the host side, the device address comes from cudaGetSymbolAddress.
+namespace {
+
+static __device__ __align__(256) unsigned char g_decode_static_scratch[IRIS_DECODE_STATIC_SCRATCH_BYTES];
+
+constexpr int kStaticMaxDevices = 64;
+float* g_static_scratch_addr[kStaticMaxDevices] = {};
+
+__global__ void __launch_bounds__(kD) decode_local_combine_kernel(const float* partial, void* out, int splits, int is_fp16) {
+  const int it = blockIdx.x, d = threadIdx.x;
+  const float* p = partial + (size_t)it * splits * (kD + 1);
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, p[s * (kD + 1) + kD]);
+  float l = 0.f, acc = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ls = p[s * (kD + 1) + kD];
+    const float w = ls == -INFINITY ? 0.f : exp2f(ls - m);
+    l += w;
+    acc += w * p[s * (kD + 1) + d];
+  }
+  const float o = l > 0.f ? acc / l : 0.f;
+  if (is_fp16) ((__half*)out)[(size_t)it * kD + d] = __float2half_rn(o);
+  else ((__nv_bfloat16*)out)[(size_t)it * kD + d] = __float2bfloat16_rn(o);
+}
+
+void static_err(char* err, int32_t errlen, const char* msg) {
+  if (err && errlen > 0) snprintf(err, (size_t)errlen, "%s", msg);
+}
+
+}  // namespace
+
+extern "C" uint64_t iris_flash_decode_static_scratch_needed(int32_t B, int32_t Hq, int32_t splits, int32_t D) {
+  return (uint64_t)B * (uint64_t)Hq * (uint64_t)splits * (uint64_t)(D + 1);
+}
+
+extern "C" int iris_flash_decode_static(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                                        const int32_t* kv_lens, void* out, int32_t B, int32_t Hq, int32_t Hkv, int32_t D,
+                                        int32_t page, int32_t max_blocks, int32_t splits, float sm_scale, float soft_cap,
+                                        int32_t dtype, void* stream, char* err, int32_t errlen) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (D != kD || Hkv <= 0 || Hq % Hkv || B <= 0 || splits <= 0 || page <= 0) {
+    static_err(err, errlen, "iris_flash_decode_static: head_dim must be 128, q_heads a multiple of kv_heads, sizes positive");
+    return -3;
+  }
+  if (dtype != IRIS_BF16 && dtype != IRIS_F16) {
+    static_err(err, errlen, "iris_flash_decode_static: dtype must be fp16 (0) or bf16 (1)");
+    return -2;
+  }
+  const uint64_t need = iris_flash_decode_static_scratch_needed(B, Hq, splits, D) * sizeof(float);
+  if (need > IRIS_DECODE_STATIC_SCRATCH_BYTES) {
+    char msg[256];
+    snprintf(msg, sizeof(msg),
+             "iris_flash_decode_static: batch %d x q_heads %d x splits %d needs %llu bytes of scratch, the built-in array holds %u; "
+             "lower splits or call iris_flash_decode with your own buffer",
+             B, Hq, splits, (unsigned long long)need, IRIS_DECODE_STATIC_SCRATCH_BYTES);
+    static_err(err, errlen, msg);
+    return IRIS_DECODE_STATIC_TOO_LARGE;
+  }
+  // set-up, once per device: the array's address on the device that is current now
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) {
+    static_err(err, errlen, "iris_flash_decode_static: no current CUDA device");
+    return -4;
+  }
+  if (!g_static_scratch_addr[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+    if (e != cudaSuccess || !p) {
+      static_err(err, errlen, "iris_flash_decode_static: cudaGetSymbolAddress failed for the scratch array");
+      return -5;
+    }
+    g_static_scratch_addr[dev] = (float*)p;
+  }
+  float* scratch = g_static_scratch_addr[dev];
+
+  DecodeArgs a;
+  a.q = (const __nv_bfloat16*)q; a.k_cache = (const __nv_bfloat16*)k_cache; a.v_cache = (const __nv_bfloat16*)v_cache;
+  a.block_table = block_table; a.kv_lens = kv_lens; a.partial = scratch;
+  a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.page = page; a.max_blocks = max_blocks; a.splits = splits;
+  a.group = Hq / Hkv; a.head_groups = (a.group + 15) / 16;
+  a.sm_scale = sm_scale; a.soft_cap = soft_cap; a.is_fp16 = dtype == IRIS_F16;
+  const int smem = kStages * 2 * kTileBytes > (int)((kWarps * 16 * kD + kWarps * 32) * sizeof(float))
+                       ? kStages * 2 * kTileBytes : (int)((kWarps * 16 * kD + kWarps * 32) * sizeof(float));
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(decode_splitk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_splitk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+      static_err(err, errlen, "iris_flash_decode_static: cannot raise the kernel's shared-memory limit");
+      return -20;
+    }
+    attr = true;
+  }
+  dim3 grid(splits, Hkv * a.head_groups, B);
+  if (a.is_fp16) decode_splitk_kernel<true><<<grid, kWarps * 32, smem, s>>>(a);
+  else decode_splitk_kernel<false><<<grid, kWarps * 32, smem, s>>>(a);
+  if (cudaGetLastError() != cudaSuccess) {
+    static_err(err, errlen, "iris_flash_decode_static: split-K kernel launch failed");
+    return -21;
+  }
+  decode_local_combine_kernel<<<B * Hq, kD, 0, s>>>(scratch, out, splits, a.is_fp16);
+  if (cudaGetLastError() != cudaSuccess) {
+    static_err(err, errlen, "iris_flash_decode_static: combine kernel launch failed");
+    return -21;
+  }
+  return 0;
+}
