@@ -43,6 +43,7 @@ class ClockSampler:
         self.rows = []
         self.proc = None
         self.thread = None
+        self.load_from = None     # wall time from which the GPU is under the benchmark's load
 
     def start(self):
         try:
@@ -58,19 +59,22 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 9:
-                self.rows.append(parts)
+                self.rows.append([time.time()] + parts)
 
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.05)
+        deadline = time.time() + 3.0
+        while not self.rows and time.time() < deadline:   # a slow first sample (many ranks start nvidia-smi at once)
+            time.sleep(0.05)
         self.proc.terminate()  # the exact child started above
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
-        for r in self.rows:
+        loaded = [r[1:] for r in self.rows if self.load_from is None or r[0] >= self.load_from]
+        for r in (loaded or [r[1:] for r in self.rows]):
             try:
                 sm.append(float(r[1])); mx.append(float(r[2])); power.append(float(r[3]))
             except ValueError:
@@ -122,6 +126,8 @@ def main() -> int:
         if world == 1 and args.gpus > 1:
             raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
     torch.cuda.set_device(local)
+    sampler = ClockSampler(local)
+    sampler.start()          # runs from here to the end of the end-to-end loop
     if not dist.is_initialized():
         if "MASTER_ADDR" not in os.environ:
             os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -153,12 +159,11 @@ def main() -> int:
         ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True, workspace=ws2, async_op=True)
 
     flops_per_rank = 2.0 * M_TOTAL * K_DIM * F_LOCAL * 2
-    sampler = ClockSampler(local)
 
     # ---------------- device-timed region: exactly `steps` steps between barriers
     # (the clock sampler runs from the warm-up to the end of the end-to-end loop, all of it the
     # same load, so that a short timed region still yields samples)
-    sampler.start()
+    sampler.load_from = time.time()
     for _ in range(max(args.warmup, 3)):
         step()
     ctx.barrier()

@@ -22,38 +22,9 @@
 using namespace iris;
 using namespace iris::gemm;
 
-static_assert(sizeof(IrisCtx) == sizeof(DeviceContext), "IrisCtx must mirror iris::DeviceContext");
+#include "gemm_host.cuh"
 
 namespace {
-
-struct Common {
-  CUtensorMap tmA;
-  CUtensorMap tmB;
-  Shape sh;
-  int tiles_m, tiles_n, group_m;
-  int n_gemm_ctas;
-  int bf16;
-  int bn;
-  const float* bias_row;
-  const float* bias_col;
-  int32_t* status;
-  int64_t* timeline;   // optional [tiles + chunks][4] nanosecond stamps (globaltimer)
-
-  IRIS_D void stamp(int slot, int what) const {
-    if (timeline) timeline[(size_t)slot * 4 + what] = (int64_t)now_ns();
-  }
-  IRIS_D Shape shape() const { return sh; }
-  IRIS_D int gemm_ctas() const { return n_gemm_ctas; }
-  IRIS_D int num_tiles() const { return tiles_m * tiles_n; }
-  IRIS_D const CUtensorMap* b_map() const { return &tmB; }
-  IRIS_D bool is_bf16() const { return bf16 != 0; }
-  IRIS_D bool has_bias() const { return bias_row != nullptr || bias_col != nullptr; }
-  IRIS_D float row_bias(int row) const { return (bias_row && row < sh.M) ? bias_row[row] : 0.f; }
-  IRIS_D float col_bias(int col) const { return (bias_col && col < sh.N) ? bias_col[col] : 0.f; }
-  IRIS_D void fail(int code) const {
-    if (status) atomicCAS(status, 0, code);
-  }
-};
 
 // ------------------------------------------------------------------------------------ local GEMM
 struct LocalGemm : Common {
@@ -117,14 +88,28 @@ struct AllGatherGemm : Common {
     int s = ctx.rank - g;
     return s < 0 ? s + ctx.world : s;
   }
+  // Row-sharded A: this rank's own shard first (nothing to wait for), then the peers' shards in
+  // the order their data lands: every source streams its 128-row chunks in order and all sources
+  // stream at once, so chunk c of every peer is complete before chunk c+1 of any peer. Visiting
+  // (chunk, source) in that order keeps the GEMM behind the transfer instead of waiting for one
+  // source's last chunk.
   IRIS_D void tile(int t, int& tm, int& tn) const {
     if (mode == 0) {
       const int per_src = chunks * tiles_n;
-      const int g = t / per_src;
-      int lm, ln;
-      swizzled_tile(t - g * per_src, chunks, tiles_n, group_m, lm, ln);
-      tm = src_of_group(g) * chunks + lm;
-      tn = ln;
+      if (t < per_src || ctx.world == 1) {
+        int lm, ln;
+        swizzled_tile(t, chunks, tiles_n, group_m, lm, ln);
+        tm = ctx.rank * chunks + lm;
+        tn = ln;
+        return;
+      }
+      const int u = t - per_src;
+      const int per_chunk = (ctx.world - 1) * tiles_n;
+      const int c = u / per_chunk;
+      const int v = u - c * per_chunk;
+      const int si = v / tiles_n;
+      tm = src_of_group(si + 1) * chunks + c;
+      tn = v - si * tiles_n;
     } else {
       swizzled_tile(t, tiles_m, tiles_n, group_m, tm, tn);
     }
@@ -582,46 +567,6 @@ struct ScatterGemmT : Common {
 };
 
 // ------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess) fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-// 2-D map over a row-major [rows, cols] 16-bit matrix with pitch `ld` elements; box = box_cols x box_rows.
-int make_map(CUtensorMap* m, const void* base, int dtype, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
-             uint32_t box_rows) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return -10;
-  if (((uint64_t)base & 15) || ((ld * 2) & 15)) return -11;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {ld * 2};
-  cuuint32_t box[2] = {box_cols, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUtensorMapDataType dt = dtype == IRIS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  CUresult r = enc(m, dt, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -12;
-}
-
-int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
-}
-
-int ceil_div(int a, int b) { return (a + b - 1) / b; }
-
 // Tile width: fewest waves over `ctas` persistent CTAs, weighted by tile cost; ties to the wider.
 int choose_bn(int M, int N, int ctas, bool mn_major) {
   const int cand[3] = {256, 224, 128};
@@ -637,19 +582,6 @@ int choose_bn(int M, int N, int ctas, bool mn_major) {
   }
   (void)mn_major;
   return best_bn;
-}
-
-template <class Cfg, class Policy>
-int launch(const Policy& pol, int grid, cudaStream_t stream) {
-  auto kern = gemm_kernel<Cfg, Policy>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e != cudaSuccess) return -20;
-    attr_set = true;
-  }
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(pol);
-  return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 template <class Policy>

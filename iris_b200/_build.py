@@ -49,10 +49,11 @@ def _cuda_include() -> str:
 
 def _headers_hash() -> str:
     h = hashlib.sha256()
-    for p in sorted(INCLUDE.rglob("*")):
-        if p.is_file():
-            h.update(p.name.encode())
-            h.update(p.read_bytes())
+    files = [p for p in INCLUDE.rglob("*") if p.is_file()]
+    files += [p for p in CSRC.rglob("*") if p.is_file() and p.suffix in (".h", ".hpp", ".cuh")]
+    for p in sorted(files):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
     return h.hexdigest()
 
 
@@ -79,7 +80,7 @@ def _compile_cu(src: Path, hh: str, verbose: bool) -> Path:
     if _needs(obj, key):
         if verbose:
             print(f"[iris_b200 build] nvcc {src.name}", flush=True)
-        _run([_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", "-c", str(src), "-o", str(obj)], log=obj.with_suffix(".ptxas.log"))
+        _run([_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{src.parent}", "-c", str(src), "-o", str(obj)], log=obj.with_suffix(".ptxas.log"))
         _stamp(obj, key)
     return obj
 

@@ -70,6 +70,7 @@ def _as_2d(t: torch.Tensor) -> torch.Tensor:
 class CCL:
     def __init__(self, ctx):
         self.ctx = ctx
+        self._desc_cache: dict = {}
 
     # ------------------------------------------------------------------ plumbing
     def _lib(self):
@@ -91,9 +92,19 @@ class CCL:
         if inp.dtype not in _lib.DTYPE_CODE:
             raise TypeError(f"dtype {inp.dtype} is not supported by the collectives")
 
-    def _desc(self, out, inp, group, config, sync_key="ccl") -> IrisCclDesc:
+    def _desc(self, out, inp, group, config, sync_key="ccl", op="") -> IrisCclDesc:
         ctx = self.ctx
+        # descriptors are cached per (buffers, shape, config): a repeated call costs one lookup
+        key = (out.data_ptr(), inp.data_ptr(), tuple(out.shape), tuple(inp.shape), out.stride(0), inp.stride(0), inp.dtype,
+               ctx._group_key(group), config.use_multicast, config.comm_sms, config.block_size_m, config.block_size_n,
+               config.all_reduce_distribution, id(ctx._ctx_epoch), op, config.reduce_scatter_rows)
+        hit = self._desc_cache.get(key)
+        if hit is not None:
+            return hit
+        if len(self._desc_cache) > 4096:
+            self._desc_cache.clear()
         d = IrisCclDesc()
+        self._desc_cache[key] = d
         d.ctx = ctx.ctx_struct(group)
         d.sync_block = ctx.sync_block((sync_key, ctx._group_key(group))).data_ptr()
         d.inp, d.out = inp.data_ptr(), out.data_ptr()
@@ -131,7 +142,7 @@ class CCL:
                 self._peer(out, r, group)[me * M:(me + 1) * M].copy_(inp)
             self._cpu_exit(group)
         else:
-            d = self._desc(out, inp, group, config)
+            d = self._desc(out, inp, group, config, op="ag")
             d.M, d.N = M, N
             d.variant = 1 if config.all_gather_variant == "partitioned" else 0
             self._launch(0, d)
@@ -154,7 +165,7 @@ class CCL:
                 self._peer(out, r, group)[:, me * N:(me + 1) * N].copy_(inp[:, r * N:(r + 1) * N])
             self._cpu_exit(group)
         else:
-            d = self._desc(out, inp, group, config)
+            d = self._desc(out, inp, group, config, op="a2a")
             d.M, d.N = M, N
             self._launch(1, d)
         self._finish(async_op, group)
@@ -224,7 +235,7 @@ class CCL:
             out.copy_(acc.to(out.dtype))
             self._cpu_exit(group)
         else:
-            d = self._desc(out, inp, group, config)
+            d = self._desc(out, inp, group, config, op="ar")
             d.M, d.N = inp.shape
             d.variant = _AR_CODE[ws.variant]
             if ws.variant == "ring":
@@ -273,7 +284,7 @@ class CCL:
                     out[r0:r1, c0:c1].copy_(acc[r0:r1, c0:c1].to(out.dtype))
             self._cpu_exit(group)
         else:
-            d = self._desc(out, inp, group, config)
+            d = self._desc(out, inp, group, config, op="rs")
             d.M, d.N = M, N
             d.rows_mode = 1 if rows else 0
             self._launch(3, d)

@@ -218,6 +218,7 @@ class Iris:
         self._device_context = torch.tensor(words, dtype=torch.int64, device=self.device)
         self._ctx_struct = None
         self._group_ctx_cache.clear()
+        self._ctx_epoch = object()    # changes whenever cached kernel descriptors become stale
 
     def _group_key(self, group):
         if group is None:

@@ -1,0 +1,164 @@
+"""Expert-sharded mixture-of-experts layer (expert parallelism over the ranks of the heap).
+
+Every rank holds ``num_experts / W`` experts (SwiGLU FFN: gate/up ``[hidden, ffn]``, down
+``[ffn, hidden]``) and ``T`` tokens. ``forward(x, router_logits)`` routes each token to its top-k
+experts (softmax over the selected k logits), moves the token rows to the experts' owners, runs
+the expert FFNs as grouped GEMMs and returns the weighted sum of the k expert outputs in token
+order. On a GPU the whole pass is the launch sequence of ``csrc/kernels/moe.cu`` on the current
+stream, with the dispatch fused into the first grouped GEMM and the combine fused into the second
+one's epilogue; the reference pipeline with its host barriers and Python-side metadata is
+examples/31_expert_sharded_moe/moe.py:195-328. Weights are bf16 here (the fp8 block-scaled variant
+is not built yet). ``reference_moe`` is the unsharded fp32 PyTorch statement of the layer.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _lib
+
+
+class IrisMoeDesc(C.Structure):
+    _fields_ = [
+        ("ctx", _lib.IrisCtx),
+        ("T", C.c_int32), ("K", C.c_int32), ("E", C.c_int32), ("El", C.c_int32), ("D", C.c_int32), ("F", C.c_int32),
+        ("capacity", C.c_int32), ("comm_ctas", C.c_int32),
+        ("x", C.c_void_p), ("logits", C.c_void_p), ("w13", C.c_void_p), ("w2", C.c_void_p), ("out", C.c_void_p),
+        ("inbox", C.c_void_p), ("H", C.c_void_p), ("comb", C.c_void_p),
+        ("sync_meta", C.c_void_p), ("sync_gemm2", C.c_void_p),
+        ("topk_idx", C.c_void_p), ("topk_w", C.c_void_p),
+        ("counts_local", C.c_void_p), ("counts_all", C.c_void_p), ("cursor", C.c_void_p), ("list_off", C.c_void_p),
+        ("sorted_pairs", C.c_void_p), ("my_off", C.c_void_p),
+        ("expert_rows", C.c_void_p), ("expert_row0", C.c_void_p), ("tile_prefix", C.c_void_p), ("expected_cum", C.c_void_p),
+        ("arrived", C.c_void_p), ("inbox_meta", C.c_void_p),
+    ]
+
+
+def route(logits: torch.Tensor, top_k: int):
+    """Top-k of the logits and softmax over the selected k (reference: topk.py:93-121)."""
+    vals, idx = torch.topk(logits.float(), top_k, dim=-1)
+    return idx, torch.softmax(vals, dim=-1)
+
+
+def reference_moe(x, logits, w_gate, w_up, w_down, top_k: int):
+    """Unsharded fp32 MoE: ``w_*`` hold ALL experts, ``[E, hidden, ffn]`` / ``[E, ffn, hidden]``."""
+    idx, w = route(logits, top_k)
+    out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+    xf = x.float()
+    for e in range(w_gate.shape[0]):
+        tok, slot = torch.nonzero(idx == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        h = xf[tok]
+        g, u = h @ w_gate[e].float(), h @ w_up[e].float()
+        y = (torch.nn.functional.silu(g) * u) @ w_down[e].float()
+        out.index_add_(0, tok, y * w[tok, slot][:, None])
+    return out
+
+
+def fuse_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """``[El, D, F]`` x 2 -> ``[El, D, 2F]`` whose 256-column blocks are ``[gate 128 | up 128]``: the
+    layout the SwiGLU epilogue expects (it pairs column c with column c + 128 of a tile)."""
+    El, D, F = w_gate.shape
+    g = w_gate.reshape(El, D, F // 128, 1, 128)
+    u = w_up.reshape(El, D, F // 128, 1, 128)
+    return torch.cat([g, u], dim=3).reshape(El, D, 2 * F).contiguous()
+
+
+class MoELayer:
+    def __init__(self, ctx, hidden: int, ffn: int, num_experts: int, top_k: int, max_tokens: int,
+                 w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, capacity_factor: float | None = None,
+                 comm_sms: int = 16):
+        W = ctx.get_num_ranks()
+        if num_experts % W:
+            raise ValueError("num_experts must be a multiple of the number of ranks")
+        El = num_experts // W
+        if tuple(w_gate.shape) != (El, hidden, ffn) or tuple(w_up.shape) != (El, hidden, ffn) or tuple(w_down.shape) != (El, ffn, hidden):
+            raise ValueError("expected local expert weights [E/W, hidden, ffn] (gate, up) and [E/W, ffn, hidden] (down)")
+        self.ctx, self.D, self.F, self.E, self.El, self.K, self.T = ctx, hidden, ffn, num_experts, El, top_k, max_tokens
+        self.comm_sms = comm_sms
+        self.w_gate, self.w_up, self.w_down = w_gate, w_up, w_down
+        if ctx.is_cpu:
+            return
+        if hidden % 256 or ffn % 128:
+            raise ValueError("the fused kernels need hidden % 256 == 0 and ffn % 128 == 0")
+        dev = ctx.get_device()
+        self.w13 = fuse_gate_up(w_gate.to(torch.bfloat16), w_up.to(torch.bfloat16))
+        self.w2 = w_down.to(torch.bfloat16).contiguous()
+        pairs = max_tokens * top_k
+        cap = W * pairs if capacity_factor is None else min(W * pairs, int(capacity_factor * pairs))
+        self.capacity = max(128, -(-cap // 128) * 128)
+        i32 = torch.int32
+        self.inbox = ctx.heap.allocate(self.capacity * hidden, torch.bfloat16).view(self.capacity, hidden)
+        self.inbox_meta = ctx.zeros(self.capacity, dtype=torch.int64)
+        self.comb = ctx.heap.allocate(pairs * hidden, torch.bfloat16).view(pairs, hidden)
+        self.counts_all = ctx.zeros((W, num_experts), dtype=i32)
+        self.arrived = ctx.zeros(El, dtype=i32)
+        self.sync_meta = ctx.zeros(80, dtype=i32)
+        self.sync_gemm2 = ctx.zeros(80, dtype=i32)
+        self.H = torch.zeros(self.capacity, ffn, dtype=torch.bfloat16, device=dev)
+        self.topk_idx = torch.zeros(max_tokens, top_k, dtype=i32, device=dev)
+        self.topk_w = torch.zeros(max_tokens, top_k, dtype=torch.float32, device=dev)
+        z = lambda n: torch.zeros(n, dtype=i32, device=dev)  # noqa: E731
+        self.counts_local, self.cursor, self.list_off, self.my_off = z(num_experts), z(num_experts), z(num_experts + 1), z(num_experts)
+        self.sorted_pairs = z(pairs)
+        self.expert_rows, self.expert_row0, self.tile_prefix, self.expected_cum = z(El), z(El + 1), z(El + 1), z(El)
+        ctx.barrier()
+
+    def _lib(self):
+        lib = _lib.kernels()
+        if not getattr(lib, "_iris_moe_typed", False):
+            lib.iris_moe_forward.argtypes = [C.POINTER(IrisMoeDesc), C.c_void_p]
+            lib.iris_moe_forward.restype = C.c_int
+            lib._iris_moe_typed = True
+        return lib
+
+    def forward(self, x: torch.Tensor, router_logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        ctx = self.ctx
+        T = x.shape[0]
+        if T > self.T or x.shape[1] != self.D or tuple(router_logits.shape) != (T, self.E):
+            raise ValueError("x must be [T <= max_tokens, hidden] and router_logits [T, num_experts]")
+        if ctx.is_cpu:
+            return self._forward_cpu(x, router_logits)
+        if x.dtype != torch.bfloat16 or not x.is_contiguous():
+            raise TypeError("the fused MoE takes contiguous bf16 tokens")
+        logits = router_logits.float().contiguous()
+        if out is None:
+            out = torch.empty_like(x)
+        d = IrisMoeDesc()
+        d.ctx = ctx.ctx_struct()
+        d.T, d.K, d.E, d.El, d.D, d.F, d.capacity, d.comm_ctas = T, self.K, self.E, self.El, self.D, self.F, self.capacity, self.comm_sms
+        d.x, d.logits, d.w13, d.w2, d.out = x.data_ptr(), logits.data_ptr(), self.w13.data_ptr(), self.w2.data_ptr(), out.data_ptr()
+        d.inbox, d.H, d.comb = self.inbox.data_ptr(), self.H.data_ptr(), self.comb.data_ptr()
+        d.sync_meta, d.sync_gemm2 = self.sync_meta.data_ptr(), self.sync_gemm2.data_ptr()
+        for name in ("topk_idx", "topk_w", "counts_local", "counts_all", "cursor", "list_off", "sorted_pairs", "my_off",
+                     "expert_rows", "expert_row0", "tile_prefix", "expected_cum", "arrived", "inbox_meta"):
+            setattr(d, name, getattr(self, name).data_ptr())
+        _lib.check(self._lib().iris_moe_forward(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "MoE forward launch")
+        self._keep = logits
+        return out
+
+    __call__ = forward
+
+    def _forward_cpu(self, x, logits):
+        """CPU backend: gather every rank's tokens, apply the local experts, sum over ranks."""
+        ctx = self.ctx
+        W, me, T = ctx.get_num_ranks(), ctx.get_rank(), x.shape[0]
+        xs = ctx.zeros((W * T, self.D), dtype=torch.float32)
+        ls = ctx.zeros((W * T, self.E), dtype=torch.float32)
+        ctx.ccl.all_gather(xs, ctx.as_symmetric(x.float().contiguous()))
+        ctx.ccl.all_gather(ls, ctx.as_symmetric(logits.float().contiguous()))
+        idx, w = route(ls, self.K)
+        part = ctx.zeros((W * T, self.D), dtype=torch.float32)
+        for j in range(self.El):
+            e = me * self.El + j
+            tok, slot = torch.nonzero(idx == e, as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            h = xs[tok]
+            y = (torch.nn.functional.silu(h @ self.w_gate[j].float()) * (h @ self.w_up[j].float())) @ self.w_down[j].float()
+            part.index_add_(0, tok, y * w[tok, slot][:, None])
+        tot = ctx.zeros((W * T, self.D), dtype=torch.float32)
+        ctx.ccl.all_reduce(tot, part)
+        return tot[me * T:(me + 1) * T].to(x.dtype)

@@ -1,0 +1,113 @@
+"""Ring attention: attention over a sequence that is split across the ranks (context parallelism).
+
+Every rank holds ``S`` consecutive tokens of the sequence: queries ``[S, Hq, D]`` and keys/values
+``[S, Hkv, D]``. ``RingAttention.forward(q, k, v, causal)`` returns this rank's ``[S, Hq, D]``
+output of attention over the WHOLE sequence. One kernel per call (``csrc/kernels/ring_attention.cu``):
+communication CTAs pass the K/V blocks round the ring with bulk copies and per-block arrival
+counters on the heap, attention CTAs consume the blocks as they arrive. The reference has no
+counterpart; ``reference_attention`` is the plain fp32 PyTorch statement used by the tests.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from .. import _lib
+
+
+class IrisRingAttnDesc(C.Structure):
+    _fields_ = [
+        ("ctx", _lib.IrisCtx),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("kv_buf", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p),
+        ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("S", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32), ("causal", C.c_int32),
+        ("n_comm", C.c_int32), ("dtype", C.c_int32), ("reserved", C.c_int32),
+        ("sm_scale", C.c_float),
+    ]
+
+
+def reference_attention(q, k, v, causal: bool = False, q_offset: int = 0, sm_scale: float | None = None):
+    """fp32 attention of ``q [Sq, Hq, D]`` over ``k, v [Sk, Hkv, D]``; query i sits at position
+    ``q_offset + i`` of the key sequence when ``causal``."""
+    Sq, Hq, D = q.shape
+    Sk, Hkv, _ = k.shape
+    sm_scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(D)
+    g = Hq // Hkv
+    kf = k.float().repeat_interleave(g, dim=1)
+    vf = v.float().repeat_interleave(g, dim=1)
+    s = torch.einsum("qhd,khd->hqk", q.float(), kf) * sm_scale
+    if causal:
+        qi = torch.arange(Sq, device=q.device)[:, None] + q_offset
+        ki = torch.arange(Sk, device=q.device)[None, :]
+        s = s.masked_fill((ki > qi)[None], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("hqk,khd->qhd", p, vf)
+
+
+class RingAttention:
+    def __init__(self, ctx, seq_per_rank: int, num_q_heads: int, num_kv_heads: int, head_dim: int = 128,
+                 sm_scale: float | None = None, comm_sms: int = 8, dtype=torch.bfloat16):
+        if head_dim != 128:
+            raise ValueError("the ring-attention kernel is specialised for head_dim 128")
+        if num_q_heads % num_kv_heads:
+            raise ValueError("num_q_heads must be a multiple of num_kv_heads")
+        self.ctx, self.S, self.Hq, self.Hkv, self.D = ctx, seq_per_rank, num_q_heads, num_kv_heads, head_dim
+        self.sm_scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(head_dim)
+        self.comm_sms, self.dtype = comm_sms, dtype
+        W = ctx.get_num_ranks()
+        esize = 2 if not ctx.is_cpu else torch.empty((), dtype=dtype).element_size()
+        # ring buffer [parity][origin rank][K | V][S, Hkv, D] and its arrival counters, on the heap
+        self.kv_buf = ctx.heap.allocate(2 * W * 2 * seq_per_rank * num_kv_heads * head_dim * esize, torch.uint8)
+        self.flags = ctx.zeros(2 * W, dtype=torch.int32)
+        self.state = ctx.zeros(2, dtype=torch.int32)
+        ctx.barrier()
+
+    def _lib(self):
+        lib = _lib.kernels()
+        if not getattr(lib, "_iris_ring_typed", False):
+            lib.iris_ring_attention.argtypes = [C.POINTER(IrisRingAttnDesc), C.c_void_p]
+            lib.iris_ring_attention.restype = C.c_int
+            lib._iris_ring_typed = True
+        return lib
+
+    def forward(self, q, k, v, causal: bool = False, out=None, return_lse: bool = False):
+        ctx = self.ctx
+        if tuple(q.shape) != (self.S, self.Hq, self.D) or tuple(k.shape) != (self.S, self.Hkv, self.D) or k.shape != v.shape:
+            raise ValueError("expected q [S, Hq, D] and k, v [S, Hkv, D] with the layer's sizes")
+        if ctx.is_cpu:
+            return self._forward_cpu(q, k, v, causal)
+        if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+            raise TypeError("ring attention takes fp16 or bf16 tensors of one dtype")
+        if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+            raise ValueError("ring attention takes contiguous tensors")
+        if out is None:
+            out = torch.empty_like(q)
+        lse = torch.empty((self.S, self.Hq), dtype=torch.float32, device=q.device) if return_lse else None
+        d = IrisRingAttnDesc()
+        d.ctx = ctx.ctx_struct()
+        d.q, d.k, d.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+        d.kv_buf, d.flags, d.state = self.kv_buf.data_ptr(), self.flags.data_ptr(), self.state.data_ptr()
+        d.out = out.data_ptr()
+        d.lse = lse.data_ptr() if lse is not None else None
+        d.S, d.Hq, d.Hkv, d.D, d.causal, d.n_comm = self.S, self.Hq, self.Hkv, self.D, int(causal), self.comm_sms
+        d.dtype = _lib.DTYPE_CODE[q.dtype]
+        d.sm_scale = self.sm_scale
+        _lib.check(self._lib().iris_ring_attention(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "ring attention launch")
+        return (out, lse) if return_lse else out
+
+    __call__ = forward
+
+    def _forward_cpu(self, q, k, v, causal):
+        """CPU backend: gather all K/V blocks through the heap, attend in PyTorch."""
+        ctx = self.ctx
+        W, me = ctx.get_num_ranks(), ctx.get_rank()
+        ks = ctx.zeros((W * self.S, self.Hkv * self.D), dtype=torch.float32)
+        vs = ctx.zeros((W * self.S, self.Hkv * self.D), dtype=torch.float32)
+        ctx.ccl.all_gather(ks, ctx.as_symmetric(k.float().reshape(self.S, -1).contiguous()))
+        ctx.ccl.all_gather(vs, ctx.as_symmetric(v.float().reshape(self.S, -1).contiguous()))
+        o = reference_attention(q, ks.view(W * self.S, self.Hkv, self.D), vs.view(W * self.S, self.Hkv, self.D), causal,
+                                q_offset=me * self.S, sm_scale=self.sm_scale)
+        return o.to(q.dtype)

@@ -291,3 +291,61 @@ def test_reference_decode_equals_dense_attention():
     o2, l2 = reference_decode(q, kc[:, :, :, :], vc, torch.tensor([0, 0], dtype=torch.int32), table)
     m = merge_partials(torch.stack([o1, o2]), torch.stack([l1, l2]))
     assert torch.allclose(m, o1, atol=1e-6)
+
+
+def _moe_cpu(rank, world):
+    import iris_b200 as iris
+    from iris_b200.models import MoELayer, reference_moe
+
+    ctx = iris.iris(1 << 26)
+    T, D, F, K = 10, 16, 8, 2
+    E = 2 * world
+    torch.manual_seed(3)
+    wg, wu, wd = torch.randn(E, D, F), torch.randn(E, D, F), torch.randn(E, F, D)
+    sl = slice(rank * 2, rank * 2 + 2)
+    layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg[sl], w_up=wu[sl], w_down=wd[sl])
+    torch.manual_seed(50 + rank)
+    x, logits = torch.randn(T, D), torch.randn(T, E)
+    out = layer(x, logits)
+    assert torch.allclose(out, reference_moe(x, logits, wg, wu, wd, K), atol=1e-4)
+    ctx.barrier()
+
+
+def test_moe_cpu_world2():
+    run_ranks(_moe_cpu, 2)
+
+
+def test_fuse_gate_up_layout():
+    from iris_b200.models import fuse_gate_up
+
+    g = torch.arange(2 * 3 * 256, dtype=torch.float32).view(2, 3, 256)
+    u = -g
+    f = fuse_gate_up(g, u)
+    assert f.shape == (2, 3, 512)
+    assert torch.equal(f[:, :, 0:128], g[:, :, 0:128]) and torch.equal(f[:, :, 128:256], u[:, :, 0:128])
+    assert torch.equal(f[:, :, 256:384], g[:, :, 128:256]) and torch.equal(f[:, :, 384:512], u[:, :, 128:256])
+
+
+def _ring_cpu(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.models import RingAttention, reference_attention
+
+    ctx = iris.iris(1 << 26)
+    S, Hq, Hkv, D = 12, 4, 2, 128
+    torch.manual_seed(rank)
+    q, k, v = torch.randn(S, Hq, D), torch.randn(S, Hkv, D), torch.randn(S, Hkv, D)
+    ks, vs = [torch.empty_like(k) for _ in range(world)], [torch.empty_like(v) for _ in range(world)]
+    dist.all_gather(ks, k)
+    dist.all_gather(vs, v)
+    layer = RingAttention(ctx, S, Hq, Hkv, dtype=torch.float32)
+    for causal in (False, True):
+        out = layer(q, k, v, causal=causal)
+        ref = reference_attention(q, torch.cat(ks), torch.cat(vs), causal, q_offset=rank * S)
+        assert torch.allclose(out, ref, atol=1e-5)
+    ctx.barrier()
+
+
+def test_ring_attention_cpu_world2():
+    run_ranks(_ring_cpu, 2)

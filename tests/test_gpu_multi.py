@@ -275,3 +275,67 @@ def _decode(rank, world):
 
 def test_distributed_flash_decode():
     run_ranks(_decode, _world(), backend="nccl")
+
+
+def _moe(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.models import MoELayer, reference_moe
+
+    ctx = iris.iris(1 << 30)
+    T, D, F, K = 160, 512, 256, 4
+    E = 4 * world
+    El = E // world
+    dt = torch.bfloat16
+    torch.manual_seed(21)                                   # every rank builds the full weight set ...
+    wg = (torch.randn(E, D, F, device="cuda") * 0.05).to(dt)
+    wu = (torch.randn(E, D, F, device="cuda") * 0.05).to(dt)
+    wd = (torch.randn(E, F, D, device="cuda") * 0.05).to(dt)
+    sl = slice(rank * El, (rank + 1) * El)                  # ... and keeps its own experts
+    layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg[sl].contiguous(), w_up=wu[sl].contiguous(), w_down=wd[sl].contiguous())
+    for it in range(3):
+        torch.manual_seed(100 * it + rank)
+        x = torch.randn(T, D, device="cuda", dtype=dt)
+        logits = torch.randn(T, E, device="cuda")
+        out = layer(x, logits)
+        ref = reference_moe(x, logits, wg, wu, wd, K)
+        err = (out.float() - ref).abs().max().item()
+        assert err < 3e-2 * max(ref.abs().max().item(), 1.0), (it, err)
+    ctx.check()
+    ctx.barrier()
+
+
+def test_expert_sharded_moe():
+    run_ranks(_moe, _world(), backend="nccl", timeout=600)
+
+
+def _ring(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.models import RingAttention, reference_attention
+
+    ctx = iris.iris(1 << 30)
+    S, Hq, Hkv, D = 192, 8, 2, 128
+    dt = torch.bfloat16
+    torch.manual_seed(30 + rank)
+    q = torch.randn(S, Hq, D, device="cuda", dtype=dt)
+    k = torch.randn(S, Hkv, D, device="cuda", dtype=dt)
+    v = torch.randn(S, Hkv, D, device="cuda", dtype=dt)
+    ks = torch.empty(world * S, Hkv, D, device="cuda", dtype=dt)
+    vs = torch.empty(world * S, Hkv, D, device="cuda", dtype=dt)
+    dist.all_gather_into_tensor(ks, k)
+    dist.all_gather_into_tensor(vs, v)
+    layer = RingAttention(ctx, S, Hq, Hkv)
+    for causal in (False, True):
+        for _ in range(3):
+            out = layer(q, k, v, causal=causal)
+        ref = reference_attention(q, ks, vs, causal, q_offset=rank * S)
+        assert (out.float() - ref).abs().max().item() < 2e-2, causal
+    ctx.check()
+    ctx.barrier()
+
+
+def test_ring_attention_between_gpus():
+    run_ranks(_ring, _world(), backend="nccl")

@@ -242,3 +242,57 @@ def test_flash_decode_matches_reference(ctx, batch, lens, page, heads):
     assert (out.float() - ro).abs().max().item() < 2e-2
     assert (lse - rlse).abs().max().item() < 2e-2
     ctx.check()
+
+
+@pytest.mark.parametrize("T,E,K", [(64, 8, 2), (200, 16, 4), (128, 32, 8)])
+def test_moe_layer_world1(ctx, T, E, K):
+    from iris_b200.models import MoELayer, reference_moe
+
+    D, F = 256, 128
+    torch.manual_seed(4)
+    dt = torch.bfloat16
+    wg = (torch.randn(E, D, F, device="cuda") * 0.05).to(dt)
+    wu = (torch.randn(E, D, F, device="cuda") * 0.05).to(dt)
+    wd = (torch.randn(E, F, D, device="cuda") * 0.05).to(dt)
+    layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg, w_up=wu, w_down=wd)
+    for it in range(2):
+        x = torch.randn(T, D, device="cuda", dtype=dt)
+        logits = torch.randn(T, E, device="cuda")
+        out = layer(x, logits)
+        ref = reference_moe(x, logits, wg, wu, wd, K)
+        err = (out.float() - ref).abs().max().item()
+        assert err < 3e-2 * max(ref.abs().max().item(), 1.0), (it, err)
+    ctx.check()
+
+
+def test_router_matches_torch_topk(ctx):
+    from iris_b200.models import MoELayer, route
+
+    T, E, K, D, F = 96, 64, 8, 256, 128
+    dt = torch.bfloat16
+    z = lambda *s: torch.zeros(*s, device="cuda", dtype=dt)  # noqa: E731
+    layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=z(E, D, F), w_up=z(E, D, F), w_down=z(E, F, D))
+    torch.manual_seed(9)
+    logits = torch.randn(T, E, device="cuda")
+    layer(torch.zeros(T, D, device="cuda", dtype=dt), logits)
+    torch.cuda.synchronize()
+    idx, w = route(logits, K)
+    assert torch.equal(layer.topk_idx.long(), idx)
+    assert torch.allclose(layer.topk_w, w, atol=1e-5)
+
+
+@pytest.mark.parametrize("S,Hq,Hkv,causal", [(128, 4, 2, False), (200, 8, 2, True), (64, 2, 2, True)])
+def test_ring_attention_world1(ctx, S, Hq, Hkv, causal):
+    from iris_b200.models import RingAttention, reference_attention
+
+    dt = torch.bfloat16
+    torch.manual_seed(6)
+    q = torch.randn(S, Hq, 128, device="cuda", dtype=dt)
+    k = torch.randn(S, Hkv, 128, device="cuda", dtype=dt)
+    v = torch.randn(S, Hkv, 128, device="cuda", dtype=dt)
+    layer = RingAttention(ctx, S, Hq, Hkv)
+    for _ in range(2):
+        out = layer(q, k, v, causal=causal)
+    ref = reference_attention(q, k, v, causal)
+    assert (out.float() - ref).abs().max().item() < 2e-2
+    ctx.check()
