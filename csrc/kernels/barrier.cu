@@ -16,13 +16,15 @@ using namespace iris;
 namespace {
 
 __global__ void device_barrier_kernel(const __grid_constant__ DeviceContext ctx, SyncBlock* sb) {
-  if (threadIdx.x != 0) return;
-  const int32_t e = read_epoch(sb);
+  const int32_t e = read_epoch(sb);      // one warp: lane r signals and polls rank r
   __threadfence_system();
-  barrier_signal(ctx, sb);
-  barrier_wait(ctx, sb, e + 1);
-  sb->epoch = e + 1;
-  __threadfence_system();
+  barrier_signal_warp(ctx, sb);
+  barrier_wait_warp(ctx, sb, e + 1);
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    sb->epoch = e + 1;
+    __threadfence_system();
+  }
 }
 
 // Waits until *flag >= target or timeout_ns elapsed; writes 0 (seen) or 1 (timed out) to *result.

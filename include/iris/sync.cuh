@@ -124,22 +124,42 @@ IRIS_D bool barrier_wait(const DeviceContext& ctx, SyncBlock* sb, int32_t target
 }
 
 #if defined(__CUDACC__)
-// Kernel epilogue: every CTA calls this (all threads) after its last remote access. The CTA that
-// arrives last runs one cross-rank round (signal, then wait for all peers), so that when the
-// kernel completes every peer's stores into this rank have been published. `rounds_before` is the
-// number of rounds this kernel already ran on the block (0 or 1), `epoch0` the epoch read at entry.
+// Warp-parallel forms: lane r talks to rank r, so the W-1 remote atomics (and their release
+// fences) and the W-1 polls overlap instead of running one after the other. All 32 lanes call.
+IRIS_D void barrier_signal_warp(const DeviceContext& ctx, SyncBlock* sb) {
+  const int lane = threadIdx.x & 31;
+  for (int r = lane; r < ctx.world; r += 32)
+    if (r != ctx.rank) red_release_sys_add(&ctx.remote(sb, r)->slots[ctx.rank], 1);
+}
+IRIS_D bool barrier_wait_warp(const DeviceContext& ctx, SyncBlock* sb, int32_t target) {
+  const int lane = threadIdx.x & 31;
+  bool ok = true;
+  for (int r = lane; r < ctx.world; r += 32)
+    if (r != ctx.rank) ok = wait_flag_ge(ctx, &sb->slots[r], target, kTimeoutBarrier) && ok;
+  return __all_sync(0xffffffffu, ok);
+}
+
+// Kernel epilogue: every CTA calls this (all threads, blockDim.x >= 32) after its last remote
+// access. The CTA that arrives last runs one cross-rank round (signal, then wait for all peers),
+// so that when the kernel completes every peer's stores into this rank have been published.
+// `rounds_before` is the number of rounds this kernel already ran on the block (0 or 1), `epoch0`
+// the epoch read at entry.
 IRIS_D void grid_exit_barrier(const DeviceContext& ctx, SyncBlock* sb, int32_t epoch0, int rounds_before) {
+  __shared__ int s_last;
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
-    int total = gridDim.x * gridDim.y * gridDim.z;
-    int old = atomicAdd(&sb->done, 1);
-    if (old == total - 1) {
-      __threadfence_system();
-      if (ctx.world > 1) {
-        barrier_signal(ctx, sb);
-        barrier_wait(ctx, sb, epoch0 + rounds_before + 1);
-      }
+    const int total = gridDim.x * gridDim.y * gridDim.z;
+    s_last = atomicAdd(&sb->done, 1) == total - 1 ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x < 32) {
+    __threadfence_system();
+    if (ctx.world > 1) {
+      barrier_signal_warp(ctx, sb);
+      barrier_wait_warp(ctx, sb, epoch0 + rounds_before + 1);
+    }
+    if (threadIdx.x == 0) {
       sb->done = 0;
       sb->epoch = epoch0 + rounds_before + 1;
       __threadfence_system();
@@ -150,16 +170,16 @@ IRIS_D void grid_exit_barrier(const DeviceContext& ctx, SyncBlock* sb, int32_t e
 // until all peers entered (their inputs are final and their previous use of buffers is over).
 IRIS_D bool grid_entry_barrier(const DeviceContext& ctx, SyncBlock* sb, int32_t epoch0) {
   __shared__ int s_ok;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {
     bool ok = true;
     if (ctx.world > 1) {
       if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
         __threadfence_system();
-        barrier_signal(ctx, sb);
+        barrier_signal_warp(ctx, sb);
       }
-      ok = barrier_wait(ctx, sb, epoch0 + 1);
+      ok = barrier_wait_warp(ctx, sb, epoch0 + 1);
     }
-    s_ok = ok ? 1 : 0;
+    if (threadIdx.x == 0) s_ok = ok ? 1 : 0;
   }
   __syncthreads();
   return s_ok != 0;
