@@ -1,0 +1,82 @@
+#!/usr/bin/env python3
+"""Small, self-terminating workloads for `ncu` captures (one GPU, a few launches, < 1 GB held).
+
+    python benchmark/profile_target.py gemm      # 3 launches of the local tcgen05 GEMM 4096x3584x8192 bf16
+    python benchmark/profile_target.py decode    # 3 flash-decode steps, batch 8, 16384 keys, 64/8 heads
+    python benchmark/profile_target.py fused     # world-size-1 all_gather_matmul + matmul_reduce_scatter
+    python benchmark/profile_target.py moe       # one MoE layer pass, 1024 tokens, 8 experts
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def ctx_world1(heap=2 << 30):
+    import iris_b200 as iris
+
+    torch.cuda.set_device(0)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29577")
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    return iris.iris(heap)
+
+
+def main():
+    what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    dt = torch.bfloat16
+    if what == "gemm":
+        from iris_b200.ops.gemm import matmul
+
+        A = torch.randn(4096, 8192, device="cuda", dtype=dt)
+        B = torch.randn(8192, 3584, device="cuda", dtype=dt) * 0.02
+        C = torch.empty(4096, 3584, device="cuda", dtype=dt)
+        for _ in range(3):
+            matmul(A, B, out=C)
+        torch.cuda.synchronize()
+        return
+    ctx = ctx_world1()
+    if what == "decode":
+        from iris_b200.models import FlashDecodeLayer
+
+        B_, L, Hq, Hkv, page = 8, 16384, 64, 8, 64
+        nb = L // page
+        kc = torch.randn(B_ * nb, page, Hkv, 128, device="cuda", dtype=dt)
+        vc = torch.randn(B_ * nb, page, Hkv, 128, device="cuda", dtype=dt)
+        table = torch.arange(B_ * nb, device="cuda", dtype=torch.int32).view(B_, nb)
+        lens = torch.full((1, B_), L, device="cuda", dtype=torch.int32)
+        q = torch.randn(B_, Hq, 128, device="cuda", dtype=dt)
+        layer = FlashDecodeLayer(ctx, Hq, Hkv, 128, max_batch=B_)
+        for _ in range(3):
+            layer(q, kc, vc, lens, table)
+    elif what == "fused":
+        X = torch.randn(4096, 8192, device="cuda", dtype=dt)
+        W1 = torch.randn(8192, 3584, device="cuda", dtype=dt) * 0.02
+        W2 = torch.randn(3584, 8192, device="cuda", dtype=dt) * 0.02
+        H = torch.empty(4096, 3584, device="cuda", dtype=dt)
+        Y = torch.empty(4096, 8192, device="cuda", dtype=dt)
+        for _ in range(2):
+            ctx.ops.all_gather_matmul(H, X, W1, shard_dim=0, async_op=True)
+            ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True, async_op=True)
+    elif what == "moe":
+        from iris_b200.models import MoELayer
+
+        T, D, F, E, K = 1024, 2048, 1024, 8, 2
+        wg = (torch.randn(E, D, F, device="cuda") * 0.02).to(dt)
+        wu = (torch.randn(E, D, F, device="cuda") * 0.02).to(dt)
+        wd = (torch.randn(E, F, D, device="cuda") * 0.02).to(dt)
+        layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg, w_up=wu, w_down=wd)
+        x = torch.randn(T, D, device="cuda", dtype=dt)
+        logits = torch.randn(T, E, device="cuda")
+        for _ in range(2):
+            layer(x, logits)
+    torch.cuda.synchronize()
+    ctx.check()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

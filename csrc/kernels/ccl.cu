@@ -98,6 +98,22 @@ __device__ __forceinline__ UT load_unit_cv(const UT* p) {
   return u;
 }
 
+// Strided loop with kUnroll independent loads in flight per thread before the first store:
+// `ld(u)` returns the value of unit u, `st(u, v)` consumes it. One NVLink round trip then covers
+// kUnroll x 16 bytes per thread instead of 16.
+template <int kUnroll, class V, class LD, class ST>
+__device__ __forceinline__ void pipelined_loop(size_t first, size_t total, size_t stride, LD ld, ST st) {
+  size_t u = first;
+  for (; u + (kUnroll - 1) * stride < total; u += kUnroll * stride) {
+    V v[kUnroll];
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) v[k] = ld(u + k * stride);
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) st(u + k * stride, v[k]);
+  }
+  for (; u < total; u += stride) st(u, ld(u));
+}
+
 __device__ __forceinline__ int peer_of(const DeviceContext& ctx, int i) {  // i-th peer after me
   int r = ctx.rank + i;
   return r >= ctx.world ? r - ctx.world : r;
@@ -124,12 +140,13 @@ __global__ void __launch_bounds__(kThreads) all_gather_kernel(const __grid_const
   const int mode = a.block_n;  // 0 persistent, 1 partitioned
   if (a.use_mc) {
     uint8_t* dst = ctx.mc(out_mine);
-    for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (size_t)gridDim.x * blockDim.x) {
-      const size_t r = u / upr, c = u - r * upr;
-      if constexpr (UB == 16) {
-        const multimem::V4 v = *(const multimem::V4*)(a.in + r * in_pitch + c * 16);
-        multimem::st_v4(dst + r * out_pitch + c * 16, v);
-      }
+    if constexpr (UB == 16) {
+      pipelined_loop<8, uint4>((size_t)blockIdx.x * blockDim.x + threadIdx.x, total, (size_t)gridDim.x * blockDim.x,
+          [&](size_t u) { const size_t r = u / upr, c = u - r * upr; return *(const uint4*)(a.in + r * in_pitch + c * 16); },
+          [&](size_t u, uint4 v) {
+            const size_t r = u / upr, c = u - r * upr;
+            multimem::st_v4(dst + r * out_pitch + c * 16, multimem::V4{v.x, v.y, v.z, v.w});
+          });
     }
   } else if (mode == 1 && (int)gridDim.x >= W) {
     const int per = gridDim.x / W;
@@ -138,20 +155,20 @@ __global__ void __launch_bounds__(kThreads) all_gather_kernel(const __grid_const
       const int dst_rank = peer_of(ctx, d);
       uint8_t* dst = ctx.remote(out_mine, dst_rank);
       const int j = blockIdx.x - d * per;
-      for (size_t u = (size_t)j * blockDim.x + threadIdx.x; u < total; u += (size_t)per * blockDim.x) {
-        const size_t r = u / upr, c = u - r * upr;
-        *(U*)(dst + r * out_pitch + c * UB) = *(const U*)(a.in + r * in_pitch + c * UB);
-      }
+      pipelined_loop<8, U>((size_t)j * blockDim.x + threadIdx.x, total, (size_t)per * blockDim.x,
+          [&](size_t u) { const size_t r = u / upr, c = u - r * upr; return *(const U*)(a.in + r * in_pitch + c * UB); },
+          [&](size_t u, U v) { const size_t r = u / upr, c = u - r * upr; *(U*)(dst + r * out_pitch + c * UB) = v; });
     }
   } else {
-    for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (size_t)gridDim.x * blockDim.x) {
-      const size_t r = u / upr, c = u - r * upr;
-      const U v = *(const U*)(a.in + r * in_pitch + c * UB);
-      for (int i = 1; i <= W; ++i) {
-        const int dst_rank = peer_of(ctx, i == W ? 0 : i);
-        *(U*)(ctx.remote(out_mine, dst_rank) + r * out_pitch + c * UB) = v;
-      }
-    }
+    pipelined_loop<8, U>((size_t)blockIdx.x * blockDim.x + threadIdx.x, total, (size_t)gridDim.x * blockDim.x,
+        [&](size_t u) { const size_t r = u / upr, c = u - r * upr; return *(const U*)(a.in + r * in_pitch + c * UB); },
+        [&](size_t u, U v) {
+          const size_t r = u / upr, c = u - r * upr;
+          for (int i = 1; i <= W; ++i) {
+            const int dst_rank = peer_of(ctx, i == W ? 0 : i);
+            *(U*)(ctx.remote(out_mine, dst_rank) + r * out_pitch + c * UB) = v;
+          }
+        });
   }
   grid_exit_barrier(ctx, a.sb, e0, 1);
 }
@@ -177,10 +194,9 @@ __global__ void __launch_bounds__(kThreads) all_to_all_kernel(const __grid_const
     const uint8_t* src = a.in + (size_t)dst_rank * chunk_bytes;
     uint8_t* dst = ctx.remote(a.out, dst_rank) + (size_t)ctx.rank * chunk_bytes;
     const int j = blockIdx.x % per;
-    for (size_t u = (size_t)j * blockDim.x + threadIdx.x; u < total; u += (size_t)per * blockDim.x) {
-      const size_t r = u / upr, c = u - r * upr;
-      *(U*)(dst + r * out_pitch + c * UB) = *(const U*)(src + r * in_pitch + c * UB);
-    }
+    pipelined_loop<8, U>((size_t)j * blockDim.x + threadIdx.x, total, (size_t)per * blockDim.x,
+        [&](size_t u) { const size_t r = u / upr, c = u - r * upr; return *(const U*)(src + r * in_pitch + c * UB); },
+        [&](size_t u, U v) { const size_t r = u / upr, c = u - r * upr; *(U*)(dst + r * out_pitch + c * UB) = v; });
   }
   grid_exit_barrier(ctx, a.sb, e0, 1);
 }
@@ -294,7 +310,17 @@ __global__ void __launch_bounds__(kThreads) all_reduce_kernel(const __grid_const
   } else if (a.variant == kArTwoShot || a.variant == kArNvls) {
     // this rank owns the units [lo, hi); start the pulls at a CTA-dependent rank to spread load
     const size_t lo = total * ctx.rank / W, hi = total * (ctx.rank + 1) / W;
-    for (size_t u = lo + gtid; u < hi; u += gstride) {
+    bool nvls_done = false;
+    if constexpr (VEC > 1 && !std::is_same<T, int32_t>::value) {
+      if (a.variant == kArNvls) {
+        // reduce in the switch (one multimem.ld_reduce per 16 bytes, 4 in flight), broadcast back
+        pipelined_loop<4, UT>(lo + gtid, hi, gstride,
+            [&](size_t u) { return nvls_reduce<T, VEC>(ctx.mc((const uint8_t*)unit_ptr<T, VEC>(a.in, a.ld_in, upr, u))); },
+            [&](size_t u, UT r) { store_unit_everywhere<T, VEC>(a, u, upr, r); });
+        nvls_done = true;
+      }
+    }
+    for (size_t u = lo + gtid; u < hi && !nvls_done; u += gstride) {
       UT r;
       if constexpr (VEC > 1 && !std::is_same<T, int32_t>::value) {
         if (a.variant == kArNvls) {

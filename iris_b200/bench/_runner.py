@@ -117,10 +117,16 @@ def run_benchmarks(ctx, benchmarks, overrides, skips, n_warmup, n_repeat) -> lis
 
     results = []
     world = ctx.get_num_ranks()
+    # the heap is a bump allocator: take what outlives a point (the collectives' sync block) first,
+    # then rewind to this mark after every point
+    ctx.device_barrier()
+    ctx.sync_block(("ccl", None))
+    mark = ctx.heap_mark()
     for bdef in benchmarks:
         for params in combinations(bdef.axes, overrides, skips):
             if params.get("num_ranks", world) != world:
                 continue
+            ctx.heap_release(mark)
             state = State(params, n_warmup, n_repeat)
             try:
                 bdef.fn(state, ctx)

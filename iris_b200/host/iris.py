@@ -137,6 +137,19 @@ class Iris:
         _lib.check(self._klib().iris_device_barrier(C.byref(ctx), C.c_void_p(sb.data_ptr()), C.c_void_p(_lib.current_stream_ptr())),
                    "device barrier launch")
 
+    def heap_mark(self) -> int:
+        """Current bump offset of the heap; pass it to ``heap_release`` to free everything allocated since."""
+        return self.heap.get_offset()
+
+    def heap_release(self, mark: int) -> None:
+        """Rewind the heap to ``mark`` (collective: every rank must do the same, and no tensor
+        allocated after the mark may be used again). Cached kernel descriptors are dropped."""
+        self.barrier()
+        self.heap.set_offset(mark)
+        self._sync_blocks = {k: v for k, v in self._sync_blocks.items() if self.heap.offset_of(v) < mark}
+        self.ccl._desc_cache.clear()
+        self.barrier()
+
     def verify_symmetry(self) -> None:
         """Raise if the ranks' heaps have diverged (different allocation sequences): symmetric
         addressing is only valid when every rank allocated the same sizes in the same order."""
