@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(kThreads) all_to_all_kernel(const __grid_const
 }
 
 // ---- all_reduce ------------------------------------------------------------------------------
-enum ArVariant { kArAtomic = 0, kArRing = 1, kArOneShot = 2, kArTwoShot = 3, kArSpinlock = 4, kArNvls = 5 };
+enum ArVariant { kArAtomic = 0, kArRing = 1, kArOneShot = 2, kArTwoShot = 3, kArSpinlock = 4, kArNvls = 5, kArPush = 6 };
 
 template <class T, int VEC>
 __device__ __forceinline__ void reduce_unit_from_all(const CclArgs& a, size_t u, int upr, typename Acc<T>::type* acc, int start) {
@@ -446,6 +446,72 @@ __global__ void __launch_bounds__(kThreads) all_reduce_kernel(const __grid_const
   grid_exit_barrier(ctx, a.sb, e0, 1);
 }
 
+// ---- all_reduce, one-shot push (latency path) -------------------------------------------------
+// Every rank writes its whole (small) input into slot [rank] of every rank's staging area
+// (multimem.st with NVLS, else one store per peer), raises a per-(source, CTA) counter there with
+// release semantics, waits for the W counters of its own CTA index and sums the W slots locally.
+// One NVLink traversal end to end, no entry or exit round: staging and counters are
+// double-buffered by call parity, and seeing every source's counter in call k proves that all
+// ranks left call k-1. ring_buf = staging [2][W][cap units], flags = [2][W][kPushMaxCtas],
+// sb->aux[1] counts the calls.
+constexpr int kPushMaxCtas = 32;
+template <class T, int VEC>
+__global__ void __launch_bounds__(kThreads) all_reduce_push_kernel(const __grid_constant__ CclArgs a, size_t cap_units) {
+  using A = typename Acc<T>::type;
+  using UT = Unit<T, VEC>;
+  const DeviceContext& ctx = a.ctx;
+  const int W = ctx.world;
+  const int call = *(volatile int32_t*)&a.sb->aux[1];
+  const int par = call & 1;
+  const int32_t tag = (call >> 1) + 1;
+  const int upr = a.N / VEC;
+  const size_t total = (size_t)a.M * upr;
+  const size_t per = (total + gridDim.x - 1) / gridDim.x;
+  const size_t lo = min(total, (size_t)blockIdx.x * per), hi = min(total, lo + per);
+  UT* stage = (UT*)a.ring_buf + (size_t)par * W * cap_units;
+  UT* mine = stage + (size_t)ctx.rank * cap_units;
+  for (size_t u = lo + threadIdx.x; u < hi; u += blockDim.x) {
+    const UT v = *unit_ptr<T, VEC>(a.in, a.ld_in, upr, u);
+    bool sent = false;
+    if constexpr (VEC > 1) {
+      if (a.use_mc) {
+        multimem::st_v4(ctx.mc((uint8_t*)(mine + u)), multimem::V4{v.raw.x, v.raw.y, v.raw.z, v.raw.w});
+        sent = true;
+      }
+    }
+    if (!sent)
+      for (int i = 0; i < W; ++i) *ctx.remote(mine + u, peer_of(ctx, i)) = v;
+  }
+  __syncthreads();
+  int32_t* my_flag = a.flags + ((size_t)par * W + ctx.rank) * kPushMaxCtas + blockIdx.x;
+  __shared__ int s_ok;
+  if (threadIdx.x < 32) {
+    for (int r = threadIdx.x; r < W; r += 32) red_release_sys_add(ctx.remote(my_flag, r), 1);
+    bool ok = true;
+    for (int r = threadIdx.x; r < W; r += 32)
+      ok = wait_flag_ge(ctx, a.flags + ((size_t)par * W + r) * kPushMaxCtas + blockIdx.x, tag) && ok;
+    ok = __all_sync(0xffffffffu, ok);
+    if (threadIdx.x == 0) s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_ok) {
+    for (size_t u = lo + threadIdx.x; u < hi; u += blockDim.x) {
+      A acc[VEC] = {};
+      for (int r = 0; r < W; ++r) load_unit_cv(stage + (size_t)r * cap_units + u).accumulate(acc);
+      *unit_ptr<T, VEC>(a.out, a.ld_out, upr, u) = UT::pack(acc);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&a.sb->aux[2], 1) == (int)gridDim.x - 1) {
+      a.sb->aux[2] = 0;
+      a.sb->aux[1] = call + 1;
+      __threadfence();
+    }
+  }
+}
+
 // ---- reduce_scatter --------------------------------------------------------------------------
 // Tile ownership as in the reference (iris/ccl/triton/reduce_scatter.py:55-70): tiles are numbered
 // row-major over (ceil(M/BM), ceil(N/BN)); distribution 0 = strided (tile % W == rank),
@@ -464,21 +530,31 @@ __global__ void __launch_bounds__(kThreads) reduce_scatter_kernel(const __grid_c
     const int rows = a.M / W;
     const size_t total = (size_t)rows * upr;
     const size_t base = (size_t)ctx.rank * rows * upr;
-    for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (size_t)gridDim.x * blockDim.x) {
-      UT r;
-      bool done = false;
-      if constexpr (VEC > 1 && !std::is_same<T, int32_t>::value) {
-        if (a.use_mc) {
-          r = nvls_reduce<T, VEC>(ctx.mc((const uint8_t*)unit_ptr<T, VEC>(a.in, a.ld_in, upr, base + u)));
-          done = true;
-        }
+    const size_t first = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
+    bool done = false;
+    if constexpr (VEC > 1 && !std::is_same<T, int32_t>::value) {
+      if (a.use_mc) {
+        pipelined_loop<4, UT>(first, total, stride,
+            [&](size_t u) { return nvls_reduce<T, VEC>(ctx.mc((const uint8_t*)unit_ptr<T, VEC>(a.in, a.ld_in, upr, base + u))); },
+            [&](size_t u, UT r) { *unit_ptr<T, VEC>(a.out, a.ld_out, upr, u) = r; });
+        done = true;
       }
-      if (!done) {
+    }
+    if (!done) {
+      // two units per thread and step: 2 x W independent peer loads in flight
+      size_t u = first;
+      for (; u + stride < total; u += 2 * stride) {
+        A acc0[VEC] = {}, acc1[VEC] = {};
+        reduce_unit_from_all<T, VEC>(a, base + u, upr, acc0, ctx.rank + blockIdx.x);
+        reduce_unit_from_all<T, VEC>(a, base + u + stride, upr, acc1, ctx.rank + blockIdx.x);
+        *unit_ptr<T, VEC>(a.out, a.ld_out, upr, u) = UT::pack(acc0);
+        *unit_ptr<T, VEC>(a.out, a.ld_out, upr, u + stride) = UT::pack(acc1);
+      }
+      for (; u < total; u += stride) {
         A acc[VEC] = {};
         reduce_unit_from_all<T, VEC>(a, base + u, upr, acc, ctx.rank + blockIdx.x);
-        r = UT::pack(acc);
+        *unit_ptr<T, VEC>(a.out, a.ld_out, upr, u) = UT::pack(acc);
       }
-      *unit_ptr<T, VEC>(a.out, a.ld_out, upr, u) = r;
     }
   } else {
     const int tiles_m = (a.M + a.block_m - 1) / a.block_m, tiles_n = (a.N + a.block_n - 1) / a.block_n;
@@ -606,6 +682,30 @@ int iris_ccl_launch(int op, const IrisCclDesc* d, void* stream) {
   if (!vec) a.use_mc = 0;
   if (op == 2 && d->variant == kArNvls && !a.use_mc) a.variant = kArTwoShot;
   if (op == 2 && W == 1) a.variant = kArOneShot;   // a single rank: every variant is a local copy
+  if (op == 2 && a.variant == kArPush) {
+    // d->block_m carries the staging capacity in bytes per (parity, source)
+    const size_t bytes = (size_t)d->M * d->N * es;
+    const size_t unit = vec ? 16 : es;
+    if (bytes > (size_t)d->block_m * (size_t)1024 || !d->ring_buf || !d->flags) return -6;
+    int g = (int)((bytes / unit + 1023) / 1024);
+    if (g < 1) g = 1;
+    if (g > kPushMaxCtas) g = kPushMaxCtas;
+    const size_t cap_units = (size_t)d->block_m * 1024 / unit;
+#define IRIS_PUSH(T)                                                                           \
+    do {                                                                                         \
+      if (vec) all_reduce_push_kernel<T, 16 / sizeof(T)><<<g, kThreads, 0, s>>>(a, cap_units);   \
+      else all_reduce_push_kernel<T, 1><<<g, kThreads, 0, s>>>(a, cap_units);                    \
+    } while (0)
+    switch (d->dtype) {
+      case IRIS_F16: IRIS_PUSH(__half); break;
+      case IRIS_BF16: IRIS_PUSH(__nv_bfloat16); break;
+      case IRIS_F32: IRIS_PUSH(float); break;
+      case IRIS_I32: IRIS_PUSH(int32_t); break;
+      default: return -2;
+    }
+#undef IRIS_PUSH
+    return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  }
   int grid = grid_for(d, (size_t)d->M * d->N * es);
   if (op == 2 && a.variant == kArRing) {
     grid = d->comm_sms > 0 ? d->comm_sms : 32;  // must match the flag layout chosen by the host

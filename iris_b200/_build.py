@@ -149,8 +149,10 @@ def build_user_kernel(src: Path, out: Path, verbose: bool = False) -> Path:
         if verbose:
             print(f"[iris_b200 build] nvcc {src.name} -> {out.name}", flush=True)
         out.parent.mkdir(parents=True, exist_ok=True)
-        _run([_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", "-shared", "-cudart", "static", str(src), "-o", str(out)],
-             log=out.with_suffix(".ptxas.log"))
+        tmp = out.with_name(out.name + f".tmp{os.getpid()}")     # ranks may compile the same file at once
+        _run([_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", "-shared", "-cudart", "static", str(src), "-o", str(tmp)],
+             log=out.with_suffix(f".ptxas{os.getpid()}.log"))
+        os.replace(tmp, out)
         _stamp(out, key)
     return out
 

@@ -22,7 +22,8 @@ from .utils import ReduceOp
 
 __all__ = ["Config", "ReduceOp", "CCL", "AllReduceWorkspace"]
 
-_AR_CODE = {"atomic": 0, "ring": 1, "one_shot": 2, "two_shot": 3, "spinlock": 4, "nvls": 5}
+_AR_CODE = {"atomic": 0, "ring": 1, "one_shot": 2, "two_shot": 3, "spinlock": 4, "nvls": 5, "push": 6}
+PUSH_CAP_KB = 512          # largest message of the one-shot push path (bytes / 1024)
 
 
 class IrisCclDesc(C.Structure):
@@ -71,6 +72,7 @@ class CCL:
     def __init__(self, ctx):
         self.ctx = ctx
         self._desc_cache: dict = {}
+        self._push_ws = None
 
     # ------------------------------------------------------------------ plumbing
     def _lib(self):
@@ -178,11 +180,15 @@ class CCL:
         nvls_ok = config.use_multicast and group is None and self.ctx.has_multicast() and dtype != torch.int32
         if v == "nvls" and not nvls_ok:
             return "two_shot"
+        if v == "push" and (nbytes > PUSH_CAP_KB * 1024 or group is not None):
+            return "two_shot"
         if v != "auto":
             return v
         # Every rank pulling everything (one_shot) is one round trip but W x the traffic: best while
         # the message is latency bound. Beyond that the owner-reduces schemes win, in the switch
         # when NVLS is available.
+        if nbytes <= PUSH_CAP_KB * 1024 and group is None:
+            return "push"           # one NVLink traversal, no barrier rounds
         if nbytes <= 256 * 1024:
             return "one_shot"
         return "nvls" if nvls_ok else "two_shot"
@@ -205,6 +211,13 @@ class CCL:
                     ws.flags = ctx.zeros(2 * (W - 1) * ws.ring_ctas, dtype=torch.int32)
                     ws.sync_block = ctx.zeros(80, dtype=torch.int32)
                     ctx.barrier()
+                elif variant == "push":
+                    if self._push_ws is None:
+                        cap = PUSH_CAP_KB * 1024
+                        self._push_ws = (ctx.heap.allocate(2 * W * cap, torch.uint8), ctx.zeros(2 * W * 32, dtype=torch.int32),
+                                         ctx.zeros(80, dtype=torch.int32))
+                        ctx.barrier()
+                    ws.ring_buffer, ws.flags, ws.sync_block = self._push_ws
                 elif variant == "spinlock":
                     nseg = -(-out.numel() // 256) + 1
                     ws.flags = ctx.zeros(2 * nseg, dtype=torch.int32)
@@ -243,6 +256,11 @@ class CCL:
                 d.ring_buf = ws.ring_buffer.data_ptr()
                 d.flags = ws.flags.data_ptr()
                 d.comm_sms = ws.ring_ctas
+            elif ws.variant == "push":
+                d.sync_block = ws.sync_block.data_ptr()
+                d.ring_buf = ws.ring_buffer.data_ptr()
+                d.flags = ws.flags.data_ptr()
+                d.block_m = PUSH_CAP_KB
             elif ws.variant == "spinlock":
                 d.flags = ws.flags.data_ptr()
             self._launch(2, d)

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-ALL_REDUCE_VARIANTS = ("auto", "atomic", "ring", "two_shot", "one_shot", "spinlock", "nvls")
+ALL_REDUCE_VARIANTS = ("auto", "atomic", "ring", "two_shot", "one_shot", "spinlock", "nvls", "push")
 ALL_GATHER_VARIANTS = ("persistent", "partitioned")
 
 

@@ -148,6 +148,8 @@ class Iris:
         self.heap.set_offset(mark)
         self._sync_blocks = {k: v for k, v in self._sync_blocks.items() if self.heap.offset_of(v) < mark}
         self.ccl._desc_cache.clear()
+        if self.ccl._push_ws is not None and self.heap.offset_of(self.ccl._push_ws[0]) >= mark:
+            self.ccl._push_ws = None
         self.barrier()
 
     def verify_symmetry(self) -> None:

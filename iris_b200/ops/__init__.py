@@ -81,6 +81,28 @@ def _make_workspace(ctx, operation, shape, dtype, variant, d) -> FusedWorkspace 
     return ws
 
 
+def _cached_desc(ws, key, build):
+    """Descriptor of a repeated call (same buffers): built once, then reused from the workspace."""
+    cache = ws.extra.setdefault("desc", {})
+    hit = cache.get(key)
+    if hit is None:
+        if len(cache) > 64:
+            cache.clear()
+        hit = cache[key] = build()
+    return hit
+
+
+def _with_bias(bias, build):
+    """Run ``build(bias_fp32)`` and keep the converted bias alive next to the descriptor it is baked into."""
+    b32 = _bias32(bias)
+    d, keep = build(b32)
+    return d, (keep, b32)
+
+
+def _ptr_key(*tensors):
+    return tuple((t.data_ptr(), t.stride(0)) if t is not None else None for t in tensors)
+
+
 def _launch(ctx, d, ws) -> None:
     d.sync_block = ws.sync_block.data_ptr()
     d.inbox = ws.inbox.data_ptr() if ws.inbox is not None else None
@@ -168,9 +190,9 @@ def all_gather_matmul(shmem, output_tensor, A_sharded, B, bias=None, async_op=Fa
         gathered = _unfused_gather(shmem, A_sharded, shard_dim)
         output_tensor.copy_(_local_matmul(gathered, B, bias, bias_dim=0))
     else:
-        d, keep = _agm_desc(shmem, output_tensor, A_sharded, B, _bias32(bias), config, shard_dim)
+        d, keep = _cached_desc(ws, _ptr_key(output_tensor, A_sharded, B, bias) + (id(shmem._ctx_epoch),),
+                               lambda: _with_bias(bias, lambda b32: _agm_desc(shmem, output_tensor, A_sharded, B, b32, config, shard_dim)))
         _launch(shmem, d, ws)
-        del keep
     _finish(shmem, async_op)
     return ws
 
@@ -235,9 +257,9 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
                 output_tensor.copy_(dst)
     else:
         op = _lib.GEMM_ALL_SCATTER if scatter_cols else _lib.GEMM_ALL_GATHER
-        d, keep = _base_desc(shmem, op, M, N, K, A, B, output_tensor, config, bias_row=_bias32(bias))
+        d, keep = _cached_desc(ws, _ptr_key(output_tensor, A, B, bias) + (id(shmem._ctx_epoch),),
+                               lambda: _with_bias(bias, lambda b32: _base_desc(shmem, op, M, N, K, A, B, output_tensor, config, bias_row=b32)))
         _launch(shmem, d, ws)
-        del keep
     _finish(shmem, async_op)
     return ws
 
@@ -276,9 +298,9 @@ def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, con
         if dst is not output_tensor:
             output_tensor.copy_(dst)
     else:
-        d, keep = _base_desc(shmem, _lib.GEMM_ALL_REDUCE, M, N, K, A, B, output_tensor, config, bias_row=_bias32(b))
+        d, keep = _cached_desc(ws, _ptr_key(output_tensor, A, B, b) + (id(shmem._ctx_epoch),),
+                               lambda: _with_bias(b, lambda b32: _base_desc(shmem, _lib.GEMM_ALL_REDUCE, M, N, K, A, B, output_tensor, config, bias_row=b32)))
         _launch(shmem, d, ws)
-        del keep
     _finish(shmem, async_op)
     return ws
 
@@ -346,9 +368,9 @@ def matmul_reduce_scatter(shmem, output_tensor, A, B, bias=None, async_op=False,
             ws.bn = bn
     else:
         op = _lib.GEMM_REDUCE_SCATTER if scatter_rows else _lib.GEMM_RS_TILES
-        d, keep = _base_desc(shmem, op, M, N, K, A, B, output_tensor, config, bias_row=_bias32(b))
+        d, keep = _cached_desc(ws, _ptr_key(output_tensor, A, B, b) + (id(shmem._ctx_epoch),),
+                               lambda: _with_bias(b, lambda b32: _base_desc(shmem, op, M, N, K, A, B, output_tensor, config, bias_row=b32)))
         _launch(shmem, d, ws)
-        del keep
     _finish(shmem, async_op)
     return ws
 

@@ -97,7 +97,7 @@ def _ccl(rank, world, nvls):
             n = N // world
             exp = torch.cat([gathered[s][:, rank * n:(rank + 1) * n] for s in range(world)], 1)
             assert torch.equal(o2, exp)
-        for v in ("one_shot", "two_shot", "atomic", "ring", "spinlock", "auto", "nvls"):
+        for v in ("one_shot", "two_shot", "atomic", "ring", "spinlock", "auto", "nvls", "push"):
             o3 = ctx.zeros((M, N), dtype=dtype)
             ctx.barrier()
             ws = None
@@ -339,3 +339,72 @@ def _ring(rank, world):
 
 def test_ring_attention_between_gpus():
     run_ranks(_ring, _world(), backend="nccl")
+
+
+def _tiles(rank, world):
+    import os
+
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200 import jit
+
+    ctx = iris.iris(1 << 28)
+    here = os.path.dirname(os.path.abspath(__file__))
+    mod = jit.compile_file(os.path.join(here, "kernels", "user_kernels.cu"))
+    call = mod.fn("tile_collective")
+    M, N, bm, bn = 96, 64 * world, 32, 32
+    g = torch.Generator(device="cuda")
+    g.manual_seed(77 + rank)
+    src = ctx.zeros((M, N), dtype=torch.float32)
+    src.copy_(torch.randn(M, N, device="cuda", generator=g))
+    parts = [torch.empty_like(src) for _ in range(world)]
+    dist.all_gather(parts, src)
+    total = torch.stack(parts).sum(0)
+    tiles_n = N // bn
+    tiles = (M // bm) * tiles_n
+    ready = 0
+    for op in (0, 1, 2, 3, 7):                      # the reductions
+        dst = ctx.zeros((M, N), dtype=torch.float32)
+        locks = ctx.zeros(tiles, dtype=torch.int32)
+        ctx.barrier()
+        ready = 1
+        call(ctx, op, src, dst, locks, M, N, M, N, bm, bn, 0, ready)
+        ctx.barrier()
+        if op in (0, 1, 2, 3):
+            if op == 3 or op == 2 or op in (0, 1):
+                assert torch.allclose(dst, total, atol=1e-4), op
+        else:                                       # reduce_scatter: contiguous tile blocks, last rank takes the rest
+            per = max(tiles // world, 1)
+            lo = min(rank * per, tiles)
+            hi = tiles if rank == world - 1 else min(lo + per, tiles)
+            exp = torch.zeros_like(total)
+            for t in range(lo, hi):
+                tm, tn = divmod(t, tiles_n)
+                exp[tm * bm:(tm + 1) * bm, tn * bn:(tn + 1) * bn] = total[tm * bm:(tm + 1) * bm, tn * bn:(tn + 1) * bn]
+            assert torch.allclose(dst, exp, atol=1e-4)
+    # all_gather along rows, gather from the next rank, all_to_all of column chunks
+    ag = ctx.zeros((world * M, N), dtype=torch.float32)
+    locks = ctx.zeros(tiles, dtype=torch.int32)
+    ctx.barrier()
+    call(ctx, 4, src, ag, locks, M, N, world * M, N, bm, bn, 0, 1)
+    ctx.barrier()
+    assert torch.equal(ag, torch.cat(parts))
+    got = ctx.zeros((M, N), dtype=torch.float32)
+    nxt = (rank + 1) % world
+    call(ctx, 5, src, got, locks, M, N, M, N, bm, bn, nxt, 1)
+    torch.cuda.synchronize()
+    assert torch.equal(got, parts[nxt])
+    a2a = ctx.zeros((M, N), dtype=torch.float32)
+    ctx.barrier()
+    n = N // world
+    call(ctx, 6, src, a2a, locks, M, N, M, N, bm, bn, n, 1)
+    ctx.barrier()
+    exp = torch.cat([parts[s][:, rank * n:(rank + 1) * n] for s in range(world)], 1)
+    assert torch.equal(a2a, exp)
+    ctx.check()
+    ctx.barrier()
+
+
+def test_tile_collectives_between_gpus():
+    run_ranks(_tiles, _world(), backend="nccl")

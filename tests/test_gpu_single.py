@@ -187,7 +187,7 @@ def test_collectives_world1(ctx, dtype):
     inp = ctx.empty((M, N), dtype=dtype)
     inp.copy_(torch.rand(M, N, device="cuda") * 2 - 1)
     out = ctx.zeros((M, N), dtype=dtype)
-    for v in ("one_shot", "two_shot", "atomic", "ring", "spinlock", "auto"):
+    for v in ("one_shot", "two_shot", "atomic", "ring", "spinlock", "auto", "push"):
         out.zero_()
         ctx.ccl.all_reduce(out, inp, config=Config(all_reduce_variant=v))
         assert torch.equal(out, inp), v
@@ -295,4 +295,44 @@ def test_ring_attention_world1(ctx, S, Hq, Hkv, causal):
         out = layer(q, k, v, causal=causal)
     ref = reference_attention(q, k, v, causal)
     assert (out.float() - ref).abs().max().item() < 2e-2
+    ctx.check()
+
+
+@pytest.fixture(scope="module")
+def user_module():
+    from iris_b200 import jit
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    return jit.compile_file(os.path.join(here, "kernels", "user_kernels.cu"))
+
+
+def test_user_kernels_functional_and_oo_api(ctx, user_module):
+    buf = ctx.zeros(4096, dtype=torch.float32)
+    user_module.fn("store_blocks")(ctx, buf, 3000, 2.5, 0)
+    torch.cuda.synchronize()
+    assert torch.all(buf[:3000] == 2.5) and torch.all(buf[3000:] == 0)      # mask: lanes past n do nothing
+    src = ctx.arange(0, 512, dtype=torch.int32)
+    out = torch.zeros(512, dtype=torch.int32, device="cuda")
+    user_module.fn("masked_load")(ctx.get_device_context(), src, out, 512, 300, 0)   # context built from the int64 tensor
+    torch.cuda.synchronize()
+    assert torch.equal(out[:300], src[:300]) and torch.all(out[300:] == -7)  # `other` for masked lanes
+    counter = ctx.zeros(1, dtype=torch.int32)
+    user_module.fn("count")(ctx, counter, 256, 0)
+    torch.cuda.synchronize()
+    assert int(counter.item()) == 256
+
+
+@pytest.mark.parametrize("op", [0, 1, 2, 3, 4, 5, 6, 7])
+def test_tile_collectives_world1(ctx, user_module, op):
+    M, N, bm, bn = 100, 72, 32, 16
+    torch.manual_seed(op)
+    src = ctx.zeros((M, N), dtype=torch.float32)
+    src.copy_(torch.randn(M, N, device="cuda"))
+    dst = ctx.zeros((M, N), dtype=torch.float32)
+    tiles = -(-M // bm) * -(-N // bn)
+    locks = ctx.zeros(tiles, dtype=torch.int32)
+    arg = N if op == 6 else 0
+    user_module.fn("tile_collective")(ctx, op, src, dst, locks, M, N, M, N, bm, bn, arg, 1)
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src), op          # with one rank every collective is the identity
     ctx.check()
