@@ -349,3 +349,24 @@ def _ring_cpu(rank, world):
 
 def test_ring_attention_cpu_world2():
     run_ranks(_ring_cpu, 2)
+
+
+def test_kernel_artifacts_parse(tmp_path):
+    from iris_b200.host import artifacts
+
+    text = """ptxas info    : Compiling entry function '_Z3fooPf' for 'sm_100a'
+ptxas info    : Function properties for _Z3fooPf
+    32 bytes stack frame, 36 bytes spill stores, 40 bytes spill loads
+ptxas info    : Used 255 registers, used 1 barriers, 32 bytes cumulative stack size, 128 bytes smem
+ptxas info    : Compiling entry function '_Z3barv' for 'sm_100a'
+    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads
+ptxas info    : Used 18 registers, used 0 barriers
+"""
+    ks = artifacts.parse_ptxas_log(text)
+    assert [k["name"] for k in ks] == ["_Z3fooPf", "_Z3barv"]
+    assert ks[0]["registers"] == 255 and ks[0]["spill_stores"] == 36 and ks[0]["smem_bytes"] == 128
+    assert ks[1]["registers"] == 18 and ks[1]["spill_loads"] == 0
+    meta = artifacts.collect()
+    if meta:                                  # a build has run in this tree
+        out = artifacts.export(tmp_path)
+        assert any((out / name.replace(".cu", "") / "metadata.json").exists() for name in meta)
