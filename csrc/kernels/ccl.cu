@@ -449,7 +449,8 @@ __global__ void __launch_bounds__(kThreads) all_reduce_kernel(const __grid_const
 // ---- all_reduce, one-shot push (latency path) -------------------------------------------------
 // Every rank writes its whole (small) input into slot [rank] of every rank's staging area
 // (multimem.st with NVLS, else one store per peer), raises a per-(source, CTA) counter there with
-// release semantics, waits for the W counters of its own CTA index and sums the W slots locally.
+// release semantics (the counter is set to the call number), waits for the W counters of its own
+// CTA index and sums the W slots locally.
 // One NVLink traversal end to end, no entry or exit round: staging and counters are
 // double-buffered by call parity, and seeing every source's counter in call k proves that all
 // ranks left call k-1. ring_buf = staging [2][W][cap units], flags = [2][W][kPushMaxCtas],
@@ -486,7 +487,9 @@ __global__ void __launch_bounds__(kThreads) all_reduce_push_kernel(const __grid_
   int32_t* my_flag = a.flags + ((size_t)par * W + ctx.rank) * kPushMaxCtas + blockIdx.x;
   __shared__ int s_ok;
   if (threadIdx.x < 32) {
-    for (int r = threadIdx.x; r < W; r += 32) red_release_sys_add(ctx.remote(my_flag, r), 1);
+    // the flag carries the call number (one writer per flag), so CTA indices that were idle in
+    // earlier, smaller calls need no catching up
+    for (int r = threadIdx.x; r < W; r += 32) { fence_sys(); st_release_sys(ctx.remote(my_flag, r), tag); }
     bool ok = true;
     for (int r = threadIdx.x; r < W; r += 32)
       ok = wait_flag_ge(ctx, a.flags + ((size_t)par * W + r) * kPushMaxCtas + blockIdx.x, tag) && ok;

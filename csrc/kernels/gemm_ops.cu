@@ -23,6 +23,7 @@ using namespace iris;
 using namespace iris::gemm;
 
 #include "gemm_host.cuh"
+#include "iris/gemm/sm100_mainloop_pair.cuh"
 
 namespace {
 
@@ -584,6 +585,18 @@ int choose_bn(int M, int N, int ctas, bool mn_major) {
   return best_bn;
 }
 
+template <class Cfg, class Policy>
+int launch_pair(const Policy& pol, int grid, cudaStream_t stream) {
+  auto kern = gemm_pair_kernel<Cfg, Policy>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -20;
+    attr_set = true;
+  }
+  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(pol);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
 template <class Policy>
 int dispatch(const Policy& pol, int bn, bool kmajor, int grid, cudaStream_t stream) {
   if (kmajor) {
@@ -709,6 +722,17 @@ extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
     r = fill_common(pol, d, p.bn, p.gemm_ctas, d->A, d->M, d->K, d->lda);
     if (r) return r;
     pol.C = (uint8_t*)d->C; pol.ldc = d->ldc;
+    if (d->two_sm == 2 && p.bn == 256) {
+      // two-SM tiles: pairs of CTAs share a 256 x 256 tile (tcgen05 cta_group::2)
+      pol.tiles_m = ceil_div(d->M, 2 * kBM);
+      make_map(&pol.tmB, d->B, d->dtype, d->b_kmajor ? d->N : d->K, d->b_kmajor ? d->K : d->N, d->ldb, 64, d->b_kmajor ? 128 : 64);
+      int pairs = pol.tiles_m * pol.tiles_n;
+      int g = sm_count() / 2 * 2;
+      if (2 * pairs < g) g = 2 * pairs;
+      pol.n_gemm_ctas = g;
+      if (d->b_kmajor) return launch_pair<PairConfig<256, true, 6>>(pol, g, stream);
+      return launch_pair<PairConfig<256, false, 6>>(pol, g, stream);
+    }
     const int tiles = pol.tiles_m * pol.tiles_n;
     return dispatch(pol, p.bn, d->b_kmajor != 0, tiles < grid ? tiles : grid, stream);
   }

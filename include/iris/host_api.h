@@ -50,7 +50,7 @@ typedef struct IrisGemmDesc {
   int32_t gemm_ctas;      // 0 = all SMs minus comm_ctas
   int32_t comm_ctas;      // CTAs that only move data (AG_M / AG_K), 0 = default
   int32_t use_mc;         // use the NVLS multicast window when the context has one
-  int32_t reserved;
+  int32_t two_sm;         // 2: pairs of CTAs share 256-row tiles (tcgen05 cta_group::2), local GEMM only
   const void* A; int64_t lda;
   const void* B; int64_t ldb;
   void* C; int64_t ldc;

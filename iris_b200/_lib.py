@@ -50,7 +50,7 @@ class IrisGemmDesc(C.Structure):
         ("gemm_ctas", C.c_int32),
         ("comm_ctas", C.c_int32),
         ("use_mc", C.c_int32),
-        ("reserved", C.c_int32),
+        ("two_sm", C.c_int32),
         ("A", C.c_void_p), ("lda", C.c_int64),
         ("B", C.c_void_p), ("ldb", C.c_int64),
         ("C", C.c_void_p), ("ldc", C.c_int64),

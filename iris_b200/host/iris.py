@@ -59,7 +59,7 @@ class Iris:
         self.device = self.heap.device
         self.heap_size = heap_size
         self.is_cpu = self.heap.kind == KIND_CPU
-        self.timeout_ms = int(os.environ.get("IRIS_TIMEOUT_MS", "10000"))
+        self.timeout_ms = int(os.environ.get("IRIS_TIMEOUT_MS", "5000"))
         # status word + sync block of the context itself (barrier) + per-purpose sync blocks
         self._status = self.heap.allocate(1, torch.int32)
         self._status.zero_()

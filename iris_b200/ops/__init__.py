@@ -77,6 +77,8 @@ def _make_workspace(ctx, operation, shape, dtype, variant, d) -> FusedWorkspace 
         ws.staging = ctx.heap.allocate(staging, torch.uint8)
         ws.aux_buffer = ws.staging
     ws.prepared = True
+    # arrival counters count communication CTAs: the number used at creation is part of the workspace
+    ws.extra["comm_ctas"] = d.comm_ctas
     ctx.barrier()
     return ws
 
@@ -109,6 +111,7 @@ def _launch(ctx, d, ws) -> None:
     d.flags = ws.flags.data_ptr() if ws.flags is not None else None
     d.staging = ws.staging.data_ptr() if ws.staging is not None else None
     d.bn = ws.bn
+    d.comm_ctas = ws.extra.get("comm_ctas", d.comm_ctas)
     tl = ws.extra.get("timeline")
     d.timeline = tl.data_ptr() if tl is not None else None
     _lib.check(_lib.kernels().iris_gemm_launch(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), f"{ws.operation} launch")
