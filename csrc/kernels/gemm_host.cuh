@@ -25,7 +25,9 @@ struct Common {
   CUtensorMap tmA;
   CUtensorMap tmB;
   Shape sh;
-  int tiles_m, tiles_n, group_m;
+  int tiles_m, tiles_n, group_m;   // tiles_m counts 128-row tiles
+  int pair;                        // 1: CTA pairs walk 256-row tiles (order_m = tiles_m / 2)
+  int order_m;                     // row tiles in the unit the tile order walks
   int n_gemm_ctas;
   int bf16;
   int bn;
@@ -39,7 +41,7 @@ struct Common {
   }
   IRIS_D Shape shape() const { return sh; }
   IRIS_D int gemm_ctas() const { return n_gemm_ctas; }
-  IRIS_D int num_tiles() const { return tiles_m * tiles_n; }
+  IRIS_D int num_tiles() const { return order_m * tiles_n; }
   IRIS_D const CUtensorMap* b_map() const { return &tmB; }
   IRIS_D bool is_bf16() const { return bf16 != 0; }
   IRIS_D bool has_bias() const { return bias_row != nullptr || bias_col != nullptr; }
@@ -92,7 +94,9 @@ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 template <class Cfg, class Policy>
 int launch(const Policy& pol, int grid, cudaStream_t stream) {
-  auto kern = gemm_kernel<Cfg, Policy>;
+  void (*kern)(const Policy);
+  if constexpr (Cfg::kPair) kern = gemm_pair_kernel<Cfg, Policy>;
+  else kern = gemm_kernel<Cfg, Policy>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);

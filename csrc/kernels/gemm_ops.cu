@@ -23,7 +23,6 @@ using namespace iris;
 using namespace iris::gemm;
 
 #include "gemm_host.cuh"
-#include "iris/gemm/sm100_mainloop_pair.cuh"
 
 namespace {
 
@@ -32,7 +31,7 @@ struct LocalGemm : Common {
   uint8_t* C;
   int64_t ldc;
   struct State {};
-  IRIS_D void tile(int t, int& tm, int& tn) const { swizzled_tile(t, tiles_m, tiles_n, group_m, tm, tn); }
+  IRIS_D void tile(int t, int& tm, int& tn) const { swizzled_tile(t, order_m, tiles_n, group_m, tm, tn); }
   IRIS_D bool a_source(State&, int tm, int kb, ASource& s) const {
     s.map = &tmA; s.x = kb * kBK; s.y = tm * kBM; s.bk = kb * kBK;
     return true;
@@ -96,11 +95,12 @@ struct AllGatherGemm : Common {
   // source's last chunk.
   IRIS_D void tile(int t, int& tm, int& tn) const {
     if (mode == 0) {
-      const int per_src = chunks * tiles_n;
+      const int oc = chunks >> pair;          // row tiles per source in tile-order units
+      const int per_src = oc * tiles_n;
       if (t < per_src || ctx.world == 1) {
         int lm, ln;
-        swizzled_tile(t, chunks, tiles_n, group_m, lm, ln);
-        tm = ctx.rank * chunks + lm;
+        swizzled_tile(t, oc, tiles_n, group_m, lm, ln);
+        tm = ctx.rank * oc + lm;
         tn = ln;
         return;
       }
@@ -109,10 +109,10 @@ struct AllGatherGemm : Common {
       const int c = u / per_chunk;
       const int v = u - c * per_chunk;
       const int si = v / tiles_n;
-      tm = src_of_group(si + 1) * chunks + c;
+      tm = src_of_group(si + 1) * oc + c;
       tn = v - si * tiles_n;
     } else {
-      swizzled_tile(t, tiles_m, tiles_n, group_m, tm, tn);
+      swizzled_tile(t, order_m, tiles_n, group_m, tm, tn);
     }
   }
   // Select the map / row of (source, chunk) and make sure the chunk has arrived. The divisions
@@ -374,10 +374,11 @@ struct ScatterGemmT : Common {
   IRIS_D size_t slot_bytes() const { return (size_t)kBM * bn * 2; }
   IRIS_D int total_tiles() const { return tiles_m * tiles_n; }
   // tiles owned by rank o
+  // (in the unit the tile order walks: 256-row tiles for CTA pairs)
   IRIS_D int owned_count(int o) const {
+    if (mode == IRIS_GEMM_REDUCE_SCATTER) return (tiles_m_per_rank >> pair) * tiles_n;
+    if (mode == IRIS_GEMM_ALL_REDUCE) return (order_m * tiles_n - o + ctx.world - 1) / ctx.world;
     const int T = total_tiles();
-    if (mode == IRIS_GEMM_REDUCE_SCATTER) return tiles_m_per_rank * tiles_n;
-    if (mode == IRIS_GEMM_ALL_REDUCE) return (T - o + ctx.world - 1) / ctx.world;
     if (o == ctx.world - 1) return max(0, T - tiles_per_rank * (ctx.world - 1));
     return min(tiles_per_rank, max(0, T - tiles_per_rank * o));
   }
@@ -387,9 +388,10 @@ struct ScatterGemmT : Common {
       owner = tm / tiles_m_per_rank;
       lt = (tm - owner * tiles_m_per_rank) * tiles_n + tn;
     } else if (mode == IRIS_GEMM_ALL_REDUCE) {
-      const int t = tm * tiles_n + tn;
+      // round-robin over the tiles the order walks; both 128-row halves of a pair tile share an owner
+      const int t = (tm >> pair) * tiles_n + tn;
       owner = t % ctx.world;
-      lt = t / ctx.world;
+      lt = pair ? (t / ctx.world) * 2 + (tm & 1) : t / ctx.world;
     } else {  // RS_TILES: contiguous blocks, last rank takes the remainder
       const int t = tm * tiles_n + tn;
       owner = min(t / tiles_per_rank, ctx.world - 1);
@@ -401,7 +403,7 @@ struct ScatterGemmT : Common {
   // has long been delivered.
   IRIS_D void tile(int t, int& tm, int& tn) const {
     if (!reducing()) {
-      swizzled_tile(t, tiles_m, tiles_n, group_m, tm, tn);
+      swizzled_tile(t, order_m, tiles_n, group_m, tm, tn);
       return;
     }
     int o = ctx.rank, k = t;
@@ -414,8 +416,8 @@ struct ScatterGemmT : Common {
     }
     if (mode == IRIS_GEMM_REDUCE_SCATTER) {
       int lm, ln;
-      swizzled_tile(k, tiles_m_per_rank, tiles_n, group_m, lm, ln);
-      tm = o * tiles_m_per_rank + lm;
+      swizzled_tile(k, tiles_m_per_rank >> pair, tiles_n, group_m, lm, ln);
+      tm = o * (tiles_m_per_rank >> pair) + lm;
       tn = ln;
     } else {
       const int id = mode == IRIS_GEMM_ALL_REDUCE ? o + k * ctx.world : o * tiles_per_rank + k;
@@ -568,37 +570,44 @@ struct ScatterGemmT : Common {
 };
 
 // ------------------------------------------------------------------------------------ host side
-// Tile width: fewest waves over `ctas` persistent CTAs, weighted by tile cost; ties to the wider.
-int choose_bn(int M, int N, int ctas, bool mn_major) {
+// Tile shape: fewest waves over `ctas` persistent CTAs, weighted by tile cost; ties go to the
+// candidate listed first. `bn_fixed` > 0 pins the width; pair_mode 0 = choose, 1 = single CTAs,
+// 2 = CTA pairs (when `pair_ok`). A wave of pair tiles costs what a wave of single tiles of the
+// same width costs, less what the halved B traffic saves (measured 4 to 7 %).
+void choose_tile(int M, int N, int ctas, int bn_fixed, int pair_mode, bool pair_ok, int& bn_out, int& pair_out) {
   const int cand[3] = {256, 224, 128};
   double best = 1e30;
-  int best_bn = 256;
-  for (int i = 0; i < 3; ++i) {
-    const int bn = cand[i];
-    const int tiles = ceil_div(M, kBM) * ceil_div(N, bn);
-    const int waves = ceil_div(tiles, ctas);
-    // cost of a tile ~ its MMA time; a 128-wide tile runs at lower efficiency (more smem traffic per flop)
-    const double cost = waves * (double)bn * (bn == 128 ? 1.12 : 1.0);
-    if (cost < best - 1e-9) { best = cost; best_bn = bn; }
+  bn_out = bn_fixed > 0 ? bn_fixed : 256;
+  pair_out = 0;
+  for (int pr = 1; pr >= 0; --pr) {
+    if (pr == 1 && (!pair_ok || pair_mode == 1 || ctas < 2)) continue;
+    if (pr == 0 && pair_mode == 2 && pair_ok && ctas >= 2 && (bn_fixed == 0 || bn_fixed >= 224)) continue;
+    for (int i = 0; i < 3; ++i) {
+      const int bn = cand[i];
+      if (bn_fixed > 0 && bn != bn_fixed) continue;
+      if (pr == 1 && bn == 128) continue;
+      const int tiles = ceil_div(M, kBM << pr) * ceil_div(N, bn);
+      const int waves = ceil_div(tiles, ctas >> pr);
+      // a 128-wide tile runs at lower efficiency (more shared-memory traffic per flop)
+      // (measured: under the power cap a pair of 224-wide tiles only pays when it saves > 15 % of the waves)
+      const double cost = waves * (double)bn * (bn == 128 ? 1.12 : 1.0) * (pr ? (bn == 224 && bn_fixed == 0 ? 1.12 : 0.95) : 1.0);
+      if (cost < best - 1e-9) { best = cost; bn_out = bn; pair_out = pr; }
+    }
   }
-  (void)mn_major;
-  return best_bn;
-}
-
-template <class Cfg, class Policy>
-int launch_pair(const Policy& pol, int grid, cudaStream_t stream) {
-  auto kern = gemm_pair_kernel<Cfg, Policy>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -20;
-    attr_set = true;
-  }
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(pol);
-  return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 template <class Policy>
 int dispatch(const Policy& pol, int bn, bool kmajor, int grid, cudaStream_t stream) {
+  if (pol.pair) {
+    if (kmajor) {
+      if (bn == 256) return launch<Config<256, true, 6, true>>(pol, grid, stream);
+      if (bn == 224) return launch<Config<224, true, 6, true>>(pol, grid, stream);
+    } else {
+      if (bn == 256) return launch<Config<256, false, 6, true>>(pol, grid, stream);
+      if (bn == 224) return launch<Config<224, false, 6, true>>(pol, grid, stream);
+    }
+    return -30;
+  }
   if (kmajor) {
     if (bn == 256) return launch<Config<256, true, 4>>(pol, grid, stream);
     if (bn == 224) return launch<Config<224, true, 4>>(pol, grid, stream);
@@ -611,17 +620,19 @@ int dispatch(const Policy& pol, int bn, bool kmajor, int grid, cudaStream_t stre
   return -30;
 }
 
-int fill_common(Common& c, const IrisGemmDesc* d, int bn, int gemm_ctas, const void* A, uint64_t a_rows, uint64_t a_cols,
-                int64_t lda) {
+int fill_common(Common& c, const IrisGemmDesc* d, int bn, int pair, int gemm_ctas, const void* A, uint64_t a_rows,
+                uint64_t a_cols, int64_t lda) {
   if (d->dtype != IRIS_BF16 && d->dtype != IRIS_F16) return -2;
   if (d->N % 8 || d->K % 8) return -3;
   int r = make_map(&c.tmA, A, d->dtype, a_rows, a_cols, lda, kBK, kBM);
   if (r) return r;
-  if (d->b_kmajor) r = make_map(&c.tmB, d->B, d->dtype, d->N, d->K, d->ldb, kBK, bn);
+  if (d->b_kmajor) r = make_map(&c.tmB, d->B, d->dtype, d->N, d->K, d->ldb, kBK, pair ? bn / 2 : bn);
   else r = make_map(&c.tmB, d->B, d->dtype, d->K, d->N, d->ldb, 64, 64);
   if (r) return r;
   c.sh = Shape{d->M, d->N, d->K};
   c.tiles_m = ceil_div(d->M, kBM);
+  c.pair = pair;
+  c.order_m = pair ? ceil_div(d->M, 2 * kBM) : c.tiles_m;
   c.tiles_n = ceil_div(d->N, bn);
   c.group_m = d->group_m > 0 ? d->group_m : 8;
   c.n_gemm_ctas = gemm_ctas;
@@ -635,7 +646,7 @@ int fill_common(Common& c, const IrisGemmDesc* d, int bn, int gemm_ctas, const v
 }
 
 struct Plan {
-  int bn, gemm_ctas, comm_ctas;
+  int bn, pair, gemm_ctas, comm_ctas;
   int chunks, rows_per_src, cols_per_src;
   int max_owned, tiles_m_per_rank, tiles_per_rank;
   uint64_t inbox_bytes, flags_bytes, staging_bytes;
@@ -656,13 +667,25 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
     int spare = sms - ceil_div(tiles, waves);
     if (spare > 32) spare = 32;
     if (spare < 8) spare = 8;
+    spare += spare & 1;            // even, so that CTA pairs stay possible
     p.comm_ctas = spare;
   }
   p.gemm_ctas = d->gemm_ctas > 0 ? d->gemm_ctas : sms - p.comm_ctas;
   if (p.gemm_ctas + p.comm_ctas > sms) return -4;  // every CTA must be resident: consumers wait on producers
-  p.bn = d->bn > 0 ? d->bn : choose_bn(d->M, d->N, p.gemm_ctas, !d->b_kmajor);
-  if (p.bn != 256 && p.bn != 224 && p.bn != 128) return -5;
-  const int tiles_m = ceil_div(d->M, kBM), tiles_n = ceil_div(d->N, p.bn);
+  if (d->bn != 0 && d->bn != 256 && d->bn != 224 && d->bn != 128) return -5;
+  // CTA pairs need whole 256-row tiles wherever a tile's rows belong to one source or owner
+  const int tiles_m = ceil_div(d->M, kBM);
+  bool pair_ok = d->N >= 224 && p.comm_ctas % 2 == 0;
+  switch (d->op) {
+    case IRIS_GEMM_LOCAL: break;
+    case IRIS_GEMM_AG_M: pair_ok = pair_ok && d->M_local % (2 * kBM) == 0; break;
+    case IRIS_GEMM_REDUCE_SCATTER: pair_ok = pair_ok && d->M % (2 * kBM * W) == 0; break;
+    case IRIS_GEMM_RS_TILES: pair_ok = false; break;
+    default: pair_ok = pair_ok && d->M % (2 * kBM) == 0; break;
+  }
+  choose_tile(d->M, d->N, p.gemm_ctas, d->bn, d->two_sm, pair_ok, p.bn, p.pair);
+  if (p.pair) p.gemm_ctas &= ~1;
+  const int tiles_n = ceil_div(d->N, p.bn);
   if (d->op == IRIS_GEMM_AG_M) {
     if (d->M_local % kBM || d->M != d->M_local * W) return -6;
     p.rows_per_src = d->M_local; p.cols_per_src = d->K; p.chunks = d->M_local / kBM;
@@ -679,7 +702,7 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
     p.tiles_m_per_rank = tiles_m / W;
     p.max_owned = p.tiles_m_per_rank * tiles_n;
   } else if (d->op == IRIS_GEMM_ALL_REDUCE) {
-    p.max_owned = ceil_div(tiles_m * tiles_n, W);
+    p.max_owned = p.pair ? 2 * ceil_div((tiles_m / 2) * tiles_n, W) : ceil_div(tiles_m * tiles_n, W);
   } else if (d->op == IRIS_GEMM_RS_TILES) {
     p.tiles_per_rank = (tiles_m * tiles_n) / W;
     if (p.tiles_per_rank == 0) p.tiles_per_rank = 1;
@@ -696,7 +719,7 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
 }  // namespace
 
 extern "C" int iris_gemm_workspace(const IrisGemmDesc* d, uint64_t* inbox_bytes, uint64_t* flags_bytes,
-                                   uint64_t* staging_bytes, int32_t* bn_out) {
+                                   uint64_t* staging_bytes, int32_t* bn_out, int32_t* pair_out) {
   Plan p;
   int r = make_plan(d, p);
   if (r) return r;
@@ -704,6 +727,7 @@ extern "C" int iris_gemm_workspace(const IrisGemmDesc* d, uint64_t* inbox_bytes,
   if (flags_bytes) *flags_bytes = p.flags_bytes;
   if (staging_bytes) *staging_bytes = p.staging_bytes;
   if (bn_out) *bn_out = p.bn;
+  if (pair_out) *pair_out = p.pair;
   return 0;
 }
 
@@ -719,27 +743,16 @@ extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
 
   if (d->op == IRIS_GEMM_LOCAL) {
     LocalGemm pol;
-    r = fill_common(pol, d, p.bn, p.gemm_ctas, d->A, d->M, d->K, d->lda);
+    r = fill_common(pol, d, p.bn, p.pair, p.gemm_ctas, d->A, d->M, d->K, d->lda);
     if (r) return r;
     pol.C = (uint8_t*)d->C; pol.ldc = d->ldc;
-    if (d->two_sm == 2 && p.bn == 256) {
-      // two-SM tiles: pairs of CTAs share a 256 x 256 tile (tcgen05 cta_group::2)
-      pol.tiles_m = ceil_div(d->M, 2 * kBM);
-      make_map(&pol.tmB, d->B, d->dtype, d->b_kmajor ? d->N : d->K, d->b_kmajor ? d->K : d->N, d->ldb, 64, d->b_kmajor ? 128 : 64);
-      int pairs = pol.tiles_m * pol.tiles_n;
-      int g = sm_count() / 2 * 2;
-      if (2 * pairs < g) g = 2 * pairs;
-      pol.n_gemm_ctas = g;
-      if (d->b_kmajor) return launch_pair<PairConfig<256, true, 6>>(pol, g, stream);
-      return launch_pair<PairConfig<256, false, 6>>(pol, g, stream);
-    }
-    const int tiles = pol.tiles_m * pol.tiles_n;
-    return dispatch(pol, p.bn, d->b_kmajor != 0, tiles < grid ? tiles : grid, stream);
+    const int ctas = (pol.order_m * pol.tiles_n) << p.pair;   // no more CTAs than tiles
+    return dispatch(pol, p.bn, d->b_kmajor != 0, ctas < grid ? ctas : grid, stream);
   }
   if (d->op == IRIS_GEMM_AG_M || d->op == IRIS_GEMM_AG_K) {
     AllGatherGemm pol;
     // tmA covers this rank's shard only
-    r = fill_common(pol, d, p.bn, p.gemm_ctas, d->A, p.rows_per_src, p.cols_per_src, d->lda);
+    r = fill_common(pol, d, p.bn, p.pair, p.gemm_ctas, d->A, p.rows_per_src, p.cols_per_src, d->lda);
     if (r) return r;
     if (ctx.world > 1) {
       r = make_map(&pol.tmInbox, d->inbox, d->dtype, 2ull * ctx.world * p.rows_per_src, p.cols_per_src, p.cols_per_src,
@@ -759,7 +772,7 @@ extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
     return dispatch(pol, p.bn, d->b_kmajor != 0, grid, stream);
   }
   auto fill = [&](auto& pol) -> int {
-    int rr = fill_common(pol, d, p.bn, p.gemm_ctas, d->A, d->M, d->K, d->lda);
+    int rr = fill_common(pol, d, p.bn, p.pair, p.gemm_ctas, d->A, d->M, d->K, d->lda);
     if (rr) return rr;
     pol.ctx = ctx; pol.sb = (SyncBlock*)d->sync_block; pol.mode = d->op;
     pol.out = (uint8_t*)d->C; pol.ld_out = d->ldc;

@@ -29,20 +29,28 @@ constexpr int kThreads = 192;    // 6 warps
 constexpr int kEpiWarps = 4;
 constexpr uint64_t kPipeTimeoutNs = 4000000000ull;
 
-template <int BN_, bool kBKMajor_, int kStages_>
+// kPair_: two CTAs of a cluster compute one 256 x BN tile with tcgen05.mma.cta_group::2. Each CTA
+// stages its own 128 rows of A and HALF of the B tile (so a stage is at most 32 KB, six fit, and B
+// leaves L2 once per pair); the even CTA issues the MMAs for both, each CTA's 128 accumulator rows
+// live in its own TMEM and each CTA runs its own epilogue.
+template <int BN_, bool kBKMajor_, int kStages_, bool kPair_ = false>
 struct Config {
   static constexpr int BN = BN_;
   static constexpr bool kBKMajor = kBKMajor_;
   static constexpr int kStages = kStages_;
+  static constexpr bool kPair = kPair_;
+  static constexpr int kBCols = kPair_ ? BN_ / 2 : BN_;                 // columns of B staged by one CTA
   static constexpr int kABytes = kBM * kBK * 2;                         // 16 KB
-  static constexpr int kBBoxes = kBKMajor_ ? 1 : (BN_ + 63) / 64;       // MN-major: 64(n) x 64(k) boxes
-  static constexpr int kBBytes = kBKMajor_ ? BN_ * kBK * 2 : kBBoxes * 8192;
+  static constexpr int kBBoxes = kBKMajor_ ? 1 : (kBCols + 63) / 64;    // MN-major: 64(n) x 64(k) boxes
+  static constexpr int kBBytes = kBKMajor_ ? kBCols * kBK * 2 : kBBoxes * 8192;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kAccCols = 256;                                  // column pitch of an accumulator buffer
   static constexpr int kTmemCols = 512;
   static constexpr int kEpiBytes = kEpiWarps * 2 * 4096;                // per warp: two 32-row x 64-col staging chunks
   static constexpr int kSmemBytes = 1024 + kStages_ * kStageBytes + kEpiBytes + 256;
   static_assert(BN_ % 32 == 0 && BN_ >= 32 && BN_ <= 256, "BN must be a multiple of 32 up to 256");
+  static_assert(!kPair_ || kBCols % 16 == 0, "a pair splits B into two halves of whole 16-column groups");
+  static_assert(kStageBytes % 1024 == 0, "stages keep the 1024-byte alignment of the 128-byte swizzle");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
@@ -58,11 +66,11 @@ IRIS_D uint64_t desc_mnmajor(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(8192 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-// Instruction descriptor, kind::f16: fp32 accumulate, A K-major, M = 128.
-IRIS_HD uint32_t make_idesc(int n, bool bf16, bool b_mn_major) {
+// Instruction descriptor, kind::f16: fp32 accumulate, A K-major, M = 128 (256 for a CTA pair).
+IRIS_HD uint32_t make_idesc(int n, bool bf16, bool b_mn_major, int m = kBM) {
   uint32_t fmt = bf16 ? 1u : 0u;
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(kBM >> 4) << 24);
+         ((uint32_t)(m >> 4) << 24);
 }
 
 struct Shape {
@@ -127,11 +135,24 @@ struct Pipeline {
 //        COLLECT_TIMESTAMPS, examples/07_gemm_all_scatter/gemm_all_scatter.py:64-66)
 // The policy is a __grid_constant__ kernel parameter (its tensor maps are used in place), so every
 // hook is const.
+//
+// Pair configurations (Cfg::kPair): tile() is asked for PAIR tiles (its m index counts 256-row
+// tiles); every other hook sees 128-row tile indices (2 * pair_m + cluster rank). Barrier wiring
+// (L = even CTA, P = odd CTA):
+//   full[s]        lives in L; both CTAs' TMA loads complete_tx on it (the .cta_group::2 load form
+//                  with L's barrier address, no multicast); L arms it with both CTAs' byte count.
+//   empty[s]       one per CTA; L's MMA thread releases both with one multicast tcgen05.commit.
+//   tmem_full[b]   one per CTA, signalled by a multicast commit; tmem_empty[b] lives in L and
+//                  counts the epilogue warps of both CTAs (P arrives remotely).
 template <class Cfg, class Policy>
 IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const Shape sh = pol.shape();
+  constexpr bool kPair = Cfg::kPair;
+  uint32_t cta = 0;
+  if constexpr (kPair) cta = ptx::cluster_ctarank();
+  const bool leader = cta == 0;
 
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
@@ -147,23 +168,35 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&pipe.tmem_full[b], 1);
-      ptx::mbar_init(&pipe.tmem_empty[b], kEpiWarps);
+      ptx::mbar_init(&pipe.tmem_empty[b], kEpiWarps * (kPair ? 2 : 1));
     }
     ptx::fence_mbar_init();
     ptx::fence_proxy_async();
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
-    ptx::tmem_relinquish();
+    if constexpr (kPair) {
+      ptx::tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);   // one warp of each CTA of the pair
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if constexpr (kPair) ptx::cluster_sync();   // both CTAs' barriers exist before anyone signals remotely
   ptx::tc_fence_after();
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
 
   const int num_tiles = pol.num_tiles();
   const int k_blocks = (sh.K + kBK - 1) / kBK;
-  const int first = blockIdx.x, step = pol.gemm_ctas();
+  const int first = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int step = kPair ? pol.gemm_ctas() >> 1 : pol.gemm_ctas();
+  // the epilogue warp's arrival that hands an accumulator buffer back to the MMA issuer
+  auto release_acc = [&](int buf) {
+    if (!kPair || leader) ptx::mbar_arrive(&pipe.tmem_empty[buf]);
+    else ptx::mbar_arrive_cluster(&pipe.tmem_empty[buf], 0);
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -175,24 +208,38 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
     for (int t = first; t < num_tiles && ok; t += step) {
       int tm, tn;
       pol.tile(t, tm, tn);
+      if constexpr (kPair) tm = 2 * tm + (int)cta;
       if (lane == 0) pol.stamp(t, 0);
       for (int kb = 0; kb < k_blocks; ++kb) {
         ASource as;
         as.bn0 = tn * Cfg::BN;
         if (!pol.a_source(st, tm, kb, as)) { ok = false; break; }
         if (kb == 0 && lane == 0) pol.stamp(t, 1);
-        if (!ptx::mbar_wait(&pipe.empty[s], ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
+        if (!ptx::mbar_wait<kPair>(&pipe.empty[s], ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
         if (lane == 0) {
           uint8_t* sa = stage_base + s * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
-          ptx::mbar_expect_tx(&pipe.full[s], Cfg::kStageBytes);
-          ptx::tma_load_2d(sa, as.map, &pipe.full[s], as.x, as.y);
-          if constexpr (Cfg::kBKMajor) {
-            ptx::tma_load_2d(sb, pol.b_map(), &pipe.full[s], as.bk, as.bn0);
-          } else {
+          if constexpr (kPair) {
+            if (leader) ptx::mbar_expect_tx(&pipe.full[s], 2 * Cfg::kStageBytes);
+            const int n0 = as.bn0 + (int)cta * Cfg::kBCols;
+            ptx::tma_load_2d_pair(sa, as.map, &pipe.full[s], as.x, as.y);
+            if constexpr (Cfg::kBKMajor) {
+              ptx::tma_load_2d_pair(sb, pol.b_map(), &pipe.full[s], as.bk, n0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < Cfg::kBBoxes; ++j)
-              ptx::tma_load_2d(sb + j * 8192, pol.b_map(), &pipe.full[s], as.bn0 + j * 64, as.bk);
+              for (int j = 0; j < Cfg::kBBoxes; ++j)
+                ptx::tma_load_2d_pair(sb + j * 8192, pol.b_map(), &pipe.full[s], n0 + j * 64, as.bk);
+            }
+          } else {
+            ptx::mbar_expect_tx(&pipe.full[s], Cfg::kStageBytes);
+            ptx::tma_load_2d(sa, as.map, &pipe.full[s], as.x, as.y);
+            if constexpr (Cfg::kBKMajor) {
+              ptx::tma_load_2d(sb, pol.b_map(), &pipe.full[s], as.bk, as.bn0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < Cfg::kBBoxes; ++j)
+                ptx::tma_load_2d(sb + j * 8192, pol.b_map(), &pipe.full[s], as.bn0 + j * 64, as.bk);
+            }
           }
         }
         __syncwarp();
@@ -201,19 +248,19 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = make_idesc(Cfg::BN, pol.is_bf16(), !Cfg::kBKMajor);
+    const uint32_t idesc = make_idesc(Cfg::BN, pol.is_bf16(), !Cfg::kBKMajor, kPair ? 2 * kBM : kBM);
     int s = 0;
     uint32_t ph = 0;
     int it = 0;
-    bool ok = true;
+    bool ok = leader;      // the even CTA of a pair issues for both
     for (int t = first; t < num_tiles && ok; t += step, ++it) {
       const int buf = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
-      if (!ptx::mbar_wait(&pipe.tmem_empty[buf], acc_ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); break; }
+      if (!ptx::mbar_wait<kPair>(&pipe.tmem_empty[buf], acc_ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); break; }
       ptx::tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * Cfg::kAccCols;
       for (int kb = 0; kb < k_blocks; ++kb) {
-        if (!ptx::mbar_wait(&pipe.full[s], ph, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
+        if (!ptx::mbar_wait<kPair>(&pipe.full[s], ph, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
         ptx::tc_fence_after();
         if (lane == 0) {
           const uint32_t sa = ptx::smem_u32(stage_base + s * Cfg::kStageBytes);
@@ -222,10 +269,16 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             uint64_t ad = desc_kmajor(sa + k * (kUmmaK * 2));
             uint64_t bd = Cfg::kBKMajor ? desc_kmajor(sb + k * (kUmmaK * 2)) : desc_mnmajor(sb + k * (kUmmaK * 128));
-            ptx::mma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+            if constexpr (kPair) ptx::mma_f16_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
+            else ptx::mma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
           }
-          ptx::mma_commit(&pipe.empty[s]);
-          if (kb == k_blocks - 1) ptx::mma_commit(&pipe.tmem_full[buf]);
+          if constexpr (kPair) {
+            ptx::mma_commit_pair(&pipe.empty[s], 3);
+            if (kb == k_blocks - 1) ptx::mma_commit_pair(&pipe.tmem_full[buf], 3);
+          } else {
+            ptx::mma_commit(&pipe.empty[s]);
+            if (kb == k_blocks - 1) ptx::mma_commit(&pipe.tmem_full[buf]);
+          }
         }
         __syncwarp();
         if (++s == Cfg::kStages) { s = 0; ph ^= 1; }
@@ -245,9 +298,10 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
       const uint32_t acc_ph = (it >> 1) & 1;
       int tm, tn;
       pol.tile(t, tm, tn);
+      if constexpr (kPair) tm = 2 * tm + (int)cta;
       // A wait that runs out still goes through this tile's named barrier (the other epilogue
       // warps may have got through) and leaves afterwards.
-      const bool live = ptx::mbar_wait(&pipe.tmem_full[buf], acc_ph, kPipeTimeoutNs);
+      const bool live = ptx::mbar_wait<kPair>(&pipe.tmem_full[buf], acc_ph, kPipeTimeoutNs);
       if (!live) {
         pol.fail(kTimeoutPipeline);
         ptx::named_barrier(1, kEpiWarps * 32);
@@ -295,7 +349,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
             if (cc == kChunks - 1 && hlf == w / 32 - 1) {
               ptx::tc_fence_before();
               __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(&pipe.tmem_empty[buf]);
+              if (lane == 0) release_acc(buf);
             }
             uint32_t packed[16];
             pack32(r, tn * Cfg::BN + cc * 64 + hlf * 32, packed);
@@ -339,7 +393,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
             if (c == 3) {
               ptx::tc_fence_before();
               __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(&pipe.tmem_empty[buf]);
+              if (lane == 0) release_acc(buf);
             }
             uint32_t r[32];
 #pragma unroll
@@ -374,7 +428,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
           if (c == Cfg::BN / 32 - 1) {
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&pipe.tmem_empty[buf]);
+            if (lane == 0) release_acc(buf);
           }
           if constexpr (Policy::kBulkEpilogue) pol.add_partials(est, quarter, c, lane, r);
           const int col0 = tn * Cfg::BN + c * 32;
@@ -405,13 +459,30 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if constexpr (kPair) ptx::cluster_sync();   // the peer's shared memory and barriers stay alive until both are done
   ptx::tc_fence_after();
-  if (warp == 1) ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if (warp == 1) {
+    if constexpr (kPair) ptx::tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    else ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
   pol.post_main();
 }
 
 template <class Cfg, class Policy>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ Policy pol_in) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x >= pol_in.gemm_ctas()) {
+    pol_in.comm_main(smem_raw, Cfg::kSmemBytes);
+    return;
+  }
+  gemm_cta_main<Cfg, Policy>(pol_in, smem_raw);
+}
+
+// Pair configurations: clusters of two CTAs. gemm_ctas() and the grid are even, so a cluster is
+// either two GEMM CTAs or two communication CTAs (which never touch the cluster barrier).
+template <class Cfg, class Policy>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_constant__ Policy pol_in) {
+  static_assert(Cfg::kPair, "pair kernel needs a pair configuration");
   extern __shared__ uint8_t smem_raw[];
   if ((int)blockIdx.x >= pol_in.gemm_ctas()) {
     pol_in.comm_main(smem_raw, Cfg::kSmemBytes);

@@ -50,7 +50,7 @@ typedef struct IrisGemmDesc {
   int32_t gemm_ctas;      // 0 = all SMs minus comm_ctas
   int32_t comm_ctas;      // CTAs that only move data (AG_M / AG_K), 0 = default
   int32_t use_mc;         // use the NVLS multicast window when the context has one
-  int32_t two_sm;         // 2: pairs of CTAs share 256-row tiles (tcgen05 cta_group::2), local GEMM only
+  int32_t two_sm;         // CTA pairs on 256-row tiles (tcgen05 cta_group::2): 0 = plan decides, 1 = never, 2 = whenever the shape allows
   const void* A; int64_t lda;
   const void* B; int64_t ldb;
   void* C; int64_t ldc;
@@ -67,9 +67,10 @@ typedef struct IrisGemmDesc {
                           // 1 operands available, 2 stored; comm CTA 0 stamps slot tiles+c, col 3)
 } IrisGemmDesc;
 
-// Bytes of workspace the op needs for this shape (inbox / flags / staging). Pure arithmetic.
+// Bytes of workspace the op needs for this shape (inbox / flags / staging) and the tile the plan
+// picked (width, and whether CTA pairs run 256-row tiles). Pure arithmetic.
 int iris_gemm_workspace(const IrisGemmDesc* d, uint64_t* inbox_bytes, uint64_t* flags_bytes, uint64_t* staging_bytes,
-                        int32_t* bn_out);
+                        int32_t* bn_out, int32_t* pair_out);
 int iris_gemm_launch(const IrisGemmDesc* d, void* stream);
 
 #ifdef __cplusplus

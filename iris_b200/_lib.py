@@ -100,7 +100,7 @@ def kernels() -> C.CDLL:
             lib.iris_gemm_launch.argtypes = [C.POINTER(IrisGemmDesc), C.c_void_p]
             lib.iris_gemm_launch.restype = C.c_int
             lib.iris_gemm_workspace.argtypes = [C.POINTER(IrisGemmDesc), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
-                                                C.POINTER(C.c_uint64), C.POINTER(C.c_int32)]
+                                                C.POINTER(C.c_uint64), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
             lib.iris_gemm_workspace.restype = C.c_int
             _kernels = lib
         return _kernels

@@ -50,20 +50,22 @@ def _base_desc(ctx, op, M, N, K, A, B, out, config, bias_row=None, bias_col=None
     keep = fill_desc(d, A, B, out, bias_row=bias_row, bias_col=bias_col, bn=config.tile_n())
     d.group_m = config.group_size_m
     d.comm_ctas = config.comm_sms
+    d.two_sm = 0 if config.two_sm is None else (2 if config.two_sm else 1)
     d.use_mc = 1 if (config.use_multicast and ctx.has_multicast()) else 0
     d.ctx = ctx.ctx_struct()
     return d, keep
 
 
 def _plan(d) -> tuple:
-    inbox, flags, staging, bn = C.c_uint64(0), C.c_uint64(0), C.c_uint64(0), C.c_int32(0)
-    rc = _lib.kernels().iris_gemm_workspace(C.byref(d), C.byref(inbox), C.byref(flags), C.byref(staging), C.byref(bn))
-    return rc, inbox.value, flags.value, staging.value, bn.value
+    inbox, flags, staging, bn, pair = C.c_uint64(0), C.c_uint64(0), C.c_uint64(0), C.c_int32(0), C.c_int32(0)
+    rc = _lib.kernels().iris_gemm_workspace(C.byref(d), C.byref(inbox), C.byref(flags), C.byref(staging), C.byref(bn),
+                                            C.byref(pair))
+    return rc, inbox.value, flags.value, staging.value, bn.value, pair.value
 
 
 def _make_workspace(ctx, operation, shape, dtype, variant, d) -> FusedWorkspace | None:
     """Allocate the op's heap buffers (collective). None when the kernel cannot take the shape."""
-    rc, inbox, flags, staging, bn = _plan(d)
+    rc, inbox, flags, staging, bn, pair = _plan(d)
     if rc != 0:
         return None
     ws = FusedWorkspace(operation=operation, shape=tuple(shape), dtype=dtype, world_size=ctx.num_ranks, variant=variant, bn=bn)
@@ -79,6 +81,8 @@ def _make_workspace(ctx, operation, shape, dtype, variant, d) -> FusedWorkspace 
     ws.prepared = True
     # arrival counters count communication CTAs: the number used at creation is part of the workspace
     ws.extra["comm_ctas"] = d.comm_ctas
+    # the staging layout depends on the tile (width, single CTA or CTA pair): pinned with the buffers
+    ws.extra["two_sm"] = 2 if pair else 1
     ctx.barrier()
     return ws
 
@@ -112,6 +116,7 @@ def _launch(ctx, d, ws) -> None:
     d.staging = ws.staging.data_ptr() if ws.staging is not None else None
     d.bn = ws.bn
     d.comm_ctas = ws.extra.get("comm_ctas", d.comm_ctas)
+    d.two_sm = ws.extra.get("two_sm", d.two_sm)
     tl = ws.extra.get("timeline")
     d.timeline = tl.data_ptr() if tl is not None else None
     _lib.check(_lib.kernels().iris_gemm_launch(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), f"{ws.operation} launch")

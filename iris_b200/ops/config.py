@@ -23,6 +23,7 @@ class FusedConfig:
     all_reduce_num_rings: int = 1
     comm_sms: int = 0
     use_multicast: bool = True
+    two_sm: bool | None = None      # CTA pairs on 256-row tiles (tcgen05 cta_group::2); None = the plan decides
     allow_tf32: bool = True
 
     def __post_init__(self):

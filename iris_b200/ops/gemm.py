@@ -49,11 +49,12 @@ def fill_desc(desc: _lib.IrisGemmDesc, A: torch.Tensor, B: torch.Tensor, out: to
 
 
 def matmul(A: torch.Tensor, B: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
-           bias_dim: int = 1, bn: int = 0, two_sm: bool = False) -> torch.Tensor:
+           bias_dim: int = 1, bn: int = 0, two_sm: bool | None = None) -> torch.Tensor:
     """``out = A @ B (+ bias)``; ``bias_dim=0`` adds ``bias[m]`` to every row m, ``1`` adds ``bias[n]``.
 
-    ``two_sm`` runs the variant in which two CTAs of a cluster share one 256 x 256 tile
-    (``tcgen05.mma.cta_group::2``); it needs ``N >= 256``."""
+    ``two_sm`` selects the variant in which the two CTAs of a cluster share one 256-row tile
+    (``tcgen05.mma.cta_group::2``): ``True`` whenever the shape allows, ``False`` never, ``None``
+    lets the plan pick by wave count."""
     M, K = A.shape
     K2, N = B.shape
     if K != K2:
@@ -66,8 +67,7 @@ def matmul(A: torch.Tensor, B: torch.Tensor, bias: torch.Tensor | None = None, o
     b32 = bias.float().contiguous() if bias is not None else None
     keep = fill_desc(desc, A, B, out, bias_row=b32 if bias_dim == 0 else None, bias_col=b32 if bias_dim == 1 else None, bn=bn)
     desc.ctx.world = 1
-    if two_sm:
-        desc.two_sm, desc.bn = 2, 256
+    desc.two_sm = 0 if two_sm is None else (2 if two_sm else 1)
     _lib.check(_lib.kernels().iris_gemm_launch(C.byref(desc), _lib.current_stream_ptr()), "gemm launch")
     del keep
     return out
