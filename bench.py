@@ -33,57 +33,131 @@ PUBLISHED_TFLOPS_PER_GPU = 2190.0 / 8
 
 
 class ClockSampler:
-    """Samples nvidia-smi while the timed region runs (clocks, power, throttle reasons)."""
+    """Reads SM clock, power and throttle reasons while the benchmark runs.
+
+    NVML is polled from a thread every few milliseconds (read-only queries), so that even a timed
+    region of a few tens of milliseconds yields samples; ``nvidia-smi -lms`` is the fallback when
+    the NVML bindings are missing. Samples taken between ``mark_timed(True)`` and
+    ``mark_timed(False)`` are the ones reported; if that window caught fewer than three, the
+    samples of the whole loaded span (warm-up to the end of the end-to-end loop) are used.
+    """
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+                   0x80: "hw_power_brake_slowdown"}
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.rows = []
+        self.rows = []            # (wall time, sm MHz, power W, set of reasons)
+        self.max_mhz = None
         self.proc = None
         self.thread = None
+        self.stop_flag = False
+        self.source = None
         self.load_from = None     # wall time from which the GPU is under the benchmark's load
+        self.timed = [None, None]
+
+    def mark_timed(self, begin: bool):
+        self.timed[0 if begin else 1] = time.time()
+
+    # ---- NVML
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            import torch
+            props = torch.cuda.get_device_properties(self.gpu_index)
+            uuid = getattr(props, "uuid", None)
+            if uuid is not None:
+                return pynvml, pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+        except Exception:
+            pass
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        idx = self.gpu_index
+        if visible:
+            try:
+                idx = int(visible.split(",")[self.gpu_index])
+            except (ValueError, IndexError):
+                pass
+        return pynvml, pynvml.nvmlDeviceGetHandleByIndex(idx)
+
+    def _poll_nvml(self, pynvml, handle):
+        reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop_flag:
+            try:
+                sm = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                power = pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0
+                mask = int(reasons_fn(handle))
+                self.rows.append((time.time(), float(sm), power, {n for b, n in self.REASON_BITS.items() if mask & b}))
+            except Exception:
+                pass
+            time.sleep(0.003)
 
     def start(self):
+        try:
+            pynvml, handle = self._nvml_handle()
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self.source = "nvml"
+            self.thread = threading.Thread(target=self._poll_nvml, args=(pynvml, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.source = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
-        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.source = "nvidia-smi"
+        self.thread = threading.Thread(target=self._read_smi, daemon=True)
         self.thread.start()
 
-    def _read(self):
+    def _read_smi(self):
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) >= 9:
-                self.rows.append([time.time()] + parts)
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        deadline = time.time() + 3.0
-        while not self.rows and time.time() < deadline:   # a slow first sample (many ranks start nvidia-smi at once)
-            time.sleep(0.05)
-        self.proc.terminate()  # the exact child started above
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons, power = [], [], set(), []
-        loaded = [r[1:] for r in self.rows if self.load_from is None or r[0] >= self.load_from]
-        for r in (loaded or [r[1:] for r in self.rows]):
+            if len(parts) < 9:
+                continue
             try:
-                sm.append(float(r[1])); mx.append(float(r[2])); power.append(float(r[3]))
+                self.max_mhz = float(parts[2])
+                self.rows.append((time.time(), float(parts[1]), float(parts[3]),
+                                  {n for n, v in zip(names, parts[5:9]) if v.lower().startswith("active")}))
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+    def stop(self) -> dict:
+        if self.source is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML and no nvidia-smi"]}
+        if self.source == "nvidia-smi":
+            deadline = time.time() + 3.0
+            while not self.rows and time.time() < deadline:   # a slow first sample (many ranks start nvidia-smi at once)
+                time.sleep(0.05)
+            self.proc.terminate()  # the exact child started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        else:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+        rows = list(self.rows)
+        window = "timed region"
+        t0, t1 = self.timed
+        use = [r for r in rows if t0 is not None and t1 is not None and t0 <= r[0] <= t1]
+        if len(use) < 3:
+            window = "warm-up to end of the end-to-end loop"
+            use = [r for r in rows if self.load_from is None or r[0] >= self.load_from]
+        if not use:
+            window = "whole run"
+            use = rows
+        reasons = set()
+        for r in use:
+            reasons |= r[3]
+        return {"sm_mhz": statistics.median([r[1] for r in use]) if use else None, "sm_max_mhz": self.max_mhz,
+                "power_w_max": max([r[2] for r in use]) if use else None, "samples": len(use), "window": window,
+                "source": self.source, "reasons": sorted(reasons)}
 
 
 def run_reference(args) -> int:
@@ -170,11 +244,13 @@ def main() -> int:
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dist.barrier()
     torch.cuda.synchronize()
+    sampler.mark_timed(True)
     start.record()
     for _ in range(args.steps):
         step()
     end.record()
     torch.cuda.synchronize()
+    sampler.mark_timed(False)
     dist.barrier()
     ms = start.elapsed_time(end) / args.steps
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
@@ -182,24 +258,47 @@ def main() -> int:
     ms = float(t.item())
     ctx.check()
 
-    # ---------------- end-to-end region: H2D of the step's input from pinned memory, the two
-    # ops through the public API, D2H of the step's scalar result, every step
-    def e2e_step():
-        X.copy_(X_host, non_blocking=True)
-        step()
-        return float(Y.float().square().mean().item())
+    # ---------------- end-to-end region: every step copies its input from pinned host memory,
+    # runs the two ops through the public API and reads the step's scalar result back. The copy
+    # of step i+1 runs on a second stream while step i computes (two device buffers); all K
+    # copies, the first one included, are inside the timed region.
+    copy_stream = torch.cuda.Stream()
+    main_stream = torch.cuda.current_stream()
+    Xb = [X, torch.empty_like(X)]
+    ready = [torch.cuda.Event(), torch.cuda.Event()]
+    consumed = [torch.cuda.Event(), torch.cuda.Event()]
 
-    for _ in range(3):
-        e2e_step()
+    def prefetch(i):
+        b = i & 1
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[b])
+            Xb[b].copy_(X_host, non_blocking=True)
+            ready[b].record(copy_stream)
+
+    def e2e_loop(n):
+        res = 0.0
+        for ev in consumed:
+            ev.record(main_stream)
+        prefetch(0)
+        for i in range(n):
+            b = i & 1
+            if i + 1 < n:
+                prefetch(i + 1)
+            main_stream.wait_event(ready[b])
+            ctx.ops.all_gather_matmul(H, Xb[b], W1, shard_dim=0, workspace=ws1, async_op=True)
+            consumed[b].record(main_stream)
+            ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True, workspace=ws2, async_op=True)
+            res = float(Y.float().square().mean().item())
+        return res
+
+    e2e_loop(3)
     ctx.barrier()
     dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
-    last = 0.0
-    for _ in range(args.steps):
-        last = e2e_step()
+    last = e2e_loop(args.steps)
     e2.record()
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
@@ -235,7 +334,7 @@ def main() -> int:
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 2), "unit": "TFLOPS", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": X_host.numel() * X_host.element_size(), "d2h_bytes_per_step": 4, "last_result": last},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": 2 * args.steps,      # one fused kernel per op per step in the device-timed region
         "impl": "ours",
     }
     if rank == 0:
