@@ -570,10 +570,12 @@ struct ScatterGemmT : Common {
 };
 
 // ------------------------------------------------------------------------------------ host side
-// Tile shape: fewest waves over `ctas` persistent CTAs, weighted by tile cost; ties go to the
-// candidate listed first. `bn_fixed` > 0 pins the width; pair_mode 0 = choose, 1 = single CTAs,
-// 2 = CTA pairs (when `pair_ok`). A wave of pair tiles costs what a wave of single tiles of the
-// same width costs, less what the halved B traffic saves (measured 4 to 7 %).
+// Tile shape: least estimated time over `ctas` persistent CTAs; ties go to the candidate listed
+// first. `bn_fixed` > 0 pins the width; pair_mode 0 = choose, 1 = single CTAs, 2 = CTA pairs (when
+// `pair_ok`). The estimate is waves x tile width x a per-shape factor. Under the power cap a
+// partly idle last wave costs less than a full one (the busy SMs clock higher), so the wave
+// count is the mean of the whole and the fractional number of waves. Factors are measured: a
+// pair tile saves 4 to 7 % (B leaves L2 once per pair), a 128-wide tile costs about 12 % more.
 void choose_tile(int M, int N, int ctas, int bn_fixed, int pair_mode, bool pair_ok, int& bn_out, int& pair_out) {
   const int cand[3] = {256, 224, 128};
   double best = 1e30;
@@ -587,10 +589,9 @@ void choose_tile(int M, int N, int ctas, int bn_fixed, int pair_mode, bool pair_
       if (bn_fixed > 0 && bn != bn_fixed) continue;
       if (pr == 1 && bn == 128) continue;
       const int tiles = ceil_div(M, kBM << pr) * ceil_div(N, bn);
-      const int waves = ceil_div(tiles, ctas >> pr);
-      // a 128-wide tile runs at lower efficiency (more shared-memory traffic per flop)
-      // (measured: under the power cap a pair of 224-wide tiles only pays when it saves > 15 % of the waves)
-      const double cost = waves * (double)bn * (bn == 128 ? 1.12 : 1.0) * (pr ? (bn == 224 && bn_fixed == 0 ? 1.12 : 0.95) : 1.0);
+      const int slots = ctas >> pr;
+      const double waves = 0.5 * (ceil_div(tiles, slots) + (double)tiles / slots);
+      const double cost = waves * bn * (bn == 128 ? 1.12 : 1.0) * (pr ? 0.95 : 1.0);
       if (cost < best - 1e-9) { best = cost; bn_out = bn; pair_out = pr; }
     }
   }

@@ -72,6 +72,7 @@ class CCL:
     def __init__(self, ctx):
         self.ctx = ctx
         self._desc_cache: dict = {}
+        self._fast: dict = {}       # whole calls that ran before: key -> (op code, descriptor copy, return value)
         self._push_ws = None
 
     # ------------------------------------------------------------------ plumbing
@@ -121,6 +122,24 @@ class CCL:
     def _launch(self, op: int, d: IrisCclDesc):
         _lib.check(self._lib().iris_ccl_launch(op, C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "collective launch")
 
+    # A repeated call (same buffers, shapes, group and configuration) skips validation and
+    # descriptor set-up: one tuple, one dictionary lookup, one launch.
+    def _fast_key(self, tag, out, inp, group, config, extra=None):
+        return (tag, out.data_ptr(), inp.data_ptr(), out.shape, inp.shape, out.stride(), inp.stride(), out.dtype, inp.dtype,
+                None if group is None else id(group), None if config is None else tuple(vars(config).values()),
+                id(self.ctx._ctx_epoch), extra)
+
+    def _remember(self, key, op: int, d: IrisCclDesc, ret=None):
+        if len(self._fast) > 4096:
+            self._fast.clear()
+        self._fast[key] = (op, IrisCclDesc.from_buffer_copy(d), ret)     # a copy: cached descriptors are rewritten per call
+
+    def _replay(self, hit, async_op, group):
+        self._launch(hit[0], hit[1])
+        if not async_op:
+            self.ctx.barrier(group=group)
+        return hit[2]
+
     def _finish(self, async_op: bool, group):
         if not async_op:
             self.ctx.barrier(group=group)
@@ -131,6 +150,10 @@ class CCL:
     # ------------------------------------------------------------------ all_gather
     def all_gather(self, output_tensor, input_tensor, group=None, async_op=False, config=None):
         """``output[(r*M):(r+1)*M, :] = input of rank r`` for every rank r of the group."""
+        key = self._fast_key("ag", output_tensor, input_tensor, group, config)
+        hit = self._fast.get(key)
+        if hit is not None:
+            return self._replay(hit, async_op, group)
         config = config or Config()
         out, inp = _as_2d(output_tensor), _as_2d(input_tensor)
         self._check(out, inp)
@@ -148,11 +171,16 @@ class CCL:
             d.M, d.N = M, N
             d.variant = 1 if config.all_gather_variant == "partitioned" else 0
             self._launch(0, d)
+            self._remember(key, 0, d)
         self._finish(async_op, group)
 
     # ------------------------------------------------------------------ all_to_all
     def all_to_all(self, output_tensor, input_tensor, group=None, async_op=False, config=None):
         """Column chunk d of rank s's input lands in column chunk s of rank d's output."""
+        key = self._fast_key("a2a", output_tensor, input_tensor, group, config)
+        hit = self._fast.get(key)
+        if hit is not None:
+            return self._replay(hit, async_op, group)
         config = config or Config()
         out, inp = _as_2d(output_tensor), _as_2d(input_tensor)
         self._check(out, inp)
@@ -170,6 +198,7 @@ class CCL:
             d = self._desc(out, inp, group, config, op="a2a")
             d.M, d.N = M, N
             self._launch(1, d)
+            self._remember(key, 1, d)
         self._finish(async_op, group)
 
     # ------------------------------------------------------------------ all_reduce
@@ -229,6 +258,10 @@ class CCL:
         """``output = sum over ranks of input`` on every rank (fp32 accumulation). Returns the workspace."""
         if op is not None and op != ReduceOp.SUM:
             raise ValueError("only ReduceOp.SUM is supported")
+        key = self._fast_key("ar", output_tensor, input_tensor, group, config, None if workspace is None else id(workspace))
+        hit = self._fast.get(key)
+        if hit is not None:
+            return self._replay(hit, async_op, group)
         config = config or Config()
         if config.use_gluon:
             raise ValueError("use_gluon has no meaning on this backend")
@@ -264,6 +297,7 @@ class CCL:
             elif ws.variant == "spinlock":
                 d.flags = ws.flags.data_ptr()
             self._launch(2, d)
+            self._remember(key, 2, d, ws)
         ws.prepared = False
         self._finish(async_op, group)
         return ws
@@ -279,6 +313,10 @@ class CCL:
         """
         if op is not None and op != ReduceOp.SUM:
             raise ValueError("only ReduceOp.SUM is supported")
+        key = self._fast_key("rs", output_tensor, input_tensor, group, config)
+        hit = self._fast.get(key)
+        if hit is not None:
+            return self._replay(hit, async_op, group)
         config = config or Config()
         out, inp = _as_2d(output_tensor), _as_2d(input_tensor)
         self._check(out, inp)
@@ -306,6 +344,7 @@ class CCL:
             d.M, d.N = M, N
             d.rows_mode = 1 if rows else 0
             self._launch(3, d)
+            self._remember(key, 3, d)
         self._finish(async_op, group)
 
     # ------------------------------------------------------------------ CPU backend helpers

@@ -37,6 +37,7 @@ __all__ = [
 ]
 
 _FUSED_DTYPES = (torch.bfloat16, torch.float16)
+_DEFAULT_CONFIG = FusedConfig()      # what config=None means; never mutated
 
 
 def _fusable(ctx, *tensors) -> bool:
@@ -166,7 +167,7 @@ def _agm_desc(ctx, out, A_sharded, B, bias, config, shard_dim):
 
 def all_gather_matmul_preamble(shmem, A_sharded, B, config=None, shard_dim=1):
     """Allocate the workspace of ``all_gather_matmul`` (collective)."""
-    config = config or FusedConfig()
+    config = config or _DEFAULT_CONFIG
     if not _fusable(shmem, A_sharded, B):
         return FusedWorkspace(operation="all_gather_matmul", variant="unfused", world_size=shmem.num_ranks, prepared=True)
     W = shmem.num_ranks
@@ -188,7 +189,7 @@ def all_gather_matmul(shmem, output_tensor, A_sharded, B, bias=None, async_op=Fa
     ``(M, K/W)``, rank r holding columns ``[r*K/W, (r+1)*K/W)``. ``shard_dim=0``: ``A_sharded`` is
     ``(M/W, K)``, rank r holding rows ``[r*M/W, (r+1)*M/W)`` and the output is ``(M, N)``.
     """
-    config = config or FusedConfig()
+    config = config or _DEFAULT_CONFIG
     W = shmem.num_ranks
     key = tuple(A_sharded.shape) + tuple(B.shape) + (shard_dim,)
     ws = workspace
@@ -220,7 +221,7 @@ def _unfused_gather(ctx, A_sharded, shard_dim):
 
 # ----------------------------------------------------------------------------- matmul_all_gather
 def matmul_all_gather_preamble(shmem, A, B, config=None, scatter_cols=False):
-    config = config or FusedConfig()
+    config = config or _DEFAULT_CONFIG
     if not _fusable(shmem, A, B):
         return FusedWorkspace(operation="matmul_all_gather", variant="unfused", world_size=shmem.num_ranks, prepared=True)
     W = shmem.num_ranks
@@ -241,7 +242,7 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
     ``[r*N_local, (r+1)*N_local)`` of every rank's ``(M, W*N_local)`` output: the "GEMM +
     all-scatter" layout of the reference's examples/07_gemm_all_scatter.
     """
-    config = config or FusedConfig()
+    config = config or _DEFAULT_CONFIG
     W = shmem.num_ranks
     M, K = A.shape
     N = B.shape[1]
@@ -274,7 +275,7 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
 
 # ----------------------------------------------------------------------------- matmul_all_reduce
 def matmul_all_reduce_preamble(shmem, C_out, A, B, config=None):
-    config = config or FusedConfig()
+    config = config or _DEFAULT_CONFIG
     if not _fusable(shmem, A, B) or not shmem.is_symmetric(C_out):
         return FusedWorkspace(operation="matmul_all_reduce", variant="unfused", world_size=shmem.num_ranks, prepared=True)
     M, K = A.shape
@@ -287,7 +288,7 @@ def matmul_all_reduce_preamble(shmem, C_out, A, B, config=None):
 def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, config=None, workspace=None):
     """``output = sum over ranks of (A_r @ B_r)`` (+ bias) on every rank
     (reference: iris/ops/matmul_all_reduce.py:222-372). The bias, if any, is added once."""
-    config = config or FusedConfig()
+    config = config or _DEFAULT_CONFIG
     W = shmem.num_ranks
     M, K = A.shape
     N = B.shape[1]
@@ -315,7 +316,7 @@ def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, con
 
 # ----------------------------------------------------------------------------- matmul_reduce_scatter
 def matmul_reduce_scatter_preamble(shmem, C_out, A, B, config=None, scatter_rows=False):
-    config = config or FusedConfig()
+    config = config or _DEFAULT_CONFIG
     if not _fusable(shmem, A, B):
         return FusedWorkspace(operation="matmul_reduce_scatter", variant="unfused", world_size=shmem.num_ranks, prepared=True)
     M, K = A.shape
@@ -345,7 +346,7 @@ def matmul_reduce_scatter(shmem, output_tensor, A, B, bias=None, async_op=False,
     ``output`` is left untouched. ``scatter_rows=True``: ``output`` is ``(M/W, N)``, this rank's row
     block of the sum (the tensor-parallel layout).
     """
-    config = config or FusedConfig()
+    config = config or _DEFAULT_CONFIG
     W = shmem.num_ranks
     M, K = A.shape
     N = B.shape[1]
