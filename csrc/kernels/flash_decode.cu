@@ -5,9 +5,12 @@
 //   1. splitk kernel  grid (splits, kv_heads * head_groups, batch): attention of the query heads
 //      of one KV head over one slice of the LOCAL KV shard, paged KV gathered through the block
 //      table, online softmax; writes a normalised partial output and its log-sum-exp per split.
-//      K/V stream through a cp.async ring of swizzled shared-memory tiles; QK^T and PV run on
-//      tensor cores with the query heads of the group as the M dimension (each K/V byte is read
-//      from HBM exactly once; the kernel is bound by HBM bandwidth).
+//      K/V stream through a ring of swizzled shared-memory tiles; QK^T and PV run on tensor
+//      cores with the query heads of the group as the M dimension (each K/V byte is read from HBM
+//      exactly once; the kernel is bound by HBM bandwidth). Two ways of filling the ring: one
+//      thread issuing TMA box loads per page through a tensor map over the cache (page sizes 8,
+//      16, 32 or a multiple of 64; completion on an mbarrier per stage), or all threads issuing
+//      16-byte cp.async copies (any page size).
 //   2. exchange kernel (persistent): phase A combines the local splits of every (batch, head) and
 //      stores (o, lse) into slot [my_rank] of every rank's gathered buffer, then raises that
 //      rank's flag for (my_rank, batch, head) with release semantics; phase B waits (acquire,
@@ -22,8 +25,11 @@
 #include <math.h>
 #include <string.h>
 
+#include <cuda.h>
+
 #include "iris/host_api.h"
 #include "iris/iris.cuh"
+#include "iris/ptx.cuh"
 #include "flash_decode_static.h"
 #include <stdio.h>
 
@@ -40,6 +46,10 @@ constexpr int kTileBytes = kBlockN * kRowBytes;   // 16 KB per K or V tile
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct DecodeArgs {
+  alignas(64) CUtensorMap tmK;     // TMA path: 2-D maps over the caches seen as [num_blocks * page, Hkv * D],
+  alignas(64) CUtensorMap tmV;     // box = 64 columns (128 bytes, swizzled) x box_rows positions
+  int box_rows;                    // min(page, 64)
+  int32_t* status;                 // context status word (a TMA wait that runs out is recorded there)
   const __nv_bfloat16* q;          // [B, Hq, D]
   const __nv_bfloat16* k_cache;    // [num_blocks, page, Hkv, D]
   const __nv_bfloat16* v_cache;
@@ -79,12 +89,23 @@ template <bool kFp16> __device__ __forceinline__ uint32_t pack2(float a, float b
   else { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); return *(uint32_t*)&h; }
 }
 
-// Shared-memory tile [kBlockN positions][16 chunks of 16 B], chunk index XOR-swizzled by row & 7.
-__device__ __forceinline__ uint32_t tile_off(int row, int chunk) { return row * kRowBytes + ((chunk ^ (row & 7)) << 4); }
+// Shared-memory tile of kBlockN positions x 16 chunks of 16 B.
+// cp.async path: [position][16 chunks], chunk index XOR-swizzled by row & 7.
+// TMA path: two halves of the head dimension, each [position][128 bytes] in the 128-byte swizzle
+// TMA writes (chunk index within the half XOR row & 7; tiles are 1024-byte aligned).
+template <bool kTma>
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+  if constexpr (kTma) return (chunk >> 3) * (kBlockN * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+  else return row * kRowBytes + ((chunk ^ (row & 7)) << 4);
+}
 
-template <bool kFp16>
+constexpr uint64_t kTmaWaitNs = 2000000000ull;
+
+template <bool kFp16, bool kTma>
 __global__ void __launch_bounds__(kWarps * 32, 2) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  // the TMA path needs 1024-byte aligned tiles (the launch adds the slack)
+  uint8_t* smem = kTma ? (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023) : smem_raw;
   const int split = blockIdx.x;
   const int kvh = blockIdx.y / a.head_groups, hg = blockIdx.y % a.head_groups;
   const int b = blockIdx.z;
@@ -135,25 +156,78 @@ __global__ void __launch_bounds__(kWarps * 32, 2) decode_splitk_kernel(const __g
       if (pos < hi) {
         const int blk = bt[pos / a.page];
         const size_t e = ((size_t)blk * a.page + pos % a.page) * pos_stride + (size_t)kvh * kD + chunk * 8;
-        cp_async16(ks + tile_off(row, chunk), a.k_cache + e);
-        cp_async16(vs + tile_off(row, chunk), a.v_cache + e);
+        cp_async16(ks + tile_off<false>(row, chunk), a.k_cache + e);
+        cp_async16(vs + tile_off<false>(row, chunk), a.v_cache + e);
       } else {
-        *(uint4*)(smem + stage * 2 * kTileBytes + tile_off(row, chunk)) = make_uint4(0, 0, 0, 0);
-        *(uint4*)(smem + stage * 2 * kTileBytes + kTileBytes + tile_off(row, chunk)) = make_uint4(0, 0, 0, 0);
+        *(uint4*)(smem + stage * 2 * kTileBytes + tile_off<false>(row, chunk)) = make_uint4(0, 0, 0, 0);
+        *(uint4*)(smem + stage * 2 * kTileBytes + kTileBytes + tile_off<false>(row, chunk)) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  // TMA path, one thread: one box per page piece and half of the head dimension, for K and for V.
+  // Tiles start at multiples of 64 positions, so a box never straddles a page.
+  uint64_t* full = (uint64_t*)(smem + kStages * 2 * kTileBytes);
+  auto issue_tile_tma = [&](int t) {
+    const int stage = t % kStages;
+    uint8_t* kdst = smem + stage * 2 * kTileBytes;
+    uint8_t* vdst = kdst + kTileBytes;
+    const int pos0 = lo + t * kBlockN;
+    const int rows = min(kBlockN, hi - pos0);
+    const int nbox = (rows + a.box_rows - 1) / a.box_rows;
+    ptx::mbar_expect_tx(&full[stage], (uint32_t)(nbox * a.box_rows * 128 * 4));
+    for (int j = 0; j < nbox; ++j) {
+      const int pos = pos0 + j * a.box_rows;
+      const int y = bt[pos / a.page] * a.page + pos % a.page;
+      const int off = j * a.box_rows * 128;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        ptx::tma_load_2d(kdst + half * (kBlockN * 128) + off, &a.tmK, &full[stage], kvh * kD + half * 64, y);
+        ptx::tma_load_2d(vdst + half * (kBlockN * 128) + off, &a.tmV, &full[stage], kvh * kD + half * 64, y);
       }
     }
   };
 
-  for (int t = 0; t < kStages - 1; ++t) {
-    if (t < n_tiles) issue_tile(t);
-    cp_async_commit();
+  if constexpr (kTma) {
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < kStages; ++i) ptx::mbar_init(&full[i], 1);
+      ptx::fence_mbar_init();
+      ptx::fence_proxy_async();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+      for (int t = 0; t < kStages - 1 && t < n_tiles; ++t) issue_tile_tma(t);
+  } else {
+    for (int t = 0; t < kStages - 1; ++t) {
+      if (t < n_tiles) issue_tile(t);
+      cp_async_commit();
+    }
   }
   for (int t = 0; t < n_tiles; ++t) {
-    cp_async_wait<kStages - 2>();
-    __syncthreads();
-    if (t + kStages - 1 < n_tiles) issue_tile(t + kStages - 1);
-    cp_async_commit();
     const int stage = t % kStages;
+    if constexpr (kTma) {
+      if (!ptx::mbar_wait(&full[stage], (uint32_t)((t / kStages) & 1), kTmaWaitNs)) {
+        if (a.status) atomicCAS(a.status, 0, (int)kTimeoutPipeline);
+        break;     // every thread of the CTA waits on the same barrier, so all of them leave here
+      }
+      __syncthreads();   // everybody is done with tile t-1: its stage can be refilled
+      if (threadIdx.x == 0 && t + kStages - 1 < n_tiles) issue_tile_tma(t + kStages - 1);
+      const int rows = hi - (lo + t * kBlockN);
+      if (rows < kBlockN) {
+        // last, partial tile: rows past the end hold whatever the page (or an older tile) held;
+        // their scores are masked below, and their V rows are cleared so that 0 * NaN cannot arise
+        uint8_t* vt = smem + stage * 2 * kTileBytes + kTileBytes;
+        for (int idx = threadIdx.x; idx < (kBlockN - rows) * 16; idx += blockDim.x) {
+          const int row = rows + (idx >> 4), chunk = idx & 15;
+          *(uint4*)(vt + tile_off<true>(row, chunk)) = make_uint4(0, 0, 0, 0);
+        }
+        __syncthreads();
+      }
+    } else {
+      cp_async_wait<kStages - 2>();
+      __syncthreads();
+      if (t + kStages - 1 < n_tiles) issue_tile(t + kStages - 1);
+      cp_async_commit();
+    }
     const uint32_t ks = smem_base + stage * 2 * kTileBytes, vs = ks + kTileBytes;
     const int p0 = warp * 16;   // this warp's 16 positions of the tile
 
@@ -163,7 +237,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) decode_splitk_kernel(const __g
     for (int kk = 0; kk < 8; ++kk) {
       uint32_t kf[4];
       const int j = lane >> 3, r = lane & 7;
-      ldmatrix_x4(kf, ks + tile_off(p0 + (j >> 1) * 8 + r, kk * 2 + (j & 1)));
+      ldmatrix_x4(kf, ks + tile_off<kTma>(p0 + (j >> 1) * 8 + r, kk * 2 + (j & 1)));
       mma16816<kFp16>(s[0], qf[kk], kf[0], kf[1]);
       mma16816<kFp16>(s[1], qf[kk], kf[2], kf[3]);
     }
@@ -220,12 +294,12 @@ __global__ void __launch_bounds__(kWarps * 32, 2) decode_splitk_kernel(const __g
     for (int nb2 = 0; nb2 < 8; ++nb2) {
       uint32_t vf[4];
       const int j = lane >> 3, r = lane & 7;
-      ldmatrix_x4_trans(vf, vs + tile_off(p0 + (j & 1) * 8 + r, nb2 * 2 + (j >> 1)));
+      ldmatrix_x4_trans(vf, vs + tile_off<kTma>(p0 + (j & 1) * 8 + r, nb2 * 2 + (j >> 1)));
       mma16816<kFp16>(o[nb2 * 2], pf, vf[0], vf[1]);
       mma16816<kFp16>(o[nb2 * 2 + 1], pf, vf[2], vf[3]);
     }
   }
-  cp_async_wait<0>();
+  if constexpr (!kTma) cp_async_wait<0>();
   __syncthreads();
 
   // ---- merge the 4 warps (each saw a quarter of the positions), write the partial for this split
@@ -373,7 +447,32 @@ typedef struct IrisDecodeDesc {
   float sm_scale, soft_cap;
   int32_t dtype;
   int32_t exchange;   // 0: only the local split-K pass, 1: also combine + exchange + merge
+  int32_t num_blocks; // pages in each cache tensor (0: unknown, the TMA path is not used)
 } IrisDecodeDesc;
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// 2-D map over a cache seen as [num_blocks * page positions, Hkv * D] 16-bit elements.
+bool make_cache_map(CUtensorMap* m, const void* base, int dtype, uint64_t positions, uint64_t row_elems, uint32_t box_rows) {
+  static EncodeTiledFn enc = nullptr;
+  if (!enc) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) return false;
+    enc = (EncodeTiledFn)p;
+  }
+  if (((uint64_t)base & 15) || ((row_elems * 2) & 15)) return false;
+  cuuint64_t dims[2] = {row_elems, positions};
+  cuuint64_t strides[1] = {row_elems * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = dtype == IRIS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return enc(m, dt, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
 
 int iris_flash_decode(const IrisDecodeDesc* d, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
@@ -386,17 +485,34 @@ int iris_flash_decode(const IrisDecodeDesc* d, void* stream) {
   a.B = d->B; a.Hq = d->Hq; a.Hkv = d->Hkv; a.page = d->page; a.max_blocks = d->max_blocks; a.splits = d->splits;
   a.group = d->Hq / d->Hkv; a.head_groups = (a.group + 15) / 16;
   a.sm_scale = d->sm_scale; a.soft_cap = d->soft_cap; a.is_fp16 = d->dtype == IRIS_F16;
+  a.status = d->ctx.status; a.box_rows = 0;
+  // TMA fill when a 64-position tile is a whole number of page pieces
+  bool tma = d->num_blocks > 0 && (d->page == 8 || d->page == 16 || d->page == 32 || d->page % 64 == 0);
+  if (tma) {
+    a.box_rows = d->page < kBlockN ? d->page : kBlockN;
+    const uint64_t positions = (uint64_t)d->num_blocks * d->page, row = (uint64_t)d->Hkv * kD;
+    tma = make_cache_map(&a.tmK, d->k_cache, d->dtype, positions, row, a.box_rows) &&
+          make_cache_map(&a.tmV, d->v_cache, d->dtype, positions, row, a.box_rows);
+  }
   const int smem = kStages * 2 * kTileBytes > (int)((kWarps * 16 * kD + kWarps * 32) * sizeof(float))
                        ? kStages * 2 * kTileBytes : (int)((kWarps * 16 * kD + kWarps * 32) * sizeof(float));
+  const int smem_tma = smem + 64 + 1024;     // stage barriers, alignment slack
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(decode_splitk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -20;
-    if (cudaFuncSetAttribute(decode_splitk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -20;
+    if (cudaFuncSetAttribute(decode_splitk_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -20;
+    if (cudaFuncSetAttribute(decode_splitk_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -20;
+    if (cudaFuncSetAttribute(decode_splitk_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tma) != cudaSuccess) return -20;
+    if (cudaFuncSetAttribute(decode_splitk_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tma) != cudaSuccess) return -20;
     attr = true;
   }
   dim3 grid(d->splits, d->Hkv * a.head_groups, d->B);
-  if (a.is_fp16) decode_splitk_kernel<true><<<grid, kWarps * 32, smem, s>>>(a);
-  else decode_splitk_kernel<false><<<grid, kWarps * 32, smem, s>>>(a);
+  if (tma) {
+    if (a.is_fp16) decode_splitk_kernel<true, true><<<grid, kWarps * 32, smem_tma, s>>>(a);
+    else decode_splitk_kernel<false, true><<<grid, kWarps * 32, smem_tma, s>>>(a);
+  } else {
+    if (a.is_fp16) decode_splitk_kernel<true, false><<<grid, kWarps * 32, smem, s>>>(a);
+    else decode_splitk_kernel<false, false><<<grid, kWarps * 32, smem, s>>>(a);
+  }
   if (cudaGetLastError() != cudaSuccess) return -21;
   if (!d->exchange) return 0;
   ExchangeArgs x;
@@ -498,20 +614,21 @@ extern "C" int iris_flash_decode_static(const void* q, const void* k_cache, cons
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.page = page; a.max_blocks = max_blocks; a.splits = splits;
   a.group = Hq / Hkv; a.head_groups = (a.group + 15) / 16;
   a.sm_scale = sm_scale; a.soft_cap = soft_cap; a.is_fp16 = dtype == IRIS_F16;
+  a.status = nullptr; a.box_rows = 0;     // the cp.async instantiation: no tensor maps
   const int smem = kStages * 2 * kTileBytes > (int)((kWarps * 16 * kD + kWarps * 32) * sizeof(float))
                        ? kStages * 2 * kTileBytes : (int)((kWarps * 16 * kD + kWarps * 32) * sizeof(float));
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(decode_splitk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(decode_splitk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(decode_splitk_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_splitk_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
       static_err(err, errlen, "iris_flash_decode_static: cannot raise the kernel's shared-memory limit");
       return -20;
     }
     attr = true;
   }
   dim3 grid(splits, Hkv * a.head_groups, B);
-  if (a.is_fp16) decode_splitk_kernel<true><<<grid, kWarps * 32, smem, s>>>(a);
-  else decode_splitk_kernel<false><<<grid, kWarps * 32, smem, s>>>(a);
+  if (a.is_fp16) decode_splitk_kernel<true, false><<<grid, kWarps * 32, smem, s>>>(a);
+  else decode_splitk_kernel<false, false><<<grid, kWarps * 32, smem, s>>>(a);
   if (cudaGetLastError() != cudaSuccess) {
     static_err(err, errlen, "iris_flash_decode_static: split-K kernel launch failed");
     return -21;

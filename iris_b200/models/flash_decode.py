@@ -36,6 +36,7 @@ class IrisDecodeDesc(C.Structure):
         ("sm_scale", C.c_float), ("soft_cap", C.c_float),
         ("dtype", C.c_int32),
         ("exchange", C.c_int32),
+        ("num_blocks", C.c_int32),
     ]
 
 
@@ -78,7 +79,8 @@ def merge_partials(o_parts, lse_parts):
 
 class FlashDecodeLayer:
     def __init__(self, ctx, num_q_heads: int, num_kv_heads: int, head_dim: int = 128, max_batch: int = 64,
-                 sm_scale: float | None = None, soft_cap: float = 0.0, max_splits: int = 64, dtype=torch.bfloat16):
+                 sm_scale: float | None = None, soft_cap: float = 0.0, max_splits: int = 64, dtype=torch.bfloat16,
+                 use_tma: bool | None = None):
         if head_dim != 128:
             raise ValueError("the decode kernel is specialised for head_dim 128")
         if num_q_heads % num_kv_heads:
@@ -89,6 +91,7 @@ class FlashDecodeLayer:
         self.sm_scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(head_dim)
         self.soft_cap = float(soft_cap)
         self.dtype = dtype
+        self.use_tma = use_tma      # None: TMA tile fill whenever the page size allows it; False: cp.async fill
         W = ctx.get_num_ranks()
         dev = ctx.get_device()
         # exchange buffers on the heap: [2][W][Bmax][Hq][D+1] fp32 and [2][W][Bmax][Hq] int32
@@ -139,6 +142,7 @@ class FlashDecodeLayer:
         d.sm_scale, d.soft_cap = self.sm_scale, self.soft_cap
         d.dtype = _lib.DTYPE_CODE[q.dtype]
         d.exchange = 1
+        d.num_blocks = 0 if self.use_tma is False else k_cache.shape[0]     # > 0 lets the kernel fill its tiles by TMA
         if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous() and block_table.is_contiguous()):
             raise ValueError("flash decode takes contiguous q, caches and block table")
         _lib.check(self._lib().iris_flash_decode(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "flash decode launch")

@@ -244,6 +244,39 @@ def test_flash_decode_matches_reference(ctx, batch, lens, page, heads):
     ctx.check()
 
 
+@pytest.mark.parametrize("page,use_tma", [(64, None), (16, None), (64, False), (48, None)])
+def test_flash_decode_ignores_positions_past_the_length(ctx, page, use_tma):
+    """Cache rows past a sequence's length (same page or unused pages) hold NaN: both tile-fill paths
+    (TMA boxes per page, cp.async for page sizes a 64-position tile does not divide into) must mask them."""
+    from iris_b200.models import FlashDecodeLayer, reference_decode
+
+    Hq, Hkv, dt = 16, 2, torch.bfloat16
+    lens = [page * 3 + 5, 70, 1]
+    batch = len(lens)
+    torch.manual_seed(5)
+    max_blocks = -(-max(lens) // page)
+    nblocks = batch * max_blocks + 2
+    kc = torch.randn(nblocks, page, Hkv, 128, device="cuda", dtype=dt)
+    vc = torch.randn(nblocks, page, Hkv, 128, device="cuda", dtype=dt)
+    table = torch.randperm(nblocks, device="cuda")[: batch * max_blocks].to(torch.int32).view(batch, max_blocks)
+    used = torch.zeros(nblocks, page, dtype=torch.bool, device="cuda")
+    for b, n in enumerate(lens):
+        for pos in range(n):
+            used[int(table[b, pos // page]), pos % page] = True
+    kc[~used] = float("nan")
+    vc[~used] = float("nan")
+    q = torch.randn(batch, Hq, 128, device="cuda", dtype=dt)
+    kv_lens = torch.tensor([lens], device="cuda", dtype=torch.int32)
+    layer = FlashDecodeLayer(ctx, Hq, Hkv, 128, max_batch=4, use_tma=use_tma)
+    out, lse = layer(q, kc, vc, kv_lens, table, return_lse=True)
+    kz, vz = torch.nan_to_num(kc, nan=0.0), torch.nan_to_num(vc, nan=0.0)
+    ro, rlse = reference_decode(q, kz, vz, kv_lens[0], table)
+    assert torch.isfinite(out.float()).all()
+    assert (out.float() - ro).abs().max().item() < 2e-2
+    assert (lse - rlse).abs().max().item() < 2e-2
+    ctx.check()
+
+
 @pytest.mark.parametrize("T,E,K", [(64, 8, 2), (200, 16, 4), (128, 32, 8)])
 def test_moe_layer_world1(ctx, T, E, K):
     from iris_b200.models import MoELayer, reference_moe
