@@ -1,0 +1,296 @@
+// Block-scaled fp8 (e4m3) GEMM for sm_100a: C[m, n] = sum_kb sA[m, kb] * sB[n / 128, kb] *
+// (sum over the 128 k of block kb of A[m, k] * B[n, k]), 16-bit output.
+//
+// The scale layout is the one of block-quantised transformer weights: activations carry one fp32
+// scale per row and 128-wide K block (1 x 128), weights one per 128 x 128 block. The reference
+// has no fp8 path (its GEMM main loop, iris/ops/matmul_all_reduce.py:95-105, is 16-bit); this
+// kernel is the local building block for fp8 variants of the fused ops.
+//
+// tcgen05.mma.kind::f8f6f4 accumulates in fp32 but knows nothing about per-block scales, so one
+// K block (128 elements = one 128-byte swizzle row = four MMAs of K 32) is accumulated into a
+// fresh TMEM buffer and then "promoted": the epilogue warps read the partial sums with tcgen05.ld,
+// multiply by sA * sB and add them to accumulators they keep in REGISTERS for the whole tile.
+// Two TMEM buffers of 256 columns alternate, so the MMAs of block kb + 1 run while block kb is
+// promoted. Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 promotion +
+// epilogue (warp w: TMEM lanes 32 * (w % 4) .. +32, output columns 128 * ((w - 2) / 4) .. +128,
+// i.e. 128 accumulators per thread). Per K block a thread issues 128 FFMA and four tcgen05.ld;
+// the MMAs of the block take about 520 cycles, so promotion is hidden as long as it issues.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <string.h>
+
+#include "iris/host_api.h"
+#include "iris/common.cuh"
+#include "iris/ptx.cuh"
+#include "iris/gemm/sm100_mainloop.cuh"
+
+using namespace iris;
+using namespace iris::gemm;
+
+namespace {
+
+constexpr int kBN8 = 256;
+constexpr int kBK8 = 128;                 // fp8 elements = bytes per swizzle row = the scale block
+constexpr int kStages8 = 4;
+constexpr int kThreads8 = 320;
+constexpr int kPromoWarps = 8;
+constexpr int kABytes8 = kBM * kBK8;      // 16 KB
+constexpr int kBBytes8 = kBN8 * kBK8;     // 32 KB
+constexpr int kStageBytes8 = kABytes8 + kBBytes8;
+constexpr int kEpiBytes8 = kPromoWarps * 2048;
+constexpr int kSmemBytes8 = 1024 + kStages8 * kStageBytes8 + kEpiBytes8 + 256;
+static_assert(kSmemBytes8 <= 227 * 1024, "shared memory budget");
+
+struct Fp8Args {
+  CUtensorMap tmA;          // [M, K] bytes, box 128 x 128
+  CUtensorMap tmB;          // [N, K] bytes, box 128 x 256
+  const float* sA;          // [M, kblocks]
+  const float* sB;          // [ceil(N / 128), kblocks]
+  uint8_t* C;               // [M, N] 16-bit, pitch ldc elements
+  int64_t ldc;
+  int M, N, K;
+  int tiles_m, tiles_n, group_m;
+  int out_bf16;
+  int32_t* status;
+};
+
+// kind::f8f6f4 instruction descriptor: fp32 accumulate, A and B e4m3 (format 0), both K-major.
+__host__ __device__ constexpr uint32_t idesc_fp8(int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(kThreads8, 1) gemm_fp8_kernel(const __grid_constant__ Fp8Args a) {
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint8_t* epi_base = smem + kStages8 * kStageBytes8;
+  uint64_t* bars = (uint64_t*)(epi_base + kEpiBytes8);
+  uint64_t* full = bars;                      // [stages]  TMA bytes landed
+  uint64_t* empty = bars + kStages8;          // [stages]  MMAs that read the stage retired
+  uint64_t* acc_full = bars + 2 * kStages8;   // [2]       partial sums of one K block complete
+  uint64_t* acc_empty = acc_full + 2;         // [2]       partial sums promoted by all 8 warps
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages8; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&acc_full[b], 1);
+      ptx::mbar_init(&acc_empty[b], kPromoWarps);
+    }
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+
+  const int num_tiles = a.tiles_m * a.tiles_n;
+  const int k_blocks = (a.K + kBK8 - 1) / kBK8;
+  const int first = blockIdx.x, step = gridDim.x;
+  auto fail = [&]() {
+    if (a.status) atomicCAS(a.status, 0, (int)kTimeoutPipeline);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      ptx::prefetch_tmap(&a.tmA);
+      ptx::prefetch_tmap(&a.tmB);
+    }
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int t = first; t < num_tiles && ok; t += step) {
+      int tm, tn;
+      swizzled_tile(t, a.tiles_m, a.tiles_n, a.group_m, tm, tn);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!ptx::mbar_wait(&empty[s], ph ^ 1, kPipeTimeoutNs)) { fail(); ok = false; break; }
+        if (lane == 0) {
+          uint8_t* sa = stage_base + s * kStageBytes8;
+          ptx::mbar_expect_tx(&full[s], kStageBytes8);
+          ptx::tma_load_2d(sa, &a.tmA, &full[s], kb * kBK8, tm * kBM);
+          ptx::tma_load_2d(sa + kABytes8, &a.tmB, &full[s], kb * kBK8, tn * kBN8);
+        }
+        __syncwarp();
+        if (++s == kStages8) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = idesc_fp8(kBN8);
+    int s = 0;
+    uint32_t ph = 0;
+    uint32_t blk = 0;      // K blocks issued so far by this CTA: selects the TMEM buffer and its phase
+    bool ok = true;
+    for (int t = first; t < num_tiles && ok; t += step) {
+      for (int kb = 0; kb < k_blocks; ++kb, ++blk) {
+        const int buf = blk & 1;
+        if (!ptx::mbar_wait(&acc_empty[buf], ((blk >> 1) & 1) ^ 1, kPipeTimeoutNs)) { fail(); ok = false; break; }
+        if (!ptx::mbar_wait(&full[s], ph, kPipeTimeoutNs)) { fail(); ok = false; break; }
+        ptx::tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = ptx::smem_u32(stage_base + s * kStageBytes8);
+          const uint32_t sb = sa + kABytes8;
+          const uint32_t d_tmem = tmem_base + buf * 256;
+#pragma unroll
+          for (int k = 0; k < kBK8 / 32; ++k)
+            ptx::mma_f8(d_tmem, desc_kmajor(sa + k * 32), desc_kmajor(sb + k * 32), idesc, k != 0);
+          ptx::mma_commit(&empty[s]);
+          ptx::mma_commit(&acc_full[buf]);
+        }
+        __syncwarp();
+        if (++s == kStages8) { s = 0; ph ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ promotion + epilogue
+    const int pw = warp - 2;
+    const int quarter = warp & 3;           // TMEM lanes this warp may read
+    const int half = pw >> 2;               // which 128 output columns
+    uint8_t* my_epi = epi_base + pw * 2048;
+    const int sb_rows = (a.N + 127) / 128;
+    uint32_t blk = 0;
+    bool ok = true;
+    for (int t = first; t < num_tiles && ok; t += step) {
+      int tm, tn;
+      swizzled_tile(t, a.tiles_m, a.tiles_n, a.group_m, tm, tn);
+      const int row = tm * kBM + quarter * 32 + lane;
+      const int srow = row < a.M ? row : a.M - 1;
+      const int sbr = min(tn * 2 + half, sb_rows - 1);
+      const float* sa_row = a.sA + (size_t)srow * k_blocks;
+      const float* sb_row = a.sB + (size_t)sbr * k_blocks;
+      float acc[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      float scale_next = __ldg(sa_row) * __ldg(sb_row);
+      for (int kb = 0; kb < k_blocks; ++kb, ++blk) {
+        const int buf = blk & 1;
+        const float scale = scale_next;
+        if (kb + 1 < k_blocks) scale_next = __ldg(sa_row + kb + 1) * __ldg(sb_row + kb + 1);
+        if (!ptx::mbar_wait(&acc_full[buf], (blk >> 1) & 1, kPipeTimeoutNs)) { fail(); ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + half * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(t_addr + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (c == 3) {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(scale, __uint_as_float(r[j]), acc[c * 32 + j]);
+        }
+      }
+      if (!ok) break;
+      // ---- tile epilogue: 16-bit, shared-memory transpose, 16-byte row-major stores
+      const int row0 = tm * kBM + quarter * 32;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int col0 = tn * kBN8 + half * 128 + c * 32;
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (a.out_bf16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(acc[c * 32 + 2 * j], acc[c * 32 + 2 * j + 1]);
+            packed[j] = *(uint32_t*)&h;
+          } else {
+            __half2 h = __floats2half2_rn(acc[c * 32 + 2 * j], acc[c * 32 + 2 * j + 1]);
+            packed[j] = *(uint32_t*)&h;
+          }
+        }
+        const int sw = (lane >> 1) & 3;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 v = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          *(uint4*)(my_epi + lane * 64 + ((j ^ sw) * 16)) = v;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int rr = i * 8 + (lane >> 2), cc = lane & 3;
+          uint4 v = *(uint4*)(my_epi + rr * 64 + ((cc ^ ((rr >> 1) & 3)) * 16));
+          const int orow = row0 + rr, ocol = col0 + cc * 8;
+          if (orow < a.M && ocol < a.N) *(uint4*)(a.C + ((int64_t)orow * a.ldc + ocol) * 2) = v;
+        }
+        __syncwarp();
+      }
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, 512);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// 2-D map over a row-major [rows, cols] byte matrix with pitch `ld` bytes; box = 128 bytes x box_rows.
+int make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  static EncodeTiledFn enc = nullptr;
+  if (!enc) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) return -10;
+    enc = (EncodeTiledFn)p;
+  }
+  if (((uint64_t)base & 15) || (ld & 15)) return -11;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
+}  // namespace
+
+extern "C" int iris_gemm_fp8_launch(const IrisFp8GemmDesc* d, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return -3;
+  if (d->K % 16 || d->N % 8 || d->lda % 16 || d->ldb % 16) return -3;   // TMA pitch and 16-byte output stores
+  if (d->out_dtype != IRIS_BF16 && d->out_dtype != IRIS_F16) return -2;
+  Fp8Args a;
+  int r = make_map_u8(&a.tmA, d->A, d->M, d->K, d->lda, kBM);
+  if (r) return r;
+  r = make_map_u8(&a.tmB, d->B, d->N, d->K, d->ldb, kBN8);
+  if (r) return r;
+  a.sA = d->scale_a; a.sB = d->scale_b;
+  a.C = (uint8_t*)d->C; a.ldc = d->ldc;
+  a.M = d->M; a.N = d->N; a.K = d->K;
+  a.tiles_m = (d->M + kBM - 1) / kBM;
+  a.tiles_n = (d->N + kBN8 - 1) / kBN8;
+  a.group_m = 8;
+  a.out_bf16 = d->out_dtype == IRIS_BF16;
+  a.status = d->status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes8) != cudaSuccess) return -20;
+    attr_set = true;
+  }
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int tiles = a.tiles_m * a.tiles_n;
+  gemm_fp8_kernel<<<tiles < sms ? tiles : sms, kThreads8, kSmemBytes8, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}

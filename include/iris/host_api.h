@@ -67,6 +67,22 @@ typedef struct IrisGemmDesc {
                           // 1 operands available, 2 stored; comm CTA 0 stamps slot tiles+c, col 3)
 } IrisGemmDesc;
 
+// Block-scaled fp8 (e4m3) GEMM: C = (A * scale_a) @ (B * scale_b)^T with A [M, K] and B [N, K]
+// row-major bytes, scale_a [M, ceil(K/128)] (one per row and 128-wide K block), scale_b
+// [ceil(N/128), ceil(K/128)] (one per 128 x 128 block), fp32 accumulation, 16-bit output.
+typedef struct IrisFp8GemmDesc {
+  const void* A;          // e4m3, pitch lda bytes (multiple of 16)
+  const void* B;          // e4m3, pitch ldb bytes (multiple of 16)
+  const float* scale_a;
+  const float* scale_b;
+  void* C;                // [M, N] 16-bit, pitch ldc elements
+  int64_t lda, ldb, ldc;
+  int32_t M, N, K;
+  int32_t out_dtype;      // IRIS_BF16 or IRIS_F16
+  int32_t* status;        // optional status word (a pipeline wait that runs out is recorded there)
+} IrisFp8GemmDesc;
+int iris_gemm_fp8_launch(const IrisFp8GemmDesc* d, void* stream);
+
 // Bytes of workspace the op needs for this shape (inbox / flags / staging) and the tile the plan
 // picked (width, and whether CTA pairs run 256-row tiles). Pure arithmetic.
 int iris_gemm_workspace(const IrisGemmDesc* d, uint64_t* inbox_bytes, uint64_t* flags_bytes, uint64_t* staging_bytes,

@@ -370,3 +370,19 @@ ptxas info    : Used 18 registers, used 0 barriers
     if meta:                                  # a build has run in this tree
         out = artifacts.export(tmp_path)
         assert any((out / name.replace(".cu", "") / "metadata.json").exists() for name in meta)
+
+
+def test_fp8_block_quantisation_round_trip():
+    """1 x 128 and 128 x 128 block scales: shapes, range, and the error of the dequantised product."""
+    from iris_b200.ops.gemm_fp8 import FP8_MAX, dequant_matmul, dequantize, quantize_1x128, quantize_128x128
+
+    torch.manual_seed(0)
+    x = torch.randn(200, 336) * 3
+    w = torch.randn(520, 336) * 0.05
+    aq, asc = quantize_1x128(x)
+    bq, bsc = quantize_128x128(w)
+    assert aq.dtype == torch.float8_e4m3fn and tuple(asc.shape) == (200, 3) and tuple(bsc.shape) == (5, 3)
+    assert aq.float().abs().max().item() <= FP8_MAX
+    assert (dequantize(aq, asc, 1) - x).abs().max().item() <= x.abs().max().item() * 0.07     # e4m3: 3 mantissa bits
+    ref = x @ w.t()
+    assert (dequant_matmul(aq, asc, bq, bsc) - ref).abs().max().item() / ref.abs().max().item() < 8e-2

@@ -244,6 +244,27 @@ def test_flash_decode_matches_reference(ctx, batch, lens, page, heads):
     ctx.check()
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 1024), (200, 520, 336), (1024, 1024, 7168)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+def test_fp8_block_scaled_gemm_matches_dequantised_product(M, N, K, out_dtype):
+    """1 x 128 activation scales, 128 x 128 weight scales, e4m3 operands: the kernel's result against
+    the fp32 product of the dequantised operands (what the scales mean)."""
+    from iris_b200.ops.gemm_fp8 import dequant_matmul, matmul_fp8, quantize_1x128, quantize_128x128
+
+    torch.manual_seed(11)
+    x = torch.randn(M, K, device="cuda") * (1 + 3 * torch.rand(M, 1, device="cuda"))     # rows of different magnitude
+    w = torch.randn(N, K, device="cuda") * 0.05
+    aq, asc = quantize_1x128(x)
+    bq, bsc = quantize_128x128(w)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = matmul_fp8(aq, asc, bq, bsc, out_dtype=out_dtype, status=status)
+    ref = dequant_matmul(aq, asc, bq, bsc)
+    assert int(status.item()) == 0
+    assert (out.float() - ref).abs().max().item() / ref.abs().max().item() < 1e-2
+    # and the quantised product stays close to the unquantised one
+    assert (out.float() - x @ w.t()).abs().max().item() / ref.abs().max().item() < 8e-2
+
+
 @pytest.mark.parametrize("page,use_tma", [(64, None), (16, None), (64, False), (48, None)])
 def test_flash_decode_ignores_positions_past_the_length(ctx, page, use_tma):
     """Cache rows past a sequence's length (same page or unused pages) hold NaN: both tile-fill paths
