@@ -5,6 +5,7 @@
     python benchmark/profile_target.py decode    # 3 flash-decode steps, batch 8, 16384 keys, 64/8 heads
     python benchmark/profile_target.py fused     # world-size-1 all_gather_matmul + matmul_reduce_scatter
     python benchmark/profile_target.py moe       # one MoE layer pass, 1024 tokens, 8 experts
+    python benchmark/profile_target.py fp8       # 3 launches of the block-scaled fp8 GEMM 4096x4096x7168
 """
 import os
 import sys
@@ -36,6 +37,16 @@ def main():
         C = torch.empty(4096, 3584, device="cuda", dtype=dt)
         for _ in range(3):
             matmul(A, B, out=C)
+        torch.cuda.synchronize()
+        return
+    if what == "fp8":
+        from iris_b200.ops.gemm_fp8 import matmul_fp8, quantize_1x128, quantize_128x128
+
+        aq, asc = quantize_1x128(torch.randn(4096, 7168, device="cuda"))
+        bq, bsc = quantize_128x128(torch.randn(4096, 7168, device="cuda") * 0.05)
+        out = torch.empty(4096, 4096, device="cuda", dtype=dt)
+        for _ in range(3):
+            matmul_fp8(aq, asc, bq, bsc, out=out)
         torch.cuda.synchronize()
         return
     ctx = ctx_world1()

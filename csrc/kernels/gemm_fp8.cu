@@ -11,10 +11,14 @@
 // fresh TMEM buffer and then "promoted": the epilogue warps read the partial sums with tcgen05.ld,
 // multiply by sA * sB and add them to accumulators they keep in REGISTERS for the whole tile.
 // Two TMEM buffers of 256 columns alternate, so the MMAs of block kb + 1 run while block kb is
-// promoted. Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 promotion +
-// epilogue (warp w: TMEM lanes 32 * (w % 4) .. +32, output columns 128 * ((w - 2) / 4) .. +128,
-// i.e. 128 accumulators per thread). Per K block a thread issues 128 FFMA and four tcgen05.ld;
-// the MMAs of the block take about 520 cycles, so promotion is hidden as long as it issues.
+// promoted. Roles (384 threads = three warpgroups): warpgroup 0 holds the TMA producer (warp 0)
+// and the MMA issuer (warp 1) and gives its registers away (setmaxnreg 40); warpgroups 1 and 2
+// (setmaxnreg 232) promote and store: warp w reads TMEM lanes 32 * (w % 4) .. +32 and owns output
+// columns 128 * (w / 4 - 1) .. +128, i.e. 128 accumulators per thread. Per K block a thread issues
+// 64 packed FMAs (fma.rn.f32x2) and four tcgen05.ld (32 columns each, two in flight at a time).
+// The MMAs of a block take about 520 cycles; reading the 128 KB of partial sums back from TMEM
+// takes about twice that (measured: with the FMAs removed the kernel tops out at 2.2 PFLOP/s),
+// so this formulation is bound by tcgen05.ld, at about 60 % of the unscaled fp8 rate.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -34,7 +38,7 @@ namespace {
 constexpr int kBN8 = 256;
 constexpr int kBK8 = 128;                 // fp8 elements = bytes per swizzle row = the scale block
 constexpr int kStages8 = 4;
-constexpr int kThreads8 = 320;
+constexpr int kThreads8 = 384;
 constexpr int kPromoWarps = 8;
 constexpr int kABytes8 = kBM * kBK8;      // 16 KB
 constexpr int kBBytes8 = kBN8 * kBK8;     // 32 KB
@@ -59,6 +63,28 @@ struct Fp8Args {
 // kind::f8f6f4 instruction descriptor: fp32 accumulate, A and B e4m3 (format 0), both K-major.
 __host__ __device__ constexpr uint32_t idesc_fp8(int n) {
   return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+// tcgen05.wait::ld with the loaded registers as in/out operands: the compiler cannot move a use
+// of them above the wait.
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+// acc[kOff / 2 .. +16) += scale * r, two columns per instruction (packed fp32 FMA).
+template <int kOff>
+__device__ __forceinline__ void promote32(unsigned long long (&acc)[64], const uint32_t (&r)[32], unsigned long long scale2) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    unsigned long long v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(r[2 * j]), "r"(r[2 * j + 1]));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[kOff / 2 + j]) : "l"(scale2), "l"(v));
+  }
 }
 
 __global__ void __launch_bounds__(kThreads8, 1) gemm_fp8_kernel(const __grid_constant__ Fp8Args a) {
@@ -103,6 +129,8 @@ __global__ void __launch_bounds__(kThreads8, 1) gemm_fp8_kernel(const __grid_con
     if (a.status) atomicCAS(a.status, 0, (int)kTimeoutPipeline);
   };
 
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -154,9 +182,11 @@ __global__ void __launch_bounds__(kThreads8, 1) gemm_fp8_kernel(const __grid_con
         if (++s == kStages8) { s = 0; ph ^= 1; }
       }
     }
+  }
   } else {
     // ------------------------------------------------------------------ promotion + epilogue
-    const int pw = warp - 2;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int pw = warp - 4;
     const int quarter = warp & 3;           // TMEM lanes this warp may read
     const int half = pw >> 2;               // which 128 output columns
     uint8_t* my_epi = epi_base + pw * 2048;
@@ -171,30 +201,36 @@ __global__ void __launch_bounds__(kThreads8, 1) gemm_fp8_kernel(const __grid_con
       const int sbr = min(tn * 2 + half, sb_rows - 1);
       const float* sa_row = a.sA + (size_t)srow * k_blocks;
       const float* sb_row = a.sB + (size_t)sbr * k_blocks;
-      float acc[128];
+      unsigned long long acc[64];      // 128 fp32 accumulators as pairs
 #pragma unroll
-      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 64; ++j) acc[j] = 0ull;
       float scale_next = __ldg(sa_row) * __ldg(sb_row);
       for (int kb = 0; kb < k_blocks; ++kb, ++blk) {
         const int buf = blk & 1;
-        const float scale = scale_next;
+        unsigned long long scale;
+        asm("mov.b64 %0, {%1, %1};" : "=l"(scale) : "f"(scale_next));
         if (kb + 1 < k_blocks) scale_next = __ldg(sa_row + kb + 1) * __ldg(sb_row + kb + 1);
         if (!ptx::mbar_wait(&acc_full[buf], (blk >> 1) & 1, kPipeTimeoutNs)) { fail(); ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + half * 128;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(t_addr + c * 32, r);
-          ptx::tmem_ld_wait();
-          if (c == 3) {
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(scale, __uint_as_float(r[j]), acc[c * 32 + j]);
-        }
+        // two loads of 32 columns in flight at a time: the latency of tcgen05.ld, not its
+        // bandwidth, bounds this loop
+        uint32_t ra[32], rb[32];
+        ptx::tmem_ld_32x32(t_addr, ra);
+        ptx::tmem_ld_32x32(t_addr + 32, rb);
+        tmem_ld_wait_on(ra);
+        tmem_ld_wait_on(rb);
+        promote32<0>(acc, ra, scale);
+        ptx::tmem_ld_32x32(t_addr + 64, ra);
+        promote32<32>(acc, rb, scale);
+        ptx::tmem_ld_32x32(t_addr + 96, rb);
+        tmem_ld_wait_on(ra);
+        tmem_ld_wait_on(rb);
+        ptx::tc_fence_before();                  // every load of this buffer has completed: hand it back
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+        promote32<64>(acc, ra, scale);
+        promote32<96>(acc, rb, scale);
       }
       if (!ok) break;
       // ---- tile epilogue: 16-bit, shared-memory transpose, 16-byte row-major stores
@@ -205,11 +241,13 @@ __global__ void __launch_bounds__(kThreads8, 1) gemm_fp8_kernel(const __grid_con
         uint32_t packed[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
+          float lo, hi;
+          asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[c * 16 + j]));
           if (a.out_bf16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(acc[c * 32 + 2 * j], acc[c * 32 + 2 * j + 1]);
+            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
             packed[j] = *(uint32_t*)&h;
           } else {
-            __half2 h = __floats2half2_rn(acc[c * 32 + 2 * j], acc[c * 32 + 2 * j + 1]);
+            __half2 h = __floats2half2_rn(lo, hi);
             packed[j] = *(uint32_t*)&h;
           }
         }

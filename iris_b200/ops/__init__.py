@@ -28,10 +28,11 @@ import torch
 from .. import _lib
 from .config import FusedConfig
 from .gemm import fill_desc, matmul
+from .gemm_fp8 import dequant_matmul, matmul_fp8, quantize_1x128, quantize_128x128
 from .workspace import FusedWorkspace
 
 __all__ = [
-    "FusedConfig", "FusedWorkspace", "OpsNamespace", "matmul",
+    "FusedConfig", "FusedWorkspace", "OpsNamespace", "matmul", "matmul_fp8", "quantize_1x128", "quantize_128x128", "dequant_matmul",
     "matmul_all_reduce", "matmul_all_reduce_preamble", "all_gather_matmul", "all_gather_matmul_preamble",
     "matmul_all_gather", "matmul_all_gather_preamble", "matmul_reduce_scatter", "matmul_reduce_scatter_preamble",
 ]
