@@ -256,9 +256,12 @@ struct GroupedGemm : Common {
   IRIS_D void add_partials(State&, int, int, int, uint32_t (&)[32]) const {}
   IRIS_D void tile_done(State&, int, int) const {}
 
-  // Dispatch (stage 1 only): groups (local expert j, destination) in j-major order; a CTA pushes
-  // whole groups. Rows go HBM -> shared memory -> destination inbox by bulk async copies driven by
-  // one thread; the 8-byte routing record of each row is stored by the other threads.
+  // Dispatch (stage 1 only): groups (local expert j, destination) in j-major order, the order in
+  // which the GEMM CTAs consume the experts. Every communication CTA pushes its slice of the rows
+  // of EVERY group, so the first expert's rows are complete after 1 / El of the dispatch instead
+  // of after a whole group per CTA. Rows go HBM -> shared memory -> destination inbox by bulk
+  // async copies driven by one thread; the 8-byte routing record of each row is stored by the
+  // other threads; each CTA adds its slice's row count to the expert's arrival counter.
   static constexpr int kSlot = 16 * 1024;
   IRIS_D void comm_main(uint8_t* smem_raw, int smem_bytes) const {
     if (kStage != 1) return;
@@ -277,13 +280,17 @@ struct GroupedGemm : Common {
     }
     __syncthreads();
     int seq = 0;   // pieces issued so far (ring slot / parity)
-    for (int g = c; g < dm.El * W; g += n_comm_ctas) {
+    for (int g = 0; g < dm.El * W; ++g) {
       const int j = g / W;
       int r = ctx.rank + g % W;
       if (r >= W) r -= W;
       const int e = r * dm.El + j;
-      const int lo = meta.list_off[e], n = meta.list_off[e + 1] - lo;
-      const int dst0 = meta.my_off[e];
+      const int n_all = meta.list_off[e + 1] - meta.list_off[e];
+      const int i0 = (int)((long long)n_all * c / n_comm_ctas), i1 = (int)((long long)n_all * (c + 1) / n_comm_ctas);
+      const int n = i1 - i0;
+      if (n == 0) continue;                      // uniform over the CTA
+      const int lo = meta.list_off[e] + i0;
+      const int dst0 = meta.my_off[e] + i0;
       uint8_t* dst_inbox = ctx.remote(inbox, r);
       long long* dst_meta = ctx.remote(meta.inbox_meta, r);
       // routing records
