@@ -288,7 +288,8 @@ def main() -> int:
             ctx.ops.all_gather_matmul(H, Xb[b], W1, shard_dim=0, workspace=ws1, async_op=True)
             consumed[b].record(main_stream)
             ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True, workspace=ws2, async_op=True)
-            res = float(Y.float().square().mean().item())
+            # the step's scalar result: one reduction kernel over Y, read back as 4 bytes
+            res = float(torch.linalg.vector_norm(Y, dtype=torch.float32).item()) ** 2 / Y.numel()
         return res
 
     e2e_loop(3)
