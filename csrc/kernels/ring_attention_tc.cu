@@ -1,0 +1,452 @@
+// Ring attention with tcgen05 attention CTAs (the communication CTAs are those of
+// ring_attention_common.cuh). One attention CTA works on items of 128 queries x one head and walks
+// the key blocks in arrival order in tiles of 128 keys:
+//
+//   warp 0      TMA producer: Q once per item, then K and V tiles (two stages each) from this
+//               rank's own K/V or from the ring-buffer slot of the block's origin, after the
+//               slot's arrival counter has been seen (acquire, bounded)
+//   warp 1      MMA issuer: S = Q K^T (tcgen05.mma, M 128, N 128, K 128) into one of two TMEM
+//               buffers, and O += P V (M 128, N 128 = head_dim, K 128 keys) into a third;
+//               S of tile j+1 is issued before P V of tile j, so the tensor pipe works while the
+//               softmax of tile j runs
+//   warps 2..5  softmax, one query row per thread: tcgen05.ld of the row's 128 scores, running
+//               max / sum in registers, P = exp2(s - max) written as 16-bit into a shared-memory
+//               tile in the swizzled K-major layout the second MMA reads; when a row's maximum
+//               moved, its O row in TMEM is rescaled (tcgen05.ld / st), which after the first
+//               tiles is rare; at the end of an item O / sum is stored
+//
+// TMEM: S0 columns [0, 128), S1 [128, 256), O [256, 384). Shared memory: Q 32 KB, K 2 x 32 KB,
+// V 2 x 32 KB, P 32 KB. Every wait (mbarriers, arrival counters) is bounded.
+#include "ring_attention_common.cuh"
+
+#include "iris/gemm/sm100_mainloop.cuh"
+
+using namespace iris;
+using namespace iris_ring;
+using iris::gemm::desc_kmajor;
+using iris::gemm::desc_mnmajor;
+using iris::gemm::make_idesc;
+
+namespace {
+
+constexpr int kTQ = 128;                 // queries per item = TMEM lanes
+constexpr int kTK = 128;                 // keys per tile
+constexpr int kTcThreads = 192;
+constexpr int kHalf = 128 * 128;         // bytes of a [128 rows][64 columns] 16-bit half tile
+constexpr int kTile = 2 * kHalf;         // 32 KB
+constexpr int kKvStages = 2;
+constexpr int kTcSmem = 1024 + kTile * (2 + 2 * kKvStages) + 512;    // Q, P, K and V stages, barriers
+constexpr uint64_t kWaitNs = 4000000000ull;
+static_assert(kTcSmem <= 227 * 1024, "shared memory budget");
+
+struct TcArgs {
+  RingArgs a;
+  CUtensorMap tmQ;       // [S, Hq * D], box 64 x 128
+  CUtensorMap tmKown;    // [S, Hkv * D], box 64 x 128
+  CUtensorMap tmVown;    // [S, Hkv * D], box 64 x 64
+  CUtensorMap tmKbuf;    // ring buffer seen as [2 * W * 2 * S, Hkv * D], box 64 x 128
+  CUtensorMap tmVbuf;    // same, box 64 x 64
+};
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+      "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// The key tiles of one item, in the order every role walks them: blocks in arrival order (own,
+// r-1, r-2, ...), tiles inside a block in order; causal items skip blocks that lie after all of
+// their queries and stop the diagonal block at their own tile.
+struct TileWalk {
+  int W, r, S, causal, qt;
+  int step = 0, t = -1, n_tiles = 0, origin = 0;
+  __device__ TileWalk(const RingArgs& a, int qt_) : W(a.ctx.world), r(a.ctx.rank), S(a.S), causal(a.causal), qt(qt_) { open_block(); }
+  __device__ void open_block() {
+    for (; step < W; ++step) {
+      origin = r - step;
+      if (origin < 0) origin += W;
+      if (causal && origin > r) continue;
+      n_tiles = (causal && origin == r) ? qt + 1 : S / kTK;
+      t = -1;
+      return;
+    }
+    n_tiles = 0;
+  }
+  // advances to the next tile; false when the item is finished
+  __device__ bool next() {
+    if (step >= W) return false;
+    if (++t < n_tiles) return true;
+    ++step;
+    open_block();
+    if (step >= W) return false;
+    t = 0;
+    return true;
+  }
+  __device__ bool diagonal() const { return causal && origin == r && t == qt; }
+};
+
+template <bool kFp16>
+__device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
+  const RingArgs& a = g.a;
+  const DeviceContext& ctx = a.ctx;
+  const int W = ctx.world, r = ctx.rank;
+  const int par = call & 1;
+  const int32_t target = ((call >> 1) + 1) * a.n_comm;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tiles = a.S / kTQ;
+  const int items = q_tiles * a.Hq;
+  const int group = a.Hq / a.Hkv;
+
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;
+  uint8_t* p_s = smem + kTile;
+  uint8_t* k_s = smem + 2 * kTile;                       // [stages][kTile]
+  uint8_t* v_s = k_s + kKvStages * kTile;
+  uint64_t* bars = (uint64_t*)(v_s + kKvStages * kTile);
+  uint64_t* q_full = bars;              // 1
+  uint64_t* q_free = bars + 1;          // 1: every S MMA of the item has read Q
+  uint64_t* k_full = bars + 2;          // [2]
+  uint64_t* k_empty = bars + 4;         // [2]
+  uint64_t* v_full = bars + 6;          // [2]
+  uint64_t* v_empty = bars + 8;         // [2]
+  uint64_t* s_full = bars + 10;         // [2]
+  uint64_t* s_empty = bars + 12;        // [2] 4 softmax warps
+  uint64_t* p_full = bars + 14;         // 4 softmax warps
+  uint64_t* p_empty = bars + 15;        // the P V MMA of the tile has read P
+  uint64_t* o_ready = bars + 16;        // O holds every tile issued so far
+  uint64_t* o_free = bars + 17;         // 4 softmax warps: the item's O has been read out
+  uint32_t* tmem_slot = (uint32_t*)(bars + 18);
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(q_full, 1);
+    ptx::mbar_init(q_free, 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&k_full[i], 1); ptx::mbar_init(&k_empty[i], 1);
+      ptx::mbar_init(&v_full[i], 1); ptx::mbar_init(&v_empty[i], 1);
+      ptx::mbar_init(&s_full[i], 1); ptx::mbar_init(&s_empty[i], 4);
+    }
+    ptx::mbar_init(p_full, 4);
+    ptx::mbar_init(p_empty, 1);
+    ptx::mbar_init(o_ready, 1);
+    ptx::mbar_init(o_free, 4);
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+  const int first = blockIdx.x - a.n_comm, stride = gridDim.x - a.n_comm;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    unsigned arrived_mask = 1u << r;
+    uint32_t n_item = 0, n_tile = 0;        // items / tiles issued so far (barrier phases)
+    bool ok = true;
+    for (int it = first; it < items && ok; it += stride, ++n_item) {
+      const int h = it % a.Hq, qt = it / a.Hq, kvh = h / group;
+      if (!ptx::mbar_wait(q_free, (n_item & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); break; }
+      if (lane == 0) {
+        ptx::mbar_expect_tx(q_full, kTile);
+        ptx::tma_load_2d(q_s, &g.tmQ, q_full, h * kD, qt * kTQ);
+        ptx::tma_load_2d(q_s + kHalf, &g.tmQ, q_full, h * kD + 64, qt * kTQ);
+      }
+      TileWalk w(a, qt);
+      while (w.next()) {
+        if (w.t == 0 && !((arrived_mask >> w.origin) & 1u)) {
+          int seen = 1;
+          if (lane == 0) seen = wait_flag_ge(ctx, a.flags + (size_t)par * W + w.origin, target) ? 1 : 0;
+          seen = __shfl_sync(0xffffffffu, seen, 0);
+          if (!seen) { ok = false; break; }
+          ptx::fence_proxy_async();
+          arrived_mask |= 1u << w.origin;
+        }
+        const int st = n_tile & 1;
+        const uint32_t ph = ((n_tile >> 1) & 1) ^ 1;
+        if (!ptx::mbar_wait(&k_empty[st], ph, kWaitNs) || !ptx::mbar_wait(&v_empty[st], ph, kWaitNs)) {
+          ctx.fail(kTimeoutPipeline); ok = false; break;
+        }
+        if (lane == 0) {
+          const bool own = w.origin == r;
+          const CUtensorMap* mk = own ? &g.tmKown : &g.tmKbuf;
+          const CUtensorMap* mv = own ? &g.tmVown : &g.tmVbuf;
+          // ring buffer rows: ((parity * W + origin) * 2 + {K: 0, V: 1}) * S + position
+          const int rowk = own ? 0 : ((par * W + w.origin) * 2) * a.S;
+          const int rowv = own ? 0 : rowk + a.S;
+          const int pos0 = w.t * kTK;
+          uint8_t* kd = k_s + st * kTile;
+          uint8_t* vd = v_s + st * kTile;
+          ptx::mbar_expect_tx(&k_full[st], kTile);
+          ptx::tma_load_2d(kd, mk, &k_full[st], kvh * kD, rowk + pos0);
+          ptx::tma_load_2d(kd + kHalf, mk, &k_full[st], kvh * kD + 64, rowk + pos0);
+          ptx::mbar_expect_tx(&v_full[st], kTile);
+#pragma unroll
+          for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb)
+              ptx::tma_load_2d(vd + kh * kHalf + nb * 8192, mv, &v_full[st], kvh * kD + nb * 64, rowv + pos0 + kh * 64);
+        }
+        __syncwarp();
+        ++n_tile;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc_s = make_idesc(kTK, !kFp16, false);     // B = K tile, K-major
+    const uint32_t idesc_o = make_idesc(kD, !kFp16, true);       // B = V tile, [keys, d] row-major
+    uint32_t n_item = 0, n_s = 0, n_pv = 0;     // items, S tiles and P V tiles issued so far
+    bool ok = true;
+    auto issue_s = [&]() -> bool {
+      const int st = n_s & 1;
+      if (!ptx::mbar_wait(&s_empty[st], ((n_s >> 1) & 1) ^ 1, kWaitNs)) return false;
+      if (!ptx::mbar_wait(&k_full[st], (n_s >> 1) & 1, kWaitNs)) return false;
+      ptx::tc_fence_after();
+      if (lane == 0) {
+        const uint32_t qa = ptx::smem_u32(q_s), kb = ptx::smem_u32(k_s + st * kTile);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
+          ptx::mma_f16(tmem_base + st * 128, desc_kmajor(qa + off), desc_kmajor(kb + off), idesc_s, k != 0);
+        }
+        ptx::mma_commit(&k_empty[st]);
+        ptx::mma_commit(&s_full[st]);
+      }
+      __syncwarp();
+      ++n_s;
+      return true;
+    };
+    auto issue_pv = [&](bool first_of_item) -> bool {
+      const int st = n_pv & 1;
+      if (!ptx::mbar_wait(p_full, n_pv & 1, kWaitNs)) return false;
+      if (!ptx::mbar_wait(&v_full[st], (n_pv >> 1) & 1, kWaitNs)) return false;
+      ptx::tc_fence_after();
+      if (lane == 0) {
+        const uint32_t pa = ptx::smem_u32(p_s), vb = ptx::smem_u32(v_s + st * kTile);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t aoff = (k >> 2) * kHalf + (k & 3) * 32;          // P: K-major halves of 64 keys
+          const uint32_t boff = (k >> 2) * kHalf + (k & 3) * 2048;        // V: 64-key halves, 16 keys = 2048 B
+          ptx::mma_f16(tmem_base + 256, desc_kmajor(pa + aoff), desc_mnmajor(vb + boff), idesc_o, !(first_of_item && k == 0));
+        }
+        ptx::mma_commit(&v_empty[st]);
+        ptx::mma_commit(p_empty);
+        ptx::mma_commit(o_ready);
+      }
+      __syncwarp();
+      ++n_pv;
+      return true;
+    };
+    for (int it = first; it < items && ok; it += stride, ++n_item) {
+      const int qt = it / a.Hq;
+      int n = 0;
+      {
+        TileWalk w(a, qt);
+        while (w.next()) ++n;
+      }
+      if (!ptx::mbar_wait(q_full, n_item & 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); break; }
+      if (!issue_s()) { ctx.fail(kTimeoutPipeline); break; }
+      for (int j = 0; j < n; ++j) {
+        if (j + 1 < n && !issue_s()) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+        if (j + 1 == n && lane == 0) ptx::mma_commit(q_free);       // every S MMA of the item is issued
+        __syncwarp();
+        // the previous item's O must have been read out before this item's first P V overwrites it
+        if (j == 0 && !ptx::mbar_wait(o_free, (n_item & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+        if (!issue_pv(j == 0)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / correction / epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                      // query row inside the tile
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const float scale2 = a.sm_scale * kLog2e;
+    uint32_t n_item = 0, n_tile = 0;
+    bool ok = true;
+    for (int it = first; it < items && ok; it += stride, ++n_item) {
+      const int h = it % a.Hq, qt = it / a.Hq;
+      const int qpos = qt * kTQ + row;                        // position inside this rank's block
+      float m_run = -INFINITY, l_run = 0.f;
+      TileWalk w(a, qt);
+      int j = 0;
+      while (w.next()) {
+        const int st = n_tile & 1;
+        if (!ptx::mbar_wait(&s_full[st], (n_tile >> 1) & 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+        ptx::tc_fence_after();
+        uint32_t s[128];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t (&chunk)[32] = *reinterpret_cast<uint32_t (*)[32]>(&s[c * 32]);
+          ptx::tmem_ld_32x32(lane_addr + st * 128 + c * 32, chunk);
+        }
+        ptx::tmem_ld_wait();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&s_empty[st]);
+        // scores in log2 units, causal mask on the diagonal tile, row maximum
+        const bool diag = w.diagonal();
+        const int kpos0 = w.t * kTK;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          float v = __uint_as_float(s[c]) * scale2;
+          if (diag && kpos0 + c > qpos) v = -INFINITY;
+          s[c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+        const float m_new = fmaxf(m_run, mx);      // finite: the diagonal tile always holds the row's own key
+        const float alpha = j == 0 ? 1.f : exp2f(m_run - m_new);
+        m_run = m_new;
+        float rs = 0.f;
+        // P may be rewritten once the previous tile's P V has read it
+        if (!ptx::mbar_wait(p_empty, (n_tile & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+#pragma unroll
+        for (int c16 = 0; c16 < 16; ++c16) {      // 16-byte groups of 8 keys
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float p0 = exp2f(__uint_as_float(s[c16 * 8 + 2 * e]) - m_new);
+            const float p1 = exp2f(__uint_as_float(s[c16 * 8 + 2 * e + 1]) - m_new);
+            rs += p0 + p1;
+            pk[e] = pack2<kFp16>(p0, p1);
+          }
+          const int half = c16 >> 3, cc = c16 & 7;
+          *(uint4*)(p_s + half * kHalf + row * 128 + ((cc ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+        l_run = l_run * alpha + rs;
+        // rescale O when some row of this warp moved its maximum (O then holds every earlier tile)
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          if (!ptx::mbar_wait(o_ready, (n_tile & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+          ptx::tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            ptx::tmem_ld_32x32(lane_addr + 256 + c * 32, o);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(lane_addr + 256 + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+        ptx::fence_proxy_async_smem();          // P (generic stores) becomes visible to the MMA
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(p_full);
+        ++n_tile;
+        ++j;
+      }
+      if (!ok) break;
+      // ---- item epilogue: wait for the last P V, O / sum -> 16-bit -> global
+      if (!ptx::mbar_wait(o_ready, (n_tile & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); break; }
+      ptx::tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      uint8_t* orow = a.out + ((size_t)(qt * kTQ + row) * a.Hq + h) * kD * 2;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        ptx::tmem_ld_32x32(lane_addr + 256 + c * 32, o);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 v;
+          v.x = pack2<kFp16>(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+          v.y = pack2<kFp16>(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+          v.z = pack2<kFp16>(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+          v.w = pack2<kFp16>(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+          *(uint4*)(orow + c * 64 + i * 16) = v;
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(o_free);
+      if (a.lse) a.lse[(size_t)(qt * kTQ + row) * a.Hq + h] = l_run > 0.f ? (m_run + log2f(l_run)) / kLog2e : -INFINITY;
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, 512);
+}
+
+template <bool kFp16>
+__global__ void __launch_bounds__(kTcThreads, 1) ring_attention_tc_kernel(const __grid_constant__ TcArgs g) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int call = *(volatile int32_t*)&g.a.state[0];
+  if ((int)blockIdx.x < g.a.n_comm) comm_main(g.a, smem, kTcSmem, call);
+  else attn_main_tc<kFp16>(g, smem, call);
+  finish_call(g.a, call);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+bool make_map16(CUtensorMap* m, const void* base, bool fp16, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  static EncodeTiledFn enc = nullptr;
+  if (!enc) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) return false;
+    enc = (EncodeTiledFn)p;
+  }
+  if (((uint64_t)base & 15) || ((cols * 2) & 15)) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(m, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+namespace iris_ring {
+
+int launch_ring_attention_tc(const RingArgs& a, cudaStream_t stream) {
+  if (a.S % kTQ || a.S <= 0) return 1;
+  const int W = a.ctx.world;
+  TcArgs g;
+  g.a = a;
+  const bool f16 = a.is_fp16 != 0;
+  const uint64_t kvc = (uint64_t)a.Hkv * kD;
+  if (!make_map16(&g.tmQ, a.q, f16, a.S, (uint64_t)a.Hq * kD, kTQ)) return 1;
+  if (!make_map16(&g.tmKown, a.k, f16, a.S, kvc, kTK)) return 1;
+  if (!make_map16(&g.tmVown, a.v, f16, a.S, kvc, 64)) return 1;
+  if (W > 1) {
+    if (!make_map16(&g.tmKbuf, a.kv_buf, f16, 4ull * W * a.S, kvc, kTK)) return 1;
+    if (!make_map16(&g.tmVbuf, a.kv_buf, f16, 4ull * W * a.S, kvc, 64)) return 1;
+  } else {
+    g.tmKbuf = g.tmKown;
+    g.tmVbuf = g.tmVown;
+  }
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(ring_attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess) return -20;
+    if (cudaFuncSetAttribute(ring_attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess) return -20;
+    attr = true;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int items = (a.S / kTQ) * a.Hq;
+  int attn = sms - a.n_comm;                 // one CTA per SM (192 KB of shared memory), all resident
+  if (attn > items) attn = items;
+  if (attn < 1) return 1;
+  const int grid = a.n_comm + attn;
+  if (f16) ring_attention_tc_kernel<true><<<grid, kTcThreads, kTcSmem, stream>>>(g);
+  else ring_attention_tc_kernel<false><<<grid, kTcThreads, kTcSmem, stream>>>(g);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+}  // namespace iris_ring

@@ -2,9 +2,11 @@
 
 Every rank holds ``S`` consecutive tokens of the sequence: queries ``[S, Hq, D]`` and keys/values
 ``[S, Hkv, D]``. ``RingAttention.forward(q, k, v, causal)`` returns this rank's ``[S, Hq, D]``
-output of attention over the WHOLE sequence. One kernel per call (``csrc/kernels/ring_attention.cu``):
-communication CTAs pass the K/V blocks round the ring with bulk copies and per-block arrival
-counters on the heap, attention CTAs consume the blocks as they arrive. The reference has no
+output of attention over the WHOLE sequence. One kernel per call: communication CTAs pass the K/V
+blocks round the ring with bulk copies and per-block arrival counters on the heap, attention CTAs
+consume the blocks as they arrive. When ``S`` is a multiple of 128 the attention CTAs run on
+tcgen05 with TMEM accumulators and TMA-fed tiles (``csrc/kernels/ring_attention_tc.cu``), otherwise
+on ``mma.sync`` (``csrc/kernels/ring_attention.cu``). The reference has no
 counterpart; ``reference_attention`` is the plain fp32 PyTorch statement used by the tests.
 """
 from __future__ import annotations
@@ -49,7 +51,7 @@ def reference_attention(q, k, v, causal: bool = False, q_offset: int = 0, sm_sca
 
 class RingAttention:
     def __init__(self, ctx, seq_per_rank: int, num_q_heads: int, num_kv_heads: int, head_dim: int = 128,
-                 sm_scale: float | None = None, comm_sms: int = 8, dtype=torch.bfloat16):
+                 sm_scale: float | None = None, comm_sms: int = 8, dtype=torch.bfloat16, use_tcgen05: bool | None = None):
         if head_dim != 128:
             raise ValueError("the ring-attention kernel is specialised for head_dim 128")
         if num_q_heads % num_kv_heads:
@@ -57,6 +59,8 @@ class RingAttention:
         self.ctx, self.S, self.Hq, self.Hkv, self.D = ctx, seq_per_rank, num_q_heads, num_kv_heads, head_dim
         self.sm_scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(head_dim)
         self.comm_sms, self.dtype = comm_sms, dtype
+        # None: tcgen05 attention CTAs whenever seq_per_rank is a multiple of 128; False: the mma.sync CTAs
+        self.use_tcgen05 = use_tcgen05
         W = ctx.get_num_ranks()
         esize = 2 if not ctx.is_cpu else torch.empty((), dtype=dtype).element_size()
         # ring buffer [parity][origin rank][K | V][S, Hkv, D] and its arrival counters, on the heap
@@ -95,6 +99,7 @@ class RingAttention:
         d.S, d.Hq, d.Hkv, d.D, d.causal, d.n_comm = self.S, self.Hq, self.Hkv, self.D, int(causal), self.comm_sms
         d.dtype = _lib.DTYPE_CODE[q.dtype]
         d.sm_scale = self.sm_scale
+        d.reserved = 1 if self.use_tcgen05 is False else 0
         _lib.check(self._lib().iris_ring_attention(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "ring attention launch")
         return (out, lse) if return_lse else out
 

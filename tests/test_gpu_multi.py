@@ -317,23 +317,24 @@ def _ring(rank, world):
     from iris_b200.models import RingAttention, reference_attention
 
     ctx = iris.iris(1 << 30)
-    S, Hq, Hkv, D = 192, 8, 2, 128
+    Hq, Hkv, D = 8, 2, 128
     dt = torch.bfloat16
     torch.manual_seed(30 + rank)
-    q = torch.randn(S, Hq, D, device="cuda", dtype=dt)
-    k = torch.randn(S, Hkv, D, device="cuda", dtype=dt)
-    v = torch.randn(S, Hkv, D, device="cuda", dtype=dt)
-    ks = torch.empty(world * S, Hkv, D, device="cuda", dtype=dt)
-    vs = torch.empty(world * S, Hkv, D, device="cuda", dtype=dt)
-    dist.all_gather_into_tensor(ks, k)
-    dist.all_gather_into_tensor(vs, v)
-    layer = RingAttention(ctx, S, Hq, Hkv)
-    for causal in (False, True):
-        for _ in range(3):
-            out = layer(q, k, v, causal=causal)
-        ref = reference_attention(q, ks, vs, causal, q_offset=rank * S)
-        assert (out.float() - ref).abs().max().item() < 2e-2, causal
-    ctx.check()
+    for S in (192, 256):          # 192: mma.sync attention CTAs, 256: tcgen05 attention CTAs
+        q = torch.randn(S, Hq, D, device="cuda", dtype=dt)
+        k = torch.randn(S, Hkv, D, device="cuda", dtype=dt)
+        v = torch.randn(S, Hkv, D, device="cuda", dtype=dt)
+        ks = torch.empty(world * S, Hkv, D, device="cuda", dtype=dt)
+        vs = torch.empty(world * S, Hkv, D, device="cuda", dtype=dt)
+        dist.all_gather_into_tensor(ks, k)
+        dist.all_gather_into_tensor(vs, v)
+        layer = RingAttention(ctx, S, Hq, Hkv)
+        for causal in (False, True):
+            for _ in range(3):
+                out = layer(q, k, v, causal=causal)
+            ref = reference_attention(q, ks, vs, causal, q_offset=rank * S)
+            assert (out.float() - ref).abs().max().item() < 2e-2, (S, causal)
+        ctx.check()
     ctx.barrier()
 
 

@@ -335,8 +335,11 @@ def test_router_matches_torch_topk(ctx):
     assert torch.allclose(layer.topk_w, w, atol=1e-5)
 
 
-@pytest.mark.parametrize("S,Hq,Hkv,causal", [(128, 4, 2, False), (200, 8, 2, True), (64, 2, 2, True)])
-def test_ring_attention_world1(ctx, S, Hq, Hkv, causal):
+@pytest.mark.parametrize("S,Hq,Hkv,causal,tc", [(128, 4, 2, False, None), (200, 8, 2, True, None), (64, 2, 2, True, None),
+                                                 (128, 2, 2, True, None), (384, 8, 2, True, None), (512, 4, 4, False, None),
+                                                 (384, 8, 2, True, False)])
+def test_ring_attention_world1(ctx, S, Hq, Hkv, causal, tc):
+    """Multiples of 128 run the tcgen05 attention CTAs, other lengths (or tc=False) the mma.sync ones."""
     from iris_b200.models import RingAttention, reference_attention
 
     dt = torch.bfloat16
@@ -344,11 +347,16 @@ def test_ring_attention_world1(ctx, S, Hq, Hkv, causal):
     q = torch.randn(S, Hq, 128, device="cuda", dtype=dt)
     k = torch.randn(S, Hkv, 128, device="cuda", dtype=dt)
     v = torch.randn(S, Hkv, 128, device="cuda", dtype=dt)
-    layer = RingAttention(ctx, S, Hq, Hkv)
+    layer = RingAttention(ctx, S, Hq, Hkv, use_tcgen05=tc)
     for _ in range(2):
-        out = layer(q, k, v, causal=causal)
+        out, lse = layer(q, k, v, causal=causal, return_lse=True)
     ref = reference_attention(q, k, v, causal)
     assert (out.float() - ref).abs().max().item() < 2e-2
+    g = Hq // Hkv
+    s = torch.einsum("qhd,khd->hqk", q.float(), k.float().repeat_interleave(g, dim=1)) / 128 ** 0.5
+    if causal:
+        s = s.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool, device="cuda"), 1)[None], float("-inf"))
+    assert (lse - torch.logsumexp(s, dim=-1).t()).abs().max().item() < 2e-2
     ctx.check()
 
 
