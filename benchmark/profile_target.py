@@ -6,6 +6,7 @@
     python benchmark/profile_target.py fused     # world-size-1 all_gather_matmul + matmul_reduce_scatter
     python benchmark/profile_target.py moe       # one MoE layer pass, 1024 tokens, 8 experts
     python benchmark/profile_target.py fp8       # 3 launches of the block-scaled fp8 GEMM 4096x4096x7168
+    python benchmark/profile_target.py ring      # 3 ring-attention calls, world size 1, 4096 tokens, 32/8 heads
 """
 import os
 import sys
@@ -63,6 +64,16 @@ def main():
         layer = FlashDecodeLayer(ctx, Hq, Hkv, 128, max_batch=B_)
         for _ in range(3):
             layer(q, kc, vc, lens, table)
+    elif what == "ring":
+        from iris_b200.models import RingAttention
+
+        S, Hq, Hkv = 4096, 32, 8
+        q = torch.randn(S, Hq, 128, device="cuda", dtype=dt)
+        k = torch.randn(S, Hkv, 128, device="cuda", dtype=dt)
+        v = torch.randn(S, Hkv, 128, device="cuda", dtype=dt)
+        layer = RingAttention(ctx, S, Hq, Hkv)
+        for _ in range(3):
+            layer(q, k, v, causal=False)
     elif what == "fused":
         X = torch.randn(4096, 8192, device="cuda", dtype=dt)
         W1 = torch.randn(8192, 3584, device="cuda", dtype=dt) * 0.02

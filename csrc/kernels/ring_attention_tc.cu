@@ -9,11 +9,14 @@
 //               buffers, and O += P V (M 128, N 128 = head_dim, K 128 keys) into a third;
 //               S of tile j+1 is issued before P V of tile j, so the tensor pipe works while the
 //               softmax of tile j runs
-//   warps 2..5  softmax, one query row per thread: tcgen05.ld of the row's 128 scores, running
-//               max / sum in registers, P = exp2(s - max) written as 16-bit into a shared-memory
-//               tile in the swizzled K-major layout the second MMA reads; when a row's maximum
-//               moved, its O row in TMEM is rescaled (tcgen05.ld / st), which after the first
-//               tiles is rare; at the end of an item O / sum is stored
+//   warps 2..9  softmax, two threads per query row (warp w: TMEM lanes 32 * (w % 4) .. +32, keys
+//               64 * ((w - 2) / 4) .. +64 of the tile): tcgen05.ld of the 64 scores, the row maximum
+//               agreed between the two threads through shared memory, P = exp2(s - max) (one FFMA
+//               and one ex2.approx per score) written as 16-bit into a shared-memory tile in the
+//               swizzled K-major layout the second MMA reads, running sum kept per thread; when a
+//               row's maximum moved, its O row in TMEM is rescaled (tcgen05.ld / st, each thread
+//               its 64 columns), which after the first tiles is rare; at the end of an item
+//               O / sum is stored
 //
 // TMEM: S0 columns [0, 128), S1 [128, 256), O [256, 384). Shared memory: Q 32 KB, K 2 x 32 KB,
 // V 2 x 32 KB, P 32 KB. Every wait (mbarriers, arrival counters) is bounded.
@@ -31,11 +34,11 @@ namespace {
 
 constexpr int kTQ = 128;                 // queries per item = TMEM lanes
 constexpr int kTK = 128;                 // keys per tile
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;
 constexpr int kHalf = 128 * 128;         // bytes of a [128 rows][64 columns] 16-bit half tile
 constexpr int kTile = 2 * kHalf;         // 32 KB
 constexpr int kKvStages = 2;
-constexpr int kTcSmem = 1024 + kTile * (2 + 2 * kKvStages) + 512;    // Q, P, K and V stages, barriers
+constexpr int kTcSmem = 1024 + kTile * (2 + 2 * kKvStages) + 256 + 3072;    // Q, P, K and V stages, barriers, row exchange
 constexpr uint64_t kWaitNs = 4000000000ull;
 static_assert(kTcSmem <= 227 * 1024, "shared memory budget");
 
@@ -60,6 +63,11 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // The key tiles of one item, in the order every role walks them: blocks in arrival order (own,
 // r-1, r-2, ...), tiles inside a block in order; causal items skip blocks that lie after all of
@@ -117,12 +125,17 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
   uint64_t* v_full = bars + 6;          // [2]
   uint64_t* v_empty = bars + 8;         // [2]
   uint64_t* s_full = bars + 10;         // [2]
-  uint64_t* s_empty = bars + 12;        // [2] 4 softmax warps
-  uint64_t* p_full = bars + 14;         // 4 softmax warps
+  uint64_t* s_empty = bars + 12;        // [2] 8 softmax warps
+  uint64_t* p_full = bars + 14;         // 8 softmax warps
   uint64_t* p_empty = bars + 15;        // the P V MMA of the tile has read P
   uint64_t* o_ready = bars + 16;        // O holds every tile issued so far
-  uint64_t* o_free = bars + 17;         // 4 softmax warps: the item's O has been read out
+  uint64_t* o_free = bars + 17;         // 8 softmax warps: the item's O has been read out
   uint32_t* tmem_slot = (uint32_t*)(bars + 18);
+  // exchange between the two threads of a row (bounded waits, no bar.sync: a thread that gave up
+  // must not leave its partner blocked): values [2 parities][2 halves][128 rows], then the number
+  // of the last exchange each (half, row) published
+  float* xchg = (float*)(bars + 20);
+  uint32_t* xseq = (uint32_t*)(xchg + 512);
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(q_full, 1);
@@ -130,15 +143,16 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&k_full[i], 1); ptx::mbar_init(&k_empty[i], 1);
       ptx::mbar_init(&v_full[i], 1); ptx::mbar_init(&v_empty[i], 1);
-      ptx::mbar_init(&s_full[i], 1); ptx::mbar_init(&s_empty[i], 4);
+      ptx::mbar_init(&s_full[i], 1); ptx::mbar_init(&s_empty[i], 8);
     }
-    ptx::mbar_init(p_full, 4);
+    ptx::mbar_init(p_full, 8);
     ptx::mbar_init(p_empty, 1);
     ptx::mbar_init(o_ready, 1);
-    ptx::mbar_init(o_free, 4);
+    ptx::mbar_init(o_free, 8);
     ptx::fence_mbar_init();
     ptx::fence_proxy_async();
   }
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) xseq[i] = 0;
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, 512);
     ptx::tmem_relinquish();
@@ -268,74 +282,108 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
   } else {
     // ------------------------------------------------------------------ softmax / correction / epilogue
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;                         // which 64 keys of a tile / 64 columns of O
     const int row = quarter * 32 + lane;                      // query row inside the tile
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const float scale2 = a.sm_scale * kLog2e;
-    uint32_t n_item = 0, n_tile = 0;
+    uint32_t n_item = 0, n_tile = 0, xtag = 0;
     bool ok = true;
+    // publishes `v`, returns the partner's value of the same exchange (false in `ok` after 4 s)
+    auto exchange = [&](float v) -> float {
+      ++xtag;
+      volatile float* val = xchg + (xtag & 1) * 256;
+      volatile uint32_t* seq = xseq;
+      val[half * 128 + row] = v;
+      __threadfence_block();
+      seq[half * 128 + row] = xtag;
+      const int other = (half ^ 1) * 128 + row;
+      if ((int)(seq[other] - xtag) < 0) {
+        const uint64_t t0 = ptx::globaltimer();
+        uint32_t spins = 0;
+        while ((int)(seq[other] - xtag) < 0) {
+          if ((++spins & 1023u) == 0 && ptx::globaltimer() - t0 > kWaitNs) { ok = false; break; }
+        }
+      }
+      __threadfence_block();
+      return val[other];
+    };
     for (int it = first; it < items && ok; it += stride, ++n_item) {
       const int h = it % a.Hq, qt = it / a.Hq;
       const int qpos = qt * kTQ + row;                        // position inside this rank's block
-      float m_run = -INFINITY, l_run = 0.f;
+      float m_run = -INFINITY, l_run = 0.f;                   // l_run: this thread's half of the row sum
       TileWalk w(a, qt);
       int j = 0;
       while (w.next()) {
         const int st = n_tile & 1;
         if (!ptx::mbar_wait(&s_full[st], (n_tile >> 1) & 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
         ptx::tc_fence_after();
-        uint32_t s[128];
+        uint32_t s[64];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t (&chunk)[32] = *reinterpret_cast<uint32_t (*)[32]>(&s[c * 32]);
-          ptx::tmem_ld_32x32(lane_addr + st * 128 + c * 32, chunk);
+          ptx::tmem_ld_32x32(lane_addr + st * 128 + half * 64 + c * 32, chunk);
         }
         ptx::tmem_ld_wait();
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&s_empty[st]);
-        // scores in log2 units, causal mask on the diagonal tile, row maximum
+        // causal mask on the diagonal tile, maximum of this thread's 64 raw scores
         const bool diag = w.diagonal();
-        const int kpos0 = w.t * kTK;
-        float mx = -INFINITY;
+        const int kpos0 = w.t * kTK + half * 64;
+        if (diag) {
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          float v = __uint_as_float(s[c]) * scale2;
-          if (diag && kpos0 + c > qpos) v = -INFINITY;
-          s[c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+          for (int c = 0; c < 64; ++c)
+            if (kpos0 + c > qpos) s[c] = 0xff800000u;     // -inf
         }
-        const float m_new = fmaxf(m_run, mx);      // finite: the diagonal tile always holds the row's own key
-        const float alpha = j == 0 ? 1.f : exp2f(m_run - m_new);
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: the maximum is latency bound otherwise
+#pragma unroll
+        for (int c = 0; c < 64; c += 4) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(s[c + u]));
+        }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // agree on the row maximum with the thread that holds the other 64 keys
+        mx = fmaxf(mx, exchange(mx));
+        if (!__all_sync(0xffffffffu, ok)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+        const float m_new = fmaxf(m_run, mx * scale2);     // finite: the diagonal tile holds the row's own key
+        const float alpha = j == 0 ? 1.f : ex2_approx(m_run - m_new);
         m_run = m_new;
-        float rs = 0.f;
         // P may be rewritten once the previous tile's P V has read it
         if (!ptx::mbar_wait(p_empty, (n_tile & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+        // p = exp2(s * scale - max): packed FMA for two scores at a time, one ex2.approx each, four sum chains
+        unsigned long long scale_pair, negm_pair;
+        asm("mov.b64 %0, {%1, %1};" : "=l"(scale_pair) : "f"(scale2));
+        asm("mov.b64 %0, {%1, %1};" : "=l"(negm_pair) : "f"(-m_new));
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c16 = 0; c16 < 16; ++c16) {      // 16-byte groups of 8 keys
+        for (int c16 = 0; c16 < 8; ++c16) {       // 16-byte groups of 8 keys
           uint32_t pk[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float p0 = exp2f(__uint_as_float(s[c16 * 8 + 2 * e]) - m_new);
-            const float p1 = exp2f(__uint_as_float(s[c16 * 8 + 2 * e + 1]) - m_new);
-            rs += p0 + p1;
+            unsigned long long sp, xp;
+            asm("mov.b64 %0, {%1, %2};" : "=l"(sp) : "r"(s[c16 * 8 + 2 * e]), "r"(s[c16 * 8 + 2 * e + 1]));
+            asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(xp) : "l"(sp), "l"(scale_pair), "l"(negm_pair));
+            float x0, x1;
+            asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(xp));
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            rs4[e] += p0 + p1;
             pk[e] = pack2<kFp16>(p0, p1);
           }
-          const int half = c16 >> 3, cc = c16 & 7;
-          *(uint4*)(p_s + half * kHalf + row * 128 + ((cc ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *(uint4*)(p_s + half * kHalf + row * 128 + ((c16 ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
-        l_run = l_run * alpha + rs;
+        l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
         // rescale O when some row of this warp moved its maximum (O then holds every earlier tile)
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
           if (!ptx::mbar_wait(o_ready, (n_tile & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
           ptx::tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t o[32];
-            ptx::tmem_ld_32x32(lane_addr + 256 + c * 32, o);
+            ptx::tmem_ld_32x32(lane_addr + 256 + half * 64 + c * 32, o);
             ptx::tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32(lane_addr + 256 + c * 32, o);
+            tmem_st_32x32(lane_addr + 256 + half * 64 + c * 32, o);
           }
           tmem_st_wait();
         }
@@ -347,15 +395,17 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
         ++j;
       }
       if (!ok) break;
-      // ---- item epilogue: wait for the last P V, O / sum -> 16-bit -> global
+      // ---- item epilogue: the row sum of both halves, the last P V, O / sum -> 16-bit -> global
+      const float l_all = l_run + exchange(l_run);
+      if (!__all_sync(0xffffffffu, ok)) { ctx.fail(kTimeoutPipeline); break; }
       if (!ptx::mbar_wait(o_ready, (n_tile & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); break; }
       ptx::tc_fence_after();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint8_t* orow = a.out + ((size_t)(qt * kTQ + row) * a.Hq + h) * kD * 2;
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      uint8_t* orow = a.out + ((size_t)(qt * kTQ + row) * a.Hq + h) * kD * 2 + half * 128;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t o[32];
-        ptx::tmem_ld_32x32(lane_addr + 256 + c * 32, o);
+        ptx::tmem_ld_32x32(lane_addr + 256 + half * 64 + c * 32, o);
         ptx::tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -370,7 +420,7 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(o_free);
-      if (a.lse) a.lse[(size_t)(qt * kTQ + row) * a.Hq + h] = l_run > 0.f ? (m_run + log2f(l_run)) / kLog2e : -INFINITY;
+      if (a.lse && half == 0) a.lse[(size_t)(qt * kTQ + row) * a.Hq + h] = l_all > 0.f ? (m_run + log2f(l_all)) / kLog2e : -INFINITY;
     }
   }
   ptx::tc_fence_before();
