@@ -11,15 +11,18 @@
 //               softmax of tile j runs
 //   warps 2..9  softmax, two threads per query row (warp w: TMEM lanes 32 * (w % 4) .. +32, keys
 //               64 * ((w - 2) / 4) .. +64 of the tile): tcgen05.ld of the 64 scores, the row maximum
-//               agreed between the two threads through shared memory, P = exp2(s - max) (one FFMA
-//               and one ex2.approx per score) written as 16-bit into a shared-memory tile in the
-//               swizzled K-major layout the second MMA reads, running sum kept per thread; when a
+//               agreed between the two threads through shared memory, P = exp2(s - max) (one packed
+//               FMA per two scores, one ex2.approx each) written as packed 16-bit pairs into TMEM
+//               (tcgen05.st), from where the second MMA takes it as its A operand: P never touches
+//               shared memory, whose bandwidth is what bounds this kernel (each MMA of a tile already
+//               reads 64 KB of operands from it); running sum kept per thread; when a
 //               row's maximum moved, its O row in TMEM is rescaled (tcgen05.ld / st, each thread
 //               its 64 columns), which after the first tiles is rare; at the end of an item
 //               O / sum is stored
 //
-// TMEM: S0 columns [0, 128), S1 [128, 256), O [256, 384). Shared memory: Q 32 KB, K 2 x 32 KB,
-// V 2 x 32 KB, P 32 KB. Every wait (mbarriers, arrival counters) is bounded.
+// TMEM: S0 columns [0, 128), S1 [128, 256), O [256, 384), P0 [384, 448), P1 [448, 512) (128 keys as
+// 64 columns of 16-bit pairs). Shared memory: Q 32 KB, K 2 x 32 KB, V 2 x 32 KB. Every wait
+// (mbarriers, arrival counters) is bounded.
 #include "ring_attention_common.cuh"
 
 #include "iris/gemm/sm100_mainloop.cuh"
@@ -38,7 +41,7 @@ constexpr int kTcThreads = 320;
 constexpr int kHalf = 128 * 128;         // bytes of a [128 rows][64 columns] 16-bit half tile
 constexpr int kTile = 2 * kHalf;         // 32 KB
 constexpr int kKvStages = 2;
-constexpr int kTcSmem = 1024 + kTile * (2 + 2 * kKvStages) + 256 + 3072;    // Q, P, K and V stages, barriers, row exchange
+constexpr int kTcSmem = 1024 + kTile * (1 + 2 * kKvStages) + 256 + 3072;    // Q, K and V stages, barriers, row exchange
 constexpr uint64_t kWaitNs = 4000000000ull;
 static_assert(kTcSmem <= 227 * 1024, "shared memory budget");
 
@@ -63,6 +66,14 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem desc]: A is read from TMEM (lane = row, 16-bit pairs along K per column).
+__device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -114,8 +125,7 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
 
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_s = smem;
-  uint8_t* p_s = smem + kTile;
-  uint8_t* k_s = smem + 2 * kTile;                       // [stages][kTile]
+  uint8_t* k_s = smem + kTile;                           // [stages][kTile]
   uint8_t* v_s = k_s + kKvStages * kTile;
   uint64_t* bars = (uint64_t*)(v_s + kKvStages * kTile);
   uint64_t* q_full = bars;              // 1
@@ -126,15 +136,15 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
   uint64_t* v_empty = bars + 8;         // [2]
   uint64_t* s_full = bars + 10;         // [2]
   uint64_t* s_empty = bars + 12;        // [2] 8 softmax warps
-  uint64_t* p_full = bars + 14;         // 8 softmax warps
-  uint64_t* p_empty = bars + 15;        // the P V MMA of the tile has read P
-  uint64_t* o_ready = bars + 16;        // O holds every tile issued so far
-  uint64_t* o_free = bars + 17;         // 8 softmax warps: the item's O has been read out
-  uint32_t* tmem_slot = (uint32_t*)(bars + 18);
+  uint64_t* p_full = bars + 14;         // [2] 8 softmax warps
+  uint64_t* p_empty = bars + 16;        // [2] the P V MMA of the tile has read P
+  uint64_t* o_ready = bars + 18;        // [2] by tile parity: O holds every tile up to that one
+  uint64_t* o_free = bars + 20;         // 8 softmax warps: the item's O has been read out
+  uint32_t* tmem_slot = (uint32_t*)(bars + 21);
   // exchange between the two threads of a row (bounded waits, no bar.sync: a thread that gave up
   // must not leave its partner blocked): values [2 parities][2 halves][128 rows], then the number
   // of the last exchange each (half, row) published
-  float* xchg = (float*)(bars + 20);
+  float* xchg = (float*)(bars + 22);
   uint32_t* xseq = (uint32_t*)(xchg + 512);
 
   if (threadIdx.x == 0) {
@@ -144,10 +154,9 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
       ptx::mbar_init(&k_full[i], 1); ptx::mbar_init(&k_empty[i], 1);
       ptx::mbar_init(&v_full[i], 1); ptx::mbar_init(&v_empty[i], 1);
       ptx::mbar_init(&s_full[i], 1); ptx::mbar_init(&s_empty[i], 8);
+      ptx::mbar_init(&p_full[i], 8); ptx::mbar_init(&p_empty[i], 1);
+      ptx::mbar_init(&o_ready[i], 1);
     }
-    ptx::mbar_init(p_full, 8);
-    ptx::mbar_init(p_empty, 1);
-    ptx::mbar_init(o_ready, 1);
     ptx::mbar_init(o_free, 8);
     ptx::fence_mbar_init();
     ptx::fence_proxy_async();
@@ -242,20 +251,20 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
     };
     auto issue_pv = [&](bool first_of_item) -> bool {
       const int st = n_pv & 1;
-      if (!ptx::mbar_wait(p_full, n_pv & 1, kWaitNs)) return false;
+      if (!ptx::mbar_wait(&p_full[st], (n_pv >> 1) & 1, kWaitNs)) return false;
       if (!ptx::mbar_wait(&v_full[st], (n_pv >> 1) & 1, kWaitNs)) return false;
       ptx::tc_fence_after();
       if (lane == 0) {
-        const uint32_t pa = ptx::smem_u32(p_s), vb = ptx::smem_u32(v_s + st * kTile);
+        const uint32_t vb = ptx::smem_u32(v_s + st * kTile);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t aoff = (k >> 2) * kHalf + (k & 3) * 32;          // P: K-major halves of 64 keys
           const uint32_t boff = (k >> 2) * kHalf + (k & 3) * 2048;        // V: 64-key halves, 16 keys = 2048 B
-          ptx::mma_f16(tmem_base + 256, desc_kmajor(pa + aoff), desc_mnmajor(vb + boff), idesc_o, !(first_of_item && k == 0));
+          // P: 16 keys = 8 columns of 16-bit pairs
+          mma_f16_ts(tmem_base + 256, tmem_base + 384 + st * 64 + k * 8, desc_mnmajor(vb + boff), idesc_o, !(first_of_item && k == 0));
         }
         ptx::mma_commit(&v_empty[st]);
-        ptx::mma_commit(p_empty);
-        ptx::mma_commit(o_ready);
+        ptx::mma_commit(&p_empty[st]);
+        ptx::mma_commit(&o_ready[st]);
       }
       __syncwarp();
       ++n_pv;
@@ -348,16 +357,16 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
         const float m_new = fmaxf(m_run, mx * scale2);     // finite: the diagonal tile holds the row's own key
         const float alpha = j == 0 ? 1.f : ex2_approx(m_run - m_new);
         m_run = m_new;
-        // P may be rewritten once the previous tile's P V has read it
-        if (!ptx::mbar_wait(p_empty, (n_tile & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+        // this P buffer may be rewritten once the P V of two tiles ago has read it
+        if (!ptx::mbar_wait(&p_empty[st], ((n_tile >> 1) & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+        uint32_t pw[32];        // this thread's 64 probabilities as 16-bit pairs
         // p = exp2(s * scale - max): packed FMA for two scores at a time, one ex2.approx each, four sum chains
         unsigned long long scale_pair, negm_pair;
         asm("mov.b64 %0, {%1, %1};" : "=l"(scale_pair) : "f"(scale2));
         asm("mov.b64 %0, {%1, %1};" : "=l"(negm_pair) : "f"(-m_new));
         float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c16 = 0; c16 < 8; ++c16) {       // 16-byte groups of 8 keys
-          uint32_t pk[4];
+        for (int c16 = 0; c16 < 8; ++c16) {       // groups of 8 keys
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             unsigned long long sp, xp;
@@ -367,14 +376,16 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
             asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(xp));
             const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
             rs4[e] += p0 + p1;
-            pk[e] = pack2<kFp16>(p0, p1);
+            pw[c16 * 4 + e] = pack2<kFp16>(p0, p1);
           }
-          *(uint4*)(p_s + half * kHalf + row * 128 + ((c16 ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
+        tmem_st_32x32(lane_addr + 384 + st * 64 + half * 32, pw);
         l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
         // rescale O when some row of this warp moved its maximum (O then holds every earlier tile)
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          if (!ptx::mbar_wait(o_ready, (n_tile & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+          // (the barrier of the previous tile's parity: between "two tiles ago", known complete from
+          //  the P buffer wait above, and "the previous tile" a phase parity is unambiguous)
+          if (!ptx::mbar_wait(&o_ready[(n_tile - 1) & 1], ((n_tile - 1) >> 1) & 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
           ptx::tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < 2; ++c) {
@@ -385,12 +396,11 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
             tmem_st_32x32(lane_addr + 256 + half * 64 + c * 32, o);
           }
-          tmem_st_wait();
         }
-        ptx::fence_proxy_async_smem();          // P (generic stores) becomes visible to the MMA
+        tmem_st_wait();                         // P (and a rescaled O) are in TMEM before the MMA is told
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(p_full);
+        if (lane == 0) ptx::mbar_arrive(&p_full[st]);
         ++n_tile;
         ++j;
       }
@@ -398,7 +408,7 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
       // ---- item epilogue: the row sum of both halves, the last P V, O / sum -> 16-bit -> global
       const float l_all = l_run + exchange(l_run);
       if (!__all_sync(0xffffffffu, ok)) { ctx.fail(kTimeoutPipeline); break; }
-      if (!ptx::mbar_wait(o_ready, (n_tile & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); break; }
+      if (!ptx::mbar_wait(&o_ready[(n_tile - 1) & 1], ((n_tile - 1) >> 1) & 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); break; }
       ptx::tc_fence_after();
       const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
       uint8_t* orow = a.out + ((size_t)(qt * kTQ + row) * a.Hq + h) * kD * 2 + half * 128;
