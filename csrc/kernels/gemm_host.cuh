@@ -86,6 +86,7 @@ int sm_count() {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;     // no device (plan queries on a machine without a GPU): a B200's count
   }
   return n;
 }

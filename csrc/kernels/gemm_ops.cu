@@ -573,9 +573,10 @@ struct ScatterGemmT : Common {
 // Tile shape: least estimated time over `ctas` persistent CTAs; ties go to the candidate listed
 // first. `bn_fixed` > 0 pins the width; pair_mode 0 = choose, 1 = single CTAs, 2 = CTA pairs (when
 // `pair_ok`). The estimate is waves x tile width x a per-shape factor. Under the power cap a
-// partly idle last wave costs less than a full one (the busy SMs clock higher), so the wave
-// count is the mean of the whole and the fractional number of waves. Factors are measured: a
-// pair tile saves 4 to 7 % (B leaves L2 once per pair), a 128-wide tile costs about 12 % more.
+// partly idle last wave costs little (the busy SMs clock higher; measured: 6.05 waves of 256-wide
+// pair tiles beat 6.92 waves of 224-wide ones), so the wave count is the fractional one, at least
+// one. Factors are measured: a pair tile saves 4 to 7 % (B leaves L2 once per pair), a 128-wide
+// tile costs about 12 % more.
 void choose_tile(int M, int N, int ctas, int bn_fixed, int pair_mode, bool pair_ok, int& bn_out, int& pair_out) {
   const int cand[3] = {256, 224, 128};
   double best = 1e30;
@@ -590,7 +591,8 @@ void choose_tile(int M, int N, int ctas, int bn_fixed, int pair_mode, bool pair_
       if (pr == 1 && bn == 128) continue;
       const int tiles = ceil_div(M, kBM << pr) * ceil_div(N, bn);
       const int slots = ctas >> pr;
-      const double waves = 0.5 * (ceil_div(tiles, slots) + (double)tiles / slots);
+      const double frac = (double)tiles / slots;
+      const double waves = frac < 1.0 ? 1.0 : frac;
       // (a 224-wide pair tile measured 2 to 12 % slower per flop than a 256-wide one: its B halves are 112 wide)
       const double cost = waves * bn * (bn == 128 ? 1.12 : 1.0) * (pr ? (bn == 224 ? 1.05 : 0.95) : 1.0);
       if (cost < best - 1e-9) { best = cost; bn_out = bn; pair_out = pr; }

@@ -386,3 +386,32 @@ def test_fp8_block_quantisation_round_trip():
     assert (dequantize(aq, asc, 1) - x).abs().max().item() <= x.abs().max().item() * 0.07     # e4m3: 3 mantissa bits
     ref = x @ w.t()
     assert (dequant_matmul(aq, asc, bq, bsc) - ref).abs().max().item() / ref.abs().max().item() < 8e-2
+
+
+def test_gemm_plan_tile_choice():
+    """The plan of the fused GEMMs is pure arithmetic behind the C ABI: large shapes get 256-wide CTA-pair
+    tiles, shapes whose rows do not split into whole 256-row tiles per source / owner keep single CTAs."""
+    import ctypes as C
+
+    from iris_b200 import _lib
+
+    lib = _lib.kernels()
+
+    def plan(op, M, N, K, W=1, M_local=0, two_sm=0, bn=0):
+        d = _lib.IrisGemmDesc()
+        d.op, d.M, d.N, d.K, d.dtype, d.M_local, d.two_sm, d.bn = op, M, N, K, 1, M_local, two_sm, bn
+        d.ctx.world = W
+        out = [C.c_uint64(), C.c_uint64(), C.c_uint64(), C.c_int32(), C.c_int32()]
+        rc = lib.iris_gemm_workspace(C.byref(d), *[C.byref(o) for o in out])
+        return rc, out[3].value, out[4].value, out[0].value, out[2].value
+
+    assert plan(_lib.GEMM_LOCAL, 8192, 3584, 8192)[:3] == (0, 256, 1)
+    assert plan(_lib.GEMM_LOCAL, 8192, 3584, 8192, two_sm=1)[2] == 0                 # pairs switched off
+    assert plan(_lib.GEMM_LOCAL, 128, 8192, 3584)[:3] == (0, 128, 0)                 # few tiles: narrow single-CTA tiles
+    rc, bn, pair, inbox, _ = plan(_lib.GEMM_AG_M, 8192, 3584, 8192, W=8, M_local=1024)
+    assert (rc, bn, pair) == (0, 256, 1) and inbox == 2 * 8 * 1024 * 8192 * 2       # double-buffered inbox of all shards
+    assert plan(_lib.GEMM_AG_M, 8 * 384, 3584, 8192, W=8, M_local=384)[2] == 0       # 384 rows per source: no whole 256-row tiles
+    rc, bn, pair, _, staging = plan(_lib.GEMM_REDUCE_SCATTER, 8192, 8192, 3584, W=8)
+    assert (rc, bn, pair) == (0, 256, 1) and staging == 2 * 8 * (8 * 32) * 128 * 256 * 2
+    assert plan(_lib.GEMM_REDUCE_SCATTER, 1000, 8192, 3584, W=8)[0] != 0             # rows must split into 128-row tiles per rank
+    assert plan(_lib.GEMM_RS_TILES, 8192, 8192, 3584, W=8)[2] == 0                   # tile-granular scatter keeps single CTAs
