@@ -2,27 +2,29 @@
 // ring_attention_common.cuh). One attention CTA works on items of 128 queries x one head and walks
 // the key blocks in arrival order in tiles of 128 keys:
 //
-//   warp 0      TMA producer: Q once per item, then K and V tiles (two stages each) from this
-//               rank's own K/V or from the ring-buffer slot of the block's origin, after the
-//               slot's arrival counter has been seen (acquire, bounded)
+//   warp 0      TMA producer: K and V tiles (three stages each) from this rank's own K/V or from
+//               the ring-buffer slot of the block's origin, after the slot's arrival counter has
+//               been seen (acquire, bounded)
 //   warp 1      MMA issuer: S = Q K^T (tcgen05.mma, M 128, N 128, K 128) into one of two TMEM
-//               buffers, and O += P V (M 128, N 128 = head_dim, K 128 keys) into a third;
-//               S of tile j+1 is issued before P V of tile j, so the tensor pipe works while the
-//               softmax of tile j runs
+//               buffers, and O += P V (M 128, N 128 = head_dim, K 128 keys) into a third. Q and P
+//               are read from TMEM (the A operand of both MMAs), only K and V come from shared
+//               memory, whose bandwidth is what bounds this kernel. S of tile j+1 is issued before
+//               P V of tile j, so the tensor pipe works while the softmax of tile j runs
 //   warps 2..9  softmax, two threads per query row (warp w: TMEM lanes 32 * (w % 4) .. +32, keys
-//               64 * ((w - 2) / 4) .. +64 of the tile): tcgen05.ld of the 64 scores, the row maximum
-//               agreed between the two threads through shared memory, P = exp2(s - max) (one packed
-//               FMA per two scores, one ex2.approx each) written as packed 16-bit pairs into TMEM
-//               (tcgen05.st), from where the second MMA takes it as its A operand: P never touches
-//               shared memory, whose bandwidth is what bounds this kernel (each MMA of a tile already
-//               reads 64 KB of operands from it); running sum kept per thread; when a
-//               row's maximum moved, its O row in TMEM is rescaled (tcgen05.ld / st, each thread
-//               its 64 columns), which after the first tiles is rare; at the end of an item
-//               O / sum is stored
+//               64 * ((w - 2) / 4) .. +64 of the tile). At the start of an item they copy their
+//               part of the Q row from global memory into TMEM (tcgen05.st). Per tile:
+//               tcgen05.ld of the 64 scores, the row maximum agreed between the two threads
+//               through shared memory, P = exp2(s - max) (one packed FMA per two scores, one
+//               ex2.approx each) written as packed 16-bit pairs over the first 64 columns of the
+//               SAME S buffer (both threads have read their scores by then; the tensor pipe runs
+//               its MMAs in issue order, so the buffer is not overwritten before P V has read it);
+//               running sum kept per thread; when a row's maximum moved, its O row in TMEM is
+//               rescaled (tcgen05.ld / st, each thread its 64 columns), which after the first tiles
+//               is rare; at the end of an item O / sum is stored
 //
-// TMEM: S0 columns [0, 128), S1 [128, 256), O [256, 384), P0 [384, 448), P1 [448, 512) (128 keys as
-// 64 columns of 16-bit pairs). Shared memory: Q 32 KB, K 2 x 32 KB, V 2 x 32 KB. Every wait
-// (mbarriers, arrival counters) is bounded.
+// TMEM: S0 / P0 columns [0, 128), S1 / P1 [128, 256), O [256, 384), Q [384, 448) (128 values as 64
+// columns of 16-bit pairs). Shared memory: K 3 x 32 KB, V 3 x 32 KB. Every wait (mbarriers, arrival
+// counters) is bounded.
 #include "ring_attention_common.cuh"
 
 #include "iris/gemm/sm100_mainloop.cuh"
@@ -40,14 +42,13 @@ constexpr int kTK = 128;                 // keys per tile
 constexpr int kTcThreads = 320;
 constexpr int kHalf = 128 * 128;         // bytes of a [128 rows][64 columns] 16-bit half tile
 constexpr int kTile = 2 * kHalf;         // 32 KB
-constexpr int kKvStages = 2;
-constexpr int kTcSmem = 1024 + kTile * (1 + 2 * kKvStages) + 256 + 3072;    // Q, K and V stages, barriers, row exchange
+constexpr int kKvStages = 3;
+constexpr int kTcSmem = 1024 + kTile * 2 * kKvStages + 256 + 3072;    // K and V stages, barriers, row exchange
 constexpr uint64_t kWaitNs = 4000000000ull;
 static_assert(kTcSmem <= 227 * 1024, "shared memory budget");
 
 struct TcArgs {
   RingArgs a;
-  CUtensorMap tmQ;       // [S, Hq * D], box 64 x 128
   CUtensorMap tmKown;    // [S, Hkv * D], box 64 x 128
   CUtensorMap tmVown;    // [S, Hkv * D], box 64 x 64
   CUtensorMap tmKbuf;    // ring buffer seen as [2 * W * 2 * S, Hkv * D], box 64 x 128
@@ -124,20 +125,17 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
   const int group = a.Hq / a.Hkv;
 
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* q_s = smem;
-  uint8_t* k_s = smem + kTile;                           // [stages][kTile]
+  uint8_t* k_s = smem;                                   // [stages][kTile]
   uint8_t* v_s = k_s + kKvStages * kTile;
   uint64_t* bars = (uint64_t*)(v_s + kKvStages * kTile);
-  uint64_t* q_full = bars;              // 1
+  uint64_t* q_full = bars;              // 8 softmax warps: the item's Q is in TMEM
   uint64_t* q_free = bars + 1;          // 1: every S MMA of the item has read Q
-  uint64_t* k_full = bars + 2;          // [2]
-  uint64_t* k_empty = bars + 4;         // [2]
-  uint64_t* v_full = bars + 6;          // [2]
-  uint64_t* v_empty = bars + 8;         // [2]
-  uint64_t* s_full = bars + 10;         // [2]
-  uint64_t* s_empty = bars + 12;        // [2] 8 softmax warps
-  uint64_t* p_full = bars + 14;         // [2] 8 softmax warps
-  uint64_t* p_empty = bars + 16;        // [2] the P V MMA of the tile has read P
+  uint64_t* k_full = bars + 2;          // [3]
+  uint64_t* k_empty = bars + 5;         // [3]
+  uint64_t* v_full = bars + 8;          // [3]
+  uint64_t* v_empty = bars + 11;        // [3]
+  uint64_t* s_full = bars + 14;         // [2]
+  uint64_t* p_full = bars + 16;         // [2] 8 softmax warps
   uint64_t* o_ready = bars + 18;        // [2] by tile parity: O holds every tile up to that one
   uint64_t* o_free = bars + 20;         // 8 softmax warps: the item's O has been read out
   uint32_t* tmem_slot = (uint32_t*)(bars + 21);
@@ -148,13 +146,15 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
   uint32_t* xseq = (uint32_t*)(xchg + 512);
 
   if (threadIdx.x == 0) {
-    ptx::mbar_init(q_full, 1);
+    ptx::mbar_init(q_full, 8);
     ptx::mbar_init(q_free, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kKvStages; ++i) {
       ptx::mbar_init(&k_full[i], 1); ptx::mbar_init(&k_empty[i], 1);
       ptx::mbar_init(&v_full[i], 1); ptx::mbar_init(&v_empty[i], 1);
-      ptx::mbar_init(&s_full[i], 1); ptx::mbar_init(&s_empty[i], 8);
-      ptx::mbar_init(&p_full[i], 8); ptx::mbar_init(&p_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&s_full[i], 1);
+      ptx::mbar_init(&p_full[i], 8);
       ptx::mbar_init(&o_ready[i], 1);
     }
     ptx::mbar_init(o_free, 8);
@@ -179,12 +179,6 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
     bool ok = true;
     for (int it = first; it < items && ok; it += stride, ++n_item) {
       const int h = it % a.Hq, qt = it / a.Hq, kvh = h / group;
-      if (!ptx::mbar_wait(q_free, (n_item & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); break; }
-      if (lane == 0) {
-        ptx::mbar_expect_tx(q_full, kTile);
-        ptx::tma_load_2d(q_s, &g.tmQ, q_full, h * kD, qt * kTQ);
-        ptx::tma_load_2d(q_s + kHalf, &g.tmQ, q_full, h * kD + 64, qt * kTQ);
-      }
       TileWalk w(a, qt);
       while (w.next()) {
         if (w.t == 0 && !((arrived_mask >> w.origin) & 1u)) {
@@ -195,8 +189,8 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
           ptx::fence_proxy_async();
           arrived_mask |= 1u << w.origin;
         }
-        const int st = n_tile & 1;
-        const uint32_t ph = ((n_tile >> 1) & 1) ^ 1;
+        const int st = n_tile % kKvStages;
+        const uint32_t ph = ((n_tile / kKvStages) & 1) ^ 1;
         if (!ptx::mbar_wait(&k_empty[st], ph, kWaitNs) || !ptx::mbar_wait(&v_empty[st], ph, kWaitNs)) {
           ctx.fail(kTimeoutPipeline); ok = false; break;
         }
@@ -230,41 +224,42 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
     const uint32_t idesc_o = make_idesc(kD, !kFp16, true);       // B = V tile, [keys, d] row-major
     uint32_t n_item = 0, n_s = 0, n_pv = 0;     // items, S tiles and P V tiles issued so far
     bool ok = true;
+    // The S buffer of tile j also holds P of tile j (its first 64 columns) until the P V MMA of
+    // tile j has read it; S of tile j + 2 is issued after that MMA and the tensor pipe runs MMAs in
+    // issue order, so no barrier guards the reuse of the buffer.
     auto issue_s = [&]() -> bool {
-      const int st = n_s & 1;
-      if (!ptx::mbar_wait(&s_empty[st], ((n_s >> 1) & 1) ^ 1, kWaitNs)) return false;
-      if (!ptx::mbar_wait(&k_full[st], (n_s >> 1) & 1, kWaitNs)) return false;
+      const int sb = n_s & 1, st = n_s % kKvStages;
+      if (!ptx::mbar_wait(&k_full[st], (n_s / kKvStages) & 1, kWaitNs)) return false;
       ptx::tc_fence_after();
       if (lane == 0) {
-        const uint32_t qa = ptx::smem_u32(q_s), kb = ptx::smem_u32(k_s + st * kTile);
+        const uint32_t kb = ptx::smem_u32(k_s + st * kTile);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < 8; ++k) {        // 16 of the 128 head dimensions per step: 8 columns of Q in TMEM
           const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
-          ptx::mma_f16(tmem_base + st * 128, desc_kmajor(qa + off), desc_kmajor(kb + off), idesc_s, k != 0);
+          mma_f16_ts(tmem_base + sb * 128, tmem_base + 384 + k * 8, desc_kmajor(kb + off), idesc_s, k != 0);
         }
         ptx::mma_commit(&k_empty[st]);
-        ptx::mma_commit(&s_full[st]);
+        ptx::mma_commit(&s_full[sb]);
       }
       __syncwarp();
       ++n_s;
       return true;
     };
     auto issue_pv = [&](bool first_of_item) -> bool {
-      const int st = n_pv & 1;
-      if (!ptx::mbar_wait(&p_full[st], (n_pv >> 1) & 1, kWaitNs)) return false;
-      if (!ptx::mbar_wait(&v_full[st], (n_pv >> 1) & 1, kWaitNs)) return false;
+      const int sb = n_pv & 1, st = n_pv % kKvStages;
+      if (!ptx::mbar_wait(&p_full[sb], (n_pv >> 1) & 1, kWaitNs)) return false;
+      if (!ptx::mbar_wait(&v_full[st], (n_pv / kKvStages) & 1, kWaitNs)) return false;
       ptx::tc_fence_after();
       if (lane == 0) {
         const uint32_t vb = ptx::smem_u32(v_s + st * kTile);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t boff = (k >> 2) * kHalf + (k & 3) * 2048;        // V: 64-key halves, 16 keys = 2048 B
-          // P: 16 keys = 8 columns of 16-bit pairs
-          mma_f16_ts(tmem_base + 256, tmem_base + 384 + st * 64 + k * 8, desc_mnmajor(vb + boff), idesc_o, !(first_of_item && k == 0));
+          // P: 16 keys = 8 columns of 16-bit pairs at the start of the tile's S buffer
+          mma_f16_ts(tmem_base + 256, tmem_base + sb * 128 + k * 8, desc_mnmajor(vb + boff), idesc_o, !(first_of_item && k == 0));
         }
         ptx::mma_commit(&v_empty[st]);
-        ptx::mma_commit(&p_empty[st]);
-        ptx::mma_commit(&o_ready[st]);
+        ptx::mma_commit(&o_ready[sb]);
       }
       __syncwarp();
       ++n_pv;
@@ -320,6 +315,23 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
       const int h = it % a.Hq, qt = it / a.Hq;
       const int qpos = qt * kTQ + row;                        // position inside this rank's block
       float m_run = -INFINITY, l_run = 0.f;                   // l_run: this thread's half of the row sum
+      // this thread's 64 values of the Q row -> TMEM (16-bit pairs), once every S MMA of the previous item is done
+      {
+        uint32_t qw[32];
+        const uint4* qsrc = (const uint4*)(a.q + ((size_t)(qt * kTQ + row) * a.Hq + h) * kD * 2 + half * 128);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 v = __ldg(qsrc + i);
+          qw[4 * i] = v.x; qw[4 * i + 1] = v.y; qw[4 * i + 2] = v.z; qw[4 * i + 3] = v.w;
+        }
+        if (!ptx::mbar_wait(q_free, (n_item & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); break; }
+        ptx::tc_fence_after();
+        tmem_st_32x32(lane_addr + 384 + half * 32, qw);
+        tmem_st_wait();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(q_full);
+      }
       TileWalk w(a, qt);
       int j = 0;
       while (w.next()) {
@@ -333,9 +345,6 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
           ptx::tmem_ld_32x32(lane_addr + st * 128 + half * 64 + c * 32, chunk);
         }
         ptx::tmem_ld_wait();
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&s_empty[st]);
         // causal mask on the diagonal tile, maximum of this thread's 64 raw scores
         const bool diag = w.diagonal();
         const int kpos0 = w.t * kTK + half * 64;
@@ -357,8 +366,8 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
         const float m_new = fmaxf(m_run, mx * scale2);     // finite: the diagonal tile holds the row's own key
         const float alpha = j == 0 ? 1.f : ex2_approx(m_run - m_new);
         m_run = m_new;
-        // this P buffer may be rewritten once the P V of two tiles ago has read it
-        if (!ptx::mbar_wait(&p_empty[st], ((n_tile >> 1) & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+        // P goes over the first 64 columns of this tile's S buffer: both threads of the row have read
+        // their scores (the partner published its maximum after its loads)
         uint32_t pw[32];        // this thread's 64 probabilities as 16-bit pairs
         // p = exp2(s * scale - max): packed FMA for two scores at a time, one ex2.approx each, four sum chains
         unsigned long long scale_pair, negm_pair;
@@ -379,7 +388,7 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
             pw[c16 * 4 + e] = pack2<kFp16>(p0, p1);
           }
         }
-        tmem_st_32x32(lane_addr + 384 + st * 64 + half * 32, pw);
+        tmem_st_32x32(lane_addr + st * 128 + half * 32, pw);
         l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
         // rescale O when some row of this warp moved its maximum (O then holds every earlier tile)
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
@@ -480,7 +489,7 @@ int launch_ring_attention_tc(const RingArgs& a, cudaStream_t stream) {
   g.a = a;
   const bool f16 = a.is_fp16 != 0;
   const uint64_t kvc = (uint64_t)a.Hkv * kD;
-  if (!make_map16(&g.tmQ, a.q, f16, a.S, (uint64_t)a.Hq * kD, kTQ)) return 1;
+  if ((uint64_t)a.q & 15) return 1;      // Q rows are read with 16-byte loads
   if (!make_map16(&g.tmKown, a.k, f16, a.S, kvc, kTK)) return 1;
   if (!make_map16(&g.tmVown, a.v, f16, a.S, kvc, 64)) return 1;
   if (W > 1) {
