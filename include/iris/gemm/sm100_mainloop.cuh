@@ -46,7 +46,9 @@ struct Config {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kAccCols = 256;                                  // column pitch of an accumulator buffer
   static constexpr int kTmemCols = 512;
-  static constexpr int kEpiBytes = kEpiWarps * 2 * 4096;                // per warp: two 32-row x 64-col staging chunks
+  static constexpr int kEpiWarpBytes = 2 * 4096 + 256;                  // per warp: 8 KB of staging (two 32-row x 64-col chunks,
+                                                                        // or one 32-row x 128-col round) + 256 B of policy scratch
+  static constexpr int kEpiBytes = kEpiWarps * kEpiWarpBytes;
   static constexpr int kSmemBytes = 1024 + kStages_ * kStageBytes + kEpiBytes + 256;
   static_assert(BN_ % 32 == 0 && BN_ >= 32 && BN_ <= 256, "BN must be a multiple of 32 up to 256");
   static_assert(!kPair_ || kBCols % 16 == 0, "a pair splits B into two halves of whole 16-column groups");
@@ -110,8 +112,8 @@ struct Pipeline {
 //   bool a_source(State&, int m_tile, int kb, ASource& s) const;   (producer warp, all lanes; false = abort)
 //   const CUtensorMap* b_map() const;  bool is_bf16() const;
 //   void begin_tile(State&, int m_tile, int n_tile, uint8_t* warp_scratch) const;
-//        (every epilogue thread, before a tile's stores; warp_scratch: 4 KB of shared memory private
-//         to the warp, free on the row-major path)
+//        (every epilogue thread, before a tile's stores; warp_scratch: 256 bytes of shared memory
+//         private to the warp)
 //   int row_origin(State&, int m_tile) const;              (first output row of the tile: m_tile*128
 //        for a plain GEMM, the group's row offset for a grouped one)
 //   static constexpr bool kSwiGLU;                         (row-major path: the tile's columns are
@@ -287,7 +289,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    uint8_t* my_epi = epi_base + (warp - 2) * (2 * 4096);
+    uint8_t* my_epi = epi_base + (warp - 2) * Cfg::kEpiWarpBytes;
     uint32_t chunk_seq = 0;   // bulk epilogue: chunks issued by this warp (selects the staging half)
     const bool bf16 = pol.is_bf16();
     const bool has_bias = pol.has_bias();
@@ -308,7 +310,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         break;
       }
       ptx::tc_fence_after();
-      pol.begin_tile(est, tm, tn, my_epi + 4096);
+      pol.begin_tile(est, tm, tn, my_epi + 8192);
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * Cfg::kAccCols;
       const int row0 = pol.row_origin(est, tm) + quarter * 32;
       const float rb = has_bias ? pol.row_bias(row0 + lane) : 0.f;
@@ -419,35 +421,47 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
             }
             __syncwarp();
           }
-        } else
+        } else {
+          // Rounds of 128 columns: four tcgen05.ld of 32 columns are packed into a [32 rows][256 B]
+          // staging tile (16-byte groups XOR-swizzled by row), then read back so that 16 consecutive
+          // lanes hold 256 contiguous bytes of one output row: remote stores (multimem, peer
+          // pointers, the per-row destinations of the MoE combine) leave as 256-byte runs.
+          constexpr int kRounds = (Cfg::BN + 127) / 128;
 #pragma unroll 1
-        for (int c = 0; c < Cfg::BN / 32; ++c) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(t_addr + c * 32, r);
-          ptx::tmem_ld_wait();
-          if (c == Cfg::BN / 32 - 1) {
-            ptx::tc_fence_before();
+          for (int rd = 0; rd < kRounds; ++rd) {
+            const int wr = (Cfg::BN - rd * 128) >= 128 ? 128 : (Cfg::BN - rd * 128);    // columns of this round
+            const int col_rd = tn * Cfg::BN + rd * 128;
+#pragma unroll 1
+            for (int q = 0; q < wr / 32; ++q) {
+              const int c = rd * 4 + q;
+              uint32_t r[32];
+              ptx::tmem_ld_32x32(t_addr + c * 32, r);
+              ptx::tmem_ld_wait();
+              if (c == Cfg::BN / 32 - 1) {
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) release_acc(buf);
+              }
+              if constexpr (Policy::kBulkEpilogue) pol.add_partials(est, quarter, c, lane, r);
+              uint32_t packed[16];
+              pack32(r, col_rd + q * 32, packed);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 v = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                *(uint4*)(stage + lane * 256 + (((q * 4 + j) ^ (lane & 15)) * 16)) = v;
+              }
+            }
             __syncwarp();
-            if (lane == 0) release_acc(buf);
-          }
-          if constexpr (Policy::kBulkEpilogue) pol.add_partials(est, quarter, c, lane, r);
-          const int col0 = tn * Cfg::BN + c * 32;
-          uint32_t packed[16];
-          pack32(r, col0, packed);
-          const int sw = (lane >> 1) & 3;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 v = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-            *(uint4*)(stage + lane * 64 + ((j ^ sw) * 16)) = v;
+            for (int i = 0; i < 16; ++i) {
+              const int rr = i * 2 + (lane >> 4), cc = lane & 15;
+              if (cc * 8 < wr) {
+                uint4 v = *(uint4*)(stage + rr * 256 + ((cc ^ (rr & 15)) * 16));
+                pol.store16(est, row0 + rr, col_rd + cc * 8, v);
+              }
+            }
+            __syncwarp();
           }
-          __syncwarp();
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int rr = i * 8 + (lane >> 2), cc = lane & 3;
-            uint4 v = *(uint4*)(stage + rr * 64 + ((cc ^ ((rr >> 1) & 3)) * 16));
-            pol.store16(est, row0 + rr, col0 + cc * 8, v);
-          }
-          __syncwarp();
         }
       }
       ptx::named_barrier(1, kEpiWarps * 32);
