@@ -409,3 +409,67 @@ def _tiles(rank, world):
 
 def test_tile_collectives_between_gpus():
     run_ranks(_tiles, _world(), backend="nccl")
+
+
+def _graph(rank, world):
+    """A tensor-parallel MLP step (all_gather_matmul, matmul_reduce_scatter, all_reduce of a checksum)
+    captured ONCE in a CUDA graph and replayed with new inputs: the kernels keep their call counters on
+    the device and double-buffer their workspaces by call parity, so a replay needs no host-side state."""
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+
+    ctx = iris.iris(2 << 30)
+    dt = torch.bfloat16
+    M_local, K, F = 256, 512, 768
+    torch.manual_seed(70 + rank)
+    X = torch.randn(M_local, K, device="cuda", dtype=dt)
+    W1 = torch.randn(K, F, device="cuda", dtype=dt) * 0.05
+    W2 = torch.randn(F, K, device="cuda", dtype=dt) * 0.05
+    H = torch.empty(world * M_local, F, device="cuda", dtype=dt)
+    Y = ctx.zeros((M_local, K), dtype=dt)
+    S = ctx.zeros((M_local, K), dtype=dt)
+    ws1 = ctx.ops.all_gather_matmul(H, X, W1, shard_dim=0)
+    ws2 = ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True)
+    ws3 = ctx.ccl.all_reduce(S, Y)
+    assert ws1.variant == "fused" and ws2.variant == "fused"
+
+    def step():
+        ctx.ops.all_gather_matmul(H, X, W1, shard_dim=0, workspace=ws1, async_op=True)
+        ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True, workspace=ws2, async_op=True)
+        ctx.ccl.all_reduce(S, Y, workspace=ws3, async_op=True)
+
+    def reference():
+        xs = [torch.empty_like(X) for _ in range(world)]
+        dist.all_gather(xs, X)
+        h = (torch.cat(xs).float() @ W1.float()).to(dt)
+        y = h.float() @ W2.float()
+        dist.all_reduce(y)                                   # sum over ranks of the partial products
+        y_mine = y[rank * M_local:(rank + 1) * M_local].to(dt).float()
+        s = y_mine.clone()
+        dist.all_reduce(s)
+        return y_mine, s
+
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        step()                                               # an odd number of eager calls before the capture
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):     # other threads (NCCL watchdog) keep running
+            step()
+        for it in range(4):
+            X.copy_(torch.randn(M_local, K, device="cuda", dtype=dt))
+            g.replay()
+            stream.synchronize()
+            y_ref, s_ref = reference()
+            tol = 3e-2 * max(1.0, y_ref.abs().max().item())
+            assert _maxerr(Y.float(), y_ref) < tol, it
+            assert _maxerr(S.float(), s_ref) < world * tol, it
+        step()                                               # eager calls still line up after replays
+        stream.synchronize()
+    ctx.check()
+    ctx.barrier()
+
+
+def test_fused_step_replays_from_a_cuda_graph():
+    run_ranks(_graph, _world(), backend="nccl", timeout=600)
