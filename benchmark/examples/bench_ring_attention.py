@@ -22,14 +22,17 @@ PEAK_TFLOPS = 1383.6
 @bench.axis("num_ranks", [1, 2, 4, 8])
 @bench.axis("seq_per_rank", [2048, 8192])
 @bench.axis("causal", [0, 1])
+@bench.axis("layout", ["contiguous", "zigzag"])
 def ring_attention(state, ctx):
     W, S, causal = ctx.get_num_ranks(), state["seq_per_rank"], bool(state["causal"])
+    if state["layout"] == "zigzag" and not causal:
+        state.skip("the layouts only differ under a causal mask")
     Hq, Hkv, D = 32, 8, 128
     dt = torch.bfloat16
     q = torch.randn(S, Hq, D, device="cuda", dtype=dt)
     k = torch.randn(S, Hkv, D, device="cuda", dtype=dt)
     v = torch.randn(S, Hkv, D, device="cuda", dtype=dt)
-    layer = RingAttention(ctx, S, Hq, Hkv, D)
+    layer = RingAttention(ctx, S, Hq, Hkv, D, layout=state["layout"])
     out = torch.empty_like(q)
     flops = 4.0 * S * (W * S) * Hq * D * (0.5 if causal else 1.0)
     state.set_flops(flops)

@@ -222,7 +222,8 @@ typedef struct IrisRingAttnDesc {
   const void* q; const void* k; const void* v;
   void* kv_buf; int32_t* flags; int32_t* state;
   void* out; float* lse;
-  int32_t S, Hq, Hkv, D, causal, n_comm, dtype, reserved;
+  int32_t S, Hq, Hkv, D, causal, n_comm, dtype;
+  int32_t options;        // bit 0: use the mma.sync attention CTAs; bit 1: zigzag layout (needs S % 256 == 0)
   float sm_scale;
 } IrisRingAttnDesc;
 
@@ -243,9 +244,12 @@ int iris_ring_attention(const IrisRingAttnDesc* d, void* stream) {
   a.S = d->S; a.Hq = d->Hq; a.Hkv = d->Hkv; a.causal = d->causal; a.is_fp16 = d->dtype == IRIS_F16;
   a.n_comm = d->ctx.world > 1 ? (d->n_comm > 0 ? d->n_comm : 8) : 0;
   a.sm_scale = d->sm_scale;
-  if (d->reserved != 1) {      // reserved == 1 forces the mma.sync attention CTAs
+  a.zigzag = (d->options & 2) ? 1 : 0;
+  if (a.zigzag && (d->S % 256 || (d->options & 1))) return -3;     // only the tcgen05 CTAs know the zigzag layout
+  if (!(d->options & 1)) {
     const int r = launch_ring_attention_tc(a, (cudaStream_t)stream);
     if (r <= 0) return r;
+    if (a.zigzag) return -3;
   }
   const int smem = kStages * 2 * kTileBytes;   // 64 KB: three CTAs per SM
   static bool attr = false;

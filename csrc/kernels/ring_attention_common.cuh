@@ -35,6 +35,7 @@ struct RingArgs {
   uint8_t* out;           // [S, Hq, D]
   float* lse;             // optional [S, Hq] natural log
   int S, Hq, Hkv, causal, n_comm, is_fp16;
+  int zigzag;             // 1: this rank's block is [chunk r | chunk 2W-1-r] of 2W chunks (tcgen05 attention CTAs only)
   float sm_scale;
 };
 

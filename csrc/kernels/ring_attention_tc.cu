@@ -82,34 +82,63 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 // The key tiles of one item, in the order every role walks them: blocks in arrival order (own,
-// r-1, r-2, ...), tiles inside a block in order; causal items skip blocks that lie after all of
-// their queries and stop the diagonal block at their own tile.
+// r-1, r-2, ...), tiles inside a block in order; causal items skip what lies after their queries.
+//
+// Contiguous layout: rank r holds tokens [r*S, (r+1)*S). A causal item of query tile qt takes all
+// tiles of earlier blocks, tiles 0..qt of its own block (the last one masked on the diagonal) and
+// nothing of later blocks - so the last rank does W times the work of the first.
+// Zigzag layout: the sequence is cut into 2W chunks of S/2 tokens and rank r holds chunks r and
+// 2W-1-r (its block = [chunk r | chunk 2W-1-r]). Under a causal mask a query of chunk r sees
+// chunks 0..r, a query of chunk 2W-1-r sees every first-half chunk and the second-half chunks
+// of origins >= r: every rank does the same amount of work.
 struct TileWalk {
-  int W, r, S, causal, qt;
-  int step = 0, t = -1, n_tiles = 0, origin = 0;
-  __device__ TileWalk(const RingArgs& a, int qt_) : W(a.ctx.world), r(a.ctx.rank), S(a.S), causal(a.causal), qt(qt_) { open_block(); }
+  int W, r, T, causal, zigzag, qt;
+  int step = 0, t = -1, origin = 0;
+  int a0 = 0, a1 = 0, b0 = 0, b1 = 0;      // tile ranges [a0, a1) and [b0, b1) of the current block (b0 >= a1)
+  int diag = -1;                           // tile of the block that needs the diagonal mask
+  bool first = false;                      // the current tile is the first one taken from its block
+  __device__ TileWalk(const RingArgs& a, int qt_)
+      : W(a.ctx.world), r(a.ctx.rank), T(a.S / kTK), causal(a.causal), zigzag(a.zigzag), qt(qt_) { open_block(); }
+  __device__ void ranges() {
+    a0 = 0; a1 = T; b0 = b1 = T; diag = -1;
+    if (!causal) return;
+    if (!zigzag) {
+      if (origin > r) a1 = 0;
+      else if (origin == r) { a1 = qt + 1; diag = qt; }
+      return;
+    }
+    const int Th = T / 2;
+    if (qt < Th) {                  // query chunk r: first halves of origins <= r
+      if (origin > r) a1 = 0;
+      else if (origin == r) { a1 = qt + 1; diag = qt; }
+      else a1 = Th;
+    } else {                        // query chunk 2W-1-r: every first half, second halves of origins >= r
+      a1 = Th;
+      if (origin > r) { b0 = Th; b1 = T; }
+      else if (origin == r) { b0 = Th; b1 = qt + 1; diag = qt; }
+    }
+  }
   __device__ void open_block() {
     for (; step < W; ++step) {
       origin = r - step;
       if (origin < 0) origin += W;
-      if (causal && origin > r) continue;
-      n_tiles = (causal && origin == r) ? qt + 1 : S / kTK;
-      t = -1;
-      return;
+      ranges();
+      if (a1 > a0 || b1 > b0) { t = -1; return; }
     }
-    n_tiles = 0;
   }
   // advances to the next tile; false when the item is finished
   __device__ bool next() {
-    if (step >= W) return false;
-    if (++t < n_tiles) return true;
-    ++step;
-    open_block();
-    if (step >= W) return false;
-    t = 0;
-    return true;
+    while (step < W) {
+      first = t < 0;
+      if (t < 0) t = a1 > a0 ? a0 : b0;
+      else if (++t == a1 && b1 > b0) t = b0;
+      if ((t >= a0 && t < a1) || (t >= b0 && t < b1)) return true;
+      ++step;
+      open_block();
+    }
+    return false;
   }
-  __device__ bool diagonal() const { return causal && origin == r && t == qt; }
+  __device__ bool diagonal() const { return t == diag; }
 };
 
 template <bool kFp16>
@@ -181,7 +210,7 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
       const int h = it % a.Hq, qt = it / a.Hq, kvh = h / group;
       TileWalk w(a, qt);
       while (w.next()) {
-        if (w.t == 0 && !((arrived_mask >> w.origin) & 1u)) {
+        if (w.first && !((arrived_mask >> w.origin) & 1u)) {
           int seen = 1;
           if (lane == 0) seen = wait_flag_ge(ctx, a.flags + (size_t)par * W + w.origin, target) ? 1 : 0;
           seen = __shfl_sync(0xffffffffu, seen, 0);

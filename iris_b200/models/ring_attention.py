@@ -26,14 +26,25 @@ class IrisRingAttnDesc(C.Structure):
         ("kv_buf", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p),
         ("out", C.c_void_p), ("lse", C.c_void_p),
         ("S", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32), ("causal", C.c_int32),
-        ("n_comm", C.c_int32), ("dtype", C.c_int32), ("reserved", C.c_int32),
+        ("n_comm", C.c_int32), ("dtype", C.c_int32), ("options", C.c_int32),
         ("sm_scale", C.c_float),
     ]
 
 
-def reference_attention(q, k, v, causal: bool = False, q_offset: int = 0, sm_scale: float | None = None):
+def zigzag_positions(rank: int, world: int, seq_per_rank: int, device=None) -> torch.Tensor:
+    """Global positions of rank ``rank``'s tokens in the zigzag layout: the sequence of
+    ``world * seq_per_rank`` tokens is cut into ``2 * world`` chunks and the rank holds chunk ``rank``
+    followed by chunk ``2 * world - 1 - rank`` (balanced work under a causal mask)."""
+    half = seq_per_rank // 2
+    a = torch.arange(half, device=device)
+    return torch.cat([rank * half + a, (2 * world - 1 - rank) * half + a])
+
+
+def reference_attention(q, k, v, causal: bool = False, q_offset: int = 0, sm_scale: float | None = None, q_pos=None,
+                        k_pos=None):
     """fp32 attention of ``q [Sq, Hq, D]`` over ``k, v [Sk, Hkv, D]``; query i sits at position
-    ``q_offset + i`` of the key sequence when ``causal``."""
+    ``q_offset + i`` of the key sequence when ``causal`` (or at ``q_pos[i]``, key j at ``k_pos[j]``,
+    when the positions are given)."""
     Sq, Hq, D = q.shape
     Sk, Hkv, _ = k.shape
     sm_scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(D)
@@ -42,8 +53,8 @@ def reference_attention(q, k, v, causal: bool = False, q_offset: int = 0, sm_sca
     vf = v.float().repeat_interleave(g, dim=1)
     s = torch.einsum("qhd,khd->hqk", q.float(), kf) * sm_scale
     if causal:
-        qi = torch.arange(Sq, device=q.device)[:, None] + q_offset
-        ki = torch.arange(Sk, device=q.device)[None, :]
+        qi = (torch.arange(Sq, device=q.device) + q_offset if q_pos is None else q_pos.to(q.device))[:, None]
+        ki = (torch.arange(Sk, device=q.device) if k_pos is None else k_pos.to(q.device))[None, :]
         s = s.masked_fill((ki > qi)[None], float("-inf"))
     p = torch.softmax(s, dim=-1)
     return torch.einsum("hqk,khd->qhd", p, vf)
@@ -51,7 +62,8 @@ def reference_attention(q, k, v, causal: bool = False, q_offset: int = 0, sm_sca
 
 class RingAttention:
     def __init__(self, ctx, seq_per_rank: int, num_q_heads: int, num_kv_heads: int, head_dim: int = 128,
-                 sm_scale: float | None = None, comm_sms: int = 8, dtype=torch.bfloat16, use_tcgen05: bool | None = None):
+                 sm_scale: float | None = None, comm_sms: int = 8, dtype=torch.bfloat16, use_tcgen05: bool | None = None,
+                 layout: str = "contiguous"):
         if head_dim != 128:
             raise ValueError("the ring-attention kernel is specialised for head_dim 128")
         if num_q_heads % num_kv_heads:
@@ -61,6 +73,13 @@ class RingAttention:
         self.comm_sms, self.dtype = comm_sms, dtype
         # None: tcgen05 attention CTAs whenever seq_per_rank is a multiple of 128; False: the mma.sync CTAs
         self.use_tcgen05 = use_tcgen05
+        # "contiguous": rank r holds tokens [r*S, (r+1)*S); "zigzag": chunks r and 2W-1-r of 2W chunks
+        # (see zigzag_positions), which balances causal attention over the ranks
+        if layout not in ("contiguous", "zigzag"):
+            raise ValueError(f"unknown layout {layout!r}")
+        if layout == "zigzag" and (seq_per_rank % 256 or use_tcgen05 is False) and not ctx.is_cpu:
+            raise ValueError("the zigzag layout needs seq_per_rank to be a multiple of 256 and the tcgen05 attention CTAs")
+        self.layout = layout
         W = ctx.get_num_ranks()
         esize = 2 if not ctx.is_cpu else torch.empty((), dtype=dtype).element_size()
         # ring buffer [parity][origin rank][K | V][S, Hkv, D] and its arrival counters, on the heap
@@ -99,7 +118,7 @@ class RingAttention:
         d.S, d.Hq, d.Hkv, d.D, d.causal, d.n_comm = self.S, self.Hq, self.Hkv, self.D, int(causal), self.comm_sms
         d.dtype = _lib.DTYPE_CODE[q.dtype]
         d.sm_scale = self.sm_scale
-        d.reserved = 1 if self.use_tcgen05 is False else 0
+        d.options = (1 if self.use_tcgen05 is False else 0) | (2 if self.layout == "zigzag" else 0)
         _lib.check(self._lib().iris_ring_attention(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "ring attention launch")
         return (out, lse) if return_lse else out
 
@@ -113,6 +132,10 @@ class RingAttention:
         vs = ctx.zeros((W * self.S, self.Hkv * self.D), dtype=torch.float32)
         ctx.ccl.all_gather(ks, ctx.as_symmetric(k.float().reshape(self.S, -1).contiguous()))
         ctx.ccl.all_gather(vs, ctx.as_symmetric(v.float().reshape(self.S, -1).contiguous()))
+        q_pos = k_pos = None
+        if self.layout == "zigzag":
+            q_pos = zigzag_positions(me, W, self.S)
+            k_pos = torch.cat([zigzag_positions(r, W, self.S) for r in range(W)])
         o = reference_attention(q, ks.view(W * self.S, self.Hkv, self.D), vs.view(W * self.S, self.Hkv, self.D), causal,
-                                q_offset=me * self.S, sm_scale=self.sm_scale)
+                                q_offset=me * self.S, sm_scale=self.sm_scale, q_pos=q_pos, k_pos=k_pos)
         return o.to(q.dtype)

@@ -415,3 +415,22 @@ def test_gemm_plan_tile_choice():
     assert (rc, bn, pair) == (0, 256, 1) and staging == 2 * 8 * (8 * 32) * 128 * 256 * 2
     assert plan(_lib.GEMM_REDUCE_SCATTER, 1000, 8192, 3584, W=8)[0] != 0             # rows must split into 128-row tiles per rank
     assert plan(_lib.GEMM_RS_TILES, 8192, 8192, 3584, W=8)[2] == 0                   # tile-granular scatter keeps single CTAs
+
+
+def test_zigzag_positions_cover_the_sequence_and_balance_causal_work():
+    from iris_b200.models import reference_attention, zigzag_positions
+
+    W, S = 4, 64
+    pos = [zigzag_positions(r, W, S) for r in range(W)]
+    assert torch.equal(torch.sort(torch.cat(pos)).values, torch.arange(W * S))
+    # every rank sees the same number of (query, key) pairs under a causal mask
+    work = [int((torch.cat(pos)[None, :] <= p[:, None]).sum()) for p in pos]
+    assert max(work) - min(work) <= S
+    # attention with explicit positions equals attention over the sorted sequence
+    torch.manual_seed(0)
+    q, k, v = torch.randn(W * S, 2, 16), torch.randn(W * S, 2, 16), torch.randn(W * S, 2, 16)
+    full = reference_attention(q, k, v, causal=True)
+    order = torch.cat(pos)
+    for r in range(W):
+        mine = reference_attention(q[pos[r]], k[order], v[order], causal=True, q_pos=pos[r], k_pos=order)
+        assert torch.allclose(mine, full[pos[r]], atol=1e-5)

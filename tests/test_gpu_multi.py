@@ -342,6 +342,41 @@ def test_ring_attention_between_gpus():
     run_ranks(_ring, _world(), backend="nccl")
 
 
+def _ring_zigzag(rank, world):
+    """Zigzag layout: rank r holds chunks r and 2W-1-r of the sequence; the causal result must equal
+    attention over the whole sequence with the tokens' global positions."""
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.models import RingAttention, reference_attention, zigzag_positions
+
+    ctx = iris.iris(1 << 30)
+    S, Hq, Hkv, D = 512, 8, 2, 128
+    dt = torch.bfloat16
+    torch.manual_seed(40 + rank)
+    q = torch.randn(S, Hq, D, device="cuda", dtype=dt)
+    k = torch.randn(S, Hkv, D, device="cuda", dtype=dt)
+    v = torch.randn(S, Hkv, D, device="cuda", dtype=dt)
+    ks = torch.empty(world * S, Hkv, D, device="cuda", dtype=dt)
+    vs = torch.empty(world * S, Hkv, D, device="cuda", dtype=dt)
+    dist.all_gather_into_tensor(ks, k)
+    dist.all_gather_into_tensor(vs, v)
+    q_pos = zigzag_positions(rank, world, S, device="cuda")
+    k_pos = torch.cat([zigzag_positions(r, world, S, device="cuda") for r in range(world)])
+    layer = RingAttention(ctx, S, Hq, Hkv, layout="zigzag")
+    for causal in (True, False):
+        for _ in range(2):
+            out = layer(q, k, v, causal=causal)
+        ref = reference_attention(q, ks, vs, causal, q_pos=q_pos, k_pos=k_pos)
+        assert (out.float() - ref).abs().max().item() < 2e-2, causal
+    ctx.check()
+    ctx.barrier()
+
+
+def test_ring_attention_zigzag_layout_between_gpus():
+    run_ranks(_ring_zigzag, _world(), backend="nccl")
+
+
 def _tiles(rank, world):
     import os
 

@@ -360,6 +360,25 @@ def test_ring_attention_world1(ctx, S, Hq, Hkv, causal, tc):
     ctx.check()
 
 
+def test_ring_attention_zigzag_world1(ctx):
+    """With one rank the zigzag block [chunk 0 | chunk 1] is the plain sequence: the zigzag tile walk
+    must reproduce ordinary causal attention."""
+    from iris_b200.models import RingAttention, reference_attention
+
+    S, Hq, Hkv, dt = 512, 4, 2, torch.bfloat16
+    torch.manual_seed(8)
+    q = torch.randn(S, Hq, 128, device="cuda", dtype=dt)
+    k = torch.randn(S, Hkv, 128, device="cuda", dtype=dt)
+    v = torch.randn(S, Hkv, 128, device="cuda", dtype=dt)
+    layer = RingAttention(ctx, S, Hq, Hkv, layout="zigzag")
+    for causal in (True, False):
+        out = layer(q, k, v, causal=causal)
+        assert (out.float() - reference_attention(q, k, v, causal)).abs().max().item() < 2e-2
+    with pytest.raises(ValueError):
+        RingAttention(ctx, 384, Hq, Hkv, layout="zigzag")
+    ctx.check()
+
+
 @pytest.fixture(scope="module")
 def user_module():
     from iris_b200 import jit
