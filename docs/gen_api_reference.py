@@ -12,7 +12,7 @@ MODULES = [
     "iris_b200.host.iris", "iris_b200.host.heap", "iris_b200.host.rma", "iris_b200.host.tracing", "iris_b200.host.topology",
     "iris_b200.host.platform", "iris_b200.host.artifacts", "iris_b200.ccl", "iris_b200.ccl.config", "iris_b200.ops",
     "iris_b200.ops.config", "iris_b200.ops.gemm", "iris_b200.ops.gemm_fp8", "iris_b200.ops.workspace",
-    "iris_b200.models.flash_decode", "iris_b200.models.moe", "iris_b200.models.ring_attention", "iris_b200.bench._core",
+    "iris_b200.models.flash_decode", "iris_b200.models.moe", "iris_b200.models.ring_attention", "iris_b200.models.tp_mlp", "iris_b200.bench._core",
     "iris_b200.bench._runner", "iris_b200.jit", "iris_b200.drivers",
 ]
 

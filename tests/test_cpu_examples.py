@@ -8,7 +8,7 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-EXAMPLES = ["rma_basics", "ccl_collectives", "ops_fused", "gemm_patterns", "all_reduce_variants", "flash_decode", "moe",
+EXAMPLES = ["rma_basics", "tp_mlp_training_step", "ccl_collectives", "ops_fused", "gemm_patterns", "all_reduce_variants", "flash_decode", "moe",
             "ring_attention", "tracing"]
 
 

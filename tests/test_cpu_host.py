@@ -434,3 +434,50 @@ def test_zigzag_positions_cover_the_sequence_and_balance_causal_work():
     for r in range(W):
         mine = reference_attention(q[pos[r]], k[order], v[order], causal=True, q_pos=pos[r], k_pos=order)
         assert torch.allclose(mine, full[pos[r]], atol=1e-5)
+
+
+def _tp_mlp_check(rank, world, dtype_name, Ml, K, F, tol):
+    """Forward and backward of TensorParallelMLP against autograd on the unsharded MLP."""
+    import torch
+
+    import iris_b200 as iris
+    from iris_b200.models import TensorParallelMLP
+
+    ctx = iris.iris(1 << 30)
+    dt = getattr(torch, dtype_name)
+    dev = ctx.get_device()
+    g = torch.Generator().manual_seed(0)          # the same full tensors on every rank
+    Xall = torch.randn(world * Ml, K, generator=g).to(dev)
+    W1 = (torch.randn(K, world * F, generator=g) * 0.1).to(dev)
+    W2 = (torch.randn(world * F, K, generator=g) * 0.1).to(dev)
+    G = torch.randn(world * Ml, K, generator=g).to(dev)
+    rows, cols = slice(rank * Ml, (rank + 1) * Ml), slice(rank * F, (rank + 1) * F)
+    for act in (None, "silu", "gelu"):
+        mlp = TensorParallelMLP(ctx, K, F, activation=act, dtype=dt, w1=W1[:, cols].to(dt).contiguous(), w2=W2[cols].to(dt).contiguous())
+        for _ in range(2):                                    # the second step reuses the fused workspaces
+            mlp.zero_grad()
+            x = Xall[rows].to(dt).clone().requires_grad_(True)
+            y = mlp(x)
+            y.backward(G[rows].to(dt))
+        Xr = Xall.to(dt).float().clone().requires_grad_(True)
+        W1r = W1.to(dt).float().clone().requires_grad_(True)
+        W2r = W2.to(dt).float().clone().requires_grad_(True)
+        hp = Xr @ W1r
+        h = hp if act is None else (torch.nn.functional.silu(hp) if act == "silu" else torch.nn.functional.gelu(hp, approximate="tanh"))
+        Yr = h @ W2r
+        Yr.backward(G.to(dt).float())
+
+        def close(a, b, what):
+            err = (a.float() - b).abs().max().item() / max(b.abs().max().item(), 1e-6)
+            assert err < tol, (act, what, err)
+
+        close(y.detach(), Yr[rows].detach(), "y")
+        close(x.grad, Xr.grad[rows], "dx")
+        close(mlp.w1.grad, W1r.grad[:, cols], "dw1")
+        close(mlp.w2.grad, W2r.grad[cols], "dw2")
+    ctx.check()
+    ctx.barrier()
+
+
+def test_tensor_parallel_mlp_forward_backward_cpu():
+    run_ranks(_tp_mlp_check, 2, args=("float32", 8, 16, 12, 1e-4))

@@ -417,3 +417,26 @@ def test_tile_collectives_world1(ctx, user_module, op):
     torch.cuda.synchronize()
     assert torch.equal(dst, src), op          # with one rank every collective is the identity
     ctx.check()
+
+
+def test_tensor_parallel_mlp_forward_backward_world1(ctx):
+    from iris_b200.models import TensorParallelMLP
+
+    dt = torch.bfloat16
+    torch.manual_seed(12)
+    M, K, F = 256, 512, 384
+    X = torch.randn(M, K, device="cuda")
+    W1 = torch.randn(K, F, device="cuda") * 0.1
+    W2 = torch.randn(F, K, device="cuda") * 0.1
+    G = torch.randn(M, K, device="cuda")
+    mlp = TensorParallelMLP(ctx, K, F, activation="silu", dtype=dt, w1=W1.to(dt), w2=W2.to(dt))
+    x = X.to(dt).requires_grad_(True)
+    y = mlp(x)
+    y.backward(G.to(dt))
+    assert mlp._ws["ag1"].variant == "fused" and mlp._ws["rs2"].variant == "fused"
+    Xr, W1r, W2r = X.to(dt).float().requires_grad_(True), W1.to(dt).float().requires_grad_(True), W2.to(dt).float().requires_grad_(True)
+    Yr = torch.nn.functional.silu(Xr @ W1r) @ W2r
+    Yr.backward(G.to(dt).float())
+    for a, b in ((y.detach(), Yr.detach()), (x.grad, Xr.grad), (mlp.w1.grad, W1r.grad), (mlp.w2.grad, W2r.grad)):
+        assert (a.float() - b).abs().max().item() / b.abs().max().item() < 3e-2
+    ctx.check()
