@@ -1,7 +1,7 @@
 // CPU backend: the device header library (include/iris/*.cuh) compiled for the host, driven over
 // ranges of elements. "Peers" are other processes whose memfd heaps are mapped into this one, so
 // translate() + an ordinary access reaches them exactly as a peer mapping does on the GPU. The
-// reference has no CPU path for its RMA ops (SURVEY of tests: everything needs real GPUs); this
+// reference has no CPU path for its RMA ops (its tests all need real GPUs); this
 // backend lets the host layer, the RMA semantics and failure handling be tested under gloo.
 #include <stdint.h>
 #include <string.h>
