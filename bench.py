@@ -189,6 +189,10 @@ def main() -> int:
     if args.impl == "reference":
         return run_reference(args)
 
+    # stdout carries ONE line (the JSON record): keep NCCL's version banner off it
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
+
     import torch
     import torch.distributed as dist
 
