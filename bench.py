@@ -190,7 +190,8 @@ def main() -> int:
         return run_reference(args)
 
     # stdout carries ONE line (the JSON record): keep NCCL's version banner off it
-    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+    # (the image's NCCL configuration prints it when NCCL_DEBUG is unset or VERSION)
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
         os.environ["NCCL_DEBUG"] = "WARN"
 
     import torch
