@@ -24,14 +24,12 @@ if __name__ == "__main__":
     target = torch.randn(rows, hidden, device=dev, dtype=dt)
     losses = []
     for step in range(5):
-        mark = ctx.heap_mark()
         opt.zero_grad()
         loss = (mlp(x).float() - target.float()).square().mean()
         loss.backward()
         opt.step()
         losses.append(float(loss))
         ctx.barrier()
-        ctx.heap_release(mark)          # the gathered activations of the backward pass
     assert losses[-1] < losses[0], losses
     ctx.check()
     ctx.info(f"loss {losses[0]:.4f} -> {losses[-1]:.4f}")

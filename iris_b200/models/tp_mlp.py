@@ -70,10 +70,11 @@ class _TPMLPFunction(torch.autograd.Function):
         layer._ws["rs2"] = ctx.ops.matmul_reduce_scatter(dx, dh, w1.t(), scatter_rows=True, workspace=layer._ws.get("rs2"), async_op=True)
         # weight gradients: gathered activations, then plain library GEMMs
         if W > 1:
-            x_all = ctx.empty((W * M_local, K), dtype=x.dtype)
-            dy_all = ctx.empty((W * M_local, K), dtype=x.dtype)
-            ctx.ccl.all_gather(x_all, ctx.as_symmetric(x), async_op=True)
-            ctx.ccl.all_gather(dy_all, ctx.as_symmetric(dy), async_op=True)
+            x_loc, dy_loc, x_all, dy_all = layer._gather_buffers(M_local, K, x.dtype)
+            x_loc.copy_(x)
+            dy_loc.copy_(dy)
+            ctx.ccl.all_gather(x_all, x_loc, async_op=True)
+            ctx.ccl.all_gather(dy_all, dy_loc, async_op=True)
         else:
             x_all, dy_all = x, dy
         h = _ACTS[layer.activation][0](h_pre) if layer.activation else h_pre
@@ -86,9 +87,8 @@ class TensorParallelMLP(torch.nn.Module):
     """``y = reduce_scatter(act(all_gather(x) @ W1_r) @ W2_r)`` with ``x``, ``y`` of shape ``(M / W, hidden)``.
 
     ``w1`` is this rank's ``(hidden, ffn / W)`` block, ``w2`` its ``(ffn / W, hidden)`` block (random
-    init when omitted). Heap allocations made by the backward pass (gathered activations) are taken
-    from the symmetric heap; call ``ctx.heap_mark()`` / ``ctx.heap_release()`` around a training
-    step to reuse them.
+    init when omitted). The workspaces of the four fused ops and the heap buffers of the backward
+    pass's all-gathers are created on first use (collectively) and reused by later steps.
     """
 
     def __init__(self, ctx, hidden: int, ffn_local: int, activation: str | None = "silu", dtype=torch.bfloat16, w1=None,
@@ -101,6 +101,16 @@ class TensorParallelMLP(torch.nn.Module):
         self.w1 = torch.nn.Parameter((torch.randn(hidden, ffn_local, device=dev) * 0.02).to(dtype) if w1 is None else w1.detach().clone())
         self.w2 = torch.nn.Parameter((torch.randn(ffn_local, hidden, device=dev) * 0.02).to(dtype) if w2 is None else w2.detach().clone())
         self._ws: dict = {}
+        self._bufs: dict = {}
+
+    def _gather_buffers(self, M_local: int, K: int, dtype):
+        """Heap tensors of the backward pass's two all-gathers, allocated once per shape (collective)."""
+        key = (M_local, K, dtype)
+        if key not in self._bufs:
+            W = self.ctx.get_num_ranks()
+            self._bufs[key] = (self.ctx.empty((M_local, K), dtype=dtype), self.ctx.empty((M_local, K), dtype=dtype),
+                               self.ctx.empty((W * M_local, K), dtype=dtype), self.ctx.empty((W * M_local, K), dtype=dtype))
+        return self._bufs[key]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return _TPMLPFunction.apply(x, self.w1, self.w2, self)
