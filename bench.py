@@ -190,9 +190,8 @@ def main() -> int:
         return run_reference(args)
 
     # stdout carries ONE line (the JSON record): keep NCCL's version banner off it
-    # (the image's NCCL configuration prints it when NCCL_DEBUG is unset or VERSION)
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # (NCCL writes its debug output, the banner included, to stdout unless told otherwise)
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
 
     import torch
     import torch.distributed as dist
