@@ -389,6 +389,7 @@ typedef struct IrisMoeDesc {
   int32_t* counts_local; int32_t* counts_all; int32_t* cursor; int32_t* list_off; int32_t* sorted_pairs; int32_t* my_off;
   int32_t* expert_rows; int32_t* expert_row0; int32_t* tile_prefix; int32_t* expected_cum; int32_t* arrived;
   void* inbox_meta;
+  int32_t weights_kmajor;   // 1: w13 is [El, 2F, D] and w2 is [El, D, F] (each expert's weight transposed: K contiguous)
 } IrisMoeDesc;
 
 int iris_moe_forward(const IrisMoeDesc* d, void* stream_) {
@@ -407,7 +408,7 @@ int iris_moe_forward(const IrisMoeDesc* d, void* stream_) {
 
   const int sms = sm_count();
   const int comm = ctx.world > 0 ? (d->comm_ctas > 0 ? d->comm_ctas : 16) : 0;
-  using Cfg = Config<256, false, 4>;
+  const bool km = d->weights_kmajor != 0;
   {
     GroupedGemm<1> pol;
     IrisGemmDesc gd;
@@ -416,7 +417,8 @@ int iris_moe_forward(const IrisMoeDesc* d, void* stream_) {
     pol.tmA = CUtensorMap{};
     int r = make_map(&pol.tmA, d->inbox, IRIS_BF16, d->capacity, d->D, d->D, kBK, kBM);
     if (r) return r;
-    r = make_map(&pol.tmB, d->w13, IRIS_BF16, (uint64_t)d->El * d->D, 2 * d->F, 2 * d->F, 64, 64);
+    if (km) r = make_map(&pol.tmB, d->w13, IRIS_BF16, (uint64_t)d->El * 2 * d->F, d->D, d->D, kBK, 256);
+    else r = make_map(&pol.tmB, d->w13, IRIS_BF16, (uint64_t)d->El * d->D, 2 * d->F, 2 * d->F, 64, 64);
     if (r) return r;
     pol.sh = Shape{d->capacity, 2 * d->F, d->D};
     pol.tiles_m = 0; pol.tiles_n = (2 * d->F) / 256; pol.group_m = 1;
@@ -424,15 +426,16 @@ int iris_moe_forward(const IrisMoeDesc* d, void* stream_) {
     pol.bias_row = nullptr; pol.bias_col = nullptr; pol.status = d->ctx.status; pol.timeline = nullptr;
     pol.ctx = ctx; pol.sb = nullptr; pol.dm = dm; pol.meta = m;
     pol.x = (const uint8_t*)d->x; pol.inbox = (uint8_t*)d->inbox; pol.H = (uint8_t*)d->H; pol.comb = (uint8_t*)d->comb;
-    pol.n_comm_ctas = comm; pol.k_per_expert = d->D; pol.n_per_expert = 0; pol.b_kmajor = 0;
-    r = launch<Cfg>(pol, sms, s);
+    pol.n_comm_ctas = comm; pol.k_per_expert = d->D; pol.n_per_expert = km ? 2 * d->F : 0; pol.b_kmajor = km;
+    r = km ? launch<Config<256, true, 4>>(pol, sms, s) : launch<Config<256, false, 4>>(pol, sms, s);
     if (r) return r;
   }
   {
     GroupedGemm<2> pol;
     int r = make_map(&pol.tmA, d->H, IRIS_BF16, d->capacity, d->F, d->F, kBK, kBM);
     if (r) return r;
-    r = make_map(&pol.tmB, d->w2, IRIS_BF16, (uint64_t)d->El * d->F, d->D, d->D, 64, 64);
+    if (km) r = make_map(&pol.tmB, d->w2, IRIS_BF16, (uint64_t)d->El * d->D, d->F, d->F, kBK, 256);
+    else r = make_map(&pol.tmB, d->w2, IRIS_BF16, (uint64_t)d->El * d->F, d->D, d->D, 64, 64);
     if (r) return r;
     pol.sh = Shape{d->capacity, d->D, d->F};
     pol.tiles_m = 0; pol.tiles_n = d->D / 256; pol.group_m = 1;
@@ -440,8 +443,8 @@ int iris_moe_forward(const IrisMoeDesc* d, void* stream_) {
     pol.bias_row = nullptr; pol.bias_col = nullptr; pol.status = d->ctx.status; pol.timeline = nullptr;
     pol.ctx = ctx; pol.sb = (SyncBlock*)d->sync_gemm2; pol.dm = dm; pol.meta = m;
     pol.x = nullptr; pol.inbox = (uint8_t*)d->inbox; pol.H = (uint8_t*)d->H; pol.comb = (uint8_t*)d->comb;
-    pol.n_comm_ctas = 0; pol.k_per_expert = d->F; pol.n_per_expert = 0; pol.b_kmajor = 0;
-    r = launch<Cfg>(pol, sms, s);
+    pol.n_comm_ctas = 0; pol.k_per_expert = d->F; pol.n_per_expert = km ? d->D : 0; pol.b_kmajor = km;
+    r = km ? launch<Config<256, true, 4>>(pol, sms, s) : launch<Config<256, false, 4>>(pol, sms, s);
     if (r) return r;
   }
   moe_reduce_kernel<<<d->T, 256, 0, s>>>((const __nv_bfloat16*)d->comb, d->topk_w, (__nv_bfloat16*)d->out, d->T, d->K, d->D);

@@ -32,6 +32,7 @@ class IrisMoeDesc(C.Structure):
         ("sorted_pairs", C.c_void_p), ("my_off", C.c_void_p),
         ("expert_rows", C.c_void_p), ("expert_row0", C.c_void_p), ("tile_prefix", C.c_void_p), ("expected_cum", C.c_void_p),
         ("arrived", C.c_void_p), ("inbox_meta", C.c_void_p),
+        ("weights_kmajor", C.c_int32),
     ]
 
 
@@ -84,8 +85,9 @@ class MoELayer:
         if hidden % 256 or ffn % 128:
             raise ValueError("the fused kernels need hidden % 256 == 0 and ffn % 128 == 0")
         dev = ctx.get_device()
-        self.w13 = fuse_gate_up(w_gate.to(torch.bfloat16), w_up.to(torch.bfloat16))
-        self.w2 = w_down.to(torch.bfloat16).contiguous()
+        # each expert's weight is kept transposed (K contiguous): the layout the tensor cores read fastest
+        self.w13 = fuse_gate_up(w_gate.to(torch.bfloat16), w_up.to(torch.bfloat16)).transpose(1, 2).contiguous()   # [El, 2F, D]
+        self.w2 = w_down.to(torch.bfloat16).transpose(1, 2).contiguous()                                          # [El, D, F]
         pairs = max_tokens * top_k
         cap = W * pairs if capacity_factor is None else min(W * pairs, int(capacity_factor * pairs))
         self.capacity = max(128, -(-cap // 128) * 128)
@@ -135,6 +137,7 @@ class MoELayer:
         for name in ("topk_idx", "topk_w", "counts_local", "counts_all", "cursor", "list_off", "sorted_pairs", "my_off",
                      "expert_rows", "expert_row0", "tile_prefix", "expected_cum", "arrived", "inbox_meta"):
             setattr(d, name, getattr(self, name).data_ptr())
+        d.weights_kmajor = 1
         _lib.check(self._lib().iris_moe_forward(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "MoE forward launch")
         self._keep = logits
         return out
