@@ -710,6 +710,11 @@ int iris_ccl_launch(int op, const IrisCclDesc* d, void* stream) {
     return cudaGetLastError() == cudaSuccess ? 0 : -21;
   }
   int grid = grid_for(d, (size_t)d->M * d->N * es);
+  // The two-shot all-reduce pulls its share from every peer: a CTA pulls about 15 GB/s, so large
+  // messages take every SM unless the caller chose a count (measured on 2 GPUs at 256 MB:
+  // 846 us with 64 CTAs, 619 us with 148; the NVLS variant is best at 64).
+  if (op == 2 && a.variant == kArTwoShot && (d->comm_sms <= 0 || d->comm_sms == 64) && (size_t)d->M * d->N * es >= ((size_t)8 << 20))
+    grid = 148;
   if (op == 2 && a.variant == kArRing) {
     grid = d->comm_sms > 0 ? d->comm_sms : 32;  // must match the flag layout chosen by the host
   }

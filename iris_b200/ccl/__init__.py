@@ -220,6 +220,8 @@ class CCL:
             return "push"           # one NVLink traversal, no barrier rounds
         if nbytes <= 256 * 1024:
             return "one_shot"
+        if self.ctx.ctx_struct(group).world == 2 and nbytes >= (8 << 20):
+            return "two_shot"       # with one peer the switch has nothing to reduce: pulling on all SMs is faster
         return "nvls" if nvls_ok else "two_shot"
 
     def all_reduce_preamble(self, output_tensor, input_tensor, config=None, workspace=None, group=None):
