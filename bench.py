@@ -189,9 +189,12 @@ def main() -> int:
     if args.impl == "reference":
         return run_reference(args)
 
-    # stdout carries ONE line (the JSON record): keep NCCL's version banner off it
-    # (NCCL writes its debug output, the banner included, to stdout unless told otherwise)
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    # stdout carries ONE line (the JSON record). Libraries write to file descriptor 1 on their own
+    # (NCCL prints its version banner there), so the descriptor is pointed at stderr for the run and
+    # the record goes to a saved copy of the original stdout at the end.
+    sys.stdout.flush()
+    record_fd = os.dup(1)
+    os.dup2(2, 1)
 
     import torch
     import torch.distributed as dist
@@ -356,7 +359,8 @@ def main() -> int:
         "impl": "ours",
     }
     if rank == 0:
-        print(json.dumps(out))
+        sys.stdout.flush()
+        os.write(record_fd, (json.dumps(out) + "\n").encode())
     ctx.barrier()
     dist.barrier()
     dist.destroy_process_group()
