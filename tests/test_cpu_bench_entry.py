@@ -1,0 +1,51 @@
+"""The parts of bench.py that need no GPU: the reference arm's record and the clock summary."""
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _bench_module():
+    spec = importlib.util.spec_from_file_location("bench_entry", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_reference_arm_prints_one_record_and_exits_zero():
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                           "--warmup", "1"], capture_output=True, text=True, timeout=120)
+    assert proc.returncode == 0
+    lines = [l for l in proc.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    rec = json.loads(lines[0])
+    assert rec["impl"] == "reference" and ("unavailable" in rec or "value" in rec)
+
+
+def test_clock_summary_prefers_the_timed_window_and_collects_reasons():
+    bench = _bench_module()
+    s = bench.ClockSampler(0)
+    s.source, s.max_mhz, s.stop_flag = "nvml", 1965.0, True
+
+    class _Done:
+        def join(self, timeout=None):
+            return None
+
+    s.thread = _Done()
+    t0 = time.time()
+    s.load_from = t0
+    s.timed = [t0 + 1.0, t0 + 2.0]
+    s.rows = [(t0 + 0.5, 1965.0, 300.0, set()), (t0 + 1.1, 1400.0, 990.0, {"sw_power_cap"}), (t0 + 1.5, 1350.0, 1000.0, {"sw_power_cap"}),
+              (t0 + 1.9, 1380.0, 995.0, set()), (t0 + 2.5, 1900.0, 400.0, {"hw_slowdown"})]
+    out = s.stop()
+    assert out["window"] == "timed region" and out["samples"] == 3
+    assert out["sm_mhz"] == 1380.0 and out["sm_max_mhz"] == 1965.0 and out["power_w_max"] == 1000.0
+    assert out["reasons"] == ["sw_power_cap"]          # the slowdown sample lies outside the timed region
+    # too few samples inside the timed region: the loaded span is used instead
+    s.timed = [t0 + 1.05, t0 + 1.2]
+    out = s.stop()
+    assert out["window"].startswith("warm-up") and out["samples"] == 5 and "hw_slowdown" in out["reasons"]
