@@ -421,8 +421,9 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
         l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
         // rescale O when some row of this warp moved its maximum (O then holds every earlier tile)
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          // (the barrier of the previous tile's parity: between "two tiles ago", known complete from
-          //  the P buffer wait above, and "the previous tile" a phase parity is unambiguous)
+          // (the barrier of the previous tile's parity: this tile's S was issued after the P V of two
+          //  tiles ago and MMAs complete in issue order, so between "two tiles ago" and "the previous
+          //  tile" a phase parity is unambiguous)
           if (!ptx::mbar_wait(&o_ready[(n_tile - 1) & 1], ((n_tile - 1) >> 1) & 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
           ptx::tc_fence_after();
 #pragma unroll 1
@@ -538,7 +539,7 @@ int launch_ring_attention_tc(const RingArgs& a, cudaStream_t stream) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int items = (a.S / kTQ) * a.Hq;
-  int attn = sms - a.n_comm;                 // one CTA per SM (192 KB of shared memory), all resident
+  int attn = sms - a.n_comm;                 // one CTA per SM (196 KB of shared memory), all resident
   if (attn > items) attn = items;
   if (attn < 1) return 1;
   const int grid = a.n_comm + attn;
