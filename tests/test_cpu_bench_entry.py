@@ -49,3 +49,18 @@ def test_clock_summary_prefers_the_timed_window_and_collects_reasons():
     s.timed = [t0 + 1.05, t0 + 1.2]
     out = s.stop()
     assert out["window"].startswith("warm-up") and out["samples"] == 5 and "hw_slowdown" in out["reasons"]
+
+
+def test_benchmark_runner_end_to_end_on_the_cpu_backend(tmp_path):
+    """The runner spawns one process per rank, sweeps the axes given on the command line and writes
+    the formatted results: here one collective on two gloo ranks."""
+    out = tmp_path / "ag.json"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, os.path.join(ROOT, "benchmark", "ccl", "bench_collectives.py"), "--axis_num_ranks=2", "--axis_bytes=4096,8192",
+           "--axis_impl=iris", "--axis_dtype=float32", "--benchmark_filter", "all_gather", "--n_warmup", "1", "--n_repeat", "2",
+           "--benchmark_format", "json", "--benchmark_out", str(out)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    res = json.loads(out.read_text())["results"]
+    assert [r["params"]["bytes"] for r in res] == ["4096", "8192"]
+    assert all(r["benchmark"] == "all_gather" and r["world_size"] == 2 and r["gpu_time_ms"] > 0 and not r["skipped"] for r in res)
