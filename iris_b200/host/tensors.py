@@ -74,7 +74,9 @@ def apply_memory_format(heap, tensor: torch.Tensor, size, memory_format, input_t
         return _strided_on_heap(heap, tensor, size, (c * h * w, 1, c * w, c))
     if memory_format == torch.channels_last_3d and len(size) == 5:
         _, c, d, h, w = size
-        return _strided_on_heap(heap, tensor, size, (c * d * h * w, 1, c * d * w, c * w, c))
+        # torch's NDHWC strides; the reference uses c*d*w for the depth stride, which aliases
+        # elements whenever d != h (iris/host/memory/tensors.py:250)
+        return _strided_on_heap(heap, tensor, size, (c * d * h * w, 1, h * w * c, w * c, c))
     if memory_format == torch.preserve_format and input_tensor is not None:
         st = input_tensor.stride()
         if len(size) in (4, 5) and len(st) == len(size) and st[1] == 1 and tuple(input_tensor.shape) == tuple(size):
