@@ -137,6 +137,7 @@ class SymmetricHeap:
         self.group = group
         self._handle = None
         self._mesh = None
+        self.poison = os.environ.get("IRIS_DEBUG", "0") not in ("", "0")
         rt = _rt()
         allocator_type = os.environ.get("IRIS_ALLOCATOR", allocator_type)
         cuda = torch.cuda.is_available() and os.environ.get("IRIS_BACKEND", "") != "cpu"
@@ -277,7 +278,12 @@ class SymmetricHeap:
         if off < 0:
             used = _rt().iris_heap_offset(self._handle)
             raise MemoryError(f"Heap out of memory: requested {nbytes} bytes, {self.heap_size - used} of {self.heap_size} free")
-        return tensor_from_ptr(self.base + off, int(num_elements), dtype, self.device, keepalive=self)
+        t = tensor_from_ptr(self.base + off, int(num_elements), dtype, self.device, keepalive=self)
+        if self.poison and nbytes:
+            # debug mode: fresh memory reads as NaN (floating point) or -1 (integers), so that a
+            # kernel that consumes data nobody wrote shows up in the first comparison
+            t.view(torch.uint8).fill_(0xFF)
+        return t
 
     def get_heap_bases(self) -> torch.Tensor:
         return self.heap_bases

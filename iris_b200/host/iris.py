@@ -22,7 +22,7 @@ from . import distributed as D
 from . import tensors as T
 from .heap import KIND_CPU, SymmetricHeap, _rt
 from .logging import DEBUG, ERROR, INFO, WARNING, log_rank, logger
-from .platform import get_cu_count, get_device_id_for_rank
+from .platform import get_cu_count, get_device_id_for_rank, is_simulation_env
 
 SYNC_BLOCK_BYTES = (8 + _lib.MAX_RANKS) * 4
 _STATUS_NAMES = {
@@ -58,8 +58,13 @@ class Iris:
         self.heap = SymmetricHeap(heap_size, max(self.gpu_id, 0), self.cur_rank, self.num_ranks, allocator_type)
         self.device = self.heap.device
         self.heap_size = heap_size
+        if is_simulation_env():
+            self._dump_heap_bases()
         self.is_cpu = self.heap.kind == KIND_CPU
         self.timeout_ms = int(os.environ.get("IRIS_TIMEOUT_MS", "5000"))
+        # IRIS_DEBUG=1: fresh heap memory is poisoned, every host barrier compares the ranks'
+        # allocation offsets, and every synchronous collective ends with check()
+        self.debug_checks = os.environ.get("IRIS_DEBUG", "0") not in ("", "0")
         # status word + sync block of the context itself (barrier) + per-purpose sync blocks
         self._status = self.heap.allocate(1, torch.int32)
         self._status.zero_()
@@ -78,6 +83,18 @@ class Iris:
         self.rma = HostRMA(self)
         self._ops = None
         D.distributed_barrier()
+
+    def _dump_heap_bases(self) -> None:
+        """Simulation runs (``IRIS_SIMULATION=1``) leave ``<prefix>_rank_<r>_heap_bases.json`` behind
+        for tools that replay a captured kernel and need the addresses it saw (prefix from
+        ``IRIS_HEAP_BASES_PREFIX``, default ``iris``; reference: iris/host/iris.py:119-134)."""
+        import json
+
+        prefix = os.environ.get("IRIS_HEAP_BASES_PREFIX", "iris")
+        record = {"rank": self.cur_rank, "num_ranks": self.num_ranks,
+                  "heap_bases": [hex(int(b)) for b in self.heap.bases_host()]}
+        with open(f"{prefix}_rank_{self.cur_rank}_heap_bases.json", "w") as f:
+            json.dump(record, f, indent=2)
 
     # ------------------------------------------------------------------ logging helpers
     def _log(self, level, message):
@@ -122,6 +139,16 @@ class Iris:
             else:
                 stream.synchronize()
         D.distributed_barrier(group)
+        if self.debug_checks:
+            self.debug_verify(group)
+
+    def debug_verify(self, group=None) -> None:
+        """What ``IRIS_DEBUG=1`` runs after every host barrier and synchronous collective: a failed
+        device-side wait raises here rather than at some later ``check()``, and (for barriers of all
+        ranks) heaps that have diverged are reported at the first barrier after the divergence."""
+        self.check()
+        if group is None:
+            self.verify_symmetry()
 
     def device_barrier(self, group=None):
         """Barrier across ranks executed on the GPU, on the current stream, without host

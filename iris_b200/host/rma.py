@@ -58,6 +58,14 @@ class HostRMA:
         for r in (from_rank, to_rank):
             if not 0 <= r < ctx.num_ranks:
                 raise ValueError(f"rank {r} out of range")
+        # A tensor whose address is translated to another rank must lie on the heap: the same
+        # offset has to exist there. (A device kernel would otherwise touch unmapped memory.)
+        me = ctx.cur_rank
+        translated = {"load": [(a, from_rank)], "store": [(a, to_rank)], "get": [(a, from_rank)], "put": [(b, to_rank)],
+                      "copy": [(a, from_rank), (b, to_rank)]}.get(op, [(a, to_rank)])
+        for t, r in translated:
+            if r != me and not ctx.is_symmetric(t):
+                raise ValueError(f"host RMA {op}: the tensor accessed on rank {r} is not on the symmetric heap")
         fval, ival, icmp = 0.0, 0, 0
         if value is not None:
             if a.dtype in (torch.float16, torch.bfloat16):
