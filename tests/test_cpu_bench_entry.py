@@ -6,6 +6,8 @@ import subprocess
 import sys
 import time
 
+import pytest
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -64,3 +66,48 @@ def test_benchmark_runner_end_to_end_on_the_cpu_backend(tmp_path):
     res = json.loads(out.read_text())["results"]
     assert [r["params"]["bytes"] for r in res] == ["4096", "8192"]
     assert all(r["benchmark"] == "all_gather" and r["world_size"] == 2 and r["gpu_time_ms"] > 0 and not r["skipped"] for r in res)
+
+
+def test_serving_shape_all_reduce_benchmark_on_the_cpu_backend(tmp_path):
+    """``(M tokens, 2880)`` bf16 all-reduce sweep: the library baseline is skipped without NCCL, the
+    variants check their result before timing."""
+    out = tmp_path / "serving.csv"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, os.path.join(ROOT, "benchmark", "ccl", "bench_all_reduce_serving_shapes.py"), "--axis_num_ranks=2",
+           "--axis_M=1,64", "--axis_variant=auto,two_shot,nvls", "--n_warmup", "1", "--n_repeat", "2", "--benchmark_format", "csv",
+           "--benchmark_out", str(out)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    import csv
+
+    rows = list(csv.DictReader(out.open()))
+    assert len(rows) == 2 + 6
+    timed = [r for r in rows if r["skipped"] == "0"]
+    assert {(r["benchmark"], r["variant"]) for r in timed} == {("iris_all_reduce", "auto"), ("iris_all_reduce", "two_shot")}
+    assert all(float(r["gpu_time_ms"]) > 0 and float(r["bandwidth_gbps"]) > 0 for r in timed)
+    assert all(r["skipped"] == "1" for r in rows if r["benchmark"] == "nccl_all_reduce" or r["variant"] == "nvls")
+
+
+def test_sweep_table_from_a_csv(tmp_path, capsys):
+    sys.path.insert(0, os.path.join(ROOT, "benchmark", "ccl"))
+    try:
+        import plot_sweep_results as plot
+    finally:
+        sys.path.pop(0)
+    src = tmp_path / "sweep.csv"
+    src.write_text("benchmark,impl,bytes,gpu_time_ms,bandwidth_gbps,skipped\n"
+                   "all_reduce,iris,4096,0.010,0.4,0\nall_reduce,nccl,4096,0.020,0.2,0\n"
+                   "all_reduce,iris,1024,0.008,0.1,0\nall_reduce,nccl,1024,0.016,0.05,0\n"
+                   "all_reduce,iris,16384,0.0,,1\nall_gather,iris,1024,0.004,0.2,0\n")
+    rows = plot.load(str(src), {"benchmark": "all_reduce"})
+    assert len(rows) == 4                                   # the skipped point and the other benchmark are gone
+    xs, names, table = plot.pivot(rows, "bytes", ["impl"], "gpu_time_ms")
+    assert xs == ["1024", "4096"] and names == ["iris", "nccl"] and table["nccl"]["4096"] == 0.020
+    text = plot.render(xs, names, table, "bytes", "gpu_time_ms", "nccl")
+    assert "iris / nccl" in text and text.splitlines()[-1].split()[-1] == "0.500"
+    assert plot.main([str(src), "--x", "bytes", "--series", "benchmark,impl", "--y", "bandwidth_gbps"]) == 0
+    assert "all_gather/iris" in capsys.readouterr().out
+    assert plot.main([str(src), "--x", "nope"]) == 2
+    assert plot.main([str(src), "--where", "impl=none"]) == 1
+    with pytest.raises(SystemExit):
+        plot.main([str(src), "--baseline", "missing"])
