@@ -15,7 +15,10 @@ collective itself) and the averages are copied back into ``param.grad``.
 Buckets are sized for launch latency and overlap, not for link count: through NVSwitch a collective
 costs the same whichever peers take part, so a few tens of megabytes per bucket amortise the launch
 while leaving several buckets to overlap with the rest of the backward pass. Every rank must build
-the buckets from the same parameter list (they are heap allocations).
+the buckets from the same parameter list (they are heap allocations), and with ``attach()`` every
+rank must run the same autograd graph: the collectives are launched in the order in which buckets
+fill up, and kernels that wait for one another have to be queued in the same order on every rank
+(a rank that differs runs into the bounded waits and ``ctx.check()`` reports it).
 """
 from __future__ import annotations
 
@@ -41,6 +44,9 @@ class _Bucket:
 
 
 class GradientBuckets:
+    """Heap buckets over ``params`` (those that require a gradient), summed or averaged across
+    ``group`` by ``all_reduce()`` after backward, or by ``attach()`` + ``finish()`` during it."""
+
     def __init__(self, ctx, params, bucket_bytes: int = 64 << 20, group=None, average: bool = True, reduce_dtype=None):
         self.ctx, self.group, self.average = ctx, group, average
         self.world = ctx.ctx_struct(group).world

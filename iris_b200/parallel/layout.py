@@ -21,6 +21,9 @@ from typing import Mapping
 
 
 class ParallelLayout:
+    """``ParallelLayout({"tp": 4, "dp": 2})``: ranks numbered with the first dimension fastest; groups
+    along a dimension are arithmetic progressions of global ranks (see the module docstring)."""
+
     def __init__(self, dims: Mapping[str, int], world_size: int | None = None, rank: int | None = None):
         if not dims:
             raise ValueError("at least one dimension is needed")

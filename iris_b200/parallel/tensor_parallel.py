@@ -65,6 +65,9 @@ class _TPLinearBase(torch.nn.Module):
 
 
 class ColumnParallelLinear(_TPLinearBase):
+    """``y = x @ W[:, r-th column block]`` with this rank's ``(in, out / W)`` weight; all-gather of
+    sequence-parallel input fused into the GEMM, optional gather of the output columns."""
+
     def __init__(self, ctx, in_features: int, out_features_local: int, bias: bool = False, sequence_parallel: bool = True,
                  gather_output: bool = False, dtype=torch.bfloat16, weight: torch.Tensor | None = None,
                  bias_value: torch.Tensor | None = None, seed: int | None = None):
@@ -123,6 +126,9 @@ class ColumnParallelLinear(_TPLinearBase):
 
 
 class RowParallelLinear(_TPLinearBase):
+    """``y = sum over ranks of x_r @ W[r-th row block]`` with this rank's ``(in / W, out)`` weight;
+    the sum is a reduce-scatter (sequence parallel) or an all-reduce fused into the GEMM."""
+
     def __init__(self, ctx, in_features_local: int, out_features: int, bias: bool = False, sequence_parallel: bool = True,
                  dtype=torch.bfloat16, weight: torch.Tensor | None = None, bias_value: torch.Tensor | None = None,
                  seed: int | None = None):

@@ -9,7 +9,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 EXAMPLES = ["rma_basics", "tp_mlp_training_step", "ccl_collectives", "ops_fused", "gemm_patterns", "all_reduce_variants", "flash_decode", "moe",
-            "ring_attention", "tracing"]
+            "ring_attention", "tracing", "parallel_layouts"]
 
 
 def _free_port() -> int:
