@@ -124,12 +124,14 @@ class Iris:
 
     # ------------------------------------------------------------------ collective host helpers
     def broadcast(self, value, src: int = 0):
-        """Broadcast a scalar, numpy array or tensor from rank ``src`` to all ranks."""
-        if isinstance(value, (torch.Tensor, np.ndarray)) or (self.cur_rank != src and value is None):
-            kind = D.distributed_broadcast_scalar("tensor" if isinstance(value, (torch.Tensor, np.ndarray)) else "scalar", src)
-            if kind == "tensor":
-                return D.distributed_broadcast_tensor(value, src)
-        return D.distributed_broadcast_scalar(value, src)
+        """Broadcast a scalar, numpy array or tensor from rank ``src`` to all ranks. What the other
+        ranks pass as ``value`` is ignored (``None`` is fine): the source's value decides the kind."""
+        is_array = isinstance(value, (torch.Tensor, np.ndarray))
+        # one object broadcast carries the kind and, for scalars, the value itself
+        kind, payload = D.distributed_broadcast_scalar(("tensor", None) if is_array else ("scalar", value), src)
+        if kind == "tensor":
+            return D.distributed_broadcast_tensor(value, src)
+        return payload
 
     def barrier(self, stream=None, group=None):
         """Host barrier: wait for this rank's GPU work (one stream or the device), then for all ranks."""

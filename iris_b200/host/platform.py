@@ -139,8 +139,8 @@ def do_bench(fn, barrier_fn=lambda: None, preamble_fn=lambda: None, n_warmup: in
     Protocol of the reference (iris/host/platform/utils.py:137-201): one untimed call, ``n_warmup``
     warm-ups, then ``n_repeat`` timed iterations, each preceded by ``barrier_fn(); preamble_fn();``
     an L2 flush and another ``barrier_fn()``. Returns milliseconds: ``return_mode`` in
-    ``mean|min|max|median|all``, or the requested quantiles. Use ``iris_b200.utils.timing`` when
-    the number has to be the maximum over ranks.
+    ``mean|min|max|median|all``, or the requested quantiles. Use ``iris_b200.utils.time_max_over_ranks``
+    when the number has to be the maximum over ranks.
     """
     if return_mode not in ("mean", "min", "max", "median", "all"):
         raise ValueError(f"unknown return_mode {return_mode!r}")

@@ -111,3 +111,38 @@ def test_sweep_table_from_a_csv(tmp_path, capsys):
     assert plot.main([str(src), "--where", "impl=none"]) == 1
     with pytest.raises(SystemExit):
         plot.main([str(src), "--baseline", "missing"])
+
+
+def test_performance_gate(tmp_path, capsys):
+    sys.path.insert(0, os.path.join(ROOT, "benchmark"))
+    try:
+        import check_regression as gate
+    finally:
+        sys.path.pop(0)
+    thresholds = json.load(open(os.path.join(ROOT, "benchmark", "dataset", "perf_thresholds.json")))
+    assert {r["n_gpus"] for r in thresholds["bench"]} == {1, 2, 4, 8}
+    good = tmp_path / "good.json"
+    good.write_text("NCCL version banner\n" + json.dumps({"metric": "tflops", "value": 1200.0, "n_gpus": 1}) + "\n"
+                    + json.dumps({"impl": "reference", "unavailable": "not installable"}) + "\n")
+    slow = tmp_path / "slow.json"
+    slow.write_text(json.dumps({"metric": "tflops", "value": 900.0, "n_gpus": 1}) + "\n")
+    assert gate.main(["--bench", str(good)]) == 0
+    out = capsys.readouterr().out
+    assert "ok    bench.py at 1 GPU(s)" in out and out.count("not measured") == 3
+    assert gate.main(["--bench", str(good), "--require-all"]) == 1
+    assert gate.main(["--bench", str(slow)]) == 1
+    assert "FAIL  bench.py at 1 GPU(s) value: 900" in capsys.readouterr().out
+    sweep = tmp_path / "sweep.json"
+    rows = [{"benchmark": "all_gather_matmul", "params": {"num_ranks": "8", "impl": "iris", "M": "8192"}, "gpu_time_ms": 0.45, "skipped": False},
+            {"benchmark": "all_gather_matmul", "params": {"num_ranks": "8", "impl": "nccl", "M": "8192"}, "gpu_time_ms": 0.56, "skipped": False},
+            {"benchmark": "matmul_reduce", "params": {"num_ranks": "8", "impl": "iris", "op": "all_reduce", "M": "8192"}, "gpu_time_ms": 0.9, "skipped": False},
+            {"benchmark": "matmul_reduce", "params": {"num_ranks": "8", "impl": "iris", "op": "reduce_scatter", "M": "8192"}, "gpu_time_ms": 0.0, "skipped": True}]
+    sweep.write_text(json.dumps({"results": rows}))
+    assert gate.main(["--sweep", str(sweep)]) == 1
+    out = capsys.readouterr().out
+    assert "ok    all_gather_matmul" in out and "FAIL  matmul_reduce" in out and "op': 'all_reduce'" in out
+    assert out.count("not measured") == 2                                 # the skipped point and the collective sweep
+    rows[2]["gpu_time_ms"] = 0.6
+    sweep.write_text(json.dumps({"results": rows}))
+    assert gate.main(["--sweep", str(sweep), "--bench", str(good)]) == 0
+    assert gate.main([]) == 2 and gate.main(["--bench", str(tmp_path / "absent.json")]) == 2

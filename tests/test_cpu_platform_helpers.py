@@ -1,0 +1,159 @@
+"""Runtime bindings, distributed helpers, timing loops and raw-pointer tensors without a GPU.
+
+The reference covers these in tests/unittests/test_hip_apis.py, test_get_num_xcc.py,
+test_iris_helpers.py, test_broadcast.py, test_logging.py and test_is_symmetric.py, all on GPUs. The
+parts that need no device are checked here; the device queries themselves are in the GPU suite.
+"""
+import ctypes
+import logging
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import run_ranks
+
+
+def test_runtime_bindings_without_a_device(monkeypatch):
+    import iris_b200 as iris
+    from iris_b200 import hip
+
+    # the names the reference exposes under iris.hip
+    for name in ("count_devices", "set_device", "get_device_id", "get_cu_count", "get_wall_clock_rate", "get_arch_string",
+                 "get_num_xcc", "get_ipc_handle", "open_ipc_handle", "get_address_range"):
+        assert callable(getattr(hip, name)), name
+    assert hip.get_num_xcc() == 1 and hip.get_num_xcc(3) == 1           # no chiplets to spread tiles over
+    assert hip.get_wall_clock_rate() == 1_000_000                        # kHz of a nanosecond counter
+    if not torch.cuda.is_available():
+        assert hip.count_devices() == 0 and hip.get_device_id() == -1
+        with pytest.raises(RuntimeError):
+            hip.get_address_range(0x1000)
+    monkeypatch.delenv("LOCAL_RANK", raising=False)
+    assert [iris.get_device_id_for_rank(r, 4) for r in range(6)] == [0, 1, 2, 3, 0, 1]
+    monkeypatch.setenv("LOCAL_RANK", "5")
+    assert iris.get_device_id_for_rank(0, 4) == 1 and iris.get_device_id_for_rank(9, 8) == 5
+    monkeypatch.setenv("IRIS_SIMULATION", "1")
+    assert iris.is_simulation_env()
+    monkeypatch.setenv("IRIS_SIMULATION", "0")
+    assert not iris.is_simulation_env()
+
+
+def test_do_bench_protocol_and_return_modes():
+    import iris_b200 as iris
+
+    log = []
+    out = iris.do_bench(lambda: log.append("fn"), barrier_fn=lambda: log.append("b"), preamble_fn=lambda: log.append("p"),
+                        n_warmup=2, n_repeat=3, return_mode="all")
+    assert isinstance(out, list) and len(out) == 3 and all(t >= 0 for t in out)
+    # one untimed call, the warm-ups, the timed calls; each wrapped as barrier, preamble, barrier, fn
+    assert log == ["b", "p", "b", "fn"] * (1 + 2 + 3)
+    for mode in ("mean", "min", "max", "median"):
+        assert isinstance(iris.do_bench(lambda: None, n_warmup=0, n_repeat=4, return_mode=mode), float)
+    q = iris.do_bench(lambda: None, n_warmup=0, n_repeat=8, quantiles=[0.2, 0.5, 0.8])
+    assert len(q) == 3 and q[0] <= q[1] <= q[2]
+    assert isinstance(iris.do_bench(lambda: None, n_warmup=0, n_repeat=4, quantiles=[0.5]), float)
+    with pytest.raises(ValueError):
+        iris.do_bench(lambda: None, return_mode="p99")
+
+
+def test_tensor_from_raw_pointer():
+    import iris_b200 as iris
+
+    for dt in (torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.int8, torch.uint8, torch.int16, torch.int32,
+               torch.int64, torch.bool):
+        n = 24
+        esize = torch.empty((), dtype=dt).element_size()
+        backing = (ctypes.c_uint8 * (n * esize))()
+        t = iris.tensor_from_ptr(ctypes.addressof(backing), n, dt, "cpu", keepalive=backing)
+        assert t.dtype == dt and t.shape == (n,) and t.data_ptr() == ctypes.addressof(backing)
+        t.fill_(1)
+        assert any(bytes(backing))                               # writes go to the wrapped memory, not to a copy
+        ctypes.memset(backing, 0, n * esize)
+        assert not t.any()
+    assert iris.tensor_from_ptr(0, 0, torch.float32, "cpu").shape == (0,)
+    cai = iris.CUDAArrayInterface(0x7000_0000_0000, (4, 2), "<f4")
+    assert cai.__cuda_array_interface__ == {"shape": (4, 2), "typestr": "<f4", "data": (0x7000_0000_0000, False), "version": 3,
+                                            "strides": None}
+
+
+def test_logger_levels(capsys):
+    import iris_b200 as iris
+
+    assert iris.logger.name == "iris"
+    iris.set_logger_level(iris.DEBUG)
+    assert iris.logger.level == logging.DEBUG
+    iris.set_logger_level(iris.ERROR)
+    assert iris.logger.level == logging.ERROR and not iris.logger.isEnabledFor(iris.WARNING)
+    iris.set_logger_level(iris.WARNING)
+    assert (iris.DEBUG, iris.INFO, iris.WARNING, iris.ERROR) == (logging.DEBUG, logging.INFO, logging.WARNING, logging.ERROR)
+
+
+def test_context_needs_a_process_group():
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+
+    assert not dist.is_initialized()
+    with pytest.raises(RuntimeError, match="init_process_group"):
+        iris.iris(1 << 20)
+
+
+def _helpers(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.host import distributed as D
+    from iris_b200.utils import time_max_over_ranks
+
+    assert D.init_distributed() == (None, rank, world)
+    for dt in (np.int32, np.int64, np.uint64, np.float32, np.float64, np.uint8, np.bool_):
+        got = D.distributed_allgather(np.array([rank + 1, 7], dtype=dt))
+        assert got.shape == (world, 2) and got.dtype == dt
+        assert got[:, 0].tolist() == [dt(r + 1) for r in range(world)] and all(got[:, 1] == dt(7))
+    big = D.distributed_allgather(np.array([2**63 + rank], dtype=np.uint64))        # above the int64 range
+    assert [int(v) for v in big[:, 0]] == [2**63 + r for r in range(world)]
+    md = D.distributed_allgather_multidim(np.full((2, 3), rank, dtype=np.int64))
+    assert md.shape == (world, 2, 3) and all((md[r] == r).all() for r in range(world))
+    objs = D.distributed_allgather_object({"rank": rank, "name": f"r{rank}"})
+    assert objs == [{"rank": r, "name": f"r{r}"} for r in range(world)]
+    src = world - 1
+    for value in (7, 2.5, True, "heap", None, (1, "a"), np.float32(1.5)):
+        assert D.distributed_broadcast_scalar(value if rank == src else "junk", src) == value
+    t = D.distributed_broadcast_tensor(torch.arange(6).view(2, 3) * (rank + 1), src)
+    assert torch.equal(torch.as_tensor(t), torch.arange(6).view(2, 3) * (src + 1))
+    a = D.distributed_broadcast_tensor(np.arange(4, dtype=np.float32) + rank, 0)
+    assert isinstance(a, np.ndarray) and a.dtype == np.float32 and a.tolist() == [0, 1, 2, 3]
+    for dt in (torch.float16, torch.bfloat16, torch.int8, torch.float64):
+        got = D.distributed_broadcast_tensor(torch.full((3,), rank + 2, dtype=dt), 0)
+        assert got.dtype == dt and torch.all(got == 2)
+    D.distributed_barrier()
+
+    ctx = iris.iris(1 << 22)
+    # Iris.broadcast: scalars come back as scalars, arrays as arrays, whatever the non-source ranks pass
+    assert ctx.broadcast(3.25 if rank == 0 else None, src=0) == 3.25
+    assert ctx.broadcast(rank, src=src) == src
+    got = ctx.broadcast(torch.ones(4) * (rank + 1) if rank == src else None, src=src)
+    assert torch.all(torch.as_tensor(got) == src + 1)
+    got = ctx.broadcast(np.array([rank, rank]), src=0)
+    assert np.asarray(got).tolist() == [0, 0]
+    # rank-prefixed logging helpers
+    for fn in (ctx.debug, ctx.info, ctx.warning, ctx.error):
+        fn("message")
+    # the slowest rank sets the reported time
+    import time
+
+    res = time_max_over_ranks(lambda: time.sleep(0.002 * (rank + 1)), ctx, n_warmup=0, n_repeat=3)
+    assert res["n_warmup"] == 3 and res["n_repeat"] == 3
+    assert res["ms"] >= 2.0 * world * 0.9 and res["ms_min_over_ranks"] <= res["ms_this_rank"] <= res["ms"] + 1e-9
+    all_ms = D.distributed_allgather(np.array([res["ms"]]))
+    assert len(set(all_ms.flatten().tolist())) == 1                 # every rank reports the same maximum
+    dist.barrier()
+    ctx.barrier()
+
+
+def test_distributed_helpers_and_broadcast_world2():
+    run_ranks(_helpers, 2, timeout=120.0)
+
+
+def test_distributed_helpers_and_broadcast_world3():
+    run_ranks(_helpers, 3, timeout=120.0)
