@@ -134,3 +134,162 @@ def test_fabric_driver_lifecycle_with_fake_runtime():
         AmdFabricDriver().initialize(0)
     assert isinstance(DriverStack("nvidia", runtime=rt).fabric, NvidiaFabricDriver)
     assert isinstance(DriverStack("amd").fabric, AmdFabricDriver)
+
+
+TOPO_NVSWITCH = """\
+\tGPU0\tGPU1\tGPU2\tGPU3\tNIC0\tCPU Affinity\tNUMA Affinity\tGPU NUMA ID
+GPU0\t X \tNV18\tNV18\tNV18\tPIX\t0-55\t0\t\tN/A
+GPU1\tNV18\t X \tNV18\tNV18\tNODE\t0-55\t0\t\tN/A
+GPU2\tNV18\tNV18\t X \tNV18\tSYS\t56-111\t1\t\tN/A
+GPU3\tNV18\tNV18\tNV18\t X \tSYS\t56-111\t1\t\tN/A
+NIC0\tPIX\tNODE\tSYS\tSYS\t X
+
+Legend:
+
+  X    = Self
+  SYS  = Connection traversing PCIe as well as the SMP interconnect between NUMA nodes
+  NV#  = Connection traversing a bonded set of # NVLinks
+"""
+
+TOPO_MIXED = """\
+        GPU0    GPU1    GPU2    GPU3    CPU Affinity
+GPU0     X      NV2     PIX     SYS     0-31
+GPU1    NV2      X      PHB     SYS     0-31
+GPU2    PIX     PHB      X      NODE    0-31
+GPU3    SYS     SYS     NODE     X      32-63
+"""
+
+
+def test_topo_matrix_parser():
+    from iris_b200.host.topology import IntraNodeLinkType as L
+    from iris_b200.host.topology import parse_topo_matrix
+
+    m = parse_topo_matrix(TOPO_NVSWITCH)
+    assert len(m) == 4 and all(len(r) == 4 for r in m)
+    assert all(m[i][i] == L.SELF for i in range(4))
+    assert all(m[i][j] == L.NVSWITCH for i in range(4) for j in range(4) if i != j)       # NV18 everywhere: a switch
+    m = parse_topo_matrix(TOPO_MIXED)
+    assert m[0][1] == L.NVLINK and m[1][0] == L.NVLINK                                    # a bridge between two GPUs
+    assert m[0][2] == L.PCIE_SWITCH and m[1][2] == L.PCIE_HOST_BRIDGE and m[2][3] == L.PCIE_NUMA and m[0][3] == L.PCIE_SYSTEM
+    assert parse_topo_matrix("no matrix here") == [] and parse_topo_matrix("") == []
+    assert str(L.NVSWITCH) == "NVSWITCH" and L(99) == L.UNKNOWN
+
+
+def test_fabric_info_and_gpu_info_round_trip():
+    from iris_b200.host.topology import FabricInfo
+
+    f = FabricInfo("ab" * 16, 7)
+    assert f.is_valid and f.domain_key == "ab" * 16 + ":7"
+    assert FabricInfo.from_dict(f.to_dict()) == f
+    assert not FabricInfo().is_valid and FabricInfo().domain_key == "" and not FabricInfo("00" * 16, 1).is_valid
+    g = GPUInfo(rank=3, hostname="n1", local_id=2, name="NVIDIA B200", pci_bus_id="0000:1b:00.0", cluster_uuid="cd" * 16, clique_id=4,
+                total_memory_mb=183359, ib_devices=["mlx5_0"], has_infiniband=True)
+    d = g.to_dict()
+    d["field_from_a_newer_version"] = 1                       # unknown keys are dropped, not fatal
+    g2 = GPUInfo.from_dict(d)
+    assert g2 == g and g2.fabric_info.domain_key == "cd" * 16 + ":4"
+    assert (g2.gpu_id, g2.local_rank, g2.device_name) == (2, 2, "NVIDIA B200")
+    assert GPUInfo(cluster_uuid="cd" * 16, clique_id=-1).fabric_info.domain_key == ""
+
+
+def _cluster():
+    """Two 2-GPU hosts in one NVLink fabric domain, a third host with PCIe-only GPUs and two ranks
+    sharing one GPU, a fourth host alone."""
+    fab = dict(cluster_uuid="aa" * 16, clique_id=1)
+    return [
+        GPUInfo(rank=0, hostname="n0", local_id=0, name="B200", pci_bus_id="0000:1b:00.0", nvlink_active_links=18, numa_node=0, **fab),
+        GPUInfo(rank=1, hostname="n0", local_id=1, name="B200", pci_bus_id="0000:2b:00.0", nvlink_active_links=18, numa_node=1, **fab),
+        GPUInfo(rank=2, hostname="n1", local_id=0, name="B200", pci_bus_id="0000:1b:00.0", nvlink_active_links=18, **fab),
+        GPUInfo(rank=3, hostname="n1", local_id=1, name="B200", pci_bus_id="0000:2b:00.0", nvlink_active_links=18, **fab),
+        GPUInfo(rank=4, hostname="n2", local_id=0, name="L4", pci_bus_id="0000:3b:00.0", numa_node=0, has_infiniband=True, ib_devices=["mlx5_0"]),
+        GPUInfo(rank=5, hostname="n2", local_id=1, name="L4", pci_bus_id="0000:5e:00.0", numa_node=1, has_infiniband=True, ib_devices=["mlx5_0"]),
+        GPUInfo(rank=6, hostname="n2", local_id=1, name="L4", pci_bus_id="0000:5e:00.0", numa_node=1, has_infiniband=True, ib_devices=["mlx5_0"]),
+        GPUInfo(rank=7, hostname="n3", local_id=0, name="B200", pci_bus_id="0000:1b:00.0",
+                nvlink_peer_pci=["0000:99:00.0"], nvlink_active_links=2),
+    ]
+
+
+def test_nodes_peers_groups_and_plans():
+    from iris_b200.host.topology import IntraNodeLinkType as L
+
+    tm = TopologyMap(_cluster())
+    assert tm.world_size == 8 and tm.num_nodes == 4 and sorted(tm.nodes) == ["n0", "n1", "n2", "n3"]
+    key = "aa" * 16 + ":1"
+    assert tm.fabric_domains == {key: ["n0", "n1"]}
+    n0, n2 = tm.nodes["n0"], tm.nodes["n2"]
+    assert n0.ranks == [0, 1] and n0.num_gpus == 2 and n0.num_ranks == 2 and n0.fabric_domain_key == key and not n0.has_infiniband
+    assert n2.ranks == [4, 5, 6] and n2.gpu_ids == [0, 1, 1] and n2.unique_gpu_ids == [0, 1] and n2.num_gpus == 2 and n2.num_ranks == 3
+    assert n2.has_infiniband and n2.ib_devices == ["mlx5_0"] and n2.fabric_domain_keys == []
+    # link types inside a host
+    assert n0.get_link_type(0, 1) == L.NVSWITCH and n0.get_link_type(1, 1) == L.SELF and n0.can_p2p_access(0, 1)
+    assert n2.get_link_type(0, 1) == L.PCIE_SYSTEM and not n2.can_p2p_access(0, 1) and n2.can_p2p_access(1, 1)
+    assert n0.get_link_type(0, 5) == L.UNKNOWN and not n0.can_p2p_access(0, 5)           # outside the matrix: no IndexError
+    assert tm.get_link_type(0, 1) == L.NVSWITCH and tm.get_link_type(5, 6) == L.SELF and tm.get_link_type(0, 2) == L.UNKNOWN
+    direct = TopologyMap([GPUInfo(rank=0, hostname="h", local_id=0, pci_bus_id="0000:01:00.0", nvlink_peer_pci=["0000:02:00.0"], nvlink_active_links=4),
+                          GPUInfo(rank=1, hostname="h", local_id=1, pci_bus_id="0000:02:00.0", nvlink_peer_pci=["0000:01:00.0"], nvlink_active_links=4)])
+    assert direct.get_link_type(0, 1) == L.NVLINK and direct.nvlink_connected(0, 1)
+    # peers of a rank
+    assert tm.get_node_peers(0) == {1} and tm.get_fabric_domain_peers(0) == {1, 2, 3} and tm.get_rdma_peers(0) == {4, 5, 6, 7}
+    assert tm.get_node_peers(5) == {4, 6} and tm.get_fabric_domain_peers(5) == set() and tm.get_rdma_peers(5) == {0, 1, 2, 3, 7}
+    assert tm.get_ranks_for_node("n1") == [2, 3] and tm.get_ranks_for_node("nowhere") == []
+    assert tm.get_ranks_for_fabric_domain(key) == [0, 1, 2, 3] and tm.get_ranks_for_fabric_domain("") == []
+    # levels
+    assert tm.get_interconnect_level(0, 3) == InterconnectLevel.INTRA_RACK_FABRIC
+    assert tm.get_interconnect_level(0, 7) == InterconnectLevel.INTER_NODE_RDMA
+    # groups per level
+    groups = tm.communication_groups()
+    assert groups[InterconnectLevel.INTRA_NODE] == [[0, 1], [2, 3], [4, 5, 6], [7]]
+    assert groups[InterconnectLevel.INTRA_RACK_FABRIC] == [[0, 1, 2, 3], [4, 5, 6], [7]]     # hosts outside a domain stand alone
+    assert groups[InterconnectLevel.INTER_NODE_RDMA] == [list(range(8))]
+    assert TopologyMap(_cluster()[4:7]).communication_groups()[InterconnectLevel.INTRA_RACK_FABRIC] == []   # no fabric anywhere
+    # heap plan for everybody
+    plan = tm.full_heap_distribution_plan()
+    assert plan[0] == {"ipc_peers": [1], "fabric_peers": [2, 3], "rdma_peers": [4, 5, 6, 7], "node": "n0", "local_rank": 0, "gpu_id": 0,
+                       "fabric_domain": key}
+    assert plan[6]["ipc_peers"] == [4, 5] and plan[6]["fabric_peers"] == [] and plan[6]["fabric_domain"] == ""
+    for r, p in plan.items():
+        assert sorted(p["ipc_peers"] + p["fabric_peers"] + p["rdma_peers"] + [r]) == list(range(8))
+    # summary
+    text = str(tm)
+    assert text.startswith("=== Iris Cluster Topology ===") and "World size: 8  |  Nodes: 4  |  Fabric domains: 1" in text
+    assert "oversubscribed: 3 ranks on 2 GPUs" in text and "IB: mlx5_0" in text and "IB: none" in text
+    assert f"{key}: 2 nodes, 4 GPUs, hosts=['n0', 'n1']" in text and "rank 7: GPU0 (B200, 0MB) PCI=0000:1b:00.0" in text
+
+
+def test_discovery_needs_discover_first_and_lists_ib(tmp_path):
+    from iris_b200.host.topology import detect_infiniband, list_infiniband_devices
+
+    d = TopologyDiscovery(rank=0, local_id=0, nvml=_fake_nvml())
+    assert d.topology is None
+    with pytest.raises(RuntimeError):
+        d.get_communication_groups()
+    with pytest.raises(RuntimeError):
+        d.get_heap_distribution_plan()
+    info = d.probe()
+    assert info.nvlink_active_links == 2
+    root = tmp_path / "infiniband"
+    assert list_infiniband_devices(str(root)) == [] and not detect_infiniband(str(root))
+    root.mkdir()
+    assert not detect_infiniband(str(root))
+    (root / "mlx5_1").mkdir()
+    (root / "mlx5_0").mkdir()
+    assert list_infiniband_devices(str(root)) == ["mlx5_0", "mlx5_1"] and detect_infiniband(str(root))
+
+
+def _discover(rank, world):
+    from iris_b200.host.topology import TopologyDiscovery as TD
+
+    d = TD(rank=rank, local_id=rank, nvml=_fake_nvml(links=0))
+    tm = d.discover()
+    assert d.topology is tm and tm.world_size == world and tm.num_nodes == 1
+    groups = d.get_communication_groups()
+    assert groups[InterconnectLevel.INTRA_NODE] == [list(range(world))]
+    plan = d.get_heap_distribution_plan()
+    assert plan[rank]["ipc_peers"] == [r for r in range(world) if r != rank] and plan[rank]["rdma_peers"] == []
+    assert tm.single_nvlink_domain()
+
+
+def test_discovery_over_gloo_ranks():
+    from helpers import run_ranks
+
+    run_ranks(_discover, 3)
