@@ -17,6 +17,7 @@ from dataclasses import dataclass
 import torch
 
 from .. import _lib
+from ..host import artifacts as _artifacts
 from .config import Config
 from .utils import ReduceOp
 
@@ -120,6 +121,13 @@ class CCL:
         return d
 
     def _launch(self, op: int, d: IrisCclDesc):
+        if _artifacts.ACTIVE:
+            name = ("all_gather", "all_to_all", "all_reduce", "reduce_scatter")[op]
+            variant = {v: k for k, v in _AR_CODE.items()}.get(d.variant, "") if op == 2 else ("rows" if d.rows_mode else "tiles") if op == 3 else ""
+            _artifacts.record_launch("ccl", name + ("_" + variant if variant else ""), self.ctx.cur_rank,
+                                     {"M": d.M, "N": d.N, "dtype": {v: k for k, v in _lib.DTYPE_CODE.items()}.get(d.dtype, d.dtype),
+                                      "world": d.ctx.world, "comm_sms": d.comm_sms, "use_multicast": bool(d.use_mc), "block_m": d.block_m,
+                                      "block_n": d.block_n, "distribution": d.distribution}, source="ccl.cu")
         _lib.check(self._lib().iris_ccl_launch(op, C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "collective launch")
 
     # A repeated call (same buffers, shapes, group and configuration) skips validation and

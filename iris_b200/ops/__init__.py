@@ -26,6 +26,7 @@ import ctypes as C
 import torch
 
 from .. import _lib
+from ..host import artifacts as _artifacts
 from .config import FusedConfig
 from .gemm import fill_desc, matmul
 from .gemm_fp8 import dequant_matmul, matmul_fp8, quantize_1x128, quantize_128x128
@@ -121,6 +122,11 @@ def _launch(ctx, d, ws) -> None:
     d.two_sm = ws.extra.get("two_sm", d.two_sm)
     tl = ws.extra.get("timeline")
     d.timeline = tl.data_ptr() if tl is not None else None
+    if _artifacts.ACTIVE:
+        _artifacts.record_launch("ops", ws.operation, ctx.cur_rank,
+                                 {"M": d.M, "N": d.N, "K": d.K, "dtype": ws.dtype, "world": ctx.num_ranks, "op_code": d.op, "tile_n": d.bn,
+                                  "cta_pairs": d.two_sm == 2, "comm_ctas": d.comm_ctas, "group_m": d.group_m, "use_multicast": bool(d.use_mc),
+                                  "timeline": tl is not None}, source="gemm_ops.cu")
     _lib.check(_lib.kernels().iris_gemm_launch(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), f"{ws.operation} launch")
 
 

@@ -481,3 +481,76 @@ def _tp_mlp_check(rank, world, dtype_name, Ml, K, F, tol):
 
 def test_tensor_parallel_mlp_forward_backward_cpu():
     run_ranks(_tp_mlp_check, 2, args=("float32", 8, 16, 12, 1e-4))
+
+
+def test_launch_records(tmp_path, monkeypatch):
+    import json
+
+    import torch
+
+    from iris_b200.host import artifacts
+
+    monkeypatch.delenv("IRIS_KERNEL_ARTIFACTS_DIR", raising=False)
+    artifacts.configure(None)
+    assert not artifacts.ACTIVE and artifacts.record_launch("ccl", "all_reduce_two_shot", 0, {"M": 8, "N": 8}) is None
+    artifacts.configure(tmp_path)
+    try:
+        assert artifacts.ACTIVE
+        params = {"M": 8192, "N": 4096, "dtype": torch.bfloat16, "world": 8, "comm_sms": 64, "use_multicast": True}
+        d = artifacts.record_launch("ccl", "all_reduce_nvls", 3, params, source="ccl.cu")
+        # <dir>/<algo>/<kernel>/rank_N/<M x N _ dtype _ world>/<sha12>/metadata.json
+        rel = d.relative_to(tmp_path).parts
+        assert rel[:4] == ("ccl", "all_reduce_nvls", "rank_3", "8192x4096_bfloat16_w8") and len(rel[4]) == 12
+        meta = json.loads((d / "metadata.json").read_text())
+        assert meta["kernel"] == "all_reduce_nvls" and meta["rank"] == 3 and meta["arch"] == "sm_100a" and meta["source"] == "ccl.cu"
+        assert meta["params"]["dtype"] == "torch.bfloat16" and meta["params"]["comm_sms"] == 64
+        if (artifacts._build.OBJDIR / "ccl.cu.ptxas.log").exists():
+            assert (d / "ptxas.log").exists() and any(k["registers"] for k in meta["compiled"])
+        # the same configuration is written once; another configuration or rank gets its own directory
+        assert artifacts.record_launch("ccl", "all_reduce_nvls", 3, params, source="ccl.cu") is None
+        d2 = artifacts.record_launch("ccl", "all_reduce_nvls", 3, dict(params, comm_sms=148), source="ccl.cu")
+        assert d2 is not None and d2 != d and d2.parent == d.parent
+        d3 = artifacts.record_launch("ops", "matmul_all_reduce", 0, {"M": 128, "N": 8192, "K": 3584, "dtype": torch.float16, "world": 2})
+        assert d3.relative_to(tmp_path).parts[:4] == ("ops", "matmul_all_reduce", "rank_0", "128x8192_float16_w2")
+        assert json.loads((d3 / "metadata.json").read_text())["compiled"] == []
+    finally:
+        artifacts.configure(None)
+    assert not artifacts.ACTIVE
+
+
+def test_launch_paths_write_records(tmp_path, monkeypatch):
+    """The GPU launch functions of the collectives and the fused ops, driven with stand-ins for the
+    native library: each distinct configuration leaves one record, the launch itself still happens."""
+    import os
+    import types
+
+    import torch
+
+    from iris_b200 import _lib, ccl, ops
+    from iris_b200.host import artifacts
+
+    calls = []
+    fake = types.SimpleNamespace(iris_ccl_launch=lambda op, d, s: calls.append(op) or 0, iris_gemm_launch=lambda d, s: calls.append("gemm") or 0)
+    monkeypatch.setattr(_lib, "current_stream_ptr", lambda: 0)
+    monkeypatch.setattr(_lib, "kernels", lambda: fake)
+    artifacts.configure(tmp_path)
+    try:
+        me = types.SimpleNamespace(ctx=types.SimpleNamespace(cur_rank=1), _lib=lambda: fake)
+        d = ccl.IrisCclDesc()
+        d.M, d.N, d.dtype, d.variant, d.ctx.world = 64, 128, 1, 5, 4
+        ccl.CCL._launch(me, 2, d)
+        ccl.CCL._launch(me, 2, d)                      # same configuration: launched again, recorded once
+        d.rows_mode = 1
+        ccl.CCL._launch(me, 3, d)
+        ccl.CCL._launch(me, 0, d)
+        g = _lib.IrisGemmDesc()
+        g.M, g.N, g.K, g.op = 256, 512, 64, _lib.GEMM_ALL_REDUCE
+        ws = ops.FusedWorkspace(operation="matmul_all_reduce", dtype=torch.bfloat16, sync_block=torch.zeros(4, dtype=torch.int32), bn=256)
+        ops._launch(types.SimpleNamespace(cur_rank=1, num_ranks=4), g, ws)
+    finally:
+        artifacts.configure(None)
+    assert calls == [2, 2, 3, 0, "gemm"]
+    found = sorted(os.path.relpath(root, tmp_path).rsplit(os.sep, 1)[0] for root, _, files in os.walk(tmp_path)
+                   if "metadata.json" in files and not os.path.relpath(root, tmp_path).startswith("build"))
+    assert found == ["ccl/all_gather/rank_1/64x128_bfloat16_w4", "ccl/all_reduce_nvls/rank_1/64x128_bfloat16_w4",
+                     "ccl/reduce_scatter_rows/rank_1/64x128_bfloat16_w4", "ops/matmul_all_reduce/rank_1/256x512_bfloat16_w4"]
