@@ -146,3 +146,27 @@ def test_performance_gate(tmp_path, capsys):
     sweep.write_text(json.dumps({"results": rows}))
     assert gate.main(["--sweep", str(sweep), "--bench", str(good)]) == 0
     assert gate.main([]) == 2 and gate.main(["--bench", str(tmp_path / "absent.json")]) == 2
+
+
+@pytest.mark.parametrize("script,args,expect", [
+    ("benchmark/ops/bench_matmul_all_reduce_stages.py", ["--axis_M=32", "--axis_K=128", "--axis_N=64"],
+     {"gemm", "all_reduce", "sequential", "fused", "library_pair"}),
+    ("benchmark/examples/bench_all_gather_gemm.py", ["--axis_m=1,64", "--axis_n=64", "--axis_k=256"], {"k", "m"}),
+])
+def test_stage_and_sweep_benchmarks_on_the_cpu_backend(tmp_path, script, args, expect):
+    """The stage breakdown of GEMM + all-reduce and the small-M all-gather + GEMM sweep check their
+    results before timing; on gloo ranks they run the unfused path end to end."""
+    import csv
+
+    out = tmp_path / "out.csv"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, os.path.join(ROOT, script), "--axis_num_ranks=2", *args, "--n_warmup", "1", "--n_repeat", "2",
+           "--benchmark_format", "csv", "--benchmark_out", str(out)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    rows = list(csv.DictReader(out.open()))
+    timed = [r for r in rows if r["skipped"] == "0"]
+    assert timed and all(float(r["gpu_time_ms"]) > 0 for r in timed)
+    assert {r.get("stage") or r.get("layout") for r in timed} == expect
+    if "layout" in rows[0]:
+        assert all(r["skipped"] == "1" for r in rows if r["layout"] == "m" and r["m"] == "1")     # one row cannot be split over two ranks
