@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from .host.logging import DEBUG, ERROR, INFO, WARNING, logger, set_logger_level
 from .host.iris import Iris, IrisTimeoutError, iris
+from .host.watchdog import BarrierTimeoutError
 from .host.tensor_utils import CUDAArrayInterface, tensor_from_ptr
 from .host.platform import do_bench, get_device_id_for_rank, is_simulation_env
 from .host import platform as hip
@@ -27,7 +28,7 @@ from .device import (DeviceContext, Context, Tile, TileView, TensorView, AllRedu
 __version__ = "0.1.0"
 
 __all__ = [
-    "Iris", "iris", "IrisTimeoutError", "DeviceContext", "Context", "TraceEvent", "Tile", "TileView", "TensorView",
+    "Iris", "iris", "IrisTimeoutError", "BarrierTimeoutError", "DeviceContext", "Context", "TraceEvent", "Tile", "TileView", "TensorView",
     "AllReduceConfig", "make_tensor_view", "load", "store", "copy", "get", "put", "atomic_add", "atomic_cas",
     "atomic_xchg", "atomic_xor", "atomic_or", "atomic_and", "atomic_min", "atomic_max", "do_bench",
     "get_device_id_for_rank", "is_simulation_env", "CUDAArrayInterface", "tensor_from_ptr", "hip", "experimental",

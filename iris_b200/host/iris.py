@@ -65,6 +65,9 @@ class Iris:
         # IRIS_DEBUG=1: fresh heap memory is poisoned, every host barrier compares the ranks'
         # allocation offsets, and every synchronous collective ends with check()
         self.debug_checks = os.environ.get("IRIS_DEBUG", "0") not in ("", "0")
+        env_limit = os.environ.get("IRIS_BARRIER_TIMEOUT_S", "")
+        self._barrier_timeout_s = float(env_limit) if env_limit else None
+        self._watchdog = None
         # status word + sync block of the context itself (barrier) + per-purpose sync blocks
         self._status = self.heap.allocate(1, torch.int32)
         self._status.zero_()
@@ -133,14 +136,25 @@ class Iris:
             return D.distributed_broadcast_tensor(value, src)
         return payload
 
-    def barrier(self, stream=None, group=None):
-        """Host barrier: wait for this rank's GPU work (one stream or the device), then for all ranks."""
+    def barrier(self, stream=None, group=None, timeout_s: float | None = None):
+        """Host barrier: wait for this rank's GPU work (one stream or the device), then for all ranks.
+
+        With ``timeout_s`` (or ``IRIS_BARRIER_TIMEOUT_S`` in the environment) the ranks meet through
+        the rendezvous store instead of a collective, and a rank that does not arrive in time makes
+        the others raise ``BarrierTimeoutError`` naming it, instead of waiting for the process
+        group's own timeout."""
         if not self.is_cpu:
             if stream is None:
                 torch.cuda.synchronize(self.device)
             else:
                 stream.synchronize()
-        D.distributed_barrier(group)
+        if timeout_s is None:
+            timeout_s = self._barrier_timeout_s
+        if timeout_s is None:
+            D.distributed_barrier(group)
+        else:
+            members = range(self.num_ranks) if group is None else dist.get_process_group_ranks(group)
+            self._store_barrier().wait(members, timeout_s)
         if self.debug_checks:
             self.debug_verify(group)
 
@@ -165,6 +179,26 @@ class Iris:
             return
         _lib.check(self._klib().iris_device_barrier(C.byref(ctx), C.c_void_p(sb.data_ptr()), C.c_void_p(_lib.current_stream_ptr())),
                    "device barrier launch")
+
+    def _store_barrier(self):
+        if self._watchdog is None:
+            from .watchdog import Heartbeat, StoreBarrier
+
+            self._watchdog = (StoreBarrier(self.cur_rank), Heartbeat(self.cur_rank, self.num_ranks))
+        return self._watchdog[0]
+
+    def heartbeat(self) -> None:
+        """Tell the other ranks that this one is alive (one small write to the rendezvous store);
+        call it once per step."""
+        self._store_barrier()
+        self._watchdog[1].beat()
+
+    def stale_ranks(self, max_age_s: float) -> list:
+        """Ranks that have not called ``heartbeat()`` during the last ``max_age_s`` seconds: ask before
+        launching kernels that wait for peers, so that a rank that left between steps is found on
+        the host and not by a device-side timeout."""
+        self._store_barrier()
+        return self._watchdog[1].stale(max_age_s)
 
     def heap_mark(self) -> int:
         """Current bump offset of the heap; pass it to ``heap_release`` to free everything allocated since."""

@@ -103,3 +103,122 @@ def test_a_rank_that_raises_is_reported_and_the_rest_time_out():
     codes, errors = run_ranks(_raising_rank, 2, expect_failures=True, timeout=120)
     assert codes[0] == 0 and codes[1] != 0
     assert len(errors) == 1 and errors[0][0] == 1 and "injected failure" in errors[0][1]
+
+
+def _host_barrier_names_missing_ranks(rank, world):
+    import iris_b200 as iris
+
+    ctx = iris.iris(1 << 22)
+    for _ in range(4):                                   # rounds are counted, old keys are dropped
+        ctx.barrier(timeout_s=20.0)
+    if rank in (1, 3):
+        time.sleep(2.5)                                  # these two are late for the next round
+        return
+    t0 = time.time()
+    with pytest.raises(iris.BarrierTimeoutError) as ei:
+        ctx.barrier(timeout_s=0.5)
+    assert ei.value.missing == [1, 3] and ei.value.rank == rank and ei.value.round == 5
+    assert "did not arrive: [1, 3]" in str(ei.value) and time.time() - t0 < 2.0
+    # the context is still usable: memory operations do not depend on the lost ranks
+    t = ctx.zeros(4, dtype=torch.int32)
+    ctx.rma.atomic_add(t, 1, to_rank=rank)
+    assert torch.all(t == 1)
+
+
+def test_host_barrier_with_a_limit_names_the_missing_ranks():
+    codes, errors = run_ranks(_host_barrier_names_missing_ranks, 4, expect_failures=True, timeout=120)
+    assert not errors, errors
+    assert all(c == 0 for c in codes)
+
+
+def _group_barrier_and_env(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+
+    ctx = iris.iris(1 << 22)
+    assert ctx._barrier_timeout_s == 15.0                # from the environment: every host barrier is bounded
+    pairs = [[0, 1], [2, 3]]
+    groups = [dist.new_group(p) for p in pairs]
+    mine = groups[0] if rank < 2 else groups[1]
+    if rank < 2:
+        for _ in range(3):
+            ctx.barrier(group=mine)                      # only the pair takes part; the other pair does nothing meanwhile
+    ctx.barrier()
+    # collectives end with the same bounded barrier
+    inp, out = ctx.full((4, 8), float(rank + 1)), ctx.zeros((4, 8))
+    ctx.ccl.all_reduce(out, inp)
+    assert torch.all(out == 10)
+    ctx.barrier()
+
+
+def test_bounded_host_barrier_from_the_environment_and_in_groups():
+    run_ranks(_group_barrier_and_env, 4, env={"IRIS_BARRIER_TIMEOUT_S": "15"})
+
+
+def _heartbeats(rank, world):
+    import iris_b200 as iris
+
+    ctx = iris.iris(1 << 22)
+    assert sorted(ctx.stale_ranks(60.0)) == [r for r in range(world) if r != rank]      # nobody has beaten yet
+    ctx.barrier()
+    ctx.heartbeat()
+    ctx.barrier()
+    assert ctx.stale_ranks(60.0) == []
+    ctx.barrier()
+    # rank 2 leaves between steps; the others keep beating and find out on the host
+    if rank == 2:
+        return
+    for _ in range(3):
+        time.sleep(0.4)
+        ctx.heartbeat()
+    assert ctx.stale_ranks(1.0) == [2]
+    assert ctx.stale_ranks(60.0) == []                   # a generous limit still accepts its last beat
+
+
+def test_heartbeats_reveal_a_rank_that_left_between_steps():
+    codes, errors = run_ranks(_heartbeats, 3, expect_failures=True, timeout=120)
+    assert not errors, errors
+    assert all(c == 0 for c in codes)
+
+
+def test_store_protocols_against_a_plain_dictionary_store():
+    """The two protocols only need set / get / check / wait / delete_key: a dictionary stands in."""
+    from iris_b200.host.watchdog import BarrierTimeoutError, Heartbeat, StoreBarrier
+
+    class DictStore:
+        def __init__(self):
+            self.d = {}
+
+        def set(self, k, v):
+            self.d[k] = v.encode() if isinstance(v, str) else v
+
+        def get(self, k):
+            return self.d[k]
+
+        def check(self, keys):
+            return all(k in self.d for k in keys)
+
+        def wait(self, keys, timeout):
+            if not self.check(keys):
+                raise RuntimeError("timeout")
+
+        def delete_key(self, k):
+            return self.d.pop(k, None) is not None
+
+    store = DictStore()
+    b0, b1 = StoreBarrier(0, store), StoreBarrier(1, store)
+    with pytest.raises(BarrierTimeoutError) as ei:
+        b0.wait([0, 1], 0.01)                            # rank 1 has not arrived
+    assert ei.value.missing == [1]
+    assert b1.wait([0, 1], 0.01) == 1                    # rank 0's key of round 1 is there: passes
+    for n in range(2, 6):
+        store.set(f"iris/barrier/0-1/{n}/1", "1")        # rank 1 arrives first in the later rounds
+        assert b0.wait([0, 1], 0.01) == n
+    assert "iris/barrier/0-1/1/0" not in store.d and "iris/barrier/0-1/5/0" in store.d       # old rounds are cleaned up
+    with pytest.raises(ValueError):
+        b0.wait([1, 2], 0.01)
+    hb0, hb1 = Heartbeat(0, 3, store), Heartbeat(1, 3, store)
+    hb1.beat(now=100.0)
+    assert hb0.last(1) == 100.0 and hb0.last(2) is None
+    assert hb0.stale(5.0, now=103.0) == [2] and hb0.stale(5.0, now=106.0) == [1, 2] and hb0.stale(5.0, ranks=[1], now=103.0) == []
