@@ -21,6 +21,8 @@ from . import ccl
 from . import ops
 from . import bench
 from . import experimental
+from . import gluon  # noqa: F401
+from . import mem  # noqa: F401
 from .device import (DeviceContext, Context, Tile, TileView, TensorView, AllReduceConfig, make_tensor_view,
                      load, store, copy, get, put, atomic_add, atomic_cas, atomic_xchg, atomic_xor, atomic_or, atomic_and,
                      atomic_min, atomic_max)

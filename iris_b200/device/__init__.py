@@ -51,3 +51,11 @@ TileView = DeviceSymbol("TileView", "include/iris/types.cuh", "struct TileView {
 TensorView = DeviceSymbol("TensorView", "include/iris/types.cuh", "template <class T> struct TensorView { ptr, M, N, stride_m, stride_n }")
 AllReduceConfig = DeviceSymbol("AllReduceConfig", "include/iris/types.cuh", "struct AllReduceConfig { variant_code, locks_ptr }")
 make_tensor_view = DeviceSymbol("make_tensor_view", "include/iris/types.cuh", "TensorView<T> make_tensor_view(T* ptr, int M, int N, int64_t stride_m, int64_t stride_n)")
+
+# Device-side tracing aggregate and intrinsics (reference: iris/mem/triton/tracing.py:19-186, iris/mem/utils.py:25-92).
+Tracing = DeviceSymbol("Tracing", "include/iris/tracing.cuh", "struct Tracing { int record_event_start(event_id, target_rank, address, pid_m, pid_n, payload_bytes); void record_event_end(int handle); }")
+read_realtime = DeviceSymbol("read_realtime", "include/iris/iris.cuh", "uint64_t read_realtime()  // nanoseconds of %globaltimer")
+get_cu_id = DeviceSymbol("get_cu_id", "include/iris/iris.cuh", "uint32_t get_cu_id()  // %smid")
+get_xcc_id = DeviceSymbol("get_xcc_id", "include/iris/iris.cuh", "uint32_t get_xcc_id()  // always 0: a B200 exposes no chiplet partition")
+# Flag helpers every kernel of this library waits with (no counterpart in the reference, which spins on atomic_cas).
+wait_flag_ge = DeviceSymbol("wait_flag_ge", "include/iris/sync.cuh", "bool wait_flag_ge(const DeviceContext& ctx, const int32_t* flag, int32_t target)  // bounded by ctx.timeout_ns")

@@ -93,6 +93,16 @@ def test_device_symbols_point_to_headers():
         assert sym.name in src
     with pytest.raises(RuntimeError):
         iris.load()
+    # every symbol of the device namespace names something that exists in its header
+    from iris_b200 import device, gluon, mem
+
+    syms = [v for v in vars(device).values() if isinstance(v, device.DeviceSymbol)]
+    assert len(syms) >= 26
+    for sym in syms:
+        assert sym.name in open(os.path.join(root, sym.header)).read(), sym
+    # the reference's module paths for the same API
+    assert gluon.IrisDeviceCtx is iris.Context and gluon.GluonDeviceTracing is device.Tracing
+    assert iris.experimental.gluon_context is gluon and mem.atomic_add is iris.atomic_add and mem.get_cu_id.cuda == "iris::get_cu_id"
 
 
 def test_owned_tiles_partition():
