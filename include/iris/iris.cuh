@@ -39,30 +39,43 @@ struct Ctx {
   IRIS_HD int world() const { return c.world; }
   IRIS_HD const uint64_t* bases() const { return c.bases; }
 
+  // Debug builds (-DIRIS_DEBUG): an access whose pointer lies outside this rank's heap, or whose
+  // target rank does not exist, is skipped and recorded as kBadTranslate in the status word (read
+  // on the host with ctx.check()). Nothing traps. Without the macro the test is the constant true.
+#if defined(IRIS_DEBUG)
+  IRIS_D bool ok(const void* p, int r) const {
+    if (r >= 0 && r < c.world && c.in_heap(p, c.rank)) return true;
+    c.fail(kBadTranslate);
+    return false;
+  }
+#else
+  IRIS_D bool ok(const void*, int) const { return true; }
+#endif
+
   template <class T, CacheOp C = CacheOp::none, bool V = false>
   IRIS_D T load(const T* p, int from_rank, bool pred = true, T other = T()) const {
-    return iris::load<T, C, V>(p, c.rank, from_rank, c.bases, pred, other);
+    return iris::load<T, C, V>(p, c.rank, from_rank, c.bases, pred && ok(p, from_rank), other);
   }
   template <class T, CacheOp C = CacheOp::none>
   IRIS_D void store(T* p, T v, int to_rank, bool pred = true) const {
-    iris::store<T, C>(p, v, c.rank, to_rank, c.bases, pred);
+    iris::store<T, C>(p, v, c.rank, to_rank, c.bases, pred && ok(p, to_rank));
   }
   template <class T>
   IRIS_D void get(const T* from_ptr, T* to_ptr, int from_rank, bool pred = true) const {
-    iris::get(from_ptr, to_ptr, from_rank, c.rank, c.bases, pred);
+    iris::get(from_ptr, to_ptr, from_rank, c.rank, c.bases, pred && ok(from_ptr, from_rank));
   }
   template <class T>
   IRIS_D void put(const T* from_ptr, T* to_ptr, int to_rank, bool pred = true) const {
-    iris::put(from_ptr, to_ptr, c.rank, to_rank, c.bases, pred);
+    iris::put(from_ptr, to_ptr, c.rank, to_rank, c.bases, pred && ok(to_ptr, to_rank));
   }
   template <class T>
   IRIS_D void copy(const T* src, T* dst, int from_rank, int to_rank, bool pred = true) const {
-    iris::copy(src, dst, from_rank, to_rank, c.rank, c.bases, pred);
+    iris::copy(src, dst, from_rank, to_rank, c.rank, c.bases, pred && ok(src, from_rank) && ok(dst, to_rank));
   }
 #define IRIS_CTX_ATOMIC(NAME)                                                       \
   template <Sem S = Sem::acq_rel, Scope P = Scope::gpu, class T>                     \
   IRIS_D T NAME(T* p, T v, int to_rank, bool pred = true) const {                    \
-    return iris::NAME<S, P>(p, v, c.rank, to_rank, c.bases, pred);                   \
+    return iris::NAME<S, P>(p, v, c.rank, to_rank, c.bases, pred && ok(p, to_rank)); \
   }
   IRIS_CTX_ATOMIC(atomic_add)
   IRIS_CTX_ATOMIC(atomic_sub)
@@ -75,6 +88,7 @@ struct Ctx {
 #undef IRIS_CTX_ATOMIC
   template <Sem S = Sem::acq_rel, Scope P = Scope::gpu, class T>
   IRIS_D T atomic_cas(T* p, T cmp, T v, int to_rank) const {
+    if (!ok(p, to_rank)) return cmp;     // debug builds only: the swap is not attempted
     return iris::atomic_cas<S, P>(p, cmp, v, c.rank, to_rank, c.bases);
   }
 };

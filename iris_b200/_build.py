@@ -141,16 +141,18 @@ def build_runtime(verbose: bool = True) -> Path:
     return runtime_lib()
 
 
-def build_user_kernel(src: Path, out: Path, verbose: bool = False) -> Path:
-    """Compile one user ``.cu`` that includes ``<iris/iris.cuh>`` into a shared object."""
+def build_user_kernel(src: Path, out: Path, verbose: bool = False, defines: tuple = ()) -> Path:
+    """Compile one user ``.cu`` that includes ``<iris/iris.cuh>`` into a shared object; ``defines``
+    are passed as ``-D`` (``IRIS_DEBUG`` turns on the device API's bounds checks)."""
     src, out = Path(src), Path(out)
-    key = hashlib.sha256((_headers_hash() + src.read_text() + " ".join(NVCC_FLAGS)).encode()).hexdigest()
+    dflags = [f"-D{d}" for d in defines]
+    key = hashlib.sha256((_headers_hash() + src.read_text() + " ".join(NVCC_FLAGS + dflags)).encode()).hexdigest()
     if _needs(out, key):
         if verbose:
             print(f"[iris_b200 build] nvcc {src.name} -> {out.name}", flush=True)
         out.parent.mkdir(parents=True, exist_ok=True)
         tmp = out.with_name(out.name + f".tmp{os.getpid()}")     # ranks may compile the same file at once
-        _run([_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", "-shared", "-cudart", "static", str(src), "-o", str(tmp)],
+        _run([_nvcc(), *NVCC_FLAGS, *dflags, f"-I{INCLUDE}", "-shared", "-cudart", "static", str(src), "-o", str(tmp)],
              log=out.with_suffix(f".ptxas{os.getpid()}.log"))
         os.replace(tmp, out)
         _stamp(out, key)

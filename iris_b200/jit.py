@@ -71,18 +71,30 @@ class Module:
         return call
 
 
-def compile_file(src: str | os.PathLike, out: str | os.PathLike | None = None, verbose: bool = False) -> Module:
+def _debug_default(debug: bool | None) -> bool:
+    return (os.environ.get("IRIS_DEBUG", "0") not in ("", "0")) if debug is None else bool(debug)
+
+
+def compile_file(src: str | os.PathLike, out: str | os.PathLike | None = None, verbose: bool = False,
+                 debug: bool | None = None) -> Module:
+    """``debug=True`` (default: ``IRIS_DEBUG=1`` in the environment) compiles with ``-DIRIS_DEBUG``: the
+    object API (``iris::Ctx``) then skips and records, as status ``kBadTranslate``, every access whose
+    pointer is outside the heap or whose rank does not exist; the library is written next to the
+    regular one as ``lib<name>_debug.so``."""
     src = Path(src)
-    out = Path(out) if out is not None else src.with_name("lib" + src.stem + ".so")
-    _build.build_user_kernel(src, out, verbose=verbose)
+    debug = _debug_default(debug)
+    out = Path(out) if out is not None else src.with_name("lib" + src.stem + ("_debug" if debug else "") + ".so")
+    _build.build_user_kernel(src, out, verbose=verbose, defines=("IRIS_DEBUG",) if debug else ())
     return Module(out)
 
 
-def compile_source(source: str, name: str = "kernel", cache_dir: str | os.PathLike | None = None, verbose: bool = False) -> Module:
+def compile_source(source: str, name: str = "kernel", cache_dir: str | os.PathLike | None = None, verbose: bool = False,
+                   debug: bool | None = None) -> Module:
     digest = hashlib.sha256(source.encode()).hexdigest()[:16]
     cache = Path(cache_dir) if cache_dir else Path(os.environ.get("IRIS_B200_CACHE", Path.home() / ".cache" / "iris_b200"))
     cache.mkdir(parents=True, exist_ok=True)
     src = cache / f"{name}_{digest}.cu"
     if not src.exists():
         src.write_text(source)
-    return compile_file(src, cache / f"lib{name}_{digest}.so", verbose=verbose)
+    debug = _debug_default(debug)
+    return compile_file(src, cache / f"lib{name}_{digest}{'_debug' if debug else ''}.so", verbose=verbose, debug=debug)

@@ -188,7 +188,51 @@ static void bounded_waits() {
   CHECK(barrier_wait(r0, &blocks[0], 1) && status == 0);
 }
 
+// Object API in a debug build: accesses outside the heap or to a rank that does not exist are
+// skipped and recorded; in a regular build the same calls are plain accesses (so they are only made
+// here when the macro is set).
+static void debug_bounds() {
+  static int32_t heap[2][32];
+  static int32_t outside[4];
+  int32_t status = 0;
+  DeviceContext ctx;
+  memset(&ctx, 0, sizeof(ctx));
+  ctx.rank = 0;
+  ctx.world = 2;
+  ctx.heap_size = sizeof(heap[0]);
+  ctx.status = &status;
+  ctx.bases[0] = (uint64_t)(uintptr_t)heap[0];
+  ctx.bases[1] = (uint64_t)(uintptr_t)heap[1];
+  Ctx c(ctx);
+  c.store(&heap[0][3], 11, 1);
+  CHECK(heap[1][3] == 11 && status == 0);               // a proper access is unaffected
+  CHECK(c.ok(&heap[0][31], 1));
+#if defined(IRIS_DEBUG)
+  outside[0] = 5;
+  c.store(outside, 99, 1);                              // not a heap pointer: skipped, recorded
+  CHECK(outside[0] == 5 && status == kBadTranslate);
+  status = 0;
+  c.store(&heap[0][3], 12, 2);                          // rank 2 does not exist
+  CHECK(heap[1][3] == 11 && status == kBadTranslate);
+  status = 0;
+  CHECK(c.load(&heap[0][3], -1, true, 77) == 77 && status == kBadTranslate);   // masked out: the default comes back
+  status = 0;
+  CHECK((c.atomic_add<Sem::relaxed, Scope::sys>(&heap[0][32], 1, 1)) == 0 && status == kBadTranslate);   // one past the end
+  status = 0;
+  CHECK((c.atomic_cas<Sem::relaxed, Scope::sys>(outside, 5, 6, 1)) == 5 && outside[0] == 5 && status == kBadTranslate);
+  status = 0;
+  c.put(&heap[0][1], outside, 1);
+  c.get(outside, &heap[0][1], 1);
+  c.copy(&heap[0][1], outside, 0, 1);
+  CHECK(outside[0] == 5 && status == kBadTranslate);
+  printf("debug bounds checks active\n");
+#else
+  CHECK(c.ok(outside, 7));                              // the regular build tests nothing
+#endif
+}
+
 int main() {
+  debug_bounds();
   tile_views();
   tile_order();
   translation();
