@@ -74,10 +74,11 @@ def _ops(rank, world):
     f = ctx.full((8,), 5, dtype=torch.int32)
     ctx.barrier()
     ctx.rma.atomic_max(f, 9 + rank, to_rank=peer)
-    ctx.rma.atomic_or(f, 16, to_rank=peer) if False else None
     ctx.barrier()
     assert torch.all(f == 9 + src)
-    old = ctx.rma.atomic_cas(f, 9 + rank, 42, to_rank=peer) if world == 1 else ctx.rma.atomic_cas(f, 9 + ((peer - 1) % world), 42, to_rank=peer)
+    # the peer's cells now hold 9 + (its predecessor) = 9 + my rank: the swap goes through
+    old = ctx.rma.atomic_cas(f, 9 + rank, 42, to_rank=peer)
+    assert torch.all(old == 9 + rank)
     ctx.barrier()
     assert torch.all(f == 42)
     x = ctx.rma.atomic_xchg(f, 7, to_rank=rank)
