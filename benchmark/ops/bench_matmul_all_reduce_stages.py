@@ -45,6 +45,12 @@ def matmul_all_reduce_stages(state, ctx):
     state.set_roofline_us(fused_target_seconds(flops if stage != "all_reduce" else 0.0, link if stage != "gemm" else 0.0) * 1e6)
     part = ctx.zeros((M, N), dtype=dt)
     out = ctx.zeros((M, N), dtype=dt)
+    P = torch.empty(M, N, dtype=dt, device=dev)
+
+    def lib():       # library pair: torch.matmul (cuBLAS) + torch.distributed all_reduce (NCCL; gloo without GPUs)
+        torch.matmul(A, B, out=P)
+        if W > 1:
+            dist.all_reduce(P)
 
     if stage == "gemm":
         state.exec(lambda: part.copy_(_local_matmul(A, B)) if ctx.is_cpu else _local_matmul(A, B))
@@ -73,15 +79,8 @@ def matmul_all_reduce_stages(state, ctx):
         assert (out.float() - want).abs().max().item() <= tol, "fused matmul_all_reduce disagrees with the fp32 sum"
         state.add_counter("fused_kernel", 0 if ws.variant == "unfused" else 1)
         state.exec(lambda: ctx.ops.matmul_all_reduce(out, A, B, workspace=ws, async_op=True))
+        state.exec_baseline(lib)          # the same point gets the library pair's time and the ratio
         return
-    # library pair: torch.matmul (cuBLAS) + torch.distributed all_reduce (NCCL; gloo without GPUs)
-    P = torch.empty(M, N, dtype=dt, device=dev)
-
-    def lib():
-        torch.matmul(A, B, out=P)
-        if W > 1:
-            dist.all_reduce(P)
-
     state.exec(lib)
 
 

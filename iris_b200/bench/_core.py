@@ -46,6 +46,8 @@ class Result:
     device_time_us_max_over_ranks: float | None = None
     roofline_us: float | None = None
     roofline_frac: float | None = None
+    nccl_baseline_us: float | None = None       # the library form of the same work, timed by the same loop
+    speedup_vs_baseline: float | None = None
 
 
 registry: list[BenchmarkDef] = []
@@ -68,6 +70,8 @@ class State:
         self._counters: dict[str, float] = {}
         self._exec_fn = None
         self._preamble_fn = None
+        self._baseline_fn = None
+        self._baseline_preamble_fn = None
         self.n_warmup, self.n_repeat = n_warmup, n_repeat
 
     def __getitem__(self, key):
@@ -101,6 +105,12 @@ class State:
 
     def exec(self, fn: Callable, preamble_fn: Callable | None = None) -> None:
         self._exec_fn, self._preamble_fn = fn, preamble_fn
+
+    def exec_baseline(self, fn: Callable, preamble_fn: Callable | None = None) -> None:
+        """Register the library form of the same work (NCCL collective, cuBLAS GEMM + NCCL, ...). It is
+        timed right after ``exec``'s function with the same warm-up, repeats, cache flush and
+        maximum over ranks, and reported as ``nccl_baseline_us`` with the ratio next to it."""
+        self._baseline_fn, self._baseline_preamble_fn = fn, preamble_fn
 
     def skip(self, reason: str = "") -> None:
         raise SkipCombination(reason)

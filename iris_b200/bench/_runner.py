@@ -64,18 +64,20 @@ def format_console(results: list) -> str:
         by_bench.setdefault(r.benchmark_name, []).append(r)
     for name, rs in by_bench.items():
         keys = list(rs[0].params.keys())
-        header = keys + ["time_us(max/ranks)", "GB/s", "TFLOPS", "roofline%"]
+        with_base = any(r.nccl_baseline_us is not None for r in rs)
+        header = keys + ["time_us(max/ranks)", "GB/s", "TFLOPS", "roofline%"] + (["baseline_us", "speedup"] if with_base else [])
         rows = []
         for r in rs:
             if r.skipped:
-                rows.append([dtype_str(r.params[k]) for k in keys] + [f"skipped: {r.skip_reason}", "", "", ""])
+                rows.append([dtype_str(r.params[k]) for k in keys] + [f"skipped: {r.skip_reason}", "", "", ""] + (["", ""] if with_base else []))
                 continue
             rows.append([dtype_str(r.params[k]) for k in keys] + [
                 f"{r.gpu_time_ms * 1e3:.2f}",
                 f"{r.bandwidth_gbps:.1f}" if r.bandwidth_gbps is not None else "",
                 f"{r.tflops:.1f}" if r.tflops is not None else "",
                 f"{100 * r.roofline_frac:.0f}" if r.roofline_frac is not None else "",
-            ])
+            ] + ([f"{r.nccl_baseline_us:.2f}" if r.nccl_baseline_us is not None else "",
+                  f"{r.speedup_vs_baseline:.2f}" if r.speedup_vs_baseline is not None else ""] if with_base else []))
         widths = [max(len(str(x)) for x in col) for col in zip(header, *rows)]
         lines.append(f"== {name} ==")
         lines.append("  ".join(str(h).ljust(w) for h, w in zip(header, widths)))
@@ -90,7 +92,8 @@ def _result_dict(r: Result) -> dict:
         "benchmark": r.benchmark_name, "params": {k: dtype_str(v) for k, v in r.params.items()}, "world_size": r.world_size,
         "gpu_time_ms": r.gpu_time_ms, "device_time_us_max_over_ranks": r.device_time_us_max_over_ranks,
         "bandwidth_gbps": r.bandwidth_gbps, "tflops": r.tflops, "roofline_us": r.roofline_us,
-        "roofline_frac": r.roofline_frac, "counters": r.counters, "skipped": r.skipped, "skip_reason": r.skip_reason,
+        "roofline_frac": r.roofline_frac, "nccl_baseline_us": r.nccl_baseline_us, "speedup_vs_baseline": r.speedup_vs_baseline,
+        "counters": r.counters, "skipped": r.skipped, "skip_reason": r.skip_reason,
     }
 
 
@@ -102,10 +105,12 @@ def format_csv(results: list) -> str:
     buf = io.StringIO()
     keys = sorted({k for r in results for k in r.params})
     w = csv.writer(buf)
-    w.writerow(["benchmark", "world_size"] + keys + ["gpu_time_ms", "bandwidth_gbps", "tflops", "roofline_frac", "skipped"])
+    w.writerow(["benchmark", "world_size"] + keys + ["gpu_time_ms", "bandwidth_gbps", "tflops", "roofline_frac", "skipped",
+                                                       "nccl_baseline_us", "speedup_vs_baseline"])
     for r in results:
         w.writerow([r.benchmark_name, r.world_size] + [dtype_str(r.params.get(k, "")) for k in keys] +
-                   [r.gpu_time_ms, r.bandwidth_gbps or "", r.tflops or "", r.roofline_frac or "", int(r.skipped)])
+                   [r.gpu_time_ms, r.bandwidth_gbps or "", r.tflops or "", r.roofline_frac or "", int(r.skipped),
+                    r.nccl_baseline_us or "", r.speedup_vs_baseline or ""])
     return buf.getvalue()
 
 
@@ -152,6 +157,14 @@ def run_benchmarks(ctx, benchmarks, overrides, skips, n_warmup, n_repeat) -> lis
             if state._roofline_us is not None and ms > 0:
                 r.roofline_us = state._roofline_us
                 r.roofline_frac = state._roofline_us / (ms * 1e3)
+            if state._baseline_fn is not None:
+                base = do_bench(state._baseline_fn, barrier_fn=ctx.barrier, preamble_fn=state._baseline_preamble_fn or (lambda: None),
+                                n_warmup=state.n_warmup, n_repeat=state.n_repeat, return_mode="all")
+                tb = torch.tensor([sum(base) / len(base)], dtype=torch.float64, device=ctx.device if not ctx.is_cpu else "cpu")
+                if world > 1:
+                    dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+                r.nccl_baseline_us = float(tb.item()) * 1e3
+                r.speedup_vs_baseline = r.nccl_baseline_us / (ms * 1e3) if ms > 0 else None
             results.append(r)
     return results
 
@@ -257,7 +270,7 @@ def main(argv: list | None = None) -> list:
     if rank0:
         rs = [Result(d["benchmark"], d["params"], d["gpu_time_ms"], [], d["bandwidth_gbps"], d["tflops"], d["counters"],
                      d["skipped"], d["skip_reason"], d["world_size"], d["device_time_us_max_over_ranks"], d["roofline_us"],
-                     d["roofline_frac"]) for d in results]
+                     d["roofline_frac"], d.get("nccl_baseline_us"), d.get("speedup_vs_baseline")) for d in results]
         text = {"console": format_console, "json": format_json, "csv": format_csv}[args.benchmark_format](rs)
         print(text)
         if args.benchmark_out:

@@ -170,3 +170,9 @@ def test_stage_and_sweep_benchmarks_on_the_cpu_backend(tmp_path, script, args, e
     assert {r.get("stage") or r.get("layout") for r in timed} == expect
     if "layout" in rows[0]:
         assert all(r["skipped"] == "1" for r in rows if r["layout"] == "m" and r["m"] == "1")     # one row cannot be split over two ranks
+    else:
+        # the fused stage carries the library pair's time, measured by the same loop, and the ratio of the two
+        fused = next(r for r in timed if r["stage"] == "fused")
+        assert float(fused["nccl_baseline_us"]) > 0
+        assert float(fused["speedup_vs_baseline"]) == pytest.approx(float(fused["nccl_baseline_us"]) / (float(fused["gpu_time_ms"]) * 1e3), rel=1e-6)
+        assert all(r["nccl_baseline_us"] == "" for r in timed if r["stage"] != "fused")
