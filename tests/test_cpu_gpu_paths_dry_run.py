@@ -1,0 +1,186 @@
+"""The GPU code paths of the Python layer, walked without a GPU.
+
+On a machine without CUDA the collectives and fused ops take their host fallbacks, so the code that
+builds kernel descriptors, sizes workspaces and picks variants would never run in the CPU suite. Here
+two gloo ranks create a normal CPU-backend context and then pretend to be on the GPU path: the
+kernel library's planning entry point (pure host code) is called for real, the launch entry points
+are replaced by recorders, and stream / synchronise calls by no-ops. Nothing is computed; what is
+checked is what each call WOULD launch: operation codes, shapes, leading dimensions, pointers,
+workspace buffers, variant choice by message size, descriptor reuse on repeated calls. The reference
+has no equivalent (its launch code only ever runs on GPUs).
+"""
+
+import torch
+
+from helpers import run_ranks
+
+
+class _Recorder:
+    """Stands in front of the real library: planning goes through, launches are recorded."""
+
+    def __init__(self, real, ccl_desc_type, gemm_desc_type):
+        self._real = real
+        self.ccl, self.gemm = [], []
+        self._ccl_t, self._gemm_t = ccl_desc_type, gemm_desc_type
+        self.iris_gemm_workspace = real.iris_gemm_workspace
+
+        def ccl_launch(op, d, stream):
+            self.ccl.append((op, self._ccl_t.from_buffer_copy(d._obj)))
+            return 0
+
+        def gemm_launch(d, stream):
+            self.gemm.append(self._gemm_t.from_buffer_copy(d._obj))
+            return 0
+
+        self.iris_ccl_launch, self.iris_gemm_launch = ccl_launch, gemm_launch
+
+
+def _pretend_gpu(ctx):
+    """Route ``ctx`` through the GPU branches with recorded launches; returns the recorder."""
+    from iris_b200 import _lib, ccl
+
+    rec = _Recorder(_lib.kernels(), ccl.IrisCclDesc, _lib.IrisGemmDesc)
+    _lib.kernels = lambda: rec
+    _lib.current_stream_ptr = lambda: 0
+    torch.cuda.synchronize = lambda *a, **k: None
+    ctx.is_cpu = False
+    ctx.device_barrier = lambda group=None: None          # a kernel launch of its own on a GPU; not part of this walk
+    return rec
+
+
+def _dry_run(rank, world):
+    import iris_b200 as iris
+    from iris_b200 import _lib
+    from iris_b200.ccl import Config
+    from iris_b200.parallel import ColumnParallelLinear, GradientBuckets, RowParallelLinear, UlyssesExchange
+
+    ctx = iris.iris(1 << 28)
+    rec = _pretend_gpu(ctx)
+    dt = torch.bfloat16
+    W = world
+
+    # ---- collectives: descriptors and variant choice
+    inp, out = ctx.zeros((64, 512), dtype=dt), ctx.zeros((64, 512), dtype=dt)          # 64 KB
+    ctx.ccl.all_reduce(out, inp)
+    op, d = rec.ccl[-1]
+    assert op == 2 and (d.M, d.N) == (64, 512) and d.dtype == _lib.DTYPE_CODE[dt] and d.ctx.world == W and d.ctx.rank == rank
+    assert d.inp == inp.data_ptr() and d.out == out.data_ptr() and d.ld_in == 512 and d.ld_out == 512
+    big_in, big_out = ctx.zeros((1024, 4096), dtype=dt), ctx.zeros((1024, 4096), dtype=dt)      # 8 MB
+    ws = ctx.ccl.all_reduce(big_out, big_in)
+    if W > 1:
+        assert d.variant == 6 and d.ring_buf and d.flags                               # small message: one-shot push, own workspace
+        assert rec.ccl[-1][1].variant == 3 and ws.variant == "two_shot"                # no multicast window here: two-shot
+        for name, code in (("one_shot", 2), ("two_shot", 3), ("atomic", 0), ("ring", 1), ("spinlock", 4)):
+            w2 = ctx.ccl.all_reduce(big_out, big_in, config=Config(all_reduce_variant=name))
+            assert rec.ccl[-1][1].variant == code and w2.variant == name
+            if name == "ring":
+                assert rec.ccl[-1][1].ring_buf == w2.ring_buffer.data_ptr() and rec.ccl[-1][1].flags == w2.flags.data_ptr()
+    else:
+        assert d.variant == 2 and ws.variant == "one_shot"                             # one rank: every variant is a copy
+    n_before = len(rec.ccl)
+    ctx.ccl.all_reduce(big_out, big_in, workspace=ws, async_op=True)
+    ctx.ccl.all_reduce(big_out, big_in, workspace=ws, async_op=True)                   # replayed from the call cache
+    assert len(rec.ccl) == n_before + 2 and bytes(rec.ccl[-1][1]) == bytes(rec.ccl[-2][1])
+    ag = ctx.zeros((W * 64, 512), dtype=dt)
+    ctx.ccl.all_gather(ag, inp)
+    op, d = rec.ccl[-1]
+    assert op == 0 and (d.M, d.N) == (64, 512) and d.out == ag.data_ptr()
+    a2a_in, a2a_out = ctx.zeros((64, 128 * W), dtype=dt), ctx.zeros((64, 128 * W), dtype=dt)
+    ctx.ccl.all_to_all(a2a_out, a2a_in)
+    assert rec.ccl[-1][0] == 1
+    rs_out = ctx.zeros((64 // W, 512), dtype=dt)
+    ctx.ccl.reduce_scatter(rs_out, inp, config=Config(reduce_scatter_rows=True))
+    op, d = rec.ccl[-1]
+    assert op == 3 and d.rows_mode == 1 and d.out == rs_out.data_ptr()
+    ctx.ccl.reduce_scatter(out, inp, config=Config(block_size_m=32, block_size_n=64, all_reduce_distribution=1))
+    op, d = rec.ccl[-1]
+    assert op == 3 and d.rows_mode == 0 and (d.block_m, d.block_n, d.distribution) == (32, 64, 1)
+
+    # ---- fused ops: operation codes, shapes, workspaces
+    Ml, K, N = 256, 512, 384
+    A = torch.zeros(Ml, K, dtype=dt)
+    B = torch.zeros(K, N, dtype=dt)
+    Cfull = torch.zeros(Ml * W, N, dtype=dt)
+    ws1 = ctx.ops.all_gather_matmul(Cfull, A, B, shard_dim=0)
+    g = rec.gemm[-1]
+    assert ws1.variant == "fused" and g.op == _lib.GEMM_AG_M and (g.M, g.N, g.K, g.M_local) == (Ml * W, N, K, Ml)
+    assert g.A == A.data_ptr() and g.C == Cfull.data_ptr() and (g.lda, g.ldc) == (K, N) and g.b_kmajor == 0
+    assert g.sync_block == ws1.sync_block.data_ptr() and g.bn == ws1.bn and g.bn in (128, 224, 256) and g.ctx.world == W
+    if W > 1:
+        assert g.inbox == ws1.inbox.data_ptr() and g.flags == ws1.flags.data_ptr()
+    Bt = torch.zeros(N, K, dtype=dt).t()                                             # a K-major weight view: no copy
+    ctx.ops.all_gather_matmul(Cfull, A, Bt, shard_dim=0)
+    assert rec.gemm[-1].b_kmajor == 1 and rec.gemm[-1].B == Bt.data_ptr()
+    n_before = len(rec.gemm)
+    ctx.ops.all_gather_matmul(Cfull, A, B, shard_dim=0, workspace=ws1, async_op=True)
+    ctx.ops.all_gather_matmul(Cfull, A, B, shard_dim=0, workspace=ws1, async_op=True)
+    assert len(rec.gemm) == n_before + 2 and bytes(rec.gemm[-1]) == bytes(rec.gemm[-2])
+    Ak = torch.zeros(Ml, K // W, dtype=dt)
+    Ck = torch.zeros(Ml, N, dtype=dt)
+    ctx.ops.all_gather_matmul(Ck, Ak, B)                                             # the reference layout: K sharded
+    g = rec.gemm[-1]
+    assert g.op == _lib.GEMM_AG_K and g.K_local == K // W and g.K == K
+    H = torch.zeros(Ml * W, N, dtype=dt)
+    W2 = torch.zeros(N, K, dtype=dt)
+    Y = torch.zeros(Ml, K, dtype=dt)
+    ws2 = ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True)
+    g = rec.gemm[-1]
+    assert ws2.variant == "fused" and g.op == _lib.GEMM_REDUCE_SCATTER and (g.M, g.N, g.K) == (Ml * W, K, N)
+    if W > 1:
+        assert g.staging == ws2.staging.data_ptr() and g.flags == ws2.flags.data_ptr()
+    Yt = ctx.zeros((Ml * W, K), dtype=dt)
+    ctx.ops.matmul_reduce_scatter(Yt, H, W2)                                         # tile ownership, full-shape output
+    assert rec.gemm[-1].op == _lib.GEMM_RS_TILES
+    bias = torch.ones(Ml * W)
+    ws3 = ctx.ops.matmul_all_reduce(Yt, H, W2, bias=bias)
+    g = rec.gemm[-1]
+    assert ws3.variant == "fused" and g.op == _lib.GEMM_ALL_REDUCE and g.C == Yt.data_ptr()
+    assert bool(g.bias_row) == (rank == 0)                                           # the bias enters the sum once
+    off_heap = torch.zeros(Ml * W, K, dtype=dt)
+    n_before = len(rec.gemm)
+    ctx.ops.matmul_all_reduce(off_heap, H, W2)                                       # output not on the heap: GEMM + collective
+    assert all(x.op == _lib.GEMM_LOCAL for x in rec.gemm[n_before:]) and rec.ccl[-1][0] == 2
+    rows = ctx.zeros((Ml * W, N), dtype=dt)
+    ctx.ops.matmul_all_gather(rows, A, B)
+    assert rec.gemm[-1].op == _lib.GEMM_ALL_GATHER
+    cols = ctx.zeros((Ml, N * W), dtype=dt)
+    ctx.ops.matmul_all_gather(cols, A, B, scatter_cols=True)
+    assert rec.gemm[-1].op == _lib.GEMM_ALL_SCATTER and rec.gemm[-1].ldc == N * W
+    # fp32 operands are outside the kernels' range: library GEMM + collective, no fused launch
+    n_before = len(rec.gemm)
+    wsf = ctx.ops.matmul_all_reduce(ctx.zeros((8, 8)), torch.zeros(8, 4), torch.zeros(4, 8))
+    assert wsf.variant == "unfused" and len(rec.gemm) == n_before
+
+    # ---- the layers of iris_b200.parallel on the same path
+    up = ColumnParallelLinear(ctx, K, N, dtype=dt, seed=1)
+    down = RowParallelLinear(ctx, N, K, dtype=dt, seed=2, bias=True)
+    n_before = len(rec.gemm)
+    y = down(up(torch.zeros(Ml, K, dtype=dt)))
+    assert y.shape == (Ml, K) and [x.op for x in rec.gemm[n_before:]] == [_lib.GEMM_AG_M, _lib.GEMM_REDUCE_SCATTER]
+    down2 = RowParallelLinear(ctx, N, K, dtype=dt, seed=2, sequence_parallel=False)
+    y2 = down2(torch.zeros(Ml * W, N, dtype=dt))
+    assert ctx.is_symmetric(y2) and rec.gemm[-1].op == _lib.GEMM_ALL_REDUCE and rec.gemm[-1].C == y2.data_ptr()
+    model = torch.nn.Linear(32, 16)
+    model(torch.ones(4, 32)).sum().backward()
+    buckets = GradientBuckets(ctx, model.parameters())
+    n_before = len(rec.ccl)
+    buckets.all_reduce()
+    launched = rec.ccl[n_before:]
+    assert len(launched) == len(buckets.buckets) == 1 and launched[0][0] == 2 and launched[0][1].N == 4096
+    assert launched[0][1].dtype == _lib.DTYPE_CODE[torch.float32] and launched[0][1].inp == buckets.buckets[0].inp.data_ptr()
+    ex = UlyssesExchange(ctx)
+    n_before = len(rec.ccl)
+    heads = ex.to_heads(torch.zeros(16, 2 * W, 8, dtype=dt))
+    assert heads.shape == (16 * W, 2, 8) and rec.ccl[-1][0] == 1 and len(rec.ccl) == n_before + 1
+    assert (rec.ccl[-1][1].M, rec.ccl[-1][1].N) == (16, 2 * 8)                        # N is the width of one rank's chunk
+    import torch.distributed as dist
+
+    dist.barrier()
+
+
+def test_gpu_paths_of_collectives_fused_ops_and_layers_world2():
+    run_ranks(_dry_run, 2)
+
+
+def test_gpu_paths_world1():
+    run_ranks(_dry_run, 1)
