@@ -210,7 +210,12 @@ class Iris:
         self.barrier()
         self.heap.set_offset(mark)
         self._sync_blocks = {k: v for k, v in self._sync_blocks.items() if self.heap.offset_of(v) < mark}
+        # descriptors remembered for repeated calls may point into the released range (workspaces,
+        # sync blocks): forget them all, and change the epoch that every cache key carries
         self.ccl._desc_cache.clear()
+        self.ccl._fast.clear()
+        self._ctx_epoch = object()
+        self._group_ctx_cache.clear()
         if self.ccl._push_ws is not None and self.heap.offset_of(self.ccl._push_ws[0]) >= mark:
             self.ccl._push_ws = None
         self.barrier()

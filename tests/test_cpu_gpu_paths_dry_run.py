@@ -173,6 +173,24 @@ def _dry_run(rank, world):
     heads = ex.to_heads(torch.zeros(16, 2 * W, 8, dtype=dt))
     assert heads.shape == (16 * W, 2, 8) and rec.ccl[-1][0] == 1 and len(rec.ccl) == n_before + 1
     assert (rec.ccl[-1][1].M, rec.ccl[-1][1].N) == (16, 2 * 8)                        # N is the width of one rank's chunk
+    # ---- rewinding the heap drops what was allocated after the mark, including cached workspaces
+    mark = ctx.heap_mark()
+    t_in, t_out = ctx.zeros((8, 256), dtype=dt), ctx.zeros((8, 256), dtype=dt)
+    ctx.ccl._push_ws = None
+    ctx.ccl.all_reduce(t_out, t_in)                                                  # allocates the push workspace after the mark
+    if W > 1:
+        assert ctx.ccl._push_ws is not None and ctx.heap.offset_of(ctx.ccl._push_ws[0]) >= mark
+    ctx.heap_release(mark)
+    assert ctx.heap_mark() == mark and ctx.ccl._push_ws is None and not ctx.ccl._desc_cache
+    old_push = rec.ccl[-1][1].ring_buf
+    t_in2, t_out2 = ctx.zeros((8, 256), dtype=dt), ctx.zeros((8, 256), dtype=dt)
+    filler = ctx.zeros(4096, dtype=torch.int32)                                      # shifts what is allocated next
+    assert t_in2.data_ptr() == t_in.data_ptr() and t_out2.data_ptr() == t_out.data_ptr()      # the space is handed out again
+    ctx.ccl.all_reduce(t_out2, t_in2)
+    if W > 1:
+        # same tensors' addresses as before the release, but the call is not replayed from the cache:
+        # its descriptor names the workspace allocated now, not the released one
+        assert rec.ccl[-1][1].ring_buf == ctx.ccl._push_ws[0].data_ptr() != old_push and filler.data_ptr() < rec.ccl[-1][1].ring_buf
     import torch.distributed as dist
 
     dist.barrier()
