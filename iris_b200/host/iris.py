@@ -216,6 +216,9 @@ class Iris:
         self.ccl._fast.clear()
         self._ctx_epoch = object()
         self._group_ctx_cache.clear()
+        kept = {k: w for k, w in self.__dict__.get("_ops_workspaces", {}).items()
+                if w.sync_block is None or self.heap.offset_of(w.sync_block) < mark}
+        self.__dict__["_ops_workspaces"] = kept
         if self.ccl._push_ws is not None and self.heap.offset_of(self.ccl._push_ws[0]) >= mark:
             self.ccl._push_ws = None
         self.barrier()

@@ -90,6 +90,18 @@ def _make_workspace(ctx, operation, shape, dtype, variant, d) -> FusedWorkspace 
     return ws
 
 
+def _auto_workspace(ctx, operation, key, dtype, config, make, extra=None):
+    """Workspace of a call that did not bring a matching one: created once per (operation, shapes,
+    dtype, tile configuration) and kept on the context, so a loop that calls an op without passing
+    the returned workspace back does not allocate heap memory (and run a barrier) on every call."""
+    cache = ctx.__dict__.setdefault("_ops_workspaces", {})
+    ck = (operation, tuple(key), dtype, config.tile_n(), config.two_sm, config.comm_sms, config.use_multicast, extra)
+    ws = cache.get(ck)
+    if ws is None:
+        ws = cache[ck] = make()
+    return ws
+
+
 def _cached_desc(ws, key, build):
     """Descriptor of a repeated call (same buffers): built once, then reused from the workspace."""
     cache = ws.extra.setdefault("desc", {})
@@ -201,7 +213,8 @@ def all_gather_matmul(shmem, output_tensor, A_sharded, B, bias=None, async_op=Fa
     key = tuple(A_sharded.shape) + tuple(B.shape) + (shard_dim,)
     ws = workspace
     if ws is None or not (ws.variant == "unfused" or ws.matches("all_gather_matmul", key, A_sharded.dtype, W, "fused")):
-        ws = all_gather_matmul_preamble(shmem, A_sharded, B, config, shard_dim)
+        ws = _auto_workspace(shmem, "all_gather_matmul", key, A_sharded.dtype, config,
+                             lambda: all_gather_matmul_preamble(shmem, A_sharded, B, config, shard_dim), extra=B.stride(-1) == 1)
     if ws.variant == "unfused":
         gathered = _unfused_gather(shmem, A_sharded, shard_dim)
         output_tensor.copy_(_local_matmul(gathered, B, bias, bias_dim=0))
@@ -259,7 +272,8 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
     key = tuple(A.shape) + tuple(B.shape) + (scatter_cols,)
     ws = workspace
     if ws is None or not (ws.variant == "unfused" or ws.matches("matmul_all_gather", key, A.dtype, W, "fused")):
-        ws = matmul_all_gather_preamble(shmem, A, B, config, scatter_cols)
+        ws = _auto_workspace(shmem, "matmul_all_gather", key, A.dtype, config,
+                             lambda: matmul_all_gather_preamble(shmem, A, B, config, scatter_cols), extra=B.stride(-1) == 1)
     if ws.variant == "unfused" or not shmem.is_symmetric(output_tensor):
         local = _local_matmul(A, B, bias, bias_dim=0)
         if scatter_cols:
@@ -304,7 +318,9 @@ def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, con
     key = tuple(A.shape) + tuple(B.shape)
     ws = workspace
     if ws is None or not (ws.variant == "unfused" or ws.matches("matmul_all_reduce", key, A.dtype, W, "fused")):
-        ws = matmul_all_reduce_preamble(shmem, output_tensor, A, B, config)
+        ws = _auto_workspace(shmem, "matmul_all_reduce", key, A.dtype, config,
+                             lambda: matmul_all_reduce_preamble(shmem, output_tensor, A, B, config),
+                             extra=(B.stride(-1) == 1, shmem.is_symmetric(output_tensor)))
     # a bias must enter the sum exactly once: rank 0 adds it to its partial product
     b = bias if (bias is not None and shmem.cur_rank == 0) else None
     if ws.variant == "unfused":
@@ -363,7 +379,8 @@ def matmul_reduce_scatter(shmem, output_tensor, A, B, bias=None, async_op=False,
     key = tuple(A.shape) + tuple(B.shape) + (scatter_rows,)
     ws = workspace
     if ws is None or not (ws.variant == "unfused" or ws.matches("matmul_reduce_scatter", key, A.dtype, W, "fused")):
-        ws = matmul_reduce_scatter_preamble(shmem, output_tensor, A, B, config, scatter_rows)
+        ws = _auto_workspace(shmem, "matmul_reduce_scatter", key, A.dtype, config,
+                             lambda: matmul_reduce_scatter_preamble(shmem, output_tensor, A, B, config, scatter_rows), extra=B.stride(-1) == 1)
     b = bias if (bias is not None and shmem.cur_rank == 0) else None
     if ws.variant == "unfused":
         from ..ccl import Config

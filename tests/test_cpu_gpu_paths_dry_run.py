@@ -115,6 +115,12 @@ def _dry_run(rank, world):
     ctx.ops.all_gather_matmul(Cfull, A, B, shard_dim=0, workspace=ws1, async_op=True)
     ctx.ops.all_gather_matmul(Cfull, A, B, shard_dim=0, workspace=ws1, async_op=True)
     assert len(rec.gemm) == n_before + 2 and bytes(rec.gemm[-1]) == bytes(rec.gemm[-2])
+    # a caller that never hands the workspace back gets the same one again: no heap growth per call
+    first = ctx.ops.all_gather_matmul(Cfull, A, B, shard_dim=0)
+    level = ctx.heap_mark()
+    for _ in range(3):
+        assert ctx.ops.all_gather_matmul(Cfull, A, B, shard_dim=0) is first
+    assert ctx.heap_mark() == level
     Ak = torch.zeros(Ml, K // W, dtype=dt)
     Ck = torch.zeros(Ml, N, dtype=dt)
     ctx.ops.all_gather_matmul(Ck, Ak, B)                                             # the reference layout: K sharded
@@ -180,8 +186,12 @@ def _dry_run(rank, world):
     ctx.ccl.all_reduce(t_out, t_in)                                                  # allocates the push workspace after the mark
     if W > 1:
         assert ctx.ccl._push_ws is not None and ctx.heap.offset_of(ctx.ccl._push_ws[0]) >= mark
+    late = ctx.ops.matmul_all_reduce(ctx.zeros((Ml * W, 256), dtype=dt), torch.zeros(Ml * W, 128, dtype=dt), torch.zeros(128, 256, dtype=dt))
+    assert late.variant == "fused" and late in ctx._ops_workspaces.values() and first in ctx._ops_workspaces.values()
     ctx.heap_release(mark)
     assert ctx.heap_mark() == mark and ctx.ccl._push_ws is None and not ctx.ccl._desc_cache
+    # workspaces kept for callers that pass none: the one allocated after the mark is gone, earlier ones stay
+    assert late not in ctx._ops_workspaces.values() and first in ctx._ops_workspaces.values()
     old_push = rec.ccl[-1][1].ring_buf
     t_in2, t_out2 = ctx.zeros((8, 256), dtype=dt), ctx.zeros((8, 256), dtype=dt)
     filler = ctx.zeros(4096, dtype=torch.int32)                                      # shifts what is allocated next
