@@ -73,6 +73,7 @@ class CCL:
     def __init__(self, ctx):
         self.ctx = ctx
         self._desc_cache: dict = {}
+        self._ws_cache: dict = {}   # all-reduce workspaces for calls that pass none
         self._fast: dict = {}       # whole calls that ran before: key -> (op code, descriptor copy, return value)
         self._push_ws = None
 
@@ -239,7 +240,14 @@ class CCL:
         variant = self._pick_all_reduce(config, out.numel() * out.element_size(), group, out.dtype)
         ws = workspace
         if ws is None or ws.variant != variant or ws.shape != tuple(out.shape) or ws.dtype != out.dtype:
-            ws = AllReduceWorkspace(variant=variant, shape=tuple(out.shape), dtype=out.dtype)
+            # calls that bring no matching workspace share one per (variant, shape, dtype, group, CTA count):
+            # the ring and spin-lock variants own heap buffers, which must not be allocated per call
+            ck = (variant, tuple(out.shape), out.dtype, self.ctx._group_key(group), config.comm_sms)
+            kept = self._ws_cache.get(ck)
+            if kept is not None:
+                kept.prepared = True
+                return kept
+            ws = self._ws_cache[ck] = AllReduceWorkspace(variant=variant, shape=tuple(out.shape), dtype=out.dtype)
             ctx = self.ctx
             if not ctx.is_cpu:
                 W = ctx.ctx_struct(group).world

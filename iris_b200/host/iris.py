@@ -214,6 +214,8 @@ class Iris:
         # sync blocks): forget them all, and change the epoch that every cache key carries
         self.ccl._desc_cache.clear()
         self.ccl._fast.clear()
+        self.ccl._ws_cache = {k: w for k, w in self.ccl._ws_cache.items()
+                              if not any(t is not None and self.heap.offset_of(t) >= mark for t in (w.ring_buffer, w.flags, w.sync_block))}
         self._ctx_epoch = object()
         self._group_ctx_cache.clear()
         kept = {k: w for k, w in self.__dict__.get("_ops_workspaces", {}).items()

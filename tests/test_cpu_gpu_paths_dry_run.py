@@ -77,6 +77,14 @@ def _dry_run(rank, world):
                 assert rec.ccl[-1][1].ring_buf == w2.ring_buffer.data_ptr() and rec.ccl[-1][1].flags == w2.flags.data_ptr()
     else:
         assert d.variant == 2 and ws.variant == "one_shot"                             # one rank: every variant is a copy
+    if W > 1:
+        # other tensors of the same shape: the ring variant's heap buffers are not allocated again
+        ring_a = ctx.ccl.all_reduce(big_out, big_in, config=Config(all_reduce_variant="ring"))
+        other_in, other_out = ctx.zeros((1024, 4096), dtype=dt), ctx.zeros((1024, 4096), dtype=dt)
+        level = ctx.heap_mark()
+        ring_b = ctx.ccl.all_reduce(other_out, other_in, config=Config(all_reduce_variant="ring"))
+        assert ring_b is ring_a and ctx.heap_mark() == level and rec.ccl[-1][1].ring_buf == ring_a.ring_buffer.data_ptr()
+        assert rec.ccl[-1][1].inp == other_in.data_ptr()
     n_before = len(rec.ccl)
     ctx.ccl.all_reduce(big_out, big_in, workspace=ws, async_op=True)
     ctx.ccl.all_reduce(big_out, big_in, workspace=ws, async_op=True)                   # replayed from the call cache
