@@ -218,8 +218,11 @@ class Iris:
                               if not any(t is not None and self.heap.offset_of(t) >= mark for t in (w.ring_buffer, w.flags, w.sync_block))}
         self._ctx_epoch = object()
         self._group_ctx_cache.clear()
-        kept = {k: w for k, w in self.__dict__.get("_ops_workspaces", {}).items()
-                if w.sync_block is None or self.heap.offset_of(w.sync_block) < mark}
+        def before_mark(w):
+            held = [w.sync_block] + list(w.extra.get("scratch", {}).values())
+            return all(t is None or t.numel() == 0 or self.heap.offset_of(t) < mark for t in held)
+
+        kept = {k: w for k, w in self.__dict__.get("_ops_workspaces", {}).items() if before_mark(w)}
         self.__dict__["_ops_workspaces"] = kept
         if self.ccl._push_ws is not None and self.heap.offset_of(self.ccl._push_ws[0]) >= mark:
             self.ccl._push_ws = None

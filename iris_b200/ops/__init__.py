@@ -102,6 +102,26 @@ def _auto_workspace(ctx, operation, key, dtype, config, make, extra=None):
     return ws
 
 
+def _scratch(ctx, ws, tag, shape, dtype):
+    """A heap buffer of the unfused path, allocated on first use (collectively) and kept in the
+    workspace: the fallback must not consume heap memory on every call either."""
+    bufs = ws.extra.setdefault("scratch", {})
+    key = (tag, tuple(shape), dtype)
+    buf = bufs.get(key)
+    if buf is None:
+        buf = bufs[key] = ctx.empty(tuple(shape), dtype=dtype)
+    return buf
+
+
+def _on_heap(ctx, ws, tag, t):
+    """``t`` itself when it is a contiguous heap tensor, else its copy in a kept heap buffer."""
+    if ctx.is_symmetric(t) and t.is_contiguous():
+        return t
+    buf = _scratch(ctx, ws, tag, t.shape, t.dtype)
+    buf.copy_(t)
+    return buf
+
+
 def _cached_desc(ws, key, build):
     """Descriptor of a repeated call (same buffers): built once, then reused from the workspace."""
     cache = ws.extra.setdefault("desc", {})
@@ -216,7 +236,7 @@ def all_gather_matmul(shmem, output_tensor, A_sharded, B, bias=None, async_op=Fa
         ws = _auto_workspace(shmem, "all_gather_matmul", key, A_sharded.dtype, config,
                              lambda: all_gather_matmul_preamble(shmem, A_sharded, B, config, shard_dim), extra=B.stride(-1) == 1)
     if ws.variant == "unfused":
-        gathered = _unfused_gather(shmem, A_sharded, shard_dim)
+        gathered = _unfused_gather(shmem, ws, A_sharded, shard_dim)
         output_tensor.copy_(_local_matmul(gathered, B, bias, bias_dim=0))
     else:
         d, keep = _cached_desc(ws, _ptr_key(output_tensor, A_sharded, B, bias) + (id(shmem._ctx_epoch),),
@@ -226,15 +246,13 @@ def all_gather_matmul(shmem, output_tensor, A_sharded, B, bias=None, async_op=Fa
     return ws
 
 
-def _unfused_gather(ctx, A_sharded, shard_dim):
+def _unfused_gather(ctx, ws, A_sharded, shard_dim):
     W = ctx.num_ranks
-    src = ctx.as_symmetric(A_sharded.contiguous())
-    if shard_dim == 0:
-        dst = ctx.empty((A_sharded.shape[0] * W, A_sharded.shape[1]), dtype=A_sharded.dtype)
-        ctx.ccl.all_gather(dst, src, async_op=False)
-        return dst
-    dst = ctx.empty((W * A_sharded.shape[0], A_sharded.shape[1]), dtype=A_sharded.dtype)
+    src = _on_heap(ctx, ws, "gather_src", A_sharded)
+    dst = _scratch(ctx, ws, "gather_dst", (W * A_sharded.shape[0], A_sharded.shape[1]), A_sharded.dtype)
     ctx.ccl.all_gather(dst, src, async_op=False)
+    if shard_dim == 0:
+        return dst
     M, Kl = A_sharded.shape
     return dst.view(W, M, Kl).permute(1, 0, 2).reshape(M, W * Kl)
 
@@ -276,13 +294,14 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
                              lambda: matmul_all_gather_preamble(shmem, A, B, config, scatter_cols), extra=B.stride(-1) == 1)
     if ws.variant == "unfused" or not shmem.is_symmetric(output_tensor):
         local = _local_matmul(A, B, bias, bias_dim=0)
+        part = _on_heap(shmem, ws, "part", local)
         if scatter_cols:
-            tmp = shmem.empty((W * M, N), dtype=A.dtype)
-            shmem.ccl.all_gather(tmp, shmem.as_symmetric(local.contiguous()))
+            tmp = _scratch(shmem, ws, "stacked", (W * M, N), A.dtype)
+            shmem.ccl.all_gather(tmp, part)
             output_tensor.copy_(tmp.view(W, M, N).permute(1, 0, 2).reshape(M, W * N))
         else:
-            dst = output_tensor if shmem.is_symmetric(output_tensor) else shmem.empty(want, dtype=A.dtype)
-            shmem.ccl.all_gather(dst, shmem.as_symmetric(local.contiguous()))
+            dst = output_tensor if shmem.is_symmetric(output_tensor) else _scratch(shmem, ws, "out", want, A.dtype)
+            shmem.ccl.all_gather(dst, part)
             if dst is not output_tensor:
                 output_tensor.copy_(dst)
     else:
@@ -324,8 +343,8 @@ def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, con
     # a bias must enter the sum exactly once: rank 0 adds it to its partial product
     b = bias if (bias is not None and shmem.cur_rank == 0) else None
     if ws.variant == "unfused":
-        part = shmem.as_symmetric(_local_matmul(A, B, b, bias_dim=0).contiguous())
-        dst = output_tensor if shmem.is_symmetric(output_tensor) else shmem.empty((M, N), dtype=A.dtype)
+        part = _on_heap(shmem, ws, "part", _local_matmul(A, B, b, bias_dim=0))
+        dst = output_tensor if shmem.is_symmetric(output_tensor) else _scratch(shmem, ws, "out", (M, N), A.dtype)
         shmem.ccl.all_reduce(dst, part)
         if dst is not output_tensor:
             output_tensor.copy_(dst)
@@ -385,13 +404,13 @@ def matmul_reduce_scatter(shmem, output_tensor, A, B, bias=None, async_op=False,
     if ws.variant == "unfused":
         from ..ccl import Config
 
-        part = shmem.as_symmetric(_local_matmul(A, B, b, bias_dim=0).contiguous())
+        part = _on_heap(shmem, ws, "part", _local_matmul(A, B, b, bias_dim=0))
         if scatter_rows:
-            dst = shmem.empty(want, dtype=A.dtype)
+            dst = _scratch(shmem, ws, "out", want, A.dtype)
             shmem.ccl.reduce_scatter(dst, part, config=Config(reduce_scatter_rows=True))
             output_tensor.copy_(dst)
         else:
-            full = shmem.empty((M, N), dtype=A.dtype)
+            full = _scratch(shmem, ws, "full", (M, N), A.dtype)
             shmem.ccl.all_reduce(full, part)
             bn = ws.bn or 256
             tiles_n = -(-N // bn)

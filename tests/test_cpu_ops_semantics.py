@@ -119,6 +119,23 @@ def _ops(rank, world):
     with pytest.raises(ValueError):
         ctx.ops.matmul_reduce_scatter(torch.zeros(Mr // world, N), Aq, Bq)
 
+    # ---- repeated calls, with or without the returned workspace, leave the heap where it is
+    def one_round():
+        ctx.ops.all_gather_matmul(out, A, B)
+        ctx.ops.all_gather_matmul(out_m, Am, B, shard_dim=0)
+        ctx.ops.matmul_all_gather(rows, Ar, Br)
+        ctx.ops.matmul_all_gather(off_heap, Arep, Bc, scatter_cols=True)
+        ctx.ops.matmul_all_reduce(off, Ap, Bp)
+        ctx.ops.matmul_reduce_scatter(mine, Aq, Bq, scatter_rows=True)
+        ctx.ops.matmul_reduce_scatter(full, At, Bt)
+
+    one_round()
+    level = ctx.heap_mark()
+    for _ in range(3):
+        one_round()
+    assert ctx.heap_mark() == level
+    assert torch.allclose(off, sum(a @ b for a, b in zip(_gather(Ap), _gather(Bp))), **tol)       # and still compute the same thing
+
     # ---- preambles return reusable workspaces; config is validated
     for fn, args in ((ops.all_gather_matmul_preamble, (ctx, A, B)), (ops.matmul_all_gather_preamble, (ctx, Ar, Br)),
                      (ops.matmul_all_reduce_preamble, (ctx, summed, Ap, Bp)), (ops.matmul_reduce_scatter_preamble, (ctx, mine, Aq, Bq))):
