@@ -148,12 +148,18 @@ class MoELayer:
         """CPU backend: gather every rank's tokens, apply the local experts, sum over ranks."""
         ctx = self.ctx
         W, me, T = ctx.get_num_ranks(), ctx.get_rank(), x.shape[0]
-        xs = ctx.zeros((W * T, self.D), dtype=torch.float32)
-        ls = ctx.zeros((W * T, self.E), dtype=torch.float32)
-        ctx.ccl.all_gather(xs, ctx.as_symmetric(x.float().contiguous()))
-        ctx.ccl.all_gather(ls, ctx.as_symmetric(logits.float().contiguous()))
+        bufs = self.__dict__.setdefault("_cpu_bufs", {})
+        if T not in bufs:            # heap buffers of this path, once per token count (collective)
+            f32 = torch.float32
+            bufs[T] = (ctx.zeros((T, self.D), dtype=f32), ctx.zeros((T, self.E), dtype=f32), ctx.zeros((W * T, self.D), dtype=f32),
+                       ctx.zeros((W * T, self.E), dtype=f32), ctx.zeros((W * T, self.D), dtype=f32), ctx.zeros((W * T, self.D), dtype=f32))
+        x_loc, l_loc, xs, ls, part, tot = bufs[T]
+        x_loc.copy_(x)
+        l_loc.copy_(logits)
+        ctx.ccl.all_gather(xs, x_loc)
+        ctx.ccl.all_gather(ls, l_loc)
         idx, w = route(ls, self.K)
-        part = ctx.zeros((W * T, self.D), dtype=torch.float32)
+        part.zero_()
         for j in range(self.El):
             e = me * self.El + j
             tok, slot = torch.nonzero(idx == e, as_tuple=True)
@@ -162,6 +168,5 @@ class MoELayer:
             h = xs[tok]
             y = (torch.nn.functional.silu(h @ self.w_gate[j].float()) * (h @ self.w_up[j].float())) @ self.w_down[j].float()
             part.index_add_(0, tok, y * w[tok, slot][:, None])
-        tot = ctx.zeros((W * T, self.D), dtype=torch.float32)
         ctx.ccl.all_reduce(tot, part)
         return tot[me * T:(me + 1) * T].to(x.dtype)

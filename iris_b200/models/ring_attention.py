@@ -128,10 +128,15 @@ class RingAttention:
         """CPU backend: gather all K/V blocks through the heap, attend in PyTorch."""
         ctx = self.ctx
         W, me = ctx.get_num_ranks(), ctx.get_rank()
-        ks = ctx.zeros((W * self.S, self.Hkv * self.D), dtype=torch.float32)
-        vs = ctx.zeros((W * self.S, self.Hkv * self.D), dtype=torch.float32)
-        ctx.ccl.all_gather(ks, ctx.as_symmetric(k.float().reshape(self.S, -1).contiguous()))
-        ctx.ccl.all_gather(vs, ctx.as_symmetric(v.float().reshape(self.S, -1).contiguous()))
+        if "_cpu_bufs" not in self.__dict__:          # heap buffers of this path, allocated once (collective)
+            f32, cols = torch.float32, self.Hkv * self.D
+            self._cpu_bufs = (ctx.zeros((self.S, cols), dtype=f32), ctx.zeros((self.S, cols), dtype=f32),
+                              ctx.zeros((W * self.S, cols), dtype=f32), ctx.zeros((W * self.S, cols), dtype=f32))
+        k_loc, v_loc, ks, vs = self._cpu_bufs
+        k_loc.copy_(k.reshape(self.S, -1))
+        v_loc.copy_(v.reshape(self.S, -1))
+        ctx.ccl.all_gather(ks, k_loc)
+        ctx.ccl.all_gather(vs, v_loc)
         q_pos = k_pos = None
         if self.layout == "zigzag":
             q_pos = zigzag_positions(me, W, self.S)
