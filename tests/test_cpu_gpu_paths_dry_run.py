@@ -220,3 +220,34 @@ def test_gpu_paths_of_collectives_fused_ops_and_layers_world2():
 
 def test_gpu_paths_world1():
     run_ranks(_dry_run, 1)
+
+
+def _groups_dry_run(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.parallel import ParallelLayout
+
+    ctx = iris.iris(1 << 26)
+    rec = _pretend_gpu(ctx)
+    layout = ParallelLayout({"tp": 2, "dp": 2}).build_groups()
+    bases = [int(b) for b in ctx.heap.bases_host()]
+    inp, out = ctx.zeros((32, 256), dtype=torch.bfloat16), ctx.zeros((32, 256), dtype=torch.bfloat16)
+    for name in ("tp", "dp"):
+        members = layout.ranks(name)
+        ctx.ccl.all_reduce(out, inp, group=layout.group(name))
+        op, d = rec.ccl[-1]
+        # inside a group ranks are renumbered, only the members' heaps are listed, in group order, and the
+        # multicast window (which spans all ranks) is not used
+        assert op == 2 and d.ctx.world == 2 and d.ctx.rank == members.index(rank)
+        assert [d.ctx.bases[i] for i in range(2)] == [bases[m] for m in members]
+        assert d.ctx.mc_base == 0 and d.use_mc == 0 and d.variant in (2, 3)            # no push / NVLS inside groups
+    # each group has its own sync block, distinct from the one of the whole job
+    ctx.ccl.all_reduce(out, inp)
+    blocks = {rec.ccl[-3][1].sync_block, rec.ccl[-2][1].sync_block, rec.ccl[-1][1].sync_block}
+    assert len(blocks) == 3 and rec.ccl[-1][1].ctx.world == world
+    dist.barrier()
+
+
+def test_gpu_paths_of_group_collectives_world4():
+    run_ranks(_groups_dry_run, 4)
