@@ -396,7 +396,20 @@ class Iris:
         return int(res.item()) == 0
 
     def close(self) -> None:
+        """Unmap and free this rank's heap and its mappings of the peers' heaps. Heap tensors must not be
+        used afterwards; call it on every rank (peers may still be reading until the barrier before it)."""
         self.heap.close()
+
+    def __enter__(self) -> "Iris":
+        return self
+
+    def __exit__(self, exc_type, exc, tb) -> bool:
+        # leave together when the block ended normally; after an exception only release local resources,
+        # because the other ranks may never reach a barrier
+        if exc_type is None:
+            self.barrier()
+        self.close()
+        return False
 
 
 def iris(heap_size: int = 1 << 30, allocator_type: str = "torch") -> Iris:

@@ -564,3 +564,23 @@ def test_launch_paths_write_records(tmp_path, monkeypatch):
                    if "metadata.json" in files and not os.path.relpath(root, tmp_path).startswith("build"))
     assert found == ["ccl/all_gather/rank_1/64x128_bfloat16_w4", "ccl/all_reduce_nvls/rank_1/64x128_bfloat16_w4",
                      "ccl/reduce_scatter_rows/rank_1/64x128_bfloat16_w4", "ops/matmul_all_reduce/rank_1/256x512_bfloat16_w4"]
+
+
+def _context_manager(rank, world):
+    import iris_b200 as iris
+
+    with iris.iris(1 << 22) as ctx:
+        t = ctx.full((8,), float(rank))
+        got = ctx.rma.load(t, from_rank=(rank + 1) % world)
+        assert torch.all(got == (rank + 1) % world)
+        del t
+    # the heap is gone; a new context can be created by the same processes
+    with iris.iris(1 << 22) as ctx2:
+        assert ctx2.get_num_ranks() == world and torch.all(ctx2.zeros(4) == 0)
+    with pytest.raises(RuntimeError, match="boom"):
+        with iris.iris(1 << 22):
+            raise RuntimeError("boom")            # no barrier on the way out: nothing hangs
+
+
+def test_context_manager_releases_the_heap():
+    run_ranks(_context_manager, 2)
