@@ -164,9 +164,13 @@ class CCL:
         if hit is not None:
             return self._replay(hit, async_op, group)
         config = config or Config()
-        out, inp = _as_2d(output_tensor), _as_2d(input_tensor)
-        self._check(out, inp)
         W, me = self._world(group)
+        if output_tensor.dim() == 1 and input_tensor.dim() == 1 and output_tensor.numel() == W * input_tensor.numel():
+            # vectors: rank r's n elements land at [r n, (r+1) n), i.e. row r of a (W, n) matrix
+            out, inp = output_tensor.view(W, -1), input_tensor.view(1, -1)
+        else:
+            out, inp = _as_2d(output_tensor), _as_2d(input_tensor)
+        self._check(out, inp)
         M, N = inp.shape
         if tuple(out.shape) != (W * M, N):
             raise ValueError(f"all_gather: output must be {(W * M, N)}, got {tuple(out.shape)}")
@@ -342,8 +346,10 @@ class CCL:
         M, N = inp.shape
         rows = config.reduce_scatter_rows
         if rows:
-            if M % W or tuple(out.shape) != (M // W, N):
-                raise ValueError(f"reduce_scatter(rows): output must be {(M // W, N)}")
+            if M % W:
+                raise ValueError(f"reduce_scatter(rows): {M} rows do not split over {W} ranks")
+            if tuple(out.shape) != (M // W, N):
+                raise ValueError(f"reduce_scatter(rows): output must be {(M // W, N)}, got {tuple(out.shape)}")
         elif out.shape != inp.shape:
             raise ValueError("reduce_scatter: output must have the input's shape (only owned tiles are written)")
         if self.ctx.is_cpu:

@@ -221,6 +221,15 @@ def _ccl_cpu(rank, world):
         ctx.ccl.all_reduce(out, torch.zeros(M, N))
     with pytest.raises(ValueError):
         ctx.ccl.all_gather(out, inp)
+    # vectors: gathered end to end; 1-D tensors of other collectives are one row
+    vec, cat = ctx.full((5,), float(rank)), ctx.zeros(5 * world)
+    ctx.ccl.all_gather(cat, vec)
+    assert cat.tolist() == [float(r) for r in range(world) for _ in range(5)]
+    vsum = ctx.zeros(5)
+    ctx.ccl.all_reduce(vsum, vec)
+    assert torch.all(vsum == sum(range(world)))
+    with pytest.raises(ValueError, match="do not split"):
+        ctx.ccl.reduce_scatter(ctx.zeros((3, 4)), ctx.zeros((2 * world + 1, 4)), config=Config(reduce_scatter_rows=True))
     # fused ops fall back to GEMM + collective on this backend, same results
     A = torch.randn(4, 8)
     B = torch.randn(8, 5)
