@@ -121,6 +121,7 @@ class FlashDecodeLayer:
         B = q.shape[0]
         if B > self.max_batch:
             raise ValueError(f"batch {B} exceeds max_batch {self.max_batch}")
+        self._validate(q, k_cache, v_cache, global_kv_lens, block_table, out)
         kv_lens = global_kv_lens[ctx.get_rank()].contiguous()
         page = k_cache.shape[1]
         if ctx.is_cpu:
@@ -149,6 +150,37 @@ class FlashDecodeLayer:
         return (out, lse) if return_lse else out
 
     __call__ = forward
+
+    def _validate(self, q, k_cache, v_cache, global_kv_lens, block_table, out) -> None:
+        """Shapes and dtypes before anything is launched: the kernel indexes the caches through the
+        block table and trusts the sizes it is given. In debug mode (``IRIS_DEBUG=1``) the VALUES are
+        checked too (block numbers inside the cache, lengths inside the table), at the cost of a
+        device synchronisation."""
+        W, B = self.ctx.get_num_ranks(), q.shape[0]
+        if tuple(q.shape) != (B, self.Hq, self.D):
+            raise ValueError(f"q must be [batch, {self.Hq}, {self.D}], got {tuple(q.shape)}")
+        if k_cache.dim() != 4 or tuple(k_cache.shape[2:]) != (self.Hkv, self.D) or k_cache.shape != v_cache.shape:
+            raise ValueError(f"k_cache and v_cache must both be [blocks, page, {self.Hkv}, {self.D}], got "
+                             f"{tuple(k_cache.shape)} and {tuple(v_cache.shape)}")
+        if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+            raise TypeError("q and the caches must have one dtype")
+        if block_table.dim() != 2 or block_table.shape[0] != B or block_table.dtype != torch.int32:
+            raise ValueError(f"block_table must be int32 [batch = {B}, blocks], got {block_table.dtype} {tuple(block_table.shape)}")
+        if global_kv_lens.dim() != 2 or tuple(global_kv_lens.shape) != (W, B) or global_kv_lens.dtype != torch.int32:
+            raise ValueError(f"global_kv_lens must be int32 [ranks = {W}, batch = {B}], got {global_kv_lens.dtype} "
+                             f"{tuple(global_kv_lens.shape)}")
+        if out is not None and (tuple(out.shape) != (B, self.Hq, self.D) or out.dtype != q.dtype or not out.is_contiguous()):
+            raise ValueError("out must be a contiguous tensor of q's shape and dtype")
+        if self.ctx.debug_checks:
+            blocks, page = k_cache.shape[0], k_cache.shape[1]
+            mine = global_kv_lens[self.ctx.get_rank()]
+            if int(mine.min()) < 0 or int(mine.max()) > block_table.shape[1] * page:
+                raise ValueError(f"a sequence length lies outside [0, {block_table.shape[1] * page}] (blocks per sequence x page)")
+            used = -(-mine.to(torch.int64) // page)
+            cols = torch.arange(block_table.shape[1], device=block_table.device)[None, :]
+            live = block_table[cols < used[:, None].to(block_table.device)]
+            if live.numel() and (int(live.min()) < 0 or int(live.max()) >= blocks):
+                raise ValueError(f"block_table names a block outside the cache of {blocks} blocks")
 
     def _forward_cpu(self, q, k_cache, v_cache, kv_lens, block_table):
         """CPU backend: same exchange layout through the shared-memory heap, math in PyTorch."""

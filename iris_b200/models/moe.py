@@ -128,6 +128,8 @@ class MoELayer:
         logits = router_logits.float().contiguous()
         if out is None:
             out = torch.empty_like(x)
+        elif out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous() or out.device != x.device:
+            raise ValueError("out must be a contiguous tensor of x's shape, dtype and device")
         d = IrisMoeDesc()
         d.ctx = ctx.ctx_struct()
         d.T, d.K, d.E, d.El, d.D, d.F, d.capacity, d.comm_ctas = T, self.K, self.E, self.El, self.D, self.F, self.capacity, self.comm_sms

@@ -108,6 +108,8 @@ class RingAttention:
             raise ValueError("ring attention takes contiguous tensors")
         if out is None:
             out = torch.empty_like(q)
+        elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous() or out.device != q.device:
+            raise ValueError("out must be a contiguous tensor of q's shape, dtype and device")
         lse = torch.empty((self.S, self.Hq), dtype=torch.float32, device=q.device) if return_lse else None
         d = IrisRingAttnDesc()
         d.ctx = ctx.ctx_struct()

@@ -280,6 +280,29 @@ def _decode_cpu(rank, world):
     dist.all_gather(os_, o)
     dist.all_gather(ls_, lse)
     assert torch.allclose(out, merge_partials(torch.stack(os_), torch.stack(ls_)), atol=1e-5)
+    # arguments are checked before anything could be launched with them
+    good = dict(q=q, k_cache=kc, v_cache=vc, global_kv_lens=torch.stack(all_lens), block_table=table)
+    for bad in (dict(q=torch.randn(B, Hq - 1, D)), dict(k_cache=torch.randn(8, page, Hkv + 1, D)), dict(v_cache=torch.randn(7, page, Hkv, D)),
+                dict(block_table=table.long()), dict(block_table=table[:1]), dict(global_kv_lens=torch.stack(all_lens).long()),
+                dict(global_kv_lens=torch.stack(all_lens)[:, :1]), dict(q=torch.randn(3, Hq, D))):
+        with pytest.raises(ValueError):
+            layer(**{**good, **bad})
+    with pytest.raises(TypeError):
+        layer(**{**good, "k_cache": kc.double(), "v_cache": vc.double()})
+    with pytest.raises(ValueError):
+        layer(**good, out=torch.empty(B, Hq, D + 1))
+    # value checks belong to debug mode
+    ctx.debug_checks = True
+    try:
+        layer(**good)
+        with pytest.raises(ValueError, match="outside the cache"):
+            layer(**{**good, "block_table": table + 5})
+        long = torch.stack(all_lens).clone()
+        long[rank, 0] = 4 * page + 1
+        with pytest.raises(ValueError, match="sequence length"):
+            layer(**{**good, "global_kv_lens": long})
+    finally:
+        ctx.debug_checks = False
     ctx.barrier()
 
 
