@@ -171,6 +171,17 @@ def _local_matmul(A, B, bias=None, bias_dim=1):
     return out
 
 
+def _check_operands(name, A, B, bias=None, bias_len=None):
+    """Shapes the kernels take on trust: the inner dimensions must agree and a bias has one entry per
+    output row (the reference's convention, iris/ops/all_gather_matmul.py:146-150)."""
+    if A.dim() != 2 or B.dim() != 2:
+        raise ValueError(f"{name}: A and B must be matrices, got {tuple(A.shape)} and {tuple(B.shape)}")
+    if A.dtype != B.dtype:
+        raise TypeError(f"{name}: A is {A.dtype}, B is {B.dtype}")
+    if bias is not None and bias_len is not None and (bias.dim() != 1 or bias.numel() != bias_len):
+        raise ValueError(f"{name}: bias must have {bias_len} entries (one per output row), got {tuple(bias.shape)}")
+
+
 def _bias32(bias):
     return bias.float().contiguous() if bias is not None else None
 
@@ -230,6 +241,11 @@ def all_gather_matmul(shmem, output_tensor, A_sharded, B, bias=None, async_op=Fa
     """
     config = config or _DEFAULT_CONFIG
     W = shmem.num_ranks
+    if shard_dim not in (0, 1):
+        raise ValueError("shard_dim is 0 (rows sharded) or 1 (K sharded)")
+    _check_operands("all_gather_matmul", A_sharded, B, bias, A_sharded.shape[0] * (W if shard_dim == 0 else 1))
+    if B.shape[0] != A_sharded.shape[1] * (W if shard_dim == 1 else 1):
+        raise ValueError(f"all_gather_matmul: gathered A has K = {A_sharded.shape[1] * (W if shard_dim == 1 else 1)}, B has {B.shape[0]} rows")
     key = tuple(A_sharded.shape) + tuple(B.shape) + (shard_dim,)
     ws = workspace
     if ws is None or not (ws.variant == "unfused" or ws.matches("all_gather_matmul", key, A_sharded.dtype, W, "fused")):
@@ -285,6 +301,9 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
     M, K = A.shape
     N = B.shape[1]
     want = (M, N * W) if scatter_cols else (M * W, N)
+    _check_operands("matmul_all_gather", A, B, bias, M)
+    if B.shape[0] != K:
+        raise ValueError(f"matmul_all_gather: A has K = {K}, B has {B.shape[0]} rows")
     if tuple(output_tensor.shape) != want:
         raise ValueError(f"matmul_all_gather: output must be {want}, got {tuple(output_tensor.shape)}")
     key = tuple(A.shape) + tuple(B.shape) + (scatter_cols,)
@@ -332,6 +351,9 @@ def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, con
     W = shmem.num_ranks
     M, K = A.shape
     N = B.shape[1]
+    _check_operands("matmul_all_reduce", A, B, bias, M)
+    if B.shape[0] != K:
+        raise ValueError(f"matmul_all_reduce: A has K = {K}, B has {B.shape[0]} rows")
     if tuple(output_tensor.shape) != (M, N):
         raise ValueError(f"matmul_all_reduce: output must be {(M, N)}, got {tuple(output_tensor.shape)}")
     key = tuple(A.shape) + tuple(B.shape)
@@ -393,6 +415,11 @@ def matmul_reduce_scatter(shmem, output_tensor, A, B, bias=None, async_op=False,
     M, K = A.shape
     N = B.shape[1]
     want = (M // W, N) if scatter_rows else (M, N)
+    _check_operands("matmul_reduce_scatter", A, B, bias, M)
+    if B.shape[0] != K:
+        raise ValueError(f"matmul_reduce_scatter: A has K = {K}, B has {B.shape[0]} rows")
+    if scatter_rows and M % W:
+        raise ValueError(f"matmul_reduce_scatter: {M} rows do not split over {W} ranks")
     if tuple(output_tensor.shape) != want:
         raise ValueError(f"matmul_reduce_scatter: output must be {want}, got {tuple(output_tensor.shape)}")
     key = tuple(A.shape) + tuple(B.shape) + (scatter_rows,)

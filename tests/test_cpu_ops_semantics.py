@@ -119,6 +119,23 @@ def _ops(rank, world):
     with pytest.raises(ValueError):
         ctx.ops.matmul_reduce_scatter(torch.zeros(Mr // world, N), Aq, Bq)
 
+    # ---- operands the kernels would take on trust are checked first
+    for call in (lambda: ctx.ops.matmul_all_reduce(summed, Ap, torch.zeros(7, N)),            # inner dimensions differ
+                 lambda: ctx.ops.matmul_all_gather(rows, Ar, torch.zeros(8, N)),
+                 lambda: ctx.ops.matmul_reduce_scatter(mine, Aq, torch.zeros(5, N), scatter_rows=True),
+                 lambda: ctx.ops.all_gather_matmul(out, A, torch.zeros(Kl * world + 1, N)),
+                 lambda: ctx.ops.all_gather_matmul(out, A, B, shard_dim=2),
+                 lambda: ctx.ops.matmul_all_reduce(summed, Ap, Bp, bias=torch.zeros(M + 1)),      # one bias entry per output row
+                 lambda: ctx.ops.all_gather_matmul(out_m, Am, B, shard_dim=0, bias=torch.zeros(Ml)),
+                 lambda: ctx.ops.matmul_all_reduce(summed, Ap[0], Bp)):                           # a vector is not a matrix
+        with pytest.raises(ValueError):
+            call()
+    with pytest.raises(TypeError):
+        ctx.ops.matmul_all_reduce(summed, Ap, Bp.double())
+    if world > 1:
+        with pytest.raises(ValueError, match="do not split"):
+            ctx.ops.matmul_reduce_scatter(torch.zeros(1, N), torch.zeros(world + 1, 6), Bq, scatter_rows=True)
+
     # ---- repeated calls, with or without the returned workspace, leave the heap where it is
     def one_round():
         ctx.ops.all_gather_matmul(out, A, B)
