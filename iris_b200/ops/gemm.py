@@ -61,6 +61,10 @@ def matmul(A: torch.Tensor, B: torch.Tensor, bias: torch.Tensor | None = None, o
         raise ValueError(f"shape mismatch {tuple(A.shape)} @ {tuple(B.shape)}")
     if out is None:
         out = torch.empty((M, N), dtype=A.dtype, device=A.device)
+    elif tuple(out.shape) != (M, N) or out.device != A.device:
+        raise ValueError(f"out must be {(M, N)} on {A.device}, got {tuple(out.shape)} on {out.device}")
+    if bias is not None and (bias_dim not in (0, 1) or bias.dim() != 1 or bias.numel() != (M if bias_dim == 0 else N)):
+        raise ValueError(f"bias must have {M if bias_dim == 0 else N} entries for bias_dim={bias_dim}, got {tuple(bias.shape)}")
     desc = _lib.IrisGemmDesc()
     desc.op = _lib.GEMM_LOCAL
     desc.M, desc.N, desc.K = M, N, K
