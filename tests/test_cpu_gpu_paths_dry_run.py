@@ -165,6 +165,26 @@ def _dry_run(rank, world):
     wsf = ctx.ops.matmul_all_reduce(ctx.zeros((8, 8)), torch.zeros(8, 4), torch.zeros(4, 8))
     assert wsf.variant == "unfused" and len(rec.gemm) == n_before
 
+    # ---- the local GEMM entry point
+    import pytest
+
+    from iris_b200.ops.gemm import matmul
+
+    col_bias, row_bias = torch.ones(N, dtype=dt), torch.ones(Ml, dtype=dt)
+    Cl = matmul(A, B, bias=col_bias)
+    g = rec.gemm[-1]
+    assert g.op == _lib.GEMM_LOCAL and (g.M, g.N, g.K) == (Ml, N, K) and g.C == Cl.data_ptr() and g.bias_col and not g.bias_row
+    matmul(A, B, bias=row_bias, bias_dim=0, out=Cl, two_sm=True)
+    assert rec.gemm[-1].bias_row and not rec.gemm[-1].bias_col and rec.gemm[-1].two_sm == 2 and rec.gemm[-1].C == Cl.data_ptr()
+    n_before = len(rec.gemm)
+    for bad in (lambda: matmul(A, torch.zeros(K + 1, N, dtype=dt)), lambda: matmul(A, B, out=torch.zeros(Ml, N + 1, dtype=dt)),
+                lambda: matmul(A, B, bias=row_bias), lambda: matmul(A, B, bias=col_bias, bias_dim=0)):
+        with pytest.raises(ValueError):
+            bad()
+    with pytest.raises(TypeError):
+        matmul(A.float(), B.float())
+    assert len(rec.gemm) == n_before                      # nothing was launched with the rejected arguments
+
     # ---- the layers of iris_b200.parallel on the same path
     up = ColumnParallelLinear(ctx, K, N, dtype=dt, seed=1)
     down = RowParallelLinear(ctx, N, K, dtype=dt, seed=2, bias=True)
