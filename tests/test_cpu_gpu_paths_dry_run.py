@@ -33,6 +33,21 @@ class _Recorder:
             return 0
 
         self.iris_ccl_launch, self.iris_gemm_launch = ccl_launch, gemm_launch
+        self.models = []
+
+        def model_entry(name, module, desc_name):
+            def call(d, stream):
+                import importlib
+
+                desc_t = getattr(importlib.import_module(module), desc_name)
+                self.models.append((name, desc_t.from_buffer_copy(d._obj)))
+                return 0
+
+            return call
+
+        self.iris_flash_decode = model_entry("decode", "iris_b200.models.flash_decode", "IrisDecodeDesc")
+        self.iris_moe_forward = model_entry("moe", "iris_b200.models.moe", "IrisMoeDesc")
+        self.iris_ring_attention = model_entry("ring", "iris_b200.models.ring_attention", "IrisRingAttnDesc")
 
 
 def _pretend_gpu(ctx):
@@ -45,6 +60,7 @@ def _pretend_gpu(ctx):
     torch.cuda.synchronize = lambda *a, **k: None
     ctx.is_cpu = False
     ctx.device_barrier = lambda group=None: None          # a kernel launch of its own on a GPU; not part of this walk
+    ctx.get_cu_count = lambda: 148
     return rec
 
 
@@ -271,3 +287,82 @@ def _groups_dry_run(rank, world):
 
 def test_gpu_paths_of_group_collectives_world4():
     run_ranks(_groups_dry_run, 4)
+
+
+def _models_dry_run(rank, world):
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200 import _lib
+    from iris_b200.models import FlashDecodeLayer, MoELayer, RingAttention
+
+    ctx = iris.iris(1 << 28)
+    rec = _pretend_gpu(ctx)
+    dt, W = torch.bfloat16, world
+
+    # ---- flash decode: sizes, pointers and the split count reach the descriptor
+    Hq, Hkv, D, page, B, blocks = 16, 2, 128, 64, 3, 5
+    dec = FlashDecodeLayer(ctx, Hq, Hkv, D, max_batch=4)
+    q = torch.zeros(B, Hq, D, dtype=dt)
+    kc, vc = torch.zeros(B * blocks, page, Hkv, D, dtype=dt), torch.zeros(B * blocks, page, Hkv, D, dtype=dt)
+    table = torch.arange(B * blocks, dtype=torch.int32).view(B, blocks)
+    lens = torch.full((W, B), 300, dtype=torch.int32)
+    out, lse = dec(q, kc, vc, lens, table, return_lse=True)
+    name, d = rec.models[-1]
+    assert name == "decode" and (d.B, d.Bmax, d.Hq, d.Hkv, d.D, d.page, d.max_blocks) == (B, 4, Hq, Hkv, D, page, blocks)
+    assert d.q == q.data_ptr() and d.k_cache == kc.data_ptr() and d.block_table == table.data_ptr() and d.out == out.data_ptr()
+    assert d.out_lse == lse.data_ptr() and d.gathered == dec.gathered.data_ptr() and d.flags == dec.signal_flags.data_ptr()
+    assert d.exchange == 1 and d.num_blocks == B * blocks and 1 <= d.splits <= 2 and d.ctx.world == W      # 320 positions: two splits at most
+    assert out.shape == (B, Hq, D) and lse.shape == (B, Hq) and d.dtype == _lib.DTYPE_CODE[dt]
+    FlashDecodeLayer(ctx, Hq, Hkv, D, max_batch=4, use_tma=False)(q, kc, vc, lens, table)
+    assert rec.models[-1][1].num_blocks == 0                                      # the cp.async tile fill was asked for
+    n_before = len(rec.models)
+    import pytest
+
+    with pytest.raises(ValueError):
+        dec(q, kc, vc, lens, table.long())
+    with pytest.raises(ValueError):
+        dec(q.transpose(0, 1).contiguous().transpose(0, 1), kc, vc, lens, table)     # not contiguous
+    assert len(rec.models) == n_before
+
+    # ---- ring attention
+    S, Hq2, Hkv2 = 256, 4, 2
+    ring = RingAttention(ctx, S, Hq2, Hkv2, layout="zigzag")
+    qa, ka, va = torch.zeros(S, Hq2, 128, dtype=dt), torch.zeros(S, Hkv2, 128, dtype=dt), torch.zeros(S, Hkv2, 128, dtype=dt)
+    o = ring(qa, ka, va, causal=True)
+    name, d = rec.models[-1]
+    assert name == "ring" and (d.S, d.Hq, d.Hkv, d.D, d.causal) == (S, Hq2, Hkv2, 128, 1) and d.options & 2 and not d.options & 1
+    assert d.q == qa.data_ptr() and d.out == o.data_ptr() and d.kv_buf == ring.kv_buf.data_ptr() and d.flags == ring.flags.data_ptr()
+    RingAttention(ctx, S, Hq2, Hkv2, use_tcgen05=False)(qa, ka, va)
+    assert rec.models[-1][1].options == 1 and rec.models[-1][1].causal == 0
+    for bad in (lambda: ring(qa[:128], ka[:128], va[:128]), lambda: ring(qa, ka, va, out=torch.zeros(S, Hq2, 64, dtype=dt)),
+                lambda: ring(qa, ka, va[:, :1])):
+        with pytest.raises(ValueError):
+            bad()
+    with pytest.raises(TypeError):
+        ring(qa.float(), ka.float(), va.float())
+
+    # ---- MoE
+    hidden, ffn, E, topk, T = 256, 128, 2 * W, 2, 64
+    El = E // W
+    moe = MoELayer(ctx, hidden, ffn, E, topk, T, w_gate=torch.zeros(El, hidden, ffn, dtype=dt), w_up=torch.zeros(El, hidden, ffn, dtype=dt),
+                   w_down=torch.zeros(El, ffn, hidden, dtype=dt))
+    x, logits = torch.zeros(T, hidden, dtype=dt), torch.zeros(T, E)
+    y = moe(x, logits)
+    name, d = rec.models[-1]
+    assert name == "moe" and (d.T, d.K, d.E, d.El, d.D, d.F) == (T, topk, E, El, hidden, ffn) and d.weights_kmajor == 1
+    assert d.x == x.data_ptr() and d.out == y.data_ptr() and d.inbox == moe.inbox.data_ptr() and d.comb == moe.comb.data_ptr()
+    assert d.w13 == moe.w13.data_ptr() and d.w2 == moe.w2.data_ptr() and d.capacity == moe.capacity and d.ctx.world == W
+    # the fused gate / up weight is K-major: [local experts, 2 ffn, hidden]; the down weight [local experts, hidden, ffn]
+    assert tuple(moe.w13.shape) == (El, 2 * ffn, hidden) and tuple(moe.w2.shape) == (El, hidden, ffn)
+    for bad in (lambda: moe(torch.zeros(T + 1, hidden, dtype=dt), torch.zeros(T + 1, E)), lambda: moe(x, torch.zeros(T, E + 1)),
+                lambda: moe(x, logits, out=torch.zeros(T, hidden + 1, dtype=dt))):
+        with pytest.raises(ValueError):
+            bad()
+    with pytest.raises(TypeError):
+        moe(x.float(), logits)
+    dist.barrier()
+
+
+def test_gpu_paths_of_the_model_layers_world2():
+    run_ranks(_models_dry_run, 2)
