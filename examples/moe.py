@@ -7,7 +7,6 @@ unsharded fp32 computation.
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 examples/moe.py
 """
 import torch
-import torch.distributed as dist
 
 from _common import finish, init
 

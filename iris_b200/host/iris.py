@@ -21,7 +21,7 @@ from .. import _lib
 from . import distributed as D
 from . import tensors as T
 from .heap import KIND_CPU, SymmetricHeap, _rt
-from .logging import DEBUG, ERROR, INFO, WARNING, log_rank, logger
+from .logging import DEBUG, ERROR, INFO, WARNING, log_rank
 from .platform import get_cu_count, get_device_id_for_rank, is_simulation_env
 
 SYNC_BLOCK_BYTES = (8 + _lib.MAX_RANKS) * 4

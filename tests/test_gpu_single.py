@@ -4,7 +4,6 @@ One process, world size 1: the heap, the device context, the collectives and the
 their real kernels (peer loops degenerate to the local rank), so every CUDA path is exercised on
 one B200. Multi-rank behaviour is covered by test_gpu_multi.py.
 """
-import math
 import os
 
 import pytest
