@@ -200,6 +200,37 @@ def _worker(rank, world, port, script, names, overrides, skips, n_warmup, n_repe
     dist.destroy_process_group()
 
 
+def _collect(q, procs, grace_s: float = 15.0) -> list:
+    """Results of rank 0, or an error as soon as a worker has died: a rank that fails (an oracle that
+    does not hold, an exception in a benchmark body) leaves the others waiting in a barrier, so they get
+    ``grace_s`` seconds to finish on their own and are then terminated (the processes started here, by
+    handle), instead of the launcher waiting for a result that will never come."""
+    import queue as _queue
+    import time
+
+    failed_at = None
+    while True:
+        try:
+            return q.get(timeout=0.5)
+        except _queue.Empty:
+            pass
+        codes = [p.exitcode for p in procs]
+        if any(c not in (None, 0) for c in codes) and failed_at is None:
+            failed_at = time.time()
+        if all(c is not None for c in codes) or (failed_at is not None and time.time() - failed_at > grace_s):
+            try:
+                return q.get(timeout=0.5)          # rank 0 may have delivered just before exiting
+            except _queue.Empty:
+                pass
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
+            for p in procs:
+                p.join(10)
+            bad = {i: p.exitcode for i, p in enumerate(procs) if p.exitcode != 0}
+            raise RuntimeError(f"benchmark workers failed (rank: exit code) {bad}; see their output above")
+
+
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(description="iris_b200 benchmark runner", allow_abbrev=False)
     p.add_argument("--benchmark_filter", default=None, help="regular expression on benchmark names")
@@ -263,7 +294,7 @@ def main(argv: list | None = None) -> list:
                                                          args.n_repeat, args.heap_size, q)) for r in range(n)]
             for p in procs:
                 p.start()
-            results += q.get()
+            results += _collect(q, procs)
             for p in procs:
                 p.join()
         rank0 = True

@@ -176,3 +176,31 @@ def test_stage_and_sweep_benchmarks_on_the_cpu_backend(tmp_path, script, args, e
         assert float(fused["nccl_baseline_us"]) > 0
         assert float(fused["speedup_vs_baseline"]) == pytest.approx(float(fused["nccl_baseline_us"]) / (float(fused["gpu_time_ms"]) * 1e3), rel=1e-6)
         assert all(r["nccl_baseline_us"] == "" for r in timed if r["stage"] != "fused")
+
+
+def test_runner_reports_a_failing_rank_instead_of_waiting(tmp_path):
+    """A benchmark whose check fails on one rank: the launcher ends with an error naming the rank,
+    within seconds, and leaves no worker behind."""
+    script = tmp_path / "bench_failing.py"
+    script.write_text(f'''import sys
+sys.path.insert(0, {ROOT!r})
+import iris_b200.bench as bench
+
+
+@bench.register
+@bench.axis("num_ranks", [2])
+def sometimes_wrong(state, ctx):
+    assert ctx.get_rank() != 1, "result mismatch on this rank"
+    state.exec(lambda: None)
+
+
+if __name__ == "__main__":
+    bench.main()
+''')
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    t0 = time.time()
+    proc = subprocess.run([sys.executable, str(script), "--n_warmup", "1", "--n_repeat", "1"], env=env, capture_output=True, text=True,
+                          timeout=240)
+    assert proc.returncode != 0
+    assert "benchmark workers failed" in proc.stderr and "result mismatch on this rank" in proc.stderr
+    assert time.time() - t0 < 120
