@@ -9,6 +9,7 @@ from __future__ import annotations
 import os
 import socket
 import sys
+import time
 import traceback
 
 import torch
@@ -61,12 +62,22 @@ def run_ranks(fn, world: int, args=(), backend: str = "gloo", timeout: float = 3
     procs = [ctx.Process(target=_entry, args=(r, world, port, backend, fn, args, errq, env)) for r in range(world)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout)
+    # Wait for all ranks, but not for ever for the peers of a rank that has failed: they are usually
+    # stuck in a barrier with it, so they get a short grace period and are then stopped.
+    deadline, failed_at, grace = time.time() + timeout, None, 20.0
+    while any(p.is_alive() for p in procs):
+        now = time.time()
+        if failed_at is None and any(p.exitcode not in (None, 0) for p in procs):
+            failed_at = now
+        if now > deadline or (failed_at is not None and now - failed_at > grace and not expect_failures):
+            break
+        time.sleep(0.05)
     hung = [p for p in procs if p.is_alive()]
     for p in hung:
         p.kill()  # the exact child processes started above
         p.join()
+    if failed_at is not None and not expect_failures:
+        hung = []           # their peer failed first: the failure below is the one to report
     errors = []
     while not errq.empty():
         errors.append(errq.get())
@@ -76,6 +87,8 @@ def run_ranks(fn, world: int, args=(), backend: str = "gloo", timeout: float = 3
     if hung:
         raise AssertionError(f"{len(hung)} rank(s) still running after {timeout}s")
     if errors:
+        # a rank whose collective broke because a peer went away is a consequence: report the cause first
+        errors.sort(key=lambda e: any(w in e[1] for w in ("Connection closed", "Connection reset", "ProcessGroup", "NCCL error")))
         rank, tb = errors[0]
         raise AssertionError(f"rank {rank} failed:\n{tb}")
     if any(c != 0 for c in codes):
