@@ -15,8 +15,9 @@ MODULES = [
     "iris_b200.models.flash_decode", "iris_b200.models.moe", "iris_b200.models.ring_attention", "iris_b200.models.tp_mlp", "iris_b200.bench._core",
     "iris_b200.bench._runner", "iris_b200.jit", "iris_b200.drivers",
     "iris_b200.parallel.layout", "iris_b200.parallel.tensor_parallel", "iris_b200.parallel.data_parallel",
-    "iris_b200.parallel.sequence_parallel", "iris_b200.parallel.expert_parallel", "iris_b200.utils.validation",
-    "iris_b200.utils.records", "iris_b200.utils.roofline",
+    "iris_b200.parallel.sequence_parallel", "iris_b200.parallel.expert_parallel", "iris_b200.parallel.p2p", "iris_b200.host.watchdog",
+    "iris_b200.utils.validation",
+    "iris_b200.utils.records", "iris_b200.utils.roofline", "iris_b200.utils.timing",
 ]
 
 

@@ -384,3 +384,61 @@ def test_dispatch_tables_and_ragged_slices():
     loc = ragged_slices(cs, odd.expt_map[0])
     assert loc.slice_sizes.tolist() == [4, 2, 3] and loc.slice_offs.tolist() == [0, 5, 14, 17]
     assert ragged_slices(cs, torch.full((6,), -1, dtype=torch.int32)).n_slices == 0
+
+
+# ----------------------------------------------------------------------------- point to point
+def _p2p(rank, world):
+    import iris_b200 as iris
+    from iris_b200.parallel import P2PChannel
+
+    ctx = iris.iris(1 << 24)
+    ch = P2PChannel(ctx, (4, 3), dtype=torch.float32, depth=2, timeout_ms=3000)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+
+    def msg(src, n):
+        return torch.full((4, 3), 100.0 * src + n)
+
+    # a pipeline: every rank sends five messages to its successor and takes five from its predecessor;
+    # with two slots the sender has to wait for acknowledgements, and messages arrive in order
+    for n in range(1, 6):
+        assert ch.send(msg(rank, n), nxt) == n
+        got = ch.recv(prv)
+        assert torch.equal(got, msg(prv, n)), (n, got[0, 0])
+    # receive into a buffer of the caller; availability can be asked without waiting
+    ch.send(msg(rank, 6), nxt)
+    ctx.barrier()
+    assert ch.pending(prv)
+    buf = torch.empty(4, 3)
+    assert ch.recv(prv, out=buf) is buf and torch.equal(buf, msg(prv, 6))
+    assert not ch.pending(prv)
+    ctx.barrier()
+    # nobody sends: the wait is bounded
+    quick = P2PChannel(ctx, (2,), depth=1, timeout_ms=200)
+    with pytest.raises(TimeoutError, match="has not reached"):
+        quick.recv(prv)
+    ctx.barrier()
+    # one slot and a receiver that does not take the message: the second send gives up, the first stays intact
+    quick.send(torch.tensor([1.0, 2.0]), nxt)
+    with pytest.raises(TimeoutError, match="has not taken"):
+        quick.send(torch.tensor([3.0, 4.0]), nxt)
+    ctx.barrier()
+    assert torch.equal(quick.recv(prv), torch.tensor([1.0, 2.0]))
+    ctx.barrier()
+    quick.send(torch.tensor([3.0, 4.0]), nxt)                    # acknowledged now: goes through
+    assert torch.equal(quick.recv(prv), torch.tensor([3.0, 4.0]))
+    for bad in (lambda: ch.send(torch.zeros(4, 4), nxt), lambda: ch.send(torch.zeros(4, 3, dtype=torch.float64), nxt),
+                lambda: ch.send(msg(0, 0), rank), lambda: ch.recv(rank), lambda: ch.recv(world)):
+        with pytest.raises(ValueError):
+            bad()
+    with pytest.raises(ValueError):
+        P2PChannel(ctx, (1,), depth=0)
+    ctx.check()
+    ctx.barrier()
+
+
+def test_point_to_point_channel_world2():
+    run_ranks(_p2p, 2)
+
+
+def test_point_to_point_channel_world3():
+    run_ranks(_p2p, 3)

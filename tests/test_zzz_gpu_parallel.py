@@ -117,7 +117,7 @@ def _multi(rank, world):
 
     import iris_b200 as iris
     from iris_b200.models import reference_attention
-    from iris_b200.parallel import GradientBuckets, UlyssesExchange, shard_sequence
+    from iris_b200.parallel import GradientBuckets, P2PChannel, UlyssesExchange, shard_sequence
 
     ctx = iris.iris(1 << 30)
     dev = ctx.get_device()
@@ -150,6 +150,13 @@ def _multi(rank, world):
     o = ex.to_sequence(reference_attention(*heads, causal=True).to(torch.bfloat16))
     want = reference_attention(q, k, v, causal=True).to(torch.bfloat16)[rank * (S // world):(rank + 1) * (S // world)]
     assert _rel(o.cpu(), want) < 2e-2
+    # point-to-point ring: more messages than slots, so acknowledgements are exercised too
+    ch = P2PChannel(ctx, (8, 16), dtype=torch.float32, depth=2, timeout_ms=3000)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    for n in range(1, 6):
+        ch.send(torch.full((8, 16), 100.0 * rank + n, device=dev), nxt)
+        got = ch.recv(prv)
+        assert torch.all(got == 100.0 * prv + n), (n, float(got[0, 0]))
     ctx.check()
     ctx.barrier()
 
