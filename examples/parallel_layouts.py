@@ -1,6 +1,6 @@
 #!/usr/bin/env python3
 """The parallelism package end to end: a layout, tensor-parallel linears, a Ulysses attention
-exchange, and data-parallel gradient buckets. No counterpart in the reference, which stops at the
+exchange, data-parallel gradient buckets and a point-to-point hand-over between neighbours. No counterpart in the reference, which stops at the
 collectives and leaves their composition to the caller.
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 examples/parallel_layouts.py
@@ -63,6 +63,15 @@ if __name__ == "__main__":
     for p, gl in zip(model.parameters(), local):
         mine = ctx.as_symmetric(gl.reshape(1, -1).contiguous())
         assert validate_all_reduce(mine, p.grad.reshape(1, -1) * W, ctx, atol=1e-4)
+    # ---- pipeline-style hand-over: every rank passes micro-batches to its successor through mailboxes
+    if W > 1:
+        from iris_b200.parallel import P2PChannel
+
+        ch = P2PChannel(ctx, (32, 64), dtype=torch.float32, depth=2)
+        for step in range(4):
+            ch.send(torch.full((32, 64), float(10 * r + step), device=dev), (r + 1) % W)
+            got = ch.recv((r - 1) % W)
+            assert torch.all(got == 10 * ((r - 1) % W) + step)
     ctx.check()
     ctx.info(f"parallel layouts validated ({len(buckets.buckets)} gradient buckets, MLP error {err:.3g} of {ref.abs().max().item():.3g})")
     dist.barrier()
