@@ -1,7 +1,8 @@
 #!/usr/bin/env python3
 """The parallelism package end to end: a layout, tensor-parallel linears, a Ulysses attention
-exchange, data-parallel gradient buckets and a point-to-point hand-over between neighbours. No counterpart in the reference, which stops at the
-collectives and leaves their composition to the caller.
+exchange, data-parallel gradient buckets and a point-to-point hand-over between neighbours. No
+counterpart in the reference, which stops at the collectives and leaves their composition to the
+caller.
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 examples/parallel_layouts.py
 
