@@ -78,6 +78,22 @@ def _rt():
         "iris_fdmesh_recv": (i32, [vp, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(u64), cp, i32]),
         "iris_fdmesh_destroy": (None, [vp]),
         "iris_close_fd": (None, [i32]),
+        "iris_rt_install_fake_driver": (i32, [i32]),
+        "iris_rt_driver_version": (i32, [C.POINTER(i32)]),
+        "iris_rt_error_string": (i32, [i32, cp, i32]),
+        "iris_rt_malloc": (i32, [i32, u64, C.POINTER(u64)]),
+        "iris_rt_free": (i32, [u64]),
+        "iris_rt_mem_granularity": (i32, [i32, i32, i32, C.POINTER(u64)]),
+        "iris_rt_mem_create": (i32, [u64, i32, i32, C.POINTER(u64)]),
+        "iris_rt_mem_release": (i32, [u64]),
+        "iris_rt_mem_address_reserve": (i32, [u64, u64, u64, C.POINTER(u64)]),
+        "iris_rt_mem_address_free": (i32, [u64, u64]),
+        "iris_rt_mem_map": (i32, [u64, u64, u64, u64]),
+        "iris_rt_mem_unmap": (i32, [u64, u64]),
+        "iris_rt_mem_set_access": (i32, [u64, u64, C.POINTER(i32), i32]),
+        "iris_rt_mem_export_fd": (i32, [u64, C.POINTER(i32)]),
+        "iris_rt_mem_import_fd": (i32, [i32, C.POINTER(u64)]),
+        "iris_rt_mem_retain_handle": (i32, [u64, C.POINTER(u64)]),
         "iris_cpu_rma": (i32, [i32, i32, i32, u64, u64, u64, C.c_double, i64, i64, u64, i32, i32, i32, C.POINTER(u64)]),
         "iris_cpu_wait_flag": (i32, [u64, C.c_int32, u64]),
         "iris_cpu_barrier": (i32, [i32, i32, C.POINTER(u64), u64, u64, u64]),

@@ -110,6 +110,147 @@ def close_ipc_handle(ptr: int) -> None:
     _rt().iris_rt_ipc_close_handle(int(ptr))
 
 
+# ---------------------------------------------------------------------------------------------------
+# Driver-level memory primitives under the reference's names (iris/host/platform/hip.py:264-846). The
+# symmetric heap does not use them; they are for code that builds its own mappings.
+class DriverError(RuntimeError):
+    """A driver call failed; ``code`` is the CUresult (1000 = no driver on this machine)."""
+
+    def __init__(self, what: str, code: int):
+        self.code = code
+        buf = C.create_string_buffer(128)
+        if code != 1000:
+            _rt().iris_rt_error_string(code, buf, 128)
+        detail = buf.value.decode() or "no CUDA driver on this machine"
+        super().__init__(f"{what} failed: {detail}")
+
+
+def gpu_try(rc: int, what: str = "driver call") -> None:
+    """Raise ``DriverError`` for a non-zero return code of the native runtime (0 passes)."""
+    if rc != 0:
+        raise DriverError(what, -rc)
+
+
+def install_fake_driver(devices: int = 0) -> int:
+    """Tests only: route the native runtime to a host-memory stand-in for the driver's memory API with
+    ``devices`` devices (0 switches back to the real driver). Touches no GPU."""
+    return _rt().iris_rt_install_fake_driver(int(devices))
+
+
+def get_driver_version() -> int:
+    v = C.c_int(0)
+    gpu_try(_rt().iris_rt_driver_version(C.byref(v)), "cuDriverGetVersion")
+    return v.value
+
+
+def get_rocm_version():
+    """The reference returns ``(major, minor)`` of ROCm; here of the CUDA driver API."""
+    v = get_driver_version()
+    return v // 1000, (v % 1000) // 10
+
+
+def get_ipc_handle_size() -> int:
+    return 64
+
+
+def hip_malloc(size: int, device_id: int | None = None) -> int:
+    """Plain device allocation; returns the address. (``malloc_fine_grained`` is the same call: device
+    memory of an NVLink domain is coherent for peers at system scope, there is no separate pool.)"""
+    ptr = C.c_uint64(0)
+    gpu_try(_rt().iris_rt_malloc(max(get_device_id(), 0) if device_id is None else device_id, int(size), C.byref(ptr)), "cuMemAlloc")
+    return ptr.value
+
+
+malloc_fine_grained = hip_malloc
+
+
+def hip_free(ptr: int) -> None:
+    gpu_try(_rt().iris_rt_free(int(ptr)), "cuMemFree")
+
+
+def get_allocation_granularity(device_id: int = 0, recommended: bool = True, fabric: bool = False) -> int:
+    g = C.c_uint64(0)
+    gpu_try(_rt().iris_rt_mem_granularity(device_id, int(fabric), int(recommended), C.byref(g)), "cuMemGetAllocationGranularity")
+    return g.value
+
+
+def mem_create(size: int, device_id: int = 0, fabric: bool = False) -> int:
+    """Physical allocation of ``size`` bytes (a multiple of the granularity); returns its handle."""
+    h = C.c_uint64(0)
+    gpu_try(_rt().iris_rt_mem_create(int(size), device_id, int(fabric), C.byref(h)), "cuMemCreate")
+    return h.value
+
+
+def mem_release(handle: int) -> None:
+    gpu_try(_rt().iris_rt_mem_release(int(handle)), "cuMemRelease")
+
+
+def mem_address_reserve(size: int, alignment: int = 0, hint: int = 0) -> int:
+    p = C.c_uint64(0)
+    gpu_try(_rt().iris_rt_mem_address_reserve(int(size), int(alignment), int(hint), C.byref(p)), "cuMemAddressReserve")
+    return p.value
+
+
+def mem_address_free(ptr: int, size: int) -> None:
+    gpu_try(_rt().iris_rt_mem_address_free(int(ptr), int(size)), "cuMemAddressFree")
+
+
+def mem_map(ptr: int, size: int, offset: int, handle: int) -> None:
+    gpu_try(_rt().iris_rt_mem_map(int(ptr), int(size), int(offset), int(handle)), "cuMemMap")
+
+
+def mem_unmap(ptr: int, size: int) -> None:
+    gpu_try(_rt().iris_rt_mem_unmap(int(ptr), int(size)), "cuMemUnmap")
+
+
+def mem_set_access(ptr: int, size: int, device_ids) -> None:
+    """Read-write access to the mapped range for the listed devices (an int or a sequence)."""
+    ids = [device_ids] if isinstance(device_ids, int) else list(device_ids)
+    arr = (C.c_int * len(ids))(*ids)
+    gpu_try(_rt().iris_rt_mem_set_access(int(ptr), int(size), arr, len(ids)), "cuMemSetAccess")
+
+
+def mem_export_to_shareable_handle(handle: int) -> int:
+    """POSIX file descriptor of an allocation (pass it to another process over the fd mesh)."""
+    fd = C.c_int(-1)
+    gpu_try(_rt().iris_rt_mem_export_fd(int(handle), C.byref(fd)), "cuMemExportToShareableHandle")
+    return fd.value
+
+
+def mem_import_from_shareable_handle(fd: int) -> int:
+    h = C.c_uint64(0)
+    gpu_try(_rt().iris_rt_mem_import_fd(int(fd), C.byref(h)), "cuMemImportFromShareableHandle")
+    return h.value
+
+
+def export_dmabuf_handle(ptr: int, size: int = 0) -> int:
+    """File descriptor for the allocation mapped at ``ptr`` (the reference exports a DMA-BUF of an
+    address range; here the range must be a VMM mapping, whose allocation handle is exported)."""
+    h = C.c_uint64(0)
+    gpu_try(_rt().iris_rt_mem_retain_handle(int(ptr), C.byref(h)), "cuMemRetainAllocationHandle")
+    try:
+        return mem_export_to_shareable_handle(h.value)
+    finally:
+        mem_release(h.value)
+
+
+def import_dmabuf_handle(fd: int, size: int, device_ids=0):
+    """Map the allocation behind ``fd`` into this process; returns ``(handle, address)``."""
+    h = mem_import_from_shareable_handle(fd)
+    ptr = mem_address_reserve(size)
+    mem_map(ptr, size, 0, h)
+    mem_set_access(ptr, size, device_ids)
+    return h, ptr
+
+
+def destroy_external_memory(handle: int, ptr: int = 0, size: int = 0) -> None:
+    """Undo ``import_dmabuf_handle``: unmap and free the range (when given), release the handle."""
+    if ptr:
+        mem_unmap(ptr, size)
+        mem_address_free(ptr, size)
+    mem_release(handle)
+
+
 def get_device_id_for_rank(rank: int, num_gpus: int | None = None) -> int:
     """Device a rank should use: ``LOCAL_RANK`` when a launcher set it, else ``rank % num_gpus``."""
     if num_gpus is None:

@@ -6,6 +6,7 @@ parts that need no device are checked here; the device queries themselves are in
 """
 import ctypes
 import logging
+import os
 
 import numpy as np
 import pytest
@@ -157,3 +158,96 @@ def test_distributed_helpers_and_broadcast_world2():
 
 def test_distributed_helpers_and_broadcast_world3():
     run_ranks(_helpers, 3, timeout=120.0)
+
+
+@pytest.fixture
+def fake_driver():
+    from iris_b200 import hip
+
+    assert hip.install_fake_driver(2) == 2
+    try:
+        yield hip
+    finally:
+        hip.install_fake_driver(0)
+
+
+def test_vmm_primitives_against_a_host_memory_driver(fake_driver):
+    """Reserve, create, map, grant access, write; export the allocation as a file descriptor, import
+    it, map it a second time and see the same bytes; take everything down again. The sequence of the
+    reference's tests/unittests/test_hip_vmem_primitives.py and test_vmem_peer_exchange.py, on a
+    stand-in for the driver that keeps allocations in memfd files (no GPU)."""
+    import iris_b200 as iris
+
+    hip = fake_driver
+    assert hip.count_devices() == 2 and hip.get_cu_count(0) == 148 and hip.get_arch_string(1) == "sm_100"
+    assert hip.get_driver_version() >= 12000 and hip.get_rocm_version() == (12, 9) and hip.get_ipc_handle_size() == 64
+    assert hip.can_access_peer(0, 1) and not hip.can_access_peer(1, 1)
+    gran = hip.get_allocation_granularity(0)
+    assert gran == hip.get_allocation_granularity(1, recommended=False) and gran % 4096 == 0
+    size = 2 * gran
+    va = hip.mem_address_reserve(2 * size)                      # room for two allocations side by side
+    h1, h2 = hip.mem_create(size, 0), hip.mem_create(size, 1)
+    hip.mem_map(va, size, 0, h1)
+    hip.mem_map(va + size, size, 0, h2)
+    hip.mem_set_access(va, 2 * size, [0, 1])                    # cumulative access over both mappings
+    t = iris.tensor_from_ptr(va, 2 * size // 4, torch.int32, "cpu")
+    t.copy_(torch.arange(t.numel(), dtype=torch.int32))
+    assert hip.get_address_range(va + size + 64) == (va + size, size)
+    # a second mapping of the first allocation, through an exported descriptor
+    fd = hip.mem_export_to_shareable_handle(h1)
+    assert fd > 2
+    h1b, va2 = hip.import_dmabuf_handle(fd, size, device_ids=[0])
+    os.close(fd)
+    peer = iris.tensor_from_ptr(va2, size // 4, torch.int32, "cpu")
+    assert torch.equal(peer, torch.arange(size // 4, dtype=torch.int32))
+    peer[7] = -5                                                # one allocation, two windows
+    assert int(t[7]) == -5
+    # the descriptor of whatever is mapped at an address
+    fd2 = hip.export_dmabuf_handle(va + size + 128)
+    h2b = hip.mem_import_from_shareable_handle(fd2)
+    os.close(fd2)
+    va3 = hip.mem_address_reserve(size)
+    hip.mem_map(va3, size, 0, h2b)
+    hip.mem_set_access(va3, size, 1)
+    assert int(iris.tensor_from_ptr(va3, 4, torch.int32, "cpu")[3]) == size // 4 + 3
+    # misuse is refused with the driver's error, nothing crashes
+    for bad in (lambda: hip.mem_create(size + 1, 0), lambda: hip.mem_create(size, 5), lambda: hip.mem_map(va, size, 0, h1),
+                lambda: hip.mem_set_access(va, size, [9]), lambda: hip.mem_address_free(va, 2 * size),      # still mapped
+                lambda: hip.mem_unmap(va + 4096, size), lambda: hip.mem_release(123456)):
+        with pytest.raises(hip.DriverError):
+            bad()
+    # orderly teardown; released allocations stay readable through live mappings until unmapped
+    hip.mem_release(h1)
+    assert int(t[7]) == -5
+    del t, peer
+    hip.destroy_external_memory(h1b, va2, size)
+    hip.destroy_external_memory(h2b, va3, size)
+    hip.mem_unmap(va, size)
+    hip.mem_unmap(va + size, size)
+    hip.mem_address_free(va, 2 * size)
+    hip.mem_release(h2)
+    with pytest.raises(RuntimeError):
+        hip.get_address_range(va)
+    # plain allocations
+    p = hip.hip_malloc(1 << 16, 0)
+    buf = iris.tensor_from_ptr(p, 1 << 16, torch.uint8, "cpu")
+    buf.fill_(3)
+    assert hip.get_address_range(p + 100)[0] == p and hip.malloc_fine_grained is hip.hip_malloc
+    del buf
+    hip.hip_free(p)
+    with pytest.raises(hip.DriverError):
+        hip.hip_free(p)
+
+
+def test_vmm_primitives_without_a_driver_raise():
+    from iris_b200 import hip
+
+    if hip.count_devices() == 0:
+        for call in (lambda: hip.mem_create(1 << 21), lambda: hip.mem_address_reserve(1 << 21), lambda: hip.hip_malloc(16),
+                     lambda: hip.get_allocation_granularity(), lambda: hip.get_driver_version()):
+            with pytest.raises(hip.DriverError) as ei:
+                call()
+            assert ei.value.code == 1000 and "no CUDA driver" in str(ei.value)
+    hip.gpu_try(0)
+    with pytest.raises(hip.DriverError):
+        hip.gpu_try(-1, "something")
