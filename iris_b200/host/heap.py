@@ -157,7 +157,15 @@ class SymmetricHeap:
         rt = _rt()
         allocator_type = os.environ.get("IRIS_ALLOCATOR", allocator_type)
         cuda = torch.cuda.is_available() and os.environ.get("IRIS_BACKEND", "") != "cpu"
-        if allocator_type == "cpu" or not cuda:
+        # Tests without a GPU: IRIS_FAKE_DRIVER_DEVICES=n routes the native runtime to a host-memory
+        # stand-in for the driver's memory API, so that the VMM path below (create, export, pass the
+        # descriptor, import, map) runs for real on shared host memory. Heap only: no kernels.
+        fake = int(os.environ.get("IRIS_FAKE_DRIVER_DEVICES", "0") or 0) if not cuda else 0
+        if fake and allocator_type in ("torch", "vmem"):
+            rt.iris_rt_install_fake_driver(fake)
+            self.device_id = device_id = cur_rank % fake
+            kinds = [KIND_VMM]
+        elif allocator_type == "cpu" or not cuda:
             kinds = [KIND_CPU]
         elif allocator_type == "ipc":
             kinds = [KIND_IPC]
@@ -168,7 +176,7 @@ class SymmetricHeap:
         else:
             raise ValueError(f"unknown allocator_type {allocator_type!r} (torch, vmem, ipc, cpu)")
         self.allocator_type = allocator_type
-        self.device = torch.device("cpu") if kinds == [KIND_CPU] else torch.device("cuda", device_id)
+        self.device = torch.device("cpu") if (kinds == [KIND_CPU] or fake) else torch.device("cuda", device_id)
 
         last_error = None
         for kind in kinds:
@@ -203,7 +211,7 @@ class SymmetricHeap:
     def _create(self, kind: int) -> None:
         rt = _rt()
         err = C.create_string_buffer(_ERRLEN)
-        if kind != KIND_CPU:
+        if kind != KIND_CPU and self.device.type == "cuda":
             torch.cuda.set_device(self.device_id)
             torch.zeros(1, device=f"cuda:{self.device_id}")  # make sure the primary context exists
         h = rt.iris_heap_create(self.heap_size, self.device_id, self.cur_rank, self.num_ranks, kind, 0, err, _ERRLEN)

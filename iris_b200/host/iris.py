@@ -20,7 +20,7 @@ import torch.distributed as dist
 from .. import _lib
 from . import distributed as D
 from . import tensors as T
-from .heap import KIND_CPU, SymmetricHeap, _rt
+from .heap import SymmetricHeap, _rt
 from .logging import DEBUG, ERROR, INFO, WARNING, log_rank
 from .platform import get_cu_count, get_device_id_for_rank, is_simulation_env
 
@@ -60,7 +60,8 @@ class Iris:
         self.heap_size = heap_size
         if is_simulation_env():
             self._dump_heap_bases()
-        self.is_cpu = self.heap.kind == KIND_CPU
+        # host backend: the shared-memory heap, or (tests) the VMM heap on the host-memory driver stand-in
+        self.is_cpu = self.heap.device.type == "cpu"
         self.timeout_ms = int(os.environ.get("IRIS_TIMEOUT_MS", "5000"))
         # IRIS_DEBUG=1: fresh heap memory is poisoned, every host barrier compares the ranks'
         # allocation offsets, and every synchronous collective ends with check()

@@ -251,3 +251,78 @@ def test_vmm_primitives_without_a_driver_raise():
     hip.gpu_try(0)
     with pytest.raises(hip.DriverError):
         hip.gpu_try(-1, "something")
+
+
+def _vmm_heap(rank, world):
+    """The symmetric heap's VMM backend end to end on the host-memory driver: every rank creates its
+    region, exports it as a file descriptor over the UNIX-socket mesh, imports and maps the others'."""
+    import torch.distributed as dist
+
+    from iris_b200.host.heap import KIND_VMM, SymmetricHeap
+
+    heap = SymmetricHeap(8 << 20, 0, rank, world, allocator_type="vmem", enable_multicast=False)
+    assert heap.kind == KIND_VMM and heap.device.type == "cpu" and heap.mc_base == 0
+    bases = [int(b) for b in heap.bases_host()]
+    assert bases[rank] == heap.base and len(set(bases)) == world            # one mapping per rank's region, in this process
+    a = heap.allocate(1000, torch.float32)
+    b = heap.allocate(7, torch.int64)
+    assert heap.is_symmetric(a) and heap.offset_of(a) == 0 and heap.offset_of(b) % 1024 == 0
+    a.fill_(float(rank + 1))
+    b.copy_(torch.arange(7) + 100 * rank)
+    dist.barrier()
+    for r in range(world):                                                 # every peer's copy, through this rank's mapping of it
+        assert torch.all(heap.peer_view(a, r) == r + 1)
+        assert torch.equal(heap.peer_view(b, r), torch.arange(7) + 100 * r)
+    dist.barrier()
+    heap.peer_view(a, (rank + 1) % world)[0] = -1.0                       # a remote write lands in the peer's memory
+    dist.barrier()
+    assert float(a[0]) == -1.0 and float(a[1]) == rank + 1
+    with pytest.raises(MemoryError):
+        heap.allocate(9 << 20, torch.uint8)
+    mark = heap.get_offset()
+    heap.allocate(4096, torch.uint8)
+    heap.set_offset(mark)
+    assert heap.get_offset() == mark
+    dist.barrier()
+    del a, b
+    heap.close()
+
+
+def test_symmetric_heap_vmm_backend_on_the_host_memory_driver_world2():
+    run_ranks(_vmm_heap, 2, env={"IRIS_FAKE_DRIVER_DEVICES": "2"}, timeout=120.0)
+
+
+def test_symmetric_heap_vmm_backend_on_the_host_memory_driver_world3():
+    run_ranks(_vmm_heap, 3, env={"IRIS_FAKE_DRIVER_DEVICES": "2"}, timeout=120.0)
+
+
+def _context_on_vmm_heap(rank, world):
+    """A whole context on top of the VMM heap of the host-memory driver: one-sided operations,
+    barriers and collectives work on it exactly as on the shared-memory heap."""
+    import iris_b200 as iris
+    from iris_b200.host.heap import KIND_VMM
+
+    ctx = iris.iris(1 << 24)
+    assert ctx.heap.kind == KIND_VMM and ctx.is_cpu
+    peer = (rank + 1) % world
+    buf = ctx.zeros(256, dtype=torch.float32)
+    cnt = ctx.zeros(1, dtype=torch.int32)
+    ctx.barrier()
+    ctx.rma.store(buf, float(rank + 1), to_rank=peer)
+    for r in range(world):
+        ctx.rma.atomic_add(cnt, 1, to_rank=r)
+    ctx.device_barrier()
+    assert torch.all(buf == (rank - 1) % world + 1) and int(cnt.item()) == world
+    inp, out = ctx.full((8, 4 * world), float(rank + 1)), ctx.zeros((8, 4 * world))
+    ctx.ccl.all_reduce(out, inp)
+    assert torch.all(out == sum(range(1, world + 1)))
+    ag = ctx.zeros((8 * world, 4 * world))
+    ctx.ccl.all_gather(ag, inp)
+    assert all(torch.all(ag[8 * r:8 * (r + 1)] == r + 1) for r in range(world))
+    ctx.verify_symmetry()
+    ctx.check()
+    ctx.barrier()
+
+
+def test_context_on_the_vmm_heap_of_the_host_memory_driver():
+    run_ranks(_context_on_vmm_heap, 3, env={"IRIS_FAKE_DRIVER_DEVICES": "4"}, timeout=120.0)
