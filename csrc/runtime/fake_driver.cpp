@@ -158,7 +158,19 @@ CUresult f_access(CUdeviceptr p, size_t size, const CUmemAccessDesc* desc, size_
   }
   return mprotect((void*)p, size, PROT_READ | PROT_WRITE) == 0 ? CUDA_SUCCESS : CUDA_ERROR_INVALID_VALUE;
 }
+// A fabric handle of the stand-in: 64 bytes holding a tag and the allocation's number. It can only be
+// imported by the process that exported it, which is all a single-process driver test needs.
+constexpr char kFabricTag[8] = {'i', 'r', 'i', 's', 'f', 'a', 'b', 0};
+
 CUresult f_export(void* out, CUmemGenericAllocationHandle h, CUmemAllocationHandleType type, unsigned long long) {
+  if (type == CU_MEM_HANDLE_TYPE_FABRIC) {
+    std::lock_guard<std::mutex> l(g_mu);
+    if (!g_allocs.count(h)) return CUDA_ERROR_INVALID_VALUE;
+    memset(out, 0, 64);
+    memcpy(out, kFabricTag, 8);
+    memcpy((char*)out + 8, &h, sizeof(h));
+    return CUDA_SUCCESS;
+  }
   if (type != CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) return CUDA_ERROR_NOT_SUPPORTED;
   std::lock_guard<std::mutex> l(g_mu);
   auto it = g_allocs.find(h);
@@ -169,6 +181,19 @@ CUresult f_export(void* out, CUmemGenericAllocationHandle h, CUmemAllocationHand
   return CUDA_SUCCESS;
 }
 CUresult f_import(CUmemGenericAllocationHandle* h, void* os_handle, CUmemAllocationHandleType type) {
+  if (type == CU_MEM_HANDLE_TYPE_FABRIC) {
+    if (memcmp(os_handle, kFabricTag, 8) != 0) return CUDA_ERROR_INVALID_VALUE;
+    CUmemGenericAllocationHandle src = 0;
+    memcpy(&src, (const char*)os_handle + 8, sizeof(src));
+    std::lock_guard<std::mutex> l(g_mu);
+    auto it = g_allocs.find(src);
+    if (it == g_allocs.end()) return CUDA_ERROR_INVALID_VALUE;
+    int fd = dup(it->second.fd);
+    if (fd < 0) return CUDA_ERROR_OUT_OF_MEMORY;
+    *h = g_next++;
+    g_allocs[*h] = Alloc{fd, it->second.size};
+    return CUDA_SUCCESS;
+  }
   if (type != CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) return CUDA_ERROR_NOT_SUPPORTED;
   int fd = dup((int)(uintptr_t)os_handle);
   if (fd < 0) return CUDA_ERROR_INVALID_VALUE;

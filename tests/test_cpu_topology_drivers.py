@@ -293,3 +293,41 @@ def test_discovery_over_gloo_ranks():
     from helpers import run_ranks
 
     run_ranks(_discover, 3)
+
+
+def test_fabric_driver_through_the_native_runtime_on_the_host_memory_driver():
+    """The same life cycle as above, but with nothing faked in Python: the native runtime creates
+    the exportable allocation, produces the 64-byte handle, imports it and maps it, on the host-memory
+    stand-in for the driver (whose fabric handles are valid inside the exporting process)."""
+    import torch
+
+    import iris_b200 as iris
+    from iris_b200 import hip
+    from iris_b200.drivers import DriverNotSupported, NvidiaFabricDriver
+
+    if hip.count_devices() == 0:
+        with pytest.raises(DriverNotSupported):
+            NvidiaFabricDriver().initialize(0)                  # no driver on this machine
+    assert hip.install_fake_driver(2) == 2
+    try:
+        drv = NvidiaFabricDriver()
+        drv.initialize(1)
+        alloc = drv.allocate_exportable(3 << 20)
+        assert alloc.size >= 3 << 20 and alloc.size % hip.get_allocation_granularity(1) == 0      # rounded up to the granularity
+        handle = drv.export_handle(alloc)
+        assert len(handle) == 64 and any(handle)
+        mapping = drv.import_and_map(handle, alloc.size)
+        assert mapping.va not in (0, alloc.va)
+        mine = iris.tensor_from_ptr(alloc.va, 1024, torch.int32, "cpu")
+        theirs = iris.tensor_from_ptr(mapping.va, 1024, torch.int32, "cpu")
+        mine.copy_(torch.arange(1024, dtype=torch.int32))
+        assert torch.equal(theirs, mine)                        # two mappings of one allocation
+        theirs[5] = 99
+        assert int(mine[5]) == 99
+        with pytest.raises(RuntimeError):
+            drv.import_and_map(bytes(64), alloc.size)           # not a handle of this driver
+        del mine, theirs
+        drv.cleanup_import(mapping)
+        assert drv.close() == 0 and drv.cleanup_local(alloc) == 0
+    finally:
+        hip.install_fake_driver(0)
