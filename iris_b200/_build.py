@@ -102,10 +102,12 @@ def _link(objs: list[Path], out: Path, cuda: bool, verbose: bool) -> None:
         return
     if verbose:
         print(f"[iris_b200 build] link {out.name}", flush=True)
+    tmp = out.with_name(out.name + f".tmp{os.getpid()}")       # processes that have the library loaded keep their copy
     if cuda:
-        _run([_nvcc(), "-shared", "-o", str(out), *map(str, objs), "-cudart", "static", "-Xcompiler", "-fPIC"])
+        _run([_nvcc(), "-shared", "-o", str(tmp), *map(str, objs), "-cudart", "static", "-Xcompiler", "-fPIC"])
     else:
-        _run(["g++", "-shared", "-o", str(out), *map(str, objs), "-ldl", "-lpthread", "-lrt"])
+        _run(["g++", "-shared", "-o", str(tmp), *map(str, objs), "-ldl", "-lpthread", "-lrt"])
+    os.replace(tmp, out)
     _stamp(out, key)
 
 
