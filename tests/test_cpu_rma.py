@@ -76,6 +76,7 @@ def _ops(rank, world):
     ctx.rma.atomic_max(f, 9 + rank, to_rank=peer)
     ctx.barrier()
     assert torch.all(f == 9 + src)
+    ctx.barrier()                 # everybody has looked before anybody changes the cells again
     # the peer's cells now hold 9 + (its predecessor) = 9 + my rank: the swap goes through
     old = ctx.rma.atomic_cas(f, 9 + rank, 42, to_rank=peer)
     assert torch.all(old == 9 + rank)
