@@ -41,6 +41,14 @@ std::map<uint64_t, Alloc> g_allocs;       // handle -> backing file
 std::map<uint64_t, Range> g_ranges;       // reserved base -> size
 std::map<uint64_t, Mapping> g_maps;       // mapped address -> mapping
 std::map<uint64_t, size_t> g_plain;       // cuMemAlloc'd blocks
+int g_fail_after = 0;                     // > 0: the g_fail_after-th memory call from now fails (fault injection on the host)
+
+// True when this call is the one that was asked to fail.
+bool injected_failure() {
+  std::lock_guard<std::mutex> l(g_mu);
+  if (g_fail_after <= 0) return false;
+  return --g_fail_after == 0;
+}
 
 CUresult f_init(unsigned) { return CUDA_SUCCESS; }
 CUresult f_version(int* v) { *v = 12090; return CUDA_SUCCESS; }
@@ -84,6 +92,7 @@ CUresult f_errstr(CUresult r, const char** s) {
 CUresult f_granularity(size_t* g, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) { *g = kGranularity; return CUDA_SUCCESS; }
 
 CUresult f_create(CUmemGenericAllocationHandle* h, size_t size, const CUmemAllocationProp* prop, unsigned long long) {
+  if (injected_failure()) return CUDA_ERROR_OUT_OF_MEMORY;
   if (size == 0 || size % kGranularity) return CUDA_ERROR_INVALID_VALUE;
   if (prop->location.id < 0 || prop->location.id >= g_devices) return CUDA_ERROR_INVALID_DEVICE;
   int fd = memfd_create("iris-fake-vmm", MFD_CLOEXEC);
@@ -103,6 +112,7 @@ CUresult f_release(CUmemGenericAllocationHandle h) {
   return CUDA_SUCCESS;
 }
 CUresult f_reserve(CUdeviceptr* p, size_t size, size_t, CUdeviceptr, unsigned long long) {
+  if (injected_failure()) return CUDA_ERROR_OUT_OF_MEMORY;
   if (size == 0 || size % kGranularity) return CUDA_ERROR_INVALID_VALUE;
   void* a = mmap(nullptr, size, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE, -1, 0);
   if (a == MAP_FAILED) return CUDA_ERROR_OUT_OF_MEMORY;
@@ -127,6 +137,7 @@ bool inside_reservation(uint64_t p, size_t size) {
   return false;
 }
 CUresult f_map(CUdeviceptr p, size_t size, size_t offset, CUmemGenericAllocationHandle h, unsigned long long) {
+  if (injected_failure()) return CUDA_ERROR_OUT_OF_MEMORY;
   std::lock_guard<std::mutex> l(g_mu);
   auto it = g_allocs.find(h);
   if (it == g_allocs.end() || offset != 0 || size != it->second.size || !inside_reservation((uint64_t)p, size)) return CUDA_ERROR_INVALID_VALUE;
@@ -145,6 +156,7 @@ CUresult f_unmap(CUdeviceptr p, size_t size) {
   return CUDA_SUCCESS;
 }
 CUresult f_access(CUdeviceptr p, size_t size, const CUmemAccessDesc* desc, size_t count) {
+  if (injected_failure()) return CUDA_ERROR_OUT_OF_MEMORY;
   std::lock_guard<std::mutex> l(g_mu);
   if (count == 0) return CUDA_ERROR_INVALID_VALUE;
   for (size_t i = 0; i < count; ++i)
@@ -163,6 +175,7 @@ CUresult f_access(CUdeviceptr p, size_t size, const CUmemAccessDesc* desc, size_
 constexpr char kFabricTag[8] = {'i', 'r', 'i', 's', 'f', 'a', 'b', 0};
 
 CUresult f_export(void* out, CUmemGenericAllocationHandle h, CUmemAllocationHandleType type, unsigned long long) {
+  if (injected_failure()) return CUDA_ERROR_OUT_OF_MEMORY;
   if (type == CU_MEM_HANDLE_TYPE_FABRIC) {
     std::lock_guard<std::mutex> l(g_mu);
     if (!g_allocs.count(h)) return CUDA_ERROR_INVALID_VALUE;
@@ -181,6 +194,7 @@ CUresult f_export(void* out, CUmemGenericAllocationHandle h, CUmemAllocationHand
   return CUDA_SUCCESS;
 }
 CUresult f_import(CUmemGenericAllocationHandle* h, void* os_handle, CUmemAllocationHandleType type) {
+  if (injected_failure()) return CUDA_ERROR_OUT_OF_MEMORY;
   if (type == CU_MEM_HANDLE_TYPE_FABRIC) {
     if (memcmp(os_handle, kFabricTag, 8) != 0) return CUDA_ERROR_INVALID_VALUE;
     CUmemGenericAllocationHandle src = 0;
@@ -254,6 +268,19 @@ CUresult f_mc_gran(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity
 DriverApi g_fake_api;
 
 }  // namespace
+
+// Fault injection for tests: the k-th memory call from now (create, reserve, map, set access, export,
+// import) returns CUDA_ERROR_OUT_OF_MEMORY; 0 disarms.
+extern "C" void iris_rt_fake_fail_after(int k) {
+  std::lock_guard<std::mutex> l(g_mu);
+  g_fail_after = k;
+}
+
+// Allocations, address reservations and mappings currently alive in the stand-in (leak checks).
+extern "C" int iris_rt_fake_live_objects() {
+  std::lock_guard<std::mutex> l(g_mu);
+  return (int)(g_allocs.size() + g_ranges.size() + g_maps.size() + g_plain.size());
+}
 
 extern "C" int iris_rt_install_fake_driver(int devices) {
   if (devices <= 0) {

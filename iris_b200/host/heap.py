@@ -79,6 +79,8 @@ def _rt():
         "iris_fdmesh_destroy": (None, [vp]),
         "iris_close_fd": (None, [i32]),
         "iris_rt_install_fake_driver": (i32, [i32]),
+        "iris_rt_fake_fail_after": (None, [i32]),
+        "iris_rt_fake_live_objects": (i32, []),
         "iris_rt_driver_version": (i32, [C.POINTER(i32)]),
         "iris_rt_error_string": (i32, [i32, cp, i32]),
         "iris_rt_malloc": (i32, [i32, u64, C.POINTER(u64)]),

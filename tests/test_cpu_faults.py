@@ -222,3 +222,57 @@ def test_store_protocols_against_a_plain_dictionary_store():
     hb1.beat(now=100.0)
     assert hb0.last(1) == 100.0 and hb0.last(2) is None
     assert hb0.stale(5.0, now=103.0) == [2] and hb0.stale(5.0, now=106.0) == [1, 2] and hb0.stale(5.0, ranks=[1], now=103.0) == []
+
+
+def test_heap_creation_cleans_up_after_an_injected_driver_failure():
+    """Fault injection on the host: the driver stand-in is told to fail its k-th memory call. Whatever
+    step of the VMM heap's construction that hits (reserve, create, map, set access), the constructor
+    raises with the driver's message, nothing stays allocated, reserved or mapped, and the next
+    attempt succeeds. (No GPU: the stand-in keeps allocations in host memory.)"""
+    import torch.distributed as dist
+
+    from helpers import free_port
+    from iris_b200.host.heap import KIND_VMM, SymmetricHeap, _rt
+
+    import os
+
+    rt = _rt()
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(free_port()), "IRIS_FAKE_DRIVER_DEVICES": "2"})
+    created_pg = not dist.is_initialized()
+    if created_pg:
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        rt.iris_rt_install_fake_driver(2)
+        baseline = rt.iris_rt_fake_live_objects()
+        failed_steps = 0
+        for k in range(1, 8):
+            rt.iris_rt_fake_fail_after(k)
+            try:
+                heap = SymmetricHeap(4 << 20, 0, 0, 1, allocator_type="vmem", enable_multicast=False)
+            except RuntimeError as e:
+                failed_steps += 1
+                assert "out of memory" in str(e) or "fake driver error" in str(e) or "cuMem" in str(e), str(e)
+                assert rt.iris_rt_fake_live_objects() == baseline, f"step {k} leaked driver objects"
+                continue
+            finally:
+                rt.iris_rt_fake_fail_after(0)
+            # the failure point lies beyond the calls a construction makes: it went through
+            assert heap.kind == KIND_VMM
+            t = heap.allocate(16, torch.int32)
+            t.fill_(k)
+            assert int(t.sum()) == 16 * k
+            del t
+            heap.close()
+            assert rt.iris_rt_fake_live_objects() == baseline
+        assert failed_steps >= 3          # reserve, create, map and set-access were each hit at least once in total
+        # a clean run after all the failures
+        heap = SymmetricHeap(4 << 20, 0, 0, 1, allocator_type="vmem", enable_multicast=False)
+        assert rt.iris_rt_fake_live_objects() > baseline
+        heap.close()
+        assert rt.iris_rt_fake_live_objects() == baseline
+    finally:
+        rt.iris_rt_fake_fail_after(0)
+        rt.iris_rt_install_fake_driver(0)
+        os.environ.pop("IRIS_FAKE_DRIVER_DEVICES", None)
+        if created_pg:
+            dist.destroy_process_group()
