@@ -276,3 +276,33 @@ def test_heap_creation_cleans_up_after_an_injected_driver_failure():
         os.environ.pop("IRIS_FAKE_DRIVER_DEVICES", None)
         if created_pg:
             dist.destroy_process_group()
+
+
+def _peer_import_fails(rank, world):
+    from iris_b200.host.heap import KIND_VMM, SymmetricHeap, _rt
+
+    rt = _rt()
+    rt.iris_rt_install_fake_driver(2)
+    baseline = rt.iris_rt_fake_live_objects()
+    if rank == 1:
+        rt.iris_rt_fake_fail_after(6)            # its own region comes up (5 calls); importing the peer's handle fails
+    with pytest.raises(RuntimeError, match="could not create a symmetric heap on every rank"):
+        SymmetricHeap(4 << 20, 0, rank, world, allocator_type="vmem", enable_multicast=False)
+    rt.iris_rt_fake_fail_after(0)
+    # the rank whose calls all succeeded gives its region up as well: nobody keeps half a heap
+    assert rt.iris_rt_fake_live_objects() == baseline
+    heap = SymmetricHeap(4 << 20, 0, rank, world, allocator_type="vmem", enable_multicast=False)
+    assert heap.kind == KIND_VMM
+    t = heap.allocate(8, torch.int32)
+    t.fill_(rank + 1)
+    import torch.distributed as dist
+
+    dist.barrier()
+    assert torch.all(heap.peer_view(t, 1 - rank) == 2 - rank)
+    dist.barrier()
+    del t
+    heap.close()
+
+
+def test_a_failed_peer_import_fails_the_heap_on_every_rank():
+    run_ranks(_peer_import_fails, 2, env={"IRIS_FAKE_DRIVER_DEVICES": "2"}, timeout=120)
