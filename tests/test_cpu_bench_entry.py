@@ -69,23 +69,23 @@ def test_benchmark_runner_end_to_end_on_the_cpu_backend(tmp_path):
 
 
 def test_serving_shape_all_reduce_benchmark_on_the_cpu_backend(tmp_path):
-    """``(M tokens, 2880)`` bf16 all-reduce sweep: the library baseline is skipped without NCCL, the
+    """``(tokens, 2880)`` bf16 all-reduce sweep: the library baseline is skipped without NCCL, the
     variants check their result before timing."""
     out = tmp_path / "serving.csv"
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
     cmd = [sys.executable, os.path.join(ROOT, "benchmark", "ccl", "bench_all_reduce_serving_shapes.py"), "--axis_num_ranks=2",
-           "--axis_M=1,64", "--axis_variant=auto,two_shot,nvls", "--n_warmup", "1", "--n_repeat", "2", "--benchmark_format", "csv",
+           "--axis_tokens=1,64", "--axis_variant=auto,two_shot,nvls", "--n_warmup", "1", "--n_repeat", "2", "--benchmark_format", "csv",
            "--benchmark_out", str(out)]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0, proc.stderr[-3000:]
     import csv
 
     rows = list(csv.DictReader(out.open()))
-    assert len(rows) == 2 + 6
+    assert len(rows) == 2 * 3 * 2                             # impl x variant x tokens
     timed = [r for r in rows if r["skipped"] == "0"]
-    assert {(r["benchmark"], r["variant"]) for r in timed} == {("iris_all_reduce", "auto"), ("iris_all_reduce", "two_shot")}
+    assert {(r["impl"], r["variant"]) for r in timed} == {("iris", "auto"), ("iris", "two_shot")}
     assert all(float(r["gpu_time_ms"]) > 0 and float(r["bandwidth_gbps"]) > 0 for r in timed)
-    assert all(r["skipped"] == "1" for r in rows if r["benchmark"] == "nccl_all_reduce" or r["variant"] == "nvls")
+    assert all(r["skipped"] == "1" for r in rows if r["impl"] == "nccl" or r["variant"] == "nvls")
 
 
 def test_sweep_table_from_a_csv(tmp_path, capsys):
