@@ -236,11 +236,41 @@ def main() -> int:
     ws1 = ctx.ops.all_gather_matmul(H, X, W1, shard_dim=0)
     ws2 = ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True)
 
+    # The record is about the fused kernels: a plan that could not take the shape would silently run
+    # GEMM + collective instead, which is not what this benchmark claims to time.
+    if ws1.variant != "fused" or ws2.variant != "fused":
+        raise SystemExit(f"bench.py: the fused kernels were not selected (all_gather_matmul: {ws1.variant}, matmul_reduce_scatter: {ws2.variant})")
+
     def step():
         ctx.ops.all_gather_matmul(H, X, W1, shard_dim=0, workspace=ws1, async_op=True)
         ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True, workspace=ws2, async_op=True)
 
     flops_per_rank = 2.0 * M_TOTAL * K_DIM * F_LOCAL * 2
+    from iris_b200 import _lib as _iris_lib
+
+    def verify() -> dict:
+        """Outside every timed region: 16 rows of each rank's block against an fp32 product of the
+        gathered inputs (NCCL gathers the rows, torch multiplies in fp32). H is checked against
+        X_all @ W1; Y against the sum over ranks of H @ W2 taken from the bf16 H the kernel wrote."""
+        rows = torch.linspace(0, M_local - 1, 16, device=dev).long()
+        xs = X[rows].contiguous()
+        x_all = torch.empty(W * 16, K_DIM, device=dev, dtype=dtype)
+        dist.all_gather_into_tensor(x_all, xs)
+        grow = (torch.arange(W, device=dev)[:, None] * M_local + rows[None, :]).flatten()
+        h_ref = x_all.float() @ W1.float()
+        h_got = H[grow]
+        y_part = h_got.float() @ W2.float()
+        dist.all_reduce(y_part)
+        y_ref = y_part[rank * 16:(rank + 1) * 16]
+        y_got = Y[rows].float()
+        eh = float((h_got.float() - h_ref).abs().max() / h_ref.abs().max())
+        ey = float((y_got - y_ref).abs().max() / y_ref.abs().max())
+        t = torch.tensor([eh, ey], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        eh, ey = float(t[0]), float(t[1])
+        ok = eh < 1e-2 and ey < 1e-2          # bf16 outputs: one rounding of values up to the maximum
+        return {"rows_checked": W * 16, "h_max_err_over_max": round(eh, 6), "y_max_err_over_max": round(ey, 6), "ok": ok,
+                "oracle": "fp32 torch.matmul of NCCL-gathered rows"}
 
     # ---------------- device-timed region: exactly `steps` steps between barriers
     # (the clock sampler runs from the warm-up to the end of the end-to-end loop, all of it the
@@ -249,9 +279,14 @@ def main() -> int:
     for _ in range(max(args.warmup, 3)):
         step()
     ctx.barrier()
+    numerics = verify()
+    if not numerics["ok"]:
+        raise SystemExit(f"bench.py: the fused step does not match the fp32 oracle: {numerics}")
+    ctx.barrier()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dist.barrier()
     torch.cuda.synchronize()
+    launches_before = _iris_lib.launch_count()
     sampler.mark_timed(True)
     start.record()
     for _ in range(args.steps):
@@ -259,12 +294,48 @@ def main() -> int:
     end.record()
     torch.cuda.synchronize()
     sampler.mark_timed(False)
+    gpu_launches = _iris_lib.launch_count() - launches_before     # counted where the library launches its kernels
     dist.barrier()
     ms = start.elapsed_time(end) / args.steps
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     ctx.check()
+
+    # ---------------- the same step done unfused on the same box, in the same process, with the same
+    # steps and warm-up: NCCL all-gather, two cuBLAS GEMMs, NCCL reduce-scatter (what stock PyTorch
+    # tensor parallelism runs; at one GPU just the two cuBLAS GEMMs). Device-timed, max over ranks.
+    Xall = torch.empty(M_TOTAL, K_DIM, device=dev, dtype=dtype) if W > 1 else None
+    P = torch.empty(M_TOTAL, K_DIM, device=dev, dtype=dtype) if W > 1 else None
+    H2 = torch.empty(M_TOTAL, F_LOCAL, device=dev, dtype=dtype)
+    Y2 = torch.empty(M_local, K_DIM, device=dev, dtype=dtype)
+
+    def unfused_step():
+        if W > 1:
+            dist.all_gather_into_tensor(Xall, X)
+            torch.matmul(Xall, W1, out=H2)
+            torch.matmul(H2, W2, out=P)
+            dist.reduce_scatter_tensor(Y2, P)
+        else:
+            torch.matmul(X, W1, out=H2)
+            torch.matmul(H2, W2, out=Y2)
+
+    for _ in range(max(args.warmup, 3)):
+        unfused_step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    bs, be = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    bs.record()
+    for _ in range(args.steps):
+        unfused_step()
+    be.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([bs.elapsed_time(be) / args.steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    base_ms = float(t.item())
+    base_err = float((Y2.float() - Y.float()).abs().max() / Y.float().abs().max())    # both paths computed the same step
+    del Xall, P, H2, Y2
 
     # ---------------- end-to-end region: every step copies its input from pinned host memory,
     # runs the two ops through the public API and reads the step's scalar result back. The copy
@@ -355,7 +426,12 @@ def main() -> int:
         "e2e": {"value": round(e2e_value, 2), "unit": "TFLOPS", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": X_host.numel() * X_host.element_size(), "d2h_bytes_per_step": 4, "last_result": last,
                 "read": "every step's result is copied to pinned host memory and read by the host one step later"},
-        "gpu_launches": 2 * args.steps,      # one fused kernel per op per step in the device-timed region
+        "gpu_launches": gpu_launches,        # this library's kernels launched inside the device-timed region (one fused kernel per op per step)
+        "numerics": numerics,
+        "same_box_nccl_cublas": {"ms_per_step": round(base_ms, 4), "value": round(flops_per_rank * W / (base_ms * 1e-3) / 1e12, 2),
+                                 "unit": "TFLOPS", "steps": args.steps, "warmup": max(args.warmup, 3),
+                                 "what": "NCCL all_gather_into_tensor + 2 x torch.matmul (cuBLAS) + NCCL reduce_scatter_tensor, same shapes, same process",
+                                 "max_diff_vs_fused_over_max": round(base_err, 6)},
         "impl": "ours",
     }
     if rank == 0:

@@ -32,6 +32,7 @@
 #include "iris/ptx.cuh"
 #include "flash_decode_static.h"
 #include <stdio.h>
+#include <mutex>
 
 using namespace iris;
 
@@ -540,6 +541,8 @@ static __device__ __align__(256) unsigned char g_decode_static_scratch[IRIS_DECO
 
 constexpr int kStaticMaxDevices = 64;
 float* g_static_scratch_addr[kStaticMaxDevices] = {};
+bool g_static_attr_done[kStaticMaxDevices] = {};   // shared-memory limit raised on that device's function handles
+std::mutex g_static_setup_mutex;
 
 __global__ void __launch_bounds__(kD) decode_local_combine_kernel(const float* partial, void* out, int splits, int is_fp16) {
   const int it = blockIdx.x, d = threadIdx.x;
@@ -597,14 +600,30 @@ extern "C" int iris_flash_decode_static(const void* q, const void* k_cache, cons
     static_err(err, errlen, "iris_flash_decode_static: no current CUDA device");
     return -4;
   }
-  if (!g_static_scratch_addr[dev]) {
-    void* p = nullptr;
-    const cudaError_t e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
-    if (e != cudaSuccess || !p) {
-      static_err(err, errlen, "iris_flash_decode_static: cudaGetSymbolAddress failed for the scratch array");
-      return -5;
+  // Both tables below are per device: the array's address differs from GPU to GPU, and the raised
+  // shared-memory limit belongs to the function handle of the device that was current when it was
+  // set. One mutex covers the set-up, so that two host threads making a device's first call agree.
+  const int smem = kStages * 2 * kTileBytes > (int)((kWarps * 16 * kD + kWarps * 32) * sizeof(float))
+                       ? kStages * 2 * kTileBytes : (int)((kWarps * 16 * kD + kWarps * 32) * sizeof(float));
+  {
+    std::lock_guard<std::mutex> guard(g_static_setup_mutex);
+    if (!g_static_scratch_addr[dev]) {
+      void* p = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+      if (e != cudaSuccess || !p) {
+        static_err(err, errlen, "iris_flash_decode_static: cudaGetSymbolAddress failed for the scratch array");
+        return -5;
+      }
+      g_static_scratch_addr[dev] = (float*)p;
     }
-    g_static_scratch_addr[dev] = (float*)p;
+    if (!g_static_attr_done[dev]) {
+      if (cudaFuncSetAttribute(decode_splitk_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+          cudaFuncSetAttribute(decode_splitk_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        static_err(err, errlen, "iris_flash_decode_static: cannot raise the kernel's shared-memory limit");
+        return -20;
+      }
+      g_static_attr_done[dev] = true;
+    }
   }
   float* scratch = g_static_scratch_addr[dev];
 
@@ -615,17 +634,6 @@ extern "C" int iris_flash_decode_static(const void* q, const void* k_cache, cons
   a.group = Hq / Hkv; a.head_groups = (a.group + 15) / 16;
   a.sm_scale = sm_scale; a.soft_cap = soft_cap; a.is_fp16 = dtype == IRIS_F16;
   a.status = nullptr; a.box_rows = 0;     // the cp.async instantiation: no tensor maps
-  const int smem = kStages * 2 * kTileBytes > (int)((kWarps * 16 * kD + kWarps * 32) * sizeof(float))
-                       ? kStages * 2 * kTileBytes : (int)((kWarps * 16 * kD + kWarps * 32) * sizeof(float));
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(decode_splitk_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(decode_splitk_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
-      static_err(err, errlen, "iris_flash_decode_static: cannot raise the kernel's shared-memory limit");
-      return -20;
-    }
-    attr = true;
-  }
   dim3 grid(splits, Hkv * a.head_groups, B);
   if (a.is_fp16) decode_splitk_kernel<true, false><<<grid, kWarps * 32, smem, s>>>(a);
   else decode_splitk_kernel<false, false><<<grid, kWarps * 32, smem, s>>>(a);

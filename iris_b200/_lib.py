@@ -110,6 +110,20 @@ def current_stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def check(code: int, what: str) -> None:
+# Kernels of this library launched by this process, by entry point ("all_gather_matmul",
+# "collective", "gemm", ...). Every launch path goes through `check(..., kernels=n)`; benchmarks report
+# the difference of `launch_count()` around their timed region.
+LAUNCHES: dict = {}
+
+
+def launch_count() -> int:
+    return sum(LAUNCHES.values())
+
+
+def check(code: int, what: str, kernels: int = 0) -> None:
+    """Raise on a non-zero return code of a native call; `kernels` is the number of GPU kernels the
+    call launched when it succeeded (counted in `LAUNCHES` under `what`)."""
     if code != 0:
         raise RuntimeError(f"iris_b200: {what} failed with code {code}")
+    if kernels:
+        LAUNCHES[what] = LAUNCHES.get(what, 0) + kernels

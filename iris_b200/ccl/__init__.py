@@ -102,7 +102,7 @@ class CCL:
         # descriptors are cached per (buffers, shape, config): a repeated call costs one lookup
         key = (out.data_ptr(), inp.data_ptr(), tuple(out.shape), tuple(inp.shape), out.stride(0), inp.stride(0), inp.dtype,
                ctx._group_key(group), config.use_multicast, config.comm_sms, config.block_size_m, config.block_size_n,
-               config.all_reduce_distribution, id(ctx._ctx_epoch), op, config.reduce_scatter_rows)
+               config.all_reduce_distribution, config.swizzle_size, id(ctx._ctx_epoch), op, config.reduce_scatter_rows)
         hit = self._desc_cache.get(key)
         if hit is not None:
             return hit
@@ -129,7 +129,7 @@ class CCL:
                                      {"M": d.M, "N": d.N, "dtype": {v: k for k, v in _lib.DTYPE_CODE.items()}.get(d.dtype, d.dtype),
                                       "world": d.ctx.world, "comm_sms": d.comm_sms, "use_multicast": bool(d.use_mc), "block_m": d.block_m,
                                       "block_n": d.block_n, "distribution": d.distribution}, source="ccl.cu")
-        _lib.check(self._lib().iris_ccl_launch(op, C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "collective launch")
+        _lib.check(self._lib().iris_ccl_launch(op, C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "collective launch", kernels=1)
 
     # A repeated call (same buffers, shapes, group and configuration) skips validation and
     # descriptor set-up: one tuple, one dictionary lookup, one launch.
@@ -303,7 +303,9 @@ class CCL:
             out.copy_(acc.to(out.dtype))
             self._cpu_exit(group)
         else:
-            d = self._desc(out, inp, group, config, op="ar")
+            # one descriptor per resolved variant: the ring, push and spin-lock variants point it at their own
+            # sync block, buffers and CTA count, which must not leak into another variant's call on the same tensors
+            d = self._desc(out, inp, group, config, op="ar:" + ws.variant)
             d.M, d.N = inp.shape
             d.variant = _AR_CODE[ws.variant]
             if ws.variant == "ring":

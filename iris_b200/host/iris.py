@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import ctypes as C
 import os
+import weakref
 
 import numpy as np
 import torch
@@ -25,6 +26,20 @@ from .logging import DEBUG, ERROR, INFO, WARNING, log_rank
 from .platform import get_cu_count, get_device_id_for_rank, is_simulation_env
 
 SYNC_BLOCK_BYTES = (8 + _lib.MAX_RANKS) * 4
+_LIVE_CONTEXTS: "weakref.WeakSet" = weakref.WeakSet()
+
+
+def close_all() -> None:
+    """Close every context this process still holds (heaps unbound from their multicast object,
+    peer mappings released). For a process that is about to leave after an error: its peers may
+    never reach a barrier, so nothing collective happens here."""
+    for ctx in list(_LIVE_CONTEXTS):
+        try:
+            ctx.close()
+        except Exception:
+            pass
+
+
 _STATUS_NAMES = {
     1: "a cross-rank barrier wait ran out (a peer never arrived)",
     2: "a wait on a producer flag ran out",
@@ -86,6 +101,8 @@ class Iris:
         self.ccl = CCL(self)
         self.rma = HostRMA(self)
         self._ops = None
+        self._closed = False
+        _LIVE_CONTEXTS.add(self)
         D.distributed_barrier()
 
     def _dump_heap_bases(self) -> None:
@@ -399,6 +416,15 @@ class Iris:
     def close(self) -> None:
         """Unmap and free this rank's heap and its mappings of the peers' heaps. Heap tensors must not be
         used afterwards; call it on every rank (peers may still be reading until the barrier before it)."""
+        if getattr(self, "_closed", False):
+            return
+        self._closed = True
+        _LIVE_CONTEXTS.discard(self)
+        if not self.is_cpu:
+            try:
+                torch.cuda.synchronize(self.device)     # none of this rank's kernels may still touch the mappings
+            except Exception:
+                pass
         self.heap.close()
 
     def __enter__(self) -> "Iris":

@@ -146,7 +146,7 @@ class FlashDecodeLayer:
         d.num_blocks = 0 if self.use_tma is False else k_cache.shape[0]     # > 0 lets the kernel fill its tiles by TMA
         if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous() and block_table.is_contiguous()):
             raise ValueError("flash decode takes contiguous q, caches and block table")
-        _lib.check(self._lib().iris_flash_decode(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "flash decode launch")
+        _lib.check(self._lib().iris_flash_decode(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "flash decode launch", kernels=2)
         return (out, lse) if return_lse else out
 
     __call__ = forward

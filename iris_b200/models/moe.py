@@ -140,7 +140,7 @@ class MoELayer:
                      "expert_rows", "expert_row0", "tile_prefix", "expected_cum", "arrived", "inbox_meta"):
             setattr(d, name, getattr(self, name).data_ptr())
         d.weights_kmajor = 1
-        _lib.check(self._lib().iris_moe_forward(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "MoE forward launch")
+        _lib.check(self._lib().iris_moe_forward(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "MoE forward launch", kernels=7)
         self._keep = logits
         return out
 

@@ -121,7 +121,7 @@ class RingAttention:
         d.dtype = _lib.DTYPE_CODE[q.dtype]
         d.sm_scale = self.sm_scale
         d.options = (1 if self.use_tcgen05 is False else 0) | (2 if self.layout == "zigzag" else 0)
-        _lib.check(self._lib().iris_ring_attention(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "ring attention launch")
+        _lib.check(self._lib().iris_ring_attention(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "ring attention launch", kernels=1)
         return (out, lse) if return_lse else out
 
     __call__ = forward

@@ -134,10 +134,20 @@ def _cached_desc(ws, key, build):
 
 
 def _with_bias(bias, build):
-    """Run ``build(bias_fp32)`` and keep the converted bias alive next to the descriptor it is baked into."""
+    """Run ``build(bias_fp32)`` and keep the converted bias, and the tensor it came from, next to the
+    descriptor it is baked into."""
     b32 = _bias32(bias)
     d, keep = build(b32)
-    return d, (keep, b32)
+    return d, (keep, b32, bias)
+
+
+def _refresh_bias(keep) -> None:
+    """The kernels read an fp32 bias. For a 16-bit bias that is a converted copy kept with the cached
+    descriptor; the source may have been updated in place since (an optimizer step, load_state_dict), so
+    the copy is rewritten on every call: one small kernel on the launching stream."""
+    _, b32, bias = keep
+    if b32 is not None and b32.data_ptr() != bias.data_ptr():
+        b32.copy_(bias)
 
 
 def _ptr_key(*tensors):
@@ -159,7 +169,7 @@ def _launch(ctx, d, ws) -> None:
                                  {"M": d.M, "N": d.N, "K": d.K, "dtype": ws.dtype, "world": ctx.num_ranks, "op_code": d.op, "tile_n": d.bn,
                                   "cta_pairs": d.two_sm == 2, "comm_ctas": d.comm_ctas, "group_m": d.group_m, "use_multicast": bool(d.use_mc),
                                   "timeline": tl is not None}, source="gemm_ops.cu")
-    _lib.check(_lib.kernels().iris_gemm_launch(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), f"{ws.operation} launch")
+    _lib.check(_lib.kernels().iris_gemm_launch(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), f"{ws.operation} launch", kernels=1)
 
 
 def _local_matmul(A, B, bias=None, bias_dim=1):
@@ -257,6 +267,7 @@ def all_gather_matmul(shmem, output_tensor, A_sharded, B, bias=None, async_op=Fa
     else:
         d, keep = _cached_desc(ws, _ptr_key(output_tensor, A_sharded, B, bias) + (id(shmem._ctx_epoch),),
                                lambda: _with_bias(bias, lambda b32: _agm_desc(shmem, output_tensor, A_sharded, B, b32, config, shard_dim)))
+        _refresh_bias(keep)
         _launch(shmem, d, ws)
     _finish(shmem, async_op)
     return ws
@@ -327,6 +338,7 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
         op = _lib.GEMM_ALL_SCATTER if scatter_cols else _lib.GEMM_ALL_GATHER
         d, keep = _cached_desc(ws, _ptr_key(output_tensor, A, B, bias) + (id(shmem._ctx_epoch),),
                                lambda: _with_bias(bias, lambda b32: _base_desc(shmem, op, M, N, K, A, B, output_tensor, config, bias_row=b32)))
+        _refresh_bias(keep)
         _launch(shmem, d, ws)
     _finish(shmem, async_op)
     return ws
@@ -373,6 +385,7 @@ def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, con
     else:
         d, keep = _cached_desc(ws, _ptr_key(output_tensor, A, B, b) + (id(shmem._ctx_epoch),),
                                lambda: _with_bias(b, lambda b32: _base_desc(shmem, _lib.GEMM_ALL_REDUCE, M, N, K, A, B, output_tensor, config, bias_row=b32)))
+        _refresh_bias(keep)
         _launch(shmem, d, ws)
     _finish(shmem, async_op)
     return ws
@@ -449,6 +462,7 @@ def matmul_reduce_scatter(shmem, output_tensor, A, B, bias=None, async_op=False,
         op = _lib.GEMM_REDUCE_SCATTER if scatter_rows else _lib.GEMM_RS_TILES
         d, keep = _cached_desc(ws, _ptr_key(output_tensor, A, B, b) + (id(shmem._ctx_epoch),),
                                lambda: _with_bias(b, lambda b32: _base_desc(shmem, op, M, N, K, A, B, output_tensor, config, bias_row=b32)))
+        _refresh_bias(keep)
         _launch(shmem, d, ws)
     _finish(shmem, async_op)
     return ws

@@ -72,6 +72,6 @@ def matmul(A: torch.Tensor, B: torch.Tensor, bias: torch.Tensor | None = None, o
     keep = fill_desc(desc, A, B, out, bias_row=b32 if bias_dim == 0 else None, bias_col=b32 if bias_dim == 1 else None, bn=bn)
     desc.ctx.world = 1
     desc.two_sm = 0 if two_sm is None else (2 if two_sm else 1)
-    _lib.check(_lib.kernels().iris_gemm_launch(C.byref(desc), _lib.current_stream_ptr()), "gemm launch")
+    _lib.check(_lib.kernels().iris_gemm_launch(C.byref(desc), _lib.current_stream_ptr()), "gemm launch", kernels=1)
     del keep
     return out

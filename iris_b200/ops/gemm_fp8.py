@@ -112,5 +112,5 @@ def matmul_fp8(a_q: torch.Tensor, a_scale: torch.Tensor, b_q: torch.Tensor, b_sc
     d.M, d.N, d.K = M, N, K
     d.out_dtype = _lib.DTYPE_CODE[out.dtype]
     d.status = status.data_ptr() if status is not None else None
-    _lib.check(_typed(_lib.kernels()).iris_gemm_fp8_launch(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "fp8 gemm launch")
+    _lib.check(_typed(_lib.kernels()).iris_gemm_fp8_launch(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "fp8 gemm launch", kernels=1)
     return out

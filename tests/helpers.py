@@ -41,6 +41,14 @@ def _entry(rank, world, port, backend, fn, args, errq, env):
         try:
             fn(rank, world, *args)
         finally:
+            # Leave in order: unbind and unmap every heap this process created (a heap may be bound
+            # to an NVLink multicast object, which must not outlive an abrupt exit), then the group.
+            try:
+                from iris_b200.host.iris import close_all
+
+                close_all()
+            except Exception:
+                pass
             try:
                 dist.destroy_process_group()
             except Exception:
@@ -59,6 +67,15 @@ def run_ranks(fn, world: int, args=(), backend: str = "gloo", timeout: float = 3
     env = dict(env or {})
     if backend == "gloo":
         env.setdefault("IRIS_BACKEND", "cpu")
+    else:
+        # GPU ranks leave on their own: a host barrier that a failed peer never joins raises
+        # BarrierTimeoutError instead of blocking (device-side waits are bounded already).
+        env.setdefault("IRIS_BARRIER_TIMEOUT_S", os.environ.get("IRIS_BARRIER_TIMEOUT_S", "60"))
+    # A GPU rank whose heap may be bound to a multicast object is never killed from here: ending it
+    # in the middle of a kernel has left NVLink faults on its peers' GPUs. Only CPU ranks, or GPU
+    # ranks started with NVLS off, get the last-resort stop.
+    nvls_off = env.get("IRIS_NVLS", os.environ.get("IRIS_NVLS", "1")) == "0"
+    may_kill = backend == "gloo" or nvls_off
     procs = [ctx.Process(target=_entry, args=(r, world, port, backend, fn, args, errq, env)) for r in range(world)]
     for p in procs:
         p.start()
@@ -69,13 +86,16 @@ def run_ranks(fn, world: int, args=(), backend: str = "gloo", timeout: float = 3
         now = time.time()
         if failed_at is None and any(p.exitcode not in (None, 0) for p in procs):
             failed_at = now
-        if now > deadline or (failed_at is not None and now - failed_at > grace and not expect_failures):
+        if may_kill and (now > deadline or (failed_at is not None and now - failed_at > grace and not expect_failures)):
+            break
+        if not may_kill and now > deadline + 180.0:      # their own barrier / process-group limits have long passed
             break
         time.sleep(0.05)
     hung = [p for p in procs if p.is_alive()]
     for p in hung:
-        p.kill()  # the exact child processes started above
-        p.join()
+        if may_kill:
+            p.kill()  # the exact child processes started above
+            p.join()
     if failed_at is not None and not expect_failures:
         hung = []           # their peer failed first: the failure below is the one to report
     errors = []

@@ -101,6 +101,16 @@ def _dry_run(rank, world):
         ring_b = ctx.ccl.all_reduce(other_out, other_in, config=Config(all_reduce_variant="ring"))
         assert ring_b is ring_a and ctx.heap_mark() == level and rec.ccl[-1][1].ring_buf == ring_a.ring_buffer.data_ptr()
         assert rec.ccl[-1][1].inp == other_in.data_ptr()
+        # ring -> two_shot -> ring on the SAME tensors: each variant keeps its own descriptor, so the
+        # two-shot call runs on the context's sync block (not on the ring workspace's) with its own CTA count
+        ctx.ccl.all_reduce(big_out, big_in, config=Config(all_reduce_variant="ring"))
+        ring_d = bytes(rec.ccl[-1][1])
+        ctx.ccl.all_reduce(big_out, big_in, config=Config(all_reduce_variant="two_shot"))
+        two = rec.ccl[-1][1]
+        assert two.variant == 3 and two.sync_block != ring_a.sync_block.data_ptr() and not two.ring_buf
+        assert two.sync_block == ctx.sync_block(("ccl", ctx._group_key(None))).data_ptr() and two.comm_sms == Config().comm_sms
+        ctx.ccl.all_reduce(big_out, big_in, config=Config(all_reduce_variant="ring"))
+        assert bytes(rec.ccl[-1][1]) == ring_d
     n_before = len(rec.ccl)
     ctx.ccl.all_reduce(big_out, big_in, workspace=ws, async_op=True)
     ctx.ccl.all_reduce(big_out, big_in, workspace=ws, async_op=True)                   # replayed from the call cache

@@ -109,7 +109,12 @@ def test_time_max_over_ranks_and_launch_records(ctx, tmp_path):
 
 
 def _world():
-    return min(torch.cuda.device_count(), 4)
+    """Ranks of the multi-GPU cases: ``IRIS_TEST_WORLD`` when set (the suite is run at 2, 4 and 8),
+    else every GPU up to four."""
+    import os
+
+    want = int(os.environ.get("IRIS_TEST_WORLD", "0"))
+    return min(torch.cuda.device_count(), want if want > 0 else 4)
 
 
 def _multi(rank, world):

@@ -47,13 +47,13 @@ def _context():
     return iris.iris(1 << 28)
 
 
-def test_static_scratch_decode_matches_regular_entry_point_twice():
+@pytest.mark.parametrize("dt,code", [(torch.bfloat16, 1), (torch.float16, 0)], ids=["bf16", "fp16"])
+def test_static_scratch_decode_matches_regular_entry_point_twice(dt, code):
     from iris_b200.models import FlashDecodeLayer
 
     fn, need = _symbol()
     ctx = _context()
     B, Hq, Hkv, D, page, splits = 3, 32, 4, 128, 64, 6
-    dt = torch.bfloat16
     torch.manual_seed(11)
     lens = [900, 64, 1531]
     max_blocks = -(-max(lens) // page)
@@ -72,7 +72,7 @@ def test_static_scratch_decode_matches_regular_entry_point_twice():
         out = torch.full((B, Hq, D), float("nan"), device="cuda", dtype=dt)
         free_before = torch.cuda.mem_get_info()[0]
         rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), table.data_ptr(), kv_lens.data_ptr(), out.data_ptr(),
-                B, Hq, Hkv, D, page, max_blocks, splits, 1.0 / D ** 0.5, 0.0, 1, stream, err, 512)
+                B, Hq, Hkv, D, page, max_blocks, splits, 1.0 / D ** 0.5, 0.0, code, stream, err, 512)
         assert rc == 0, err.value.decode()
         torch.cuda.synchronize()
         assert torch.cuda.mem_get_info()[0] >= free_before - (1 << 20)  # nothing was allocated by the call
