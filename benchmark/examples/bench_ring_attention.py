@@ -5,11 +5,16 @@ Every rank holds `seq_per_rank` tokens (32 query heads, 8 KV heads, head_dim 128
 over the whole sequence of `num_ranks * seq_per_rank` tokens. FLOPs counted per rank:
 4 * S * (W * S) * Hq * D (halved when causal). Roofline: those FLOPs at the measured sustained
 bf16 tensor throughput; the K/V bytes that must cross NVLink ((W - 1) * S * Hkv * D * 2 * 2 per
-rank at 770 GB/s) are far below it at these sizes."""
+rank at 770 GB/s) are far below it at these sizes.
+
+``impl=nccl`` is the unfused form: NCCL ``all_gather_into_tensor`` of K and V, then one library attention
+call over the gathered keys (flash_attn, whose causal mask is aligned to the end of the key sequence, so
+rank r attends to keys [0, (r + 1) * S); contiguous layout only)."""
 import os
 import sys
 
 import torch
+import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 import iris_b200.bench as bench  # noqa: E402
@@ -20,6 +25,7 @@ PEAK_TFLOPS = 1383.6
 
 @bench.register
 @bench.axis("num_ranks", [1, 2, 4, 8])
+@bench.axis("impl", ["iris", "nccl"])
 @bench.axis("seq_per_rank", [2048, 8192])
 @bench.axis("causal", [0, 1])
 @bench.axis("layout", ["contiguous", "zigzag"])
@@ -39,6 +45,29 @@ def ring_attention(state, ctx):
     state.set_roofline_us(flops / (PEAK_TFLOPS * 1e6))
     state.set_repeat(20)
     state.set_warmup(5)
+    if state["impl"] == "nccl":
+        if state["layout"] != "contiguous":
+            state.skip("the NCCL baseline gathers a contiguous sequence")
+        try:
+            from flash_attn import flash_attn_func
+        except Exception:
+            state.skip("flash_attn is not importable")
+        kall = torch.empty(W * S, Hkv, D, device="cuda", dtype=dt)
+        vall = torch.empty(W * S, Hkv, D, device="cuda", dtype=dt)
+        rank = ctx.get_rank()
+
+        def base():
+            if W > 1:
+                dist.all_gather_into_tensor(kall, k)
+                dist.all_gather_into_tensor(vall, v)
+            else:
+                kall.copy_(k)
+                vall.copy_(v)
+            n = (rank + 1) * S if causal else W * S
+            out.copy_(flash_attn_func(q[None], kall[None, :n], vall[None, :n], causal=causal)[0])
+
+        state.exec(base)
+        return
     state.exec(lambda: layer(q, k, v, causal=causal, out=out))
 
 

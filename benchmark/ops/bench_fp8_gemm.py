@@ -1,7 +1,10 @@
 #!/usr/bin/env python3
 """Block-scaled fp8 GEMM on one GPU: numerics against the fp32 product of the dequantised operands,
-then throughput next to the bf16 kernel of this package, torch.matmul (cuBLAS bf16) and
-torch._scaled_mm (cuBLASLt fp8 with ONE scale per tensor: a library upper bound, it does less work).
+then throughput of the two kernels of this package (scales applied by the tensor core from UE8M0 bytes
+in TMEM, for power-of-two scales; promotion of every K block in registers, for arbitrary fp32 scales)
+next to the bf16 kernel, torch.matmul (cuBLAS bf16) and torch._scaled_mm (cuBLASLt fp8: with the same
+1 x 128 / 128 x 128 block scales when this PyTorch accepts them, and with ONE scale per tensor, a library
+upper bound that does less work).
 
     python benchmark/ops/bench_fp8_gemm.py [--iters 20]
 
@@ -16,7 +19,8 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 from iris_b200.ops.gemm import matmul  # noqa: E402
-from iris_b200.ops.gemm_fp8 import dequant_matmul, matmul_fp8, quantize_1x128, quantize_128x128  # noqa: E402
+from iris_b200.ops.gemm_fp8 import (blockscaled_tile_n, dequant_matmul, matmul_fp8, matmul_fp8_blockscaled, pack_scales_a,  # noqa: E402
+                                    pack_scales_b, quantize_1x128, quantize_128x128)
 
 
 def check(M, N, K):
@@ -56,8 +60,22 @@ def bench(M, N, K, iters):
     del x, w
     cols = []
     fl = 2.0 * M * N * K
+    ap, asp = quantize_1x128(xq_src := xb.float(), pow2=True)
+    bp, bsp = quantize_128x128(wb.float(), pow2=True)
+    del xq_src
+    sfa, sfb = pack_scales_a(asp), pack_scales_b(bsp, N, blockscaled_tile_n(M, N))
+    for two_sm, name in ((False, "fp8 tensor-core scaling"), (True, "same, CTA pairs")):
+        ms = timed(lambda: matmul_fp8_blockscaled(ap, sfa, bp, sfb, out=out, two_sm=two_sm), iters)
+        cols.append(f"{name} {ms:.3f} ms {fl / ms / 1e9:.0f} TF")
     ms = timed(lambda: matmul_fp8(aq, asc, bq, bsc, out=out), iters)
-    cols.append(f"fp8 block-scaled {ms:.3f} ms {fl / ms / 1e9:.0f} TF")
+    cols.append(f"fp8 register promotion {ms:.3f} ms {fl / ms / 1e9:.0f} TF")
+    try:   # cuBLASLt with the same block scales (scale_a [M, K/128], scale_b [K/128, N/128] as PyTorch lays them out)
+        sa_lt = asc.t().contiguous().t()
+        sb_lt = bsc.t().contiguous()
+        ms = timed(lambda: torch._scaled_mm(aq, bq.t(), scale_a=sa_lt, scale_b=sb_lt, out_dtype=torch.bfloat16), iters)
+        cols.append(f"cuBLASLt fp8 block scales {ms:.3f} ms {fl / ms / 1e9:.0f} TF")
+    except Exception as e:
+        cols.append(f"cuBLASLt fp8 block scales unavailable ({type(e).__name__})")
     ms = timed(lambda: matmul(xb, wb.t(), out=out), iters)
     cols.append(f"bf16 (this package) {ms:.3f} ms {fl / ms / 1e9:.0f} TF")
     ms = timed(lambda: torch.matmul(xb, wb.t(), out=out), iters)

@@ -7,6 +7,13 @@
     python benchmark/profile_target.py moe       # one MoE layer pass, 1024 tokens, 8 experts
     python benchmark/profile_target.py fp8       # 3 launches of the block-scaled fp8 GEMM 4096x4096x7168
     python benchmark/profile_target.py ring      # 3 ring-attention calls, world size 1, 4096 tokens, 32/8 heads
+    python benchmark/profile_target.py fp8hw     # 3 launches of the hardware block-scaled fp8 GEMM 4096x3584x8192
+    python benchmark/profile_target.py ar        # world-size-1 matmul_all_reduce (two_shot, one_shot) and matmul_all_gather
+    python benchmark/profile_target.py ccl       # world-size-1 all_reduce / all_gather / reduce_scatter kernels, 256 MB
+
+The fused ops and collectives run here with ONE rank: the same kernel templates as on several GPUs
+(policy code, epilogues, flag protocol) with no peer to wait for, which is the form a replaying
+profiler can capture safely.
 """
 import os
 import sys
@@ -50,8 +57,36 @@ def main():
             matmul_fp8(aq, asc, bq, bsc, out=out)
         torch.cuda.synchronize()
         return
+    if what == "fp8hw":
+        from iris_b200.ops import matmul, quantize_activation, quantize_weight
+
+        a = quantize_activation(torch.randn(4096, 8192, device="cuda"))
+        b = quantize_weight(torch.randn(3584, 8192, device="cuda") * 0.05)
+        out = torch.empty(4096, 3584, device="cuda", dtype=dt)
+        for _ in range(3):
+            matmul(a, b, out=out)
+        torch.cuda.synchronize()
+        return
     ctx = ctx_world1()
-    if what == "decode":
+    if what == "ar":
+        from iris_b200.ops import FusedConfig
+
+        A = torch.randn(4096, 3584, device="cuda", dtype=dt)
+        B = torch.randn(3584, 8192, device="cuda", dtype=dt) * 0.02
+        C = ctx.zeros((4096, 8192), dtype=dt)
+        for variant in ("two_shot", "one_shot"):
+            for _ in range(2):
+                ctx.ops.matmul_all_reduce(C, A, B, config=FusedConfig(all_reduce_variant=variant), async_op=True)
+        for _ in range(2):
+            ctx.ops.matmul_all_gather(C, A, B, async_op=True)
+    elif what == "ccl":
+        x = ctx.zeros((8192, 16384), dtype=dt)            # 256 MB
+        y = ctx.zeros((8192, 16384), dtype=dt)
+        for _ in range(2):
+            ctx.ccl.all_reduce(y, x, async_op=True)
+            ctx.ccl.all_gather(y, x, async_op=True)
+            ctx.ccl.reduce_scatter(y, x, async_op=True)
+    elif what == "decode":
         from iris_b200.models import FlashDecodeLayer
 
         B_, L, Hq, Hkv, page = 8, 16384, 64, 8, 64

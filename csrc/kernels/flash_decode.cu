@@ -433,6 +433,28 @@ __global__ void __launch_bounds__(kD) decode_exchange_kernel(const __grid_consta
   }
 }
 
+// Local-only finish (exchange == 2): fold this rank's splits into (o, lse) without talking to any peer.
+// What a decode over a KV shard returns when the cross-rank merge is done elsewhere, e.g. by an
+// all-gather of the partial results as in the reference's RCCL baseline
+// (examples/benchmark/reference/flash_decode_rccl/flash_decode_layer_rccl.py:100-130).
+__global__ void __launch_bounds__(kD) decode_local_finish_kernel(const float* partial, void* out, float* out_lse, int splits, int is_fp16) {
+  const int it = blockIdx.x, d = threadIdx.x;
+  const float* p = partial + (size_t)it * splits * (kD + 1);
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, p[s * (kD + 1) + kD]);
+  float l = 0.f, acc = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ls = p[s * (kD + 1) + kD];
+    const float w = ls == -INFINITY ? 0.f : exp2f(ls - m);
+    l += w;
+    acc += w * p[s * (kD + 1) + d];
+  }
+  const float o = l > 0.f ? acc / l : 0.f;
+  if (is_fp16) ((__half*)out)[(size_t)it * kD + d] = __float2half_rn(o);
+  else ((__nv_bfloat16*)out)[(size_t)it * kD + d] = __float2bfloat16_rn(o);
+  if (out_lse && d == 0) out_lse[it] = l > 0.f ? (m + log2f(l)) / kLog2e : -INFINITY;
+}
+
 }  // namespace
 
 extern "C" {
@@ -447,7 +469,7 @@ typedef struct IrisDecodeDesc {
   int32_t B, Bmax, Hq, Hkv, D, page, max_blocks, splits;
   float sm_scale, soft_cap;
   int32_t dtype;
-  int32_t exchange;   // 0: only the local split-K pass, 1: also combine + exchange + merge
+  int32_t exchange;   // 0: only the local split-K pass, 1: also combine + exchange + merge, 2: combine locally (out, lse of this rank's shard)
   int32_t num_blocks; // pages in each cache tensor (0: unknown, the TMA path is not used)
 } IrisDecodeDesc;
 
@@ -516,6 +538,10 @@ int iris_flash_decode(const IrisDecodeDesc* d, void* stream) {
   }
   if (cudaGetLastError() != cudaSuccess) return -21;
   if (!d->exchange) return 0;
+  if (d->exchange == 2) {
+    decode_local_finish_kernel<<<d->B * d->Hq, kD, 0, s>>>(d->partial, d->out, d->out_lse, d->splits, a.is_fp16);
+    return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  }
   ExchangeArgs x;
   memcpy(&x.ctx, &d->ctx, sizeof(DeviceContext));
   if (x.ctx.world > 64) return -4;

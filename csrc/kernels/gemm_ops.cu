@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 #include <string.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "iris/host_api.h"
 #include "iris/context.cuh"
@@ -33,7 +34,8 @@ struct LocalGemm : Common {
   struct State {};
   IRIS_D void tile(int t, int& tm, int& tn) const { swizzled_tile(t, order_m, tiles_n, group_m, tm, tn); }
   IRIS_D bool a_source(State&, int tm, int kb, ASource& s) const {
-    s.map = &tmA; s.x = kb * kBK; s.y = tm * kBM; s.bk = kb * kBK;
+    s.map = &tmA; s.x = kb * bk; s.y = tm * kBM; s.bk = kb * bk;
+    s.sf_map = &tmSFA; s.sf_row = tm * kblocks + kb;
     return true;
   }
   IRIS_D void begin_tile(State&, int, int, uint8_t*) const {}
@@ -42,10 +44,9 @@ struct LocalGemm : Common {
   IRIS_D void store16(State&, int row, int col, uint4 v) const {
     if (row < sh.M && col < sh.N) *(uint4*)(C + ((int64_t)row * ldc + col) * 2) = v;
   }
-  static constexpr bool kBulkEpilogue = false;
-  IRIS_D void store_chunk(State&, int, int, int, const uint8_t*) const {}
-  IRIS_D bool reduce_here(State&) const { return false; }
-  IRIS_D void add_partials(State&, int, int, int, uint32_t (&)[32]) const {}
+  static constexpr bool kBulkEpilogue = true;
+  IRIS_D bool bulk_tile(State&) const { return c_bulk != 0; }
+  IRIS_D void store_chunk(State&, int, int, int width, const uint8_t* smem, int row, int col) const { store_chunk_local(width, smem, row, col); }
   IRIS_D void tile_done(State&, int, int) const {}
   IRIS_D void comm_main(uint8_t*, int) const {}
   IRIS_D void post_main() const {}
@@ -75,6 +76,12 @@ struct AllGatherGemm : Common {
   int chunks;              // 128-row chunks per source
   int n_comm_ctas;
   int use_mc;
+  // fp8: the shard's scale atoms [chunks][K blocks per source][512 B] travel with it into a second inbox
+  int esz;                 // bytes per element of A: 2, or 1 (e4m3)
+  int kb_per_src;          // K blocks (stages) per source column range
+  CUtensorMap tmSFInbox;   // [2][W][chunks][kb_per_src] atoms
+  const uint8_t* sf_local;
+  uint8_t* sf_inbox;
 
   struct State {
     int key = -1;        // (source, chunk) whose arrival has been confirmed
@@ -83,6 +90,8 @@ struct AllGatherGemm : Common {
     int src = 0, chunk = 0, g = 0, kb_next_src = 0, kb0 = 0;
     const CUtensorMap* map = nullptr;
     int y = 0;
+    const CUtensorMap* sf_map = nullptr;
+    int sf_row0 = 0;
   };
   IRIS_D int src_of_group(int g) const {  // own shard first, then the order the pushes arrive in
     int s = ctx.rank - g;
@@ -121,12 +130,13 @@ struct AllGatherGemm : Common {
     st.src = src; st.chunk = chunk;
     if (src == ctx.rank) {       // own shard: read in place, nothing to wait for
       st.map = &tmA; st.y = chunk * kBM;
+      st.sf_map = &tmSFA; st.sf_row0 = chunk * kb_per_src;
       return true;
     }
     const int buf = st.epoch & 1;
     const int key = src * chunks + chunk;
     if (key != st.key) {
-      const int target = ((st.epoch >> 1) + 1) * n_comm_ctas;
+      const int target = ((st.epoch >> 1) + 1) * arrivals_per_chunk();
       if (!wait_flag_ge(ctx, flags + ((size_t)buf * ctx.world + src) * chunks + chunk, target)) return false;
       st.key = key;
       // The data was written by another GPU (generic proxy, remote); order the TMA (async proxy)
@@ -134,6 +144,7 @@ struct AllGatherGemm : Common {
       ptx::fence_proxy_async();
     }
     st.map = &tmInbox; st.y = ((buf * ctx.world + src) * rows_per_src) + chunk * kBM;
+    st.sf_map = &tmSFInbox; st.sf_row0 = ((buf * ctx.world + src) * chunks + chunk) * kb_per_src;
     return true;
   }
   IRIS_D bool a_source(State& st, int tm, int kb, ASource& s) const {
@@ -144,18 +155,19 @@ struct AllGatherGemm : Common {
         const int src = tm / chunks;
         if (!select(st, src, tm - src * chunks)) return false;
       }
-      s.map = st.map; s.x = kb * kBK; s.y = st.y; s.bk = s.x;
+      s.map = st.map; s.x = kb * bk; s.y = st.y; s.bk = s.x;
+      s.sf_map = st.sf_map; s.sf_row = st.sf_row0 + kb;
       return true;
     }
     // K-sharded: walk the sources along K, own shard first
     if (kb == 0 || kb == st.kb_next_src) {
-      const int kb_per_src = cols_per_src / kBK;
       st.g = kb == 0 ? 0 : st.g + 1;
       st.kb0 = st.g * kb_per_src;
       st.kb_next_src = st.kb0 + kb_per_src;
       if (!select(st, src_of_group(st.g), tm)) return false;
     }
-    s.map = st.map; s.x = (kb - st.kb0) * kBK; s.y = st.y; s.bk = st.src * cols_per_src + s.x;
+    s.map = st.map; s.x = (kb - st.kb0) * bk; s.y = st.y; s.bk = st.src * cols_per_src + s.x;
+    s.sf_map = st.sf_map; s.sf_row = st.sf_row0 + (kb - st.kb0);
     return true;
   }
   IRIS_D void begin_tile(State&, int, int, uint8_t*) const {}
@@ -164,21 +176,29 @@ struct AllGatherGemm : Common {
   IRIS_D void store16(State&, int row, int col, uint4 v) const {
     if (row < sh.M && col < sh.N) *(uint4*)(C + ((int64_t)row * ldc + col) * 2) = v;
   }
-  static constexpr bool kBulkEpilogue = false;
-  IRIS_D void store_chunk(State&, int, int, int, const uint8_t*) const {}
-  IRIS_D bool reduce_here(State&) const { return false; }
-  IRIS_D void add_partials(State&, int, int, int, uint32_t (&)[32]) const {}
+  static constexpr bool kBulkEpilogue = true;
+  IRIS_D bool bulk_tile(State&) const { return c_bulk != 0; }
+  IRIS_D void store_chunk(State&, int, int, int width, const uint8_t* smem, int row, int col) const { store_chunk_local(width, smem, row, col); }
   IRIS_D void tile_done(State&, int, int) const {}
 
-  // Communication CTAs: CTA j moves slice j (of n_comm_ctas) of every 128-row chunk, chunk by
-  // chunk, so chunk 0 is complete everywhere first. The slice streams through a ring of shared
-  // memory buffers filled by bulk async copies (cp.async.bulk, local HBM read once); from there it
-  // goes either to each peer with bulk async stores issued by one thread (unicast), or to all
-  // ranks at once with multimem.st issued by every thread (NVLS). After the last piece of a chunk
-  // the stores are drained and the chunk's arrival counter is raised on the receivers.
+  // Communication CTAs: CTA j moves slice j (of n_comm_ctas) of every 128-row chunk, chunk by chunk,
+  // so chunk 0 is complete everywhere first. Three roles inside the CTA:
+  //   mover    (warp 0, one thread)  streams the CTA's pieces (32 KB) through a ring of shared-memory
+  //            slots without ever draining it: bulk async copy HBM -> slot, then one bulk async store per
+  //            peer, loads running ahead across chunk boundaries. It never fences. A chunk whose stores
+  //            were all issued is handed to the signaller once enough later traffic has been issued that
+  //            waiting for its bulk groups no longer stalls (a store completes only after everything
+  //            queued in front of it on the link: several microseconds), or at the end.
+  //   signaller (warp 1)             waits for the hand-over, then lane p raises the chunk's arrival counter
+  //            on peer p (release, system scope). The fences this needs cost a link round trip each; here
+  //            they delay only the signal, not the data.
+  //   scales   (warp 2, fp8 only)    copies the CTA's share of the chunk's scale atoms to the peers.
+  // A chunk has arrived at a receiver when its counter shows n_comm_ctas arrivals for this call.
   static constexpr int kPiece = 32 * 1024;
-  // wait until at most `n` of the most recent bulk groups are still pending
-  IRIS_D static void bulk_wait_upto(int n) {
+  static constexpr int kSlots = 6;
+  static constexpr int kMaxChunksTracked = 1024;
+  IRIS_D int arrivals_per_chunk() const { return n_comm_ctas; }
+  IRIS_D static void bulk_wait_upto(int n) {      // wait until at most `n` of the most recent bulk groups are pending
     switch (n) {
       case 0: ptx::bulk_wait<0>(); break;
       case 1: ptx::bulk_wait<1>(); break;
@@ -189,42 +209,51 @@ struct AllGatherGemm : Common {
       case 6: ptx::bulk_wait<6>(); break;
       case 7: ptx::bulk_wait<7>(); break;
       case 8: ptx::bulk_wait<8>(); break;
-      default: ptx::bulk_wait<0>(); break;   // more groups than cases: drain everything
-    }
-  }
-  IRIS_D void signal_chunk(int buf, int c) const {
-    int32_t* flag_local = flags + ((size_t)buf * ctx.world + ctx.rank) * chunks + c;
-    ptx::fence_proxy_async();
-    fence_sys();
-    for (int p = 1; p < ctx.world; ++p) {
-      int dst_rank = ctx.rank + p;
-      if (dst_rank >= ctx.world) dst_rank -= ctx.world;
-      red_release_sys_add(ctx.remote(flag_local, dst_rank), 1);
+      case 9: ptx::bulk_wait<9>(); break;
+      case 10: ptx::bulk_wait<10>(); break;
+      case 11: ptx::bulk_wait<11>(); break;
+      case 12: ptx::bulk_wait<12>(); break;
+      case 13: ptx::bulk_wait<13>(); break;
+      case 14: ptx::bulk_wait<14>(); break;
+      case 15: ptx::bulk_wait<15>(); break;
+      default: ptx::bulk_wait<16>(); break;        // more recent groups than that may stay pending either way
     }
   }
   IRIS_D void comm_main(uint8_t* smem_raw, int smem_bytes) const {
     const int j = blockIdx.x - n_gemm_ctas;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int epoch = read_epoch(sb);
     const int buf = epoch & 1;
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
-    int nb = (smem_bytes - 1024) / kPiece;
-    if (nb > 6) nb = 6;
-    uint64_t* bars = (uint64_t*)(smem + (size_t)nb * kPiece);
+    uint64_t* bars = (uint64_t*)(smem + (size_t)kSlots * kPiece);
+    volatile int* handed = (volatile int*)(bars + kSlots);          // chunks handed to the signaller
+    volatile int* sf_done = handed + 1;                              // chunks whose scale atoms were written (fp8)
+    volatile int* aborted = handed + 2;
+    int* g_last = (int*)(handed + 4);                                // per chunk: bulk groups committed when its last piece was
     if (threadIdx.x == 0) {
-      for (int i = 0; i < nb; ++i) ptx::mbar_init(&bars[i], 1);
+      for (int i = 0; i < kSlots; ++i) ptx::mbar_init(&bars[i], 1);
+      *handed = 0; *sf_done = 0; *aborted = 0;
       ptx::fence_mbar_init();
       ptx::fence_proxy_async();
     }
     __syncthreads();
-    const size_t row_bytes = (size_t)cols_per_src * 2;
-    const size_t src_pitch = (size_t)lda * 2;
+    const size_t row_bytes = (size_t)cols_per_src * esz;
+    const size_t src_pitch = (size_t)lda * esz;
     const bool flat = src_pitch == row_bytes;
     const int pieces_per_row = (int)((row_bytes + kPiece - 1) / kPiece);
-    // piece i of a slice of `nrows` rows starting at byte offsets (src0, dst0): (src, dst, bytes)
-    auto piece = [&](int i, size_t slice_bytes, size_t& soff, size_t& doff, uint32_t& bytes) {
+    const int tracked = min(chunks, kMaxChunksTracked);
+    // this CTA's slice of chunk c: first row, rows, pieces
+    auto slice = [&](int c, int& row_lo, int& nrows, int& n) {
+      const int r0 = c * kBM;
+      const int nrows_c = min(kBM, rows_per_src - r0);
+      const int lo = (int)((int64_t)nrows_c * j / n_comm_ctas), hi = (int)((int64_t)nrows_c * (j + 1) / n_comm_ctas);
+      row_lo = r0 + lo; nrows = hi - lo;
+      n = nrows == 0 ? 0 : (flat ? (int)(((size_t)nrows * row_bytes + kPiece - 1) / kPiece) : nrows * pieces_per_row);
+    };
+    auto piece = [&](int i, int nrows, size_t& soff, size_t& doff, uint32_t& bytes) {
       if (flat) {
         soff = doff = (size_t)i * kPiece;
-        bytes = (uint32_t)min((size_t)kPiece, slice_bytes - soff);
+        bytes = (uint32_t)min((size_t)kPiece, (size_t)nrows * row_bytes - soff);
       } else {
         const int r = i / pieces_per_row, k = i - r * pieces_per_row;
         soff = (size_t)r * src_pitch + (size_t)k * kPiece;
@@ -232,92 +261,115 @@ struct AllGatherGemm : Common {
         bytes = (uint32_t)min((size_t)kPiece, row_bytes - (size_t)k * kPiece);
       }
     };
-    __shared__ int s_abort;
-    if (threadIdx.x == 0) s_abort = 0;
-    __syncthreads();
-    int it_global = 0;   // pieces issued so far by this CTA (selects ring slot and barrier parity)
-    for (int c = 0; c < chunks; ++c) {
-      const int r0 = c * kBM;
-      const int nrows_c = min(kBM, rows_per_src - r0);
-      const int rows_lo = (int)((int64_t)nrows_c * j / n_comm_ctas), rows_hi = (int)((int64_t)nrows_c * (j + 1) / n_comm_ctas);
-      const int nrows = rows_hi - rows_lo;
-      const size_t slice_bytes = (size_t)nrows * row_bytes;
-      const int n = nrows == 0 ? 0 : (flat ? (int)((slice_bytes + kPiece - 1) / kPiece) : nrows * pieces_per_row);
-      const uint8_t* src0 = A_local + (size_t)(r0 + rows_lo) * src_pitch;
-      uint8_t* dst_local = inbox + (((size_t)buf * ctx.world + ctx.rank) * rows_per_src + r0 + rows_lo) * row_bytes;
-      int32_t* flag_local = flags + ((size_t)buf * ctx.world + ctx.rank) * chunks + c;
-      const int base = it_global;
-      auto issue_load = [&](int i) {   // thread 0 only
-        size_t so, d_o; uint32_t by;
-        piece(i, slice_bytes, so, d_o, by);
-        const int slot = (base + i) % nb;
-        ptx::mbar_expect_tx(&bars[slot], by);
-        ptx::bulk_load(smem + (size_t)slot * kPiece, src0 + so, by, &bars[slot]);
+    if (w == 0 && lane == 0) {
+      // ---------------------------------------------------------------- mover
+      // two cursors over the CTA's pieces in (chunk, piece) order: `ld` runs ahead of `st` by up to kSlots
+      int ld_c = 0, ld_i = 0, ld_seq = 0;
+      int st_seq = 0;
+      int groups = 0, next_hand = 0;
+      bool ok = true;
+      // a chunk is handed over once this many groups were committed after its last one
+      const int depth = max(1, min(16, (12 + ctx.world - 2) / (ctx.world - 1)));
+      auto advance_ld = [&]() -> bool {           // move `ld` to the next existing piece; false at the end
+        while (ld_c < chunks) {
+          int row_lo, nrows, n;
+          slice(ld_c, row_lo, nrows, n);
+          if (ld_i < n) return true;
+          ++ld_c; ld_i = 0;
+        }
+        return false;
       };
-      if (use_mc) {
-        uint8_t* dst_mc = ctx.mc(dst_local);
-        if (threadIdx.x == 0)
-          for (int i = 0; i < min(nb, n); ++i) issue_load(i);
+      auto issue_load = [&]() {
+        int row_lo, nrows, n;
+        slice(ld_c, row_lo, nrows, n);
+        size_t so, d_o; uint32_t by;
+        piece(ld_i, nrows, so, d_o, by);
+        const int s = ld_seq % kSlots;
+        ptx::mbar_expect_tx(&bars[s], by);
+        ptx::bulk_load(smem + (size_t)s * kPiece, A_local + (size_t)row_lo * src_pitch + so, by, &bars[s]);
+        ++ld_seq; ++ld_i;
+      };
+      auto hand_over = [&](bool all) {
+        const int before = next_hand;
+        while (next_hand < chunks) {
+          const int gl = next_hand < tracked ? g_last[next_hand] : groups;
+          if (gl < 0) break;                                       // its last piece has not been issued yet
+          if (!all && groups - gl < depth) break;
+          bulk_wait_upto(groups - gl);
+          ++next_hand;
+        }
+        if (next_hand == before) return;
+        ptx::fence_proxy_async();
+        asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(ptx::smem_u32((const void*)handed)), "r"(next_hand) : "memory");
+      };
+      for (int c = 0; c < tracked; ++c) g_last[c] = -1;
+      while (ld_seq < kSlots && advance_ld()) issue_load();
+      for (int c = 0; c < chunks && ok; ++c) {
+        int row_lo, nrows, n;
+        slice(c, row_lo, nrows, n);
+        uint8_t* dst_local = inbox + (((size_t)buf * ctx.world + ctx.rank) * rows_per_src + row_lo) * row_bytes;
         for (int i = 0; i < n; ++i) {
-          const int slot = (base + i) % nb;
-          const uint32_t parity = (uint32_t)(((base + i) / nb) & 1);
-          if (!ptx::mbar_wait(&bars[slot], parity, kPipeTimeoutNs)) { fail(kTimeoutPipeline); s_abort = 1; }
-          __syncthreads();
-          if (s_abort) break;
+          const int s = st_seq % kSlots;
+          if (!ptx::mbar_wait(&bars[s], (uint32_t)((st_seq / kSlots) & 1), kPipeTimeoutNs)) { fail(kTimeoutPipeline); ok = false; break; }
           size_t so, d_o; uint32_t by;
-          piece(i, slice_bytes, so, d_o, by);
-          const uint8_t* sp = smem + (size_t)slot * kPiece;
-          for (uint32_t u = threadIdx.x * 16; u < by; u += blockDim.x * 16) {
-            const multimem::V4 v = *(const multimem::V4*)(sp + u);
-            multimem::st_v4(dst_mc + d_o + u, v);
-          }
-          __syncthreads();
-          if (threadIdx.x == 0 && i + nb < n) {
-            ptx::fence_proxy_async();   // generic reads of the slot precede the async refill
-            issue_load(i + nb);
-          }
-        }
-        __syncthreads();
-        if (threadIdx.x == 0 && !s_abort) {
-          fence_sys();
-          multimem::red_release_add_u32(ctx.mc(flag_local), 1);
-        }
-      } else if (threadIdx.x == 0) {
-        int next_load = min(nb, n);
-        for (int i = 0; i < next_load; ++i) issue_load(i);
-        bool ok = true;
-        for (int i = 0; i < n && ok; ++i) {
-          const int slot = (base + i) % nb;
-          const uint32_t parity = (uint32_t)(((base + i) / nb) & 1);
-          if (!ptx::mbar_wait(&bars[slot], parity, kPipeTimeoutNs)) { fail(kTimeoutPipeline); ok = false; break; }
-          size_t so, d_o; uint32_t by;
-          piece(i, slice_bytes, so, d_o, by);
+          piece(i, nrows, so, d_o, by);
           for (int p = 1; p < ctx.world; ++p) {
             int dst_rank = ctx.rank + p;
             if (dst_rank >= ctx.world) dst_rank -= ctx.world;
-            ptx::bulk_store(ctx.remote(dst_local, dst_rank) + d_o, smem + (size_t)slot * kPiece, by);
+            ptx::bulk_store(ctx.remote(dst_local, dst_rank) + d_o, smem + (size_t)s * kPiece, by);
           }
           ptx::bulk_commit();
-          ptx::bulk_wait_read<1>();
-          while (next_load <= i - 1 + nb && next_load < n) issue_load(next_load++);
+          ++groups; ++st_seq;
+          ptx::bulk_wait_read<1>();                  // every slot but the one just sent has been read out
+          while (ld_seq < st_seq - 1 + kSlots && advance_ld()) issue_load();
+          if (i == n - 1 && c < tracked) g_last[c] = groups;
+          hand_over(false);
         }
-        if (!ok) { s_abort = 1; }
-        // The stores of chunk c are only known complete once all but the groups committed after
-        // them have drained: raise chunk c-1's counter now (its groups are older than the n just
-        // committed), and the last chunk's after a full drain. Keeps the pipe busy across chunks.
-        if (!s_abort) {
-          if (c > 0) {
-            bulk_wait_upto(n);
-            signal_chunk(buf, c - 1);
-          }
-          if (c == chunks - 1) {
-            ptx::bulk_wait<0>();
-            signal_chunk(buf, c);
-          }
-        }
+        if (n == 0 && c < tracked) { g_last[c] = groups; hand_over(false); }
       }
-      it_global += n;
-      if (threadIdx.x == 0 && j == 0) stamp(tiles_m * tiles_n + c, 3);
+      if (ok) hand_over(true);
+      else *aborted = 1;
+    } else if (w == 1) {
+      // ---------------------------------------------------------------- signaller
+      const uint64_t t0 = now_ns();
+      for (int c = 0; c < chunks; ++c) {
+        bool ok = true;
+        unsigned spins = 0;
+        while (true) {
+          int h, sfd = chunks;
+          asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(h) : "r"(ptx::smem_u32((const void*)handed)) : "memory");
+          if (sf_local) asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(sfd) : "r"(ptx::smem_u32((const void*)sf_done)) : "memory");
+          if (h > c && sfd > c) break;
+          if (*aborted || ((++spins & 1023u) == 0 && now_ns() - t0 > 2 * kPipeTimeoutNs)) { ok = false; break; }
+          __nanosleep(64);
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        int32_t* flag_local = flags + ((size_t)buf * ctx.world + ctx.rank) * chunks + c;
+        fence_sys();
+        for (int r = lane; r < ctx.world; r += 32)
+          if (r != ctx.rank) red_release_sys_add(ctx.remote(flag_local, r), 1);
+        if (lane == 0 && j == 0) stamp(tiles_m * tiles_n + c, 3);
+      }
+    } else if (w == 2 && sf_local) {
+      // ---------------------------------------------------------------- scale atoms (fp8)
+      const size_t sf_chunk = (size_t)kb_per_src * 512;
+      const size_t sf_lo = (sf_chunk / 16 * j / n_comm_ctas) * 16, sf_hi = (sf_chunk / 16 * (j + 1) / n_comm_ctas) * 16;
+      for (int c = 0; c < chunks; ++c) {
+        const uint8_t* sf_src = sf_local + (size_t)c * sf_chunk;
+        uint8_t* sf_dst = sf_inbox + (((size_t)buf * ctx.world + ctx.rank) * chunks + c) * sf_chunk;
+        for (size_t u = sf_lo + lane * 16; u < sf_hi; u += 32 * 16) {
+          const uint4 v = *(const uint4*)(sf_src + u);
+          for (int p = 1; p < ctx.world; ++p) {
+            int dst_rank = ctx.rank + p;
+            if (dst_rank >= ctx.world) dst_rank -= ctx.world;
+            *(uint4*)(ctx.remote(sf_dst, dst_rank) + u) = v;
+          }
+        }
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(ptx::smem_u32((const void*)sf_done)), "r"(c + 1) : "memory");
+      }
     }
     finish();
   }
@@ -426,7 +478,8 @@ struct ScatterGemmT : Common {
     }
   }
   IRIS_D bool a_source(State&, int tm, int kb, ASource& s) const {
-    s.map = &tmA; s.x = kb * kBK; s.y = tm * kBM; s.bk = kb * kBK;
+    s.map = &tmA; s.x = kb * bk; s.y = tm * kBM; s.bk = kb * bk;
+    s.sf_map = &tmSFA; s.sf_row = tm * kblocks + kb;
     return true;
   }
   IRIS_D bool reducing() const {
@@ -435,6 +488,7 @@ struct ScatterGemmT : Common {
   static constexpr bool kSwiGLU = false;
   IRIS_D int row_origin(State&, int tm) const { return tm * kBM; }
   IRIS_D void begin_tile(State& st, int tm, int tn, uint8_t*) const {
+    if (mode == IRIS_GEMM_AR_ONE_SHOT && st.buf < 0) st.buf = read_epoch(sb) & 1;
     if (!reducing()) return;
     if (st.buf < 0) {
       const int e = read_epoch(sb);
@@ -458,6 +512,11 @@ struct ScatterGemmT : Common {
     }
   }
   IRIS_D bool reduce_here(State& st) const { return st.mine; }
+  // A tile finished elsewhere always leaves as bulk stores into the owner's staging; a tile finished here
+  // leaves through the output's tensor maps when it stays on this rank (reduce-scatter), and by rows
+  // when every rank gets it (all-reduce: multimem / per-peer stores).
+  IRIS_D bool bulk_tile(State& st) const { return !st.mine || (c_bulk != 0 && mode != IRIS_GEMM_ALL_REDUCE); }
+  IRIS_D bool signals_tile(State& st) const { return !st.mine; }
   // Staging slot layout (private to this kernel): [64-col chunk][quarter][32 rows][width cols],
   // 16-byte groups XOR-swizzled by row exactly as staged in shared memory by the epilogue.
   IRIS_D void add_partials(State& st, int quarter, int c32, int lane, uint32_t (&acc)[32]) const {
@@ -515,9 +574,35 @@ struct ScatterGemmT : Common {
       }
     }
   }
-  IRIS_D void store16(State&, int row, int col, uint4 v) const {
+  // Add the 8 16-bit values to the same place of every rank's output (remote atomics; in the switch with NVLS).
+  IRIS_D void add_everywhere(uint8_t* local_ptr, uint4 v) const {
+    if (use_mc) {
+      multimem::V4 m{v.x, v.y, v.z, v.w};
+      if (bf16) multimem::red_add_bf16x8(ctx.mc(local_ptr), m);
+      else multimem::red_add_f16x8(ctx.mc(local_ptr), m);
+      return;
+    }
+    const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+    for (int p = 0; p < ctx.world; ++p) {
+      int r = ctx.rank + p;
+      if (r >= ctx.world) r -= ctx.world;
+      uint8_t* dst = ctx.remote(local_ptr, r);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (bf16) asm volatile("red.relaxed.sys.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + 4 * e), "r"(w4[e]) : "memory");
+        else asm volatile("red.relaxed.sys.global.add.noftz.f16x2 [%0], %1;" ::"l"(dst + 4 * e), "r"(w4[e]) : "memory");
+      }
+    }
+  }
+  IRIS_D void store16(State& st, int row, int col, uint4 v) const {
     if (row >= sh.M || col >= sh.N) return;
     switch (mode) {
+      case IRIS_GEMM_AR_ONE_SHOT:      // my partial, into slot [call parity][my rank] of every rank's staging
+        store_everywhere(staging + ((((size_t)st.buf * ctx.world + ctx.rank) * sh.M + row) * sh.N + col) * 2, v);
+        break;
+      case IRIS_GEMM_AR_ATOMIC:
+        add_everywhere(out + ((int64_t)row * ld_out + col) * 2, v);
+        break;
       case IRIS_GEMM_ALL_GATHER:
         store_everywhere(out + (((int64_t)ctx.rank * sh.M + row) * ld_out + col) * 2, v);
         break;
@@ -537,14 +622,70 @@ struct ScatterGemmT : Common {
   }
   // A tile finished elsewhere: rows [32*quarter, +32) x columns [64*chunk, +width) go to the
   // owner's staging slot as one contiguous piece.
-  IRIS_D void store_chunk(State& st, int quarter, int chunk, int width, const uint8_t* smem) const {
+  IRIS_D void store_chunk(State& st, int quarter, int chunk, int width, const uint8_t* smem, int row, int col) const {
+    if (st.mine) {
+      store_chunk_local(width, smem, mode == IRIS_GEMM_REDUCE_SCATTER ? row - ctx.rank * tiles_m_per_rank * kBM : row, col);
+      return;
+    }
     uint8_t* dst = st.slot + (size_t)chunk * (kBM * 64 * 2) + (size_t)quarter * (32 * width * 2);
     ptx::bulk_store(dst, smem, 32 * width * 2);
   }
-  IRIS_D void tile_done(State& st, int, int) const {
+  IRIS_D void tile_done(State& st, int tm, int tn) const {
+    if (mode == IRIS_GEMM_AR_ONE_SHOT) {       // this tile of my partial is on its way to every rank: count it everywhere
+      int32_t* fl = flags + (size_t)st.buf * max_owned + (tm * tiles_n + tn);
+      fence_sys();
+      if (use_mc) {
+        multimem::red_release_add_u32(ctx.mc(fl), 1);
+      } else {
+        for (int p = 0; p < ctx.world; ++p) {
+          int r = ctx.rank + p;
+          if (r >= ctx.world) r -= ctx.world;
+          red_release_sys_add(ctx.remote(fl, r), 1);
+        }
+      }
+      return;
+    }
     if (!reducing() || st.mine) return;
     fence_sys();
     red_release_sys_add(ctx.remote(flags + (size_t)st.buf * max_owned + st.lt, st.owner), 1);
+  }
+  // One-shot all-reduce, second half: the CTAs share out the output tiles; a tile is summed (fp32) over
+  // the W partials in this rank's staging once its counter shows W arrivals for this call. Only this
+  // rank's own output is written, so the kernel needs no cross-rank round at its end: collecting every
+  // rank's partials for call k proves that all ranks have left call k - 1 (the parity double-buffering).
+  IRIS_D void one_shot_reduce(int epoch) const {
+    __shared__ int s_ok;
+    const int buf = epoch & 1;
+    const int32_t target = ((epoch >> 1) + 1) * ctx.world;
+    const int units_per_row = bn / 8;
+    for (int t = blockIdx.x; t < tiles_m * tiles_n; t += gridDim.x) {
+      __syncthreads();
+      if (threadIdx.x == 0) s_ok = wait_flag_ge(ctx, flags + (size_t)buf * max_owned + t, target) ? 1 : 0;
+      __syncthreads();
+      if (!s_ok) return;
+      const int tm = t / tiles_n, tn = t - tm * tiles_n;
+      for (int u = threadIdx.x; u < kBM * units_per_row; u += blockDim.x) {
+        const int r = u / units_per_row, row = tm * kBM + r, col = tn * bn + (u - r * units_per_row) * 8;
+        if (row >= sh.M || col >= sh.N) continue;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int src = 0; src < ctx.world; ++src) {
+          const uint4 v = __ldcg((const uint4*)(staging + ((((size_t)buf * ctx.world + src) * sh.M + row) * sh.N + col) * 2));
+          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = bf16 ? __bfloat1622float2(*(const __nv_bfloat162*)&w4[e]) : __half22float2(*(const __half2*)&w4[e]);
+            acc[2 * e] += f.x; acc[2 * e + 1] += f.y;
+          }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (bf16) { __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]); o[e] = *(uint32_t*)&h; }
+          else { __half2 h = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]); o[e] = *(uint32_t*)&h; }
+        }
+        *(uint4*)(out + ((int64_t)row * ld_out + col) * 2) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
   }
   IRIS_D void comm_main(uint8_t*, int) const {}
   IRIS_D void post_main() const {
@@ -553,7 +694,8 @@ struct ScatterGemmT : Common {
     // too because a rank that owns no tile would otherwise never learn that its peers moved on.
     // Row reduce-scatter needs none: waiting for every peer's partials in call k proves that all
     // ranks left call k-1, which is what makes the double-buffered staging safe to reuse.
-    if (mode != IRIS_GEMM_REDUCE_SCATTER) {
+    if (mode == IRIS_GEMM_AR_ONE_SHOT) one_shot_reduce(epoch);
+    if (mode != IRIS_GEMM_REDUCE_SCATTER && mode != IRIS_GEMM_AR_ONE_SHOT) {
       grid_exit_barrier(ctx, sb, epoch, 0);
     } else {
       __syncthreads();
@@ -602,6 +744,16 @@ void choose_tile(int M, int N, int ctas, int bn_fixed, int pair_mode, bool pair_
 
 template <class Policy>
 int dispatch(const Policy& pol, int bn, bool kmajor, int grid, cudaStream_t stream) {
+  if (pol.fp8) {      // e4m3 with hardware block scaling: K-major B, tiles at most 240 wide
+    if (!kmajor) return -30;
+    if (pol.pair) {
+      if (bn == 224) return launch<Config<224, true, 6, true, true>>(pol, grid, stream);
+      return -30;
+    }
+    if (bn == 224) return launch<Config<224, true, 4, false, true>>(pol, grid, stream);
+    if (bn == 128) return launch<Config<128, true, 5, false, true>>(pol, grid, stream);
+    return -30;
+  }
   if (pol.pair) {
     if (kmajor) {
       if (bn == 256) return launch<Config<256, true, 6, true>>(pol, grid, stream);
@@ -624,13 +776,22 @@ int dispatch(const Policy& pol, int bn, bool kmajor, int grid, cudaStream_t stre
   return -30;
 }
 
+bool is_fp8(const IrisGemmDesc* d) { return d->in_dtype == IRIS_F8E4M3; }
+
+// `sf_a_atoms`: scale atoms behind d->sf_a (rows of A this call reads directly, in 128-row tiles, times
+// the K blocks of those rows).
 int fill_common(Common& c, const IrisGemmDesc* d, int bn, int pair, int gemm_ctas, const void* A, uint64_t a_rows,
                 uint64_t a_cols, int64_t lda) {
   if (d->dtype != IRIS_BF16 && d->dtype != IRIS_F16) return -2;
-  if (d->N % 8 || d->K % 8) return -3;
-  int r = make_map(&c.tmA, A, d->dtype, a_rows, a_cols, lda, kBK, kBM);
+  const bool f8 = is_fp8(d);
+  if (d->in_dtype != 0 && !f8 && d->in_dtype != d->dtype) return -2;
+  if (d->N % 8 || d->K % (f8 ? 16 : 8)) return -3;
+  const int in_dt = f8 ? IRIS_F8E4M3 : d->dtype;
+  const int bk = f8 ? 128 : kBK;
+  int r = make_map(&c.tmA, A, in_dt, a_rows, a_cols, lda, bk, kBM);
   if (r) return r;
-  if (d->b_kmajor) r = make_map(&c.tmB, d->B, d->dtype, d->N, d->K, d->ldb, kBK, pair ? bn / 2 : bn);
+  if (f8 && !d->b_kmajor) return -13;       // e4m3 weights are taken as [N, K]
+  if (d->b_kmajor) r = make_map(&c.tmB, d->B, in_dt, d->N, d->K, d->ldb, bk, pair ? bn / 2 : bn);
   else r = make_map(&c.tmB, d->B, d->dtype, d->K, d->N, d->ldb, 64, 64);
   if (r) return r;
   c.sh = Shape{d->M, d->N, d->K};
@@ -642,6 +803,17 @@ int fill_common(Common& c, const IrisGemmDesc* d, int bn, int pair, int gemm_cta
   c.n_gemm_ctas = gemm_ctas;
   c.bf16 = d->dtype == IRIS_BF16;
   c.bn = bn;
+  c.fp8 = f8;
+  c.bk = bk;
+  c.kblocks = ceil_div(d->K, bk);
+  c.sfb_atoms = ceil_div(bn, 128);
+  if (f8) {
+    if (!d->sf_a || !d->sf_b) return -14;
+    r = make_sf_map(&c.tmSFA, d->sf_a, (uint64_t)ceil_div((int)a_rows, kBM) * ceil_div((int)a_cols, bk), 1);
+    if (r) return r;
+    r = make_sf_map(&c.tmSFB, d->sf_b, (uint64_t)c.tiles_n * c.kblocks * c.sfb_atoms, c.sfb_atoms);
+    if (r) return r;
+  }
   c.bias_row = d->bias_row;
   c.bias_col = d->bias_col;
   c.status = d->ctx.status;
@@ -653,7 +825,8 @@ struct Plan {
   int bn, pair, gemm_ctas, comm_ctas;
   int chunks, rows_per_src, cols_per_src;
   int max_owned, tiles_m_per_rank, tiles_per_rank;
-  uint64_t inbox_bytes, flags_bytes, staging_bytes;
+  uint64_t inbox_bytes, flags_bytes, staging_bytes, sf_inbox_bytes;
+  int kb_per_src;
 };
 
 int make_plan(const IrisGemmDesc* d, Plan& p) {
@@ -662,10 +835,11 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
   const int sms = sm_count();
   const bool ag = d->op == IRIS_GEMM_AG_M || d->op == IRIS_GEMM_AG_K;
   p.comm_ctas = ag && W > 1 ? (d->comm_ctas > 0 ? d->comm_ctas : 8) : 0;
+  // With NVLS the gather is done by a warp of every GEMM CTA: no communication CTAs unless asked for.
   if (ag && W > 1 && d->comm_ctas <= 0 && d->gemm_ctas <= 0) {
     // Communication CTAs are free as long as the GEMM keeps its number of waves: give them every
     // SM the last wave would leave idle (between 8 and 32).
-    const int bn0 = d->bn > 0 ? d->bn : 256;
+    const int bn0 = d->bn > 0 ? d->bn : (is_fp8(d) ? 224 : 256);
     const int tiles = ceil_div(d->M, kBM) * ceil_div(d->N, bn0);
     const int waves = ceil_div(tiles, sms - 8);
     int spare = sms - ceil_div(tiles, waves);
@@ -687,19 +861,31 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
     case IRIS_GEMM_RS_TILES: pair_ok = false; break;
     default: pair_ok = pair_ok && d->M % (2 * kBM) == 0; break;
   }
-  choose_tile(d->M, d->N, p.gemm_ctas, d->bn, d->two_sm, pair_ok, p.bn, p.pair);
+  if (is_fp8(d)) {
+    // block-scaled e4m3 tiles are 224 (or 128) wide: two accumulator buffers plus the scale cells fill TMEM.
+    // CTA pairs only on request.
+    if (d->bn != 0 && d->bn != 224 && d->bn != 128) return -5;
+    choose_tile(d->M, d->N, p.gemm_ctas, d->bn == 128 ? 128 : 224, d->two_sm == 2 ? 2 : 1, pair_ok && d->bn != 128, p.bn, p.pair);
+  } else {
+    choose_tile(d->M, d->N, p.gemm_ctas, d->bn, d->two_sm, pair_ok, p.bn, p.pair);
+  }
   if (p.pair) p.gemm_ctas &= ~1;
   const int tiles_n = ceil_div(d->N, p.bn);
   if (d->op == IRIS_GEMM_AG_M) {
     if (d->M_local % kBM || d->M != d->M_local * W) return -6;
     p.rows_per_src = d->M_local; p.cols_per_src = d->K; p.chunks = d->M_local / kBM;
   } else if (d->op == IRIS_GEMM_AG_K) {
-    if (d->K_local % kBK || d->K != d->K_local * W) return -6;
+    if (d->K_local % (is_fp8(d) ? 128 : kBK) || d->K != d->K_local * W) return -6;
     p.rows_per_src = d->M; p.cols_per_src = d->K_local; p.chunks = tiles_m;
   }
   if (ag) {
-    p.inbox_bytes = 2ull * W * p.rows_per_src * p.cols_per_src * 2;
+    p.inbox_bytes = 2ull * W * p.rows_per_src * p.cols_per_src * (is_fp8(d) ? 1 : 2);
     p.flags_bytes = 2ull * W * p.chunks * 4;
+    if (is_fp8(d)) {
+      if (p.cols_per_src % 128 || p.rows_per_src % kBM) return -6;     // whole scale atoms per source
+      p.kb_per_src = p.cols_per_src / 128;
+      p.sf_inbox_bytes = 2ull * W * p.chunks * p.kb_per_src * 512;
+    }
   }
   if (d->op == IRIS_GEMM_REDUCE_SCATTER) {
     if (tiles_m % W || d->M % (W * kBM)) return -7;
@@ -707,6 +893,9 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
     p.max_owned = p.tiles_m_per_rank * tiles_n;
   } else if (d->op == IRIS_GEMM_ALL_REDUCE) {
     p.max_owned = p.pair ? 2 * ceil_div((tiles_m / 2) * tiles_n, W) : ceil_div(tiles_m * tiles_n, W);
+  } else if (d->op == IRIS_GEMM_AR_ONE_SHOT) {
+    if (d->N % 8) return -3;
+    p.max_owned = tiles_m * tiles_n;            // one arrival counter per tile
   } else if (d->op == IRIS_GEMM_RS_TILES) {
     p.tiles_per_rank = (tiles_m * tiles_n) / W;
     if (p.tiles_per_rank == 0) p.tiles_per_rank = 1;
@@ -714,7 +903,7 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
     if (p.max_owned < p.tiles_per_rank) p.max_owned = p.tiles_per_rank;
   }
   if (p.max_owned) {
-    p.staging_bytes = 2ull * W * p.max_owned * kBM * p.bn * 2;
+    p.staging_bytes = d->op == IRIS_GEMM_AR_ONE_SHOT ? 2ull * W * d->M * d->N * 2 : 2ull * W * p.max_owned * kBM * p.bn * 2;
     p.flags_bytes = 2ull * p.max_owned * 4;
   }
   return 0;
@@ -735,6 +924,11 @@ extern "C" int iris_gemm_workspace(const IrisGemmDesc* d, uint64_t* inbox_bytes,
   return 0;
 }
 
+extern "C" uint64_t iris_gemm_sf_inbox_bytes(const IrisGemmDesc* d) {
+  Plan p;
+  return make_plan(d, p) ? 0 : p.sf_inbox_bytes;
+}
+
 extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   Plan p;
@@ -750,6 +944,7 @@ extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
     r = fill_common(pol, d, p.bn, p.pair, p.gemm_ctas, d->A, d->M, d->K, d->lda);
     if (r) return r;
     pol.C = (uint8_t*)d->C; pol.ldc = d->ldc;
+    pol.c_bulk = make_out_maps(&pol.tmC, &pol.tmC32, d->C, d->dtype, d->M, d->N, d->ldc);
     const int ctas = (pol.order_m * pol.tiles_n) << p.pair;   // no more CTAs than tiles
     return dispatch(pol, p.bn, d->b_kmajor != 0, ctas < grid ? ctas : grid, stream);
   }
@@ -758,21 +953,33 @@ extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
     // tmA covers this rank's shard only
     r = fill_common(pol, d, p.bn, p.pair, p.gemm_ctas, d->A, p.rows_per_src, p.cols_per_src, d->lda);
     if (r) return r;
+    const bool f8 = is_fp8(d);
+    pol.tmSFInbox = pol.tmSFA;
     if (ctx.world > 1) {
-      r = make_map(&pol.tmInbox, d->inbox, d->dtype, 2ull * ctx.world * p.rows_per_src, p.cols_per_src, p.cols_per_src,
-                   kBK, kBM);
+      r = make_map(&pol.tmInbox, d->inbox, f8 ? (int)IRIS_F8E4M3 : d->dtype, 2ull * ctx.world * p.rows_per_src, p.cols_per_src,
+                   p.cols_per_src, f8 ? 128 : kBK, kBM);
       if (r) return r;
+      if (f8) {
+        if (!d->sf_inbox) return -14;
+        r = make_sf_map(&pol.tmSFInbox, d->sf_inbox, 2ull * ctx.world * p.chunks * p.kb_per_src, 1);
+        if (r) return r;
+      }
     } else {
       pol.tmInbox = pol.tmA;
     }
+    pol.esz = f8 ? 1 : 2;
+    pol.kb_per_src = p.cols_per_src / pol.bk;
+    pol.sf_local = f8 ? (const uint8_t*)d->sf_a : nullptr;
+    pol.sf_inbox = (uint8_t*)d->sf_inbox;
     pol.ctx = ctx; pol.sb = (SyncBlock*)d->sync_block;
     pol.A_local = (const uint8_t*)d->A; pol.lda = d->lda;
     pol.inbox = (uint8_t*)d->inbox; pol.flags = d->flags;
     pol.C = (uint8_t*)d->C; pol.ldc = d->ldc;
+    pol.c_bulk = make_out_maps(&pol.tmC, &pol.tmC32, d->C, d->dtype, d->M, d->N, d->ldc);
     pol.mode = d->op == IRIS_GEMM_AG_M ? 0 : 1;
     pol.rows_per_src = p.rows_per_src; pol.cols_per_src = p.cols_per_src; pol.chunks = p.chunks;
     pol.n_comm_ctas = p.comm_ctas; pol.use_mc = use_mc;
-    if ((p.cols_per_src * 2) % 16) return -8;
+    if ((p.cols_per_src * pol.esz) % 16) return -8;
     return dispatch(pol, p.bn, d->b_kmajor != 0, grid, stream);
   }
   auto fill = [&](auto& pol) -> int {
@@ -783,10 +990,15 @@ extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
     pol.staging = (uint8_t*)d->staging; pol.flags = d->flags;
     pol.max_owned = p.max_owned; pol.tiles_m_per_rank = p.tiles_m_per_rank; pol.tiles_per_rank = p.tiles_per_rank;
     pol.use_mc = use_mc;
+    pol.c_bulk = 0;
+    if (d->op == IRIS_GEMM_REDUCE_SCATTER)
+      pol.c_bulk = make_out_maps(&pol.tmC, &pol.tmC32, d->C, d->dtype, (uint64_t)p.tiles_m_per_rank * kBM, d->N, d->ldc);
+    else if (d->op == IRIS_GEMM_RS_TILES)
+      pol.c_bulk = make_out_maps(&pol.tmC, &pol.tmC32, d->C, d->dtype, d->M, d->N, d->ldc);
     return 0;
   };
   // reducers stride over all GEMM CTAs, so launch the full grid even for few tiles
-  if (d->op == IRIS_GEMM_ALL_GATHER || d->op == IRIS_GEMM_ALL_SCATTER) {
+  if (d->op == IRIS_GEMM_ALL_GATHER || d->op == IRIS_GEMM_ALL_SCATTER || d->op == IRIS_GEMM_AR_ONE_SHOT || d->op == IRIS_GEMM_AR_ATOMIC) {
     ScatterGemmT<false> pol;
     r = fill(pol);
     if (r) return r;

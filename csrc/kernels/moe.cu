@@ -251,9 +251,6 @@ struct GroupedGemm : Common {
       if (p && col < dm.D) *(uint4*)(p + (size_t)col * 2) = v;
     }
   }
-  IRIS_D void store_chunk(State&, int, int, int, const uint8_t*) const {}
-  IRIS_D bool reduce_here(State&) const { return false; }
-  IRIS_D void add_partials(State&, int, int, int, uint32_t (&)[32]) const {}
   IRIS_D void tile_done(State&, int, int) const {}
 
   // Dispatch (stage 1 only): groups (local expert j, destination) in j-major order, the order in
@@ -422,7 +419,7 @@ int iris_moe_forward(const IrisMoeDesc* d, void* stream_) {
     if (r) return r;
     pol.sh = Shape{d->capacity, 2 * d->F, d->D};
     pol.tiles_m = 0; pol.tiles_n = (2 * d->F) / 256; pol.group_m = 1;
-    pol.n_gemm_ctas = sms - comm; pol.bf16 = 1; pol.bn = 256;
+    pol.n_gemm_ctas = sms - comm; pol.bf16 = 1; pol.bn = 256; pol.fp8 = 0; pol.bk = kBK; pol.kblocks = 0; pol.sfb_atoms = 0; pol.c_bulk = 0;
     pol.bias_row = nullptr; pol.bias_col = nullptr; pol.status = d->ctx.status; pol.timeline = nullptr;
     pol.ctx = ctx; pol.sb = nullptr; pol.dm = dm; pol.meta = m;
     pol.x = (const uint8_t*)d->x; pol.inbox = (uint8_t*)d->inbox; pol.H = (uint8_t*)d->H; pol.comb = (uint8_t*)d->comb;
@@ -439,7 +436,7 @@ int iris_moe_forward(const IrisMoeDesc* d, void* stream_) {
     if (r) return r;
     pol.sh = Shape{d->capacity, d->D, d->F};
     pol.tiles_m = 0; pol.tiles_n = d->D / 256; pol.group_m = 1;
-    pol.n_gemm_ctas = sms; pol.bf16 = 1; pol.bn = 256;
+    pol.n_gemm_ctas = sms; pol.bf16 = 1; pol.bn = 256; pol.fp8 = 0; pol.bk = kBK; pol.kblocks = 0; pol.sfb_atoms = 0; pol.c_bulk = 0;
     pol.bias_row = nullptr; pol.bias_col = nullptr; pol.status = d->ctx.status; pol.timeline = nullptr;
     pol.ctx = ctx; pol.sb = (SyncBlock*)d->sync_gemm2; pol.dm = dm; pol.meta = m;
     pol.x = nullptr; pol.inbox = (uint8_t*)d->inbox; pol.H = (uint8_t*)d->H; pol.comb = (uint8_t*)d->comb;

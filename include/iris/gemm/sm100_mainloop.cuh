@@ -33,26 +33,46 @@ constexpr uint64_t kPipeTimeoutNs = 4000000000ull;
 // stages its own 128 rows of A and HALF of the B tile (so a stage is at most 32 KB, six fit, and B
 // leaves L2 once per pair); the even CTA issues the MMAs for both, each CTA's 128 accumulator rows
 // live in its own TMEM and each CTA runs its own epilogue.
-template <int BN_, bool kBKMajor_, int kStages_, bool kPair_ = false>
+//
+// kFp8_: e4m3 operands with block scales applied by the tensor core (tcgen05.mma.kind::mxf8f6f4.
+// block_scale). A stage still holds 128 bytes of K per row, i.e. 128 elements = one scale block of
+// the 1 x 128 / 128 x 128 quantisation; it is consumed by four MMAs of K 32, each with its own
+// UE8M0 scale byte per row (the four bytes of a block are equal when the scales come from a 128-wide
+// quantiser). Per stage the producer also brings one scale atom for the tile's 128 rows of A and
+// ceil(BN / 128) atoms for B (512 bytes each: row r of the atom at byte (r % 32) * 16 + (r / 32) * 4,
+// four bytes = the four K groups); the MMA thread copies them to TMEM (tcgen05.cp) in front of the
+// block's MMAs. The two accumulator buffers are packed BN columns apart and the scales use 16
+// columns behind them, so BN is at most 240.
+template <int BN_, bool kBKMajor_, int kStages_, bool kPair_ = false, bool kFp8_ = false>
 struct Config {
   static constexpr int BN = BN_;
   static constexpr bool kBKMajor = kBKMajor_;
   static constexpr int kStages = kStages_;
   static constexpr bool kPair = kPair_;
+  static constexpr bool kFp8 = kFp8_;
+  static constexpr int kBKElems = kFp8_ ? 128 : kBK;                    // elements of K per stage (128 bytes per row either way)
+  static constexpr int kUmmaKElems = kFp8_ ? 32 : kUmmaK;               // K of one MMA (32 bytes per row either way)
   static constexpr int kBCols = kPair_ ? BN_ / 2 : BN_;                 // columns of B staged by one CTA
   static constexpr int kABytes = kBM * kBK * 2;                         // 16 KB
   static constexpr int kBBoxes = kBKMajor_ ? 1 : (kBCols + 63) / 64;    // MN-major: 64(n) x 64(k) boxes
   static constexpr int kBBytes = kBKMajor_ ? kBCols * kBK * 2 : kBBoxes * 8192;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kAccCols = 256;                                  // column pitch of an accumulator buffer
+  static constexpr int kSfbAtoms = kFp8_ ? (BN_ + 127) / 128 : 0;       // scale atoms of B per stage (every CTA of a pair holds all of them)
+  static constexpr int kSfBytes = kFp8_ ? (1 + kSfbAtoms) * 512 : 0;    // scale bytes per stage
+  static constexpr int kAccCols = kFp8_ ? BN_ : 256;                    // column pitch of an accumulator buffer
+  static constexpr int kSfaCol = 2 * kAccCols;                          // TMEM columns of the scales (fp8 only): A 4, then B 4 per atom;
+  static constexpr int kSfbCol = kSfaCol + 4;                           // two such sets, used by alternate K blocks, so that the copy
+  static constexpr int kSfSetCols = 4 + 4 * kSfbAtoms;                  // for block kb + 1 does not wait for the MMAs of block kb
   static constexpr int kTmemCols = 512;
   static constexpr int kEpiWarpBytes = 2 * 4096 + 256;                  // per warp: 8 KB of staging (two 32-row x 64-col chunks,
                                                                         // or one 32-row x 128-col round) + 256 B of policy scratch
+                                                                        // (all staging first, 1024-byte aligned, then the scratch)
   static constexpr int kEpiBytes = kEpiWarps * kEpiWarpBytes;
-  static constexpr int kSmemBytes = 1024 + kStages_ * kStageBytes + kEpiBytes + 256;
+  static constexpr int kSmemBytes = 1024 + kStages_ * (kStageBytes + kSfBytes) + kEpiBytes + 256;
   static_assert(BN_ % 32 == 0 && BN_ >= 32 && BN_ <= 256, "BN must be a multiple of 32 up to 256");
   static_assert(!kPair_ || kBCols % 16 == 0, "a pair splits B into two halves of whole 16-column groups");
   static_assert(kStageBytes % 1024 == 0, "stages keep the 1024-byte alignment of the 128-byte swizzle");
+  static_assert(!kFp8_ || (kBKMajor_ && 2 * BN_ + 2 * (4 + 4 * kSfbAtoms) <= 512), "fp8: K-major B, and accumulators plus scales must fit TMEM");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
@@ -75,6 +95,17 @@ IRIS_HD uint32_t make_idesc(int n, bool bf16, bool b_mn_major, int m = kBM) {
          ((uint32_t)(m >> 4) << 24);
 }
 
+// Instruction descriptor, kind::mxf8f6f4.block_scale: e4m3 x e4m3, both K-major, UE8M0 scales.
+// `sf_id` (0..3) selects which byte of the 32-bit scale cells in TMEM this MMA uses, for A and for B.
+IRIS_HD uint32_t make_idesc_mxf8(int n, int m, uint32_t sf_id) {
+  return (sf_id << 4) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(m >> 4) << 24) | (sf_id << 29);
+}
+// Shared-memory descriptor of one scale atom for tcgen05.cp: K-major, no swizzle, 8-row x 16-byte
+// core matrices stacked 128 bytes apart (SBO); a single core matrix along K, so LBO is unused.
+IRIS_D uint64_t desc_sf(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+
 struct Shape {
   int M, N, K;
 };
@@ -85,6 +116,9 @@ struct ASource {
   int x, y;   // coordinates of the A box in `map`
   int bk;     // K offset of the matching B rows/columns (differs from x when A is gathered along K)
   int bn0;    // first output column of the tile inside B's N dimension (grouped GEMMs offset it per group)
+  // fp8 only: where the scale atom of this (128-row tile, K block) is: row of a [atoms, 128 x u32] map
+  const CUtensorMap* sf_map;
+  int sf_row;
 };
 
 // GROUP_M swizzled tile order (same idea as the reference's GROUP_SIZE_M, all_reduce.py:182-187).
@@ -120,12 +154,16 @@ struct Pipeline {
 //        [gate 128 | up 128]; emit silu(gate) * up, 128 columns per 256-wide tile)
 //   void store16(State&, int row, int col, uint4 v) const; (8 consecutive outputs of one row)
 //   float row_bias(int row) const;  float col_bias(int col) const;  bool has_bias() const;
-//   static constexpr bool kBulkEpilogue;                   (true: chunks leave through store_chunk)
-//   void store_chunk(State&, int quarter, int chunk, int width, const uint8_t* smem) const;
-//        (lane 0 of an epilogue warp: issue the bulk store(s) of rows [32*quarter, +32) x columns
-//         [64*chunk, +width) of the current tile, staged in `smem` in the swizzled chunk layout)
-//   bool reduce_here(State&) const;                        (bulk policies: this tile is finished on
-//        this rank: take the row-major path and add the other ranks' partials first)
+//   static constexpr bool kBulkEpilogue;                   (true: tiles may leave through store_chunk)
+//   bool bulk_tile(State&) const;                          (this tile leaves in 64-column chunks staged in
+//        shared memory in the 128-byte-swizzle layout, each stored by ONE asynchronous bulk / tensor store)
+//   void store_chunk(State&, int quarter, int chunk, int width, const uint8_t* smem, int row, int col) const;
+//        (lane 0 of an epilogue warp: issue the store of rows [32*quarter, +32) x columns
+//         [64*chunk, +width) of the current tile, i.e. output rows [row, +32) x columns [col, +width))
+//   bool signals_tile(State&) const;                       (tile_done tells a peer about the tile, so its
+//        stores must be complete, not just issued, before that)
+//   bool reduce_here(State&) const;                        (this tile is finished on this rank: the other
+//        ranks' partials are added to the accumulators first)
 //   void add_partials(State&, int quarter, int c32, int lane, uint32_t (&acc)[32]) const;
 //        (add to the fp32 accumulators of row `lane` of the quarter, columns [32*c32, +32))
 //   void tile_done(State&, int m_tile, int n_tile) const;  (one thread, after the tile's stores)
@@ -158,8 +196,12 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
 
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
+  // epilogue staging: 8 KB per warp, 1024-byte aligned (tensor stores apply the hardware swizzle to
+  // absolute shared-memory addresses), then 256 bytes of policy scratch per warp, then the scales
   uint8_t* epi_base = smem + Cfg::kStages * Cfg::kStageBytes;
-  uint64_t* bars = (uint64_t*)(epi_base + Cfg::kEpiBytes);
+  uint8_t* scratch_base = epi_base + kEpiWarps * 8192;
+  uint8_t* sf_base = scratch_base + kEpiWarps * 256;               // fp8: per stage one scale atom of A, then B's
+  uint64_t* bars = (uint64_t*)(sf_base + Cfg::kStages * Cfg::kSfBytes);
   Pipeline pipe{bars, bars + Cfg::kStages, bars + 2 * Cfg::kStages, bars + 2 * Cfg::kStages + 2};
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * Cfg::kStages + 4);
 
@@ -191,7 +233,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
 
   const int num_tiles = pol.num_tiles();
-  const int k_blocks = (sh.K + kBK - 1) / kBK;
+  const int k_blocks = (sh.K + Cfg::kBKElems - 1) / Cfg::kBKElems;
   const int first = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int step = kPair ? pol.gemm_ctas() >> 1 : pol.gemm_ctas();
   // the epilogue warp's arrival that hands an accumulator buffer back to the MMA issuer
@@ -222,7 +264,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
           uint8_t* sa = stage_base + s * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
           if constexpr (kPair) {
-            if (leader) ptx::mbar_expect_tx(&pipe.full[s], 2 * Cfg::kStageBytes);
+            if (leader) ptx::mbar_expect_tx(&pipe.full[s], 2 * (Cfg::kStageBytes + Cfg::kSfBytes));
             const int n0 = as.bn0 + (int)cta * Cfg::kBCols;
             ptx::tma_load_2d_pair(sa, as.map, &pipe.full[s], as.x, as.y);
             if constexpr (Cfg::kBKMajor) {
@@ -233,7 +275,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
                 ptx::tma_load_2d_pair(sb + j * 8192, pol.b_map(), &pipe.full[s], n0 + j * 64, as.bk);
             }
           } else {
-            ptx::mbar_expect_tx(&pipe.full[s], Cfg::kStageBytes);
+            ptx::mbar_expect_tx(&pipe.full[s], Cfg::kStageBytes + Cfg::kSfBytes);
             ptx::tma_load_2d(sa, as.map, &pipe.full[s], as.x, as.y);
             if constexpr (Cfg::kBKMajor) {
               ptx::tma_load_2d(sb, pol.b_map(), &pipe.full[s], as.bk, as.bn0);
@@ -241,6 +283,19 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
 #pragma unroll
               for (int j = 0; j < Cfg::kBBoxes; ++j)
                 ptx::tma_load_2d(sb + j * 8192, pol.b_map(), &pipe.full[s], as.bn0 + j * 64, as.bk);
+            }
+          }
+          if constexpr (Cfg::kFp8) {
+            // scale atoms: this tile's 128 rows of A, and all of the tile's columns of B (each
+            // CTA of a pair keeps the whole of B's scales: its MMA half multiplies every column)
+            uint8_t* ssf = sf_base + s * Cfg::kSfBytes;
+            const int brow = pol.b_sf_row(tn, as.bk / Cfg::kBKElems);   // B's K block: not kb when A is gathered along K
+            if constexpr (kPair) {
+              ptx::tma_load_2d_pair(ssf, as.sf_map, &pipe.full[s], 0, as.sf_row);
+              ptx::tma_load_2d_pair(ssf + 512, pol.sfb_map(), &pipe.full[s], 0, brow);
+            } else {
+              ptx::tma_load_2d(ssf, as.sf_map, &pipe.full[s], 0, as.sf_row);
+              ptx::tma_load_2d(ssf + 512, pol.sfb_map(), &pipe.full[s], 0, brow);
             }
           }
         }
@@ -267,12 +322,36 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         if (lane == 0) {
           const uint32_t sa = ptx::smem_u32(stage_base + s * Cfg::kStageBytes);
           const uint32_t sb = sa + Cfg::kABytes;
+          if constexpr (Cfg::kFp8) {
+            // this block's scales: shared memory -> TMEM, in front of the MMAs that use them (the
+            // copies and the MMAs of one thread execute in issue order, so the cells are rewritten
+            // only after the previous block's MMAs have read them)
+            const uint32_t ssf = ptx::smem_u32(sf_base + s * Cfg::kSfBytes);
+            const uint32_t t_sfa = tmem_base + Cfg::kSfaCol + (kb & 1) * Cfg::kSfSetCols, t_sfb = t_sfa + 4;
+            if constexpr (kPair) {
+              ptx::tmem_cp_sf_pair(t_sfa, desc_sf(ssf));
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            uint64_t ad = desc_kmajor(sa + k * (kUmmaK * 2));
-            uint64_t bd = Cfg::kBKMajor ? desc_kmajor(sb + k * (kUmmaK * 2)) : desc_mnmajor(sb + k * (kUmmaK * 128));
-            if constexpr (kPair) ptx::mma_f16_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
-            else ptx::mma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+              for (int j = 0; j < Cfg::kSfbAtoms; ++j) ptx::tmem_cp_sf_pair(t_sfb + 4 * j, desc_sf(ssf + 512 + 512 * j));
+            } else {
+              ptx::tmem_cp_sf(t_sfa, desc_sf(ssf));
+#pragma unroll
+              for (int j = 0; j < Cfg::kSfbAtoms; ++j) ptx::tmem_cp_sf(t_sfb + 4 * j, desc_sf(ssf + 512 + 512 * j));
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {     // four MMAs of K 32, each with its own scale byte
+              const uint64_t ad = desc_kmajor(sa + k * 32), bd = desc_kmajor(sb + k * 32);
+              const uint32_t id8 = make_idesc_mxf8(Cfg::BN, kPair ? 2 * kBM : kBM, (uint32_t)k);
+              if constexpr (kPair) ptx::mma_mxf8_pair(d_tmem, ad, bd, id8, (kb | k) != 0, t_sfa, t_sfb);
+              else ptx::mma_mxf8(d_tmem, ad, bd, id8, (kb | k) != 0, t_sfa, t_sfb);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              uint64_t ad = desc_kmajor(sa + k * (kUmmaK * 2));
+              uint64_t bd = Cfg::kBKMajor ? desc_kmajor(sb + k * (kUmmaK * 2)) : desc_mnmajor(sb + k * (kUmmaK * 128));
+              if constexpr (kPair) ptx::mma_f16_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
+              else ptx::mma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+            }
           }
           if constexpr (kPair) {
             ptx::mma_commit_pair(&pipe.empty[s], 3);
@@ -289,7 +368,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    uint8_t* my_epi = epi_base + (warp - 2) * Cfg::kEpiWarpBytes;
+    uint8_t* my_epi = epi_base + (warp - 2) * 8192;
     uint32_t chunk_seq = 0;   // bulk epilogue: chunks issued by this warp (selects the staging half)
     const bool bf16 = pol.is_bf16();
     const bool has_bias = pol.has_bias();
@@ -310,7 +389,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         break;
       }
       ptx::tc_fence_after();
-      pol.begin_tile(est, tm, tn, my_epi + 8192);
+      pol.begin_tile(est, tm, tn, scratch_base + (warp - 2) * 256);
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * Cfg::kAccCols;
       const int row0 = pol.row_origin(est, tm) + quarter * 32;
       const float rb = has_bias ? pol.row_bias(row0 + lane) : 0.f;
@@ -330,7 +409,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         }
       };
       bool bulk = false;
-      if constexpr (Policy::kBulkEpilogue) bulk = !pol.reduce_here(est);
+      if constexpr (Policy::kBulkEpilogue) bulk = pol.bulk_tile(est);
       if (bulk) {
         // The tile leaves in 64-column chunks: TMEM -> registers -> swizzled shared memory, then
         // ONE bulk async store per chunk (4 KB, or 2 KB for a 32-column tail) issued by lane 0
@@ -353,6 +432,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
               __syncwarp();
               if (lane == 0) release_acc(buf);
             }
+            if (pol.reduce_here(est)) pol.add_partials(est, quarter, cc * 2 + hlf, lane, r);
             uint32_t packed[16];
             pack32(r, tn * Cfg::BN + cc * 64 + hlf * 32, packed);
 #pragma unroll
@@ -366,13 +446,13 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            pol.store_chunk(est, quarter, cc, w, stage);
+            pol.store_chunk(est, quarter, cc, w, stage, row0, tn * Cfg::BN + cc * 64);
             ptx::bulk_commit();
           }
           ++chunk_seq;
         }
-        if (lane == 0) {
-          ptx::bulk_wait<0>();          // this warp's stores of the tile are complete
+        if (lane == 0 && pol.signals_tile(est)) {
+          ptx::bulk_wait<0>();          // a peer is told about this tile: this warp's stores of it are complete first
           ptx::fence_proxy_async();
         }
         __syncwarp();
@@ -442,7 +522,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
                 __syncwarp();
                 if (lane == 0) release_acc(buf);
               }
-              if constexpr (Policy::kBulkEpilogue) pol.add_partials(est, quarter, c, lane, r);
+              if constexpr (Policy::kBulkEpilogue) { if (pol.reduce_here(est)) pol.add_partials(est, quarter, c, lane, r); }
               uint32_t packed[16];
               pack32(r, col_rd + q * 32, packed);
 #pragma unroll
@@ -469,6 +549,9 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         pol.tile_done(est, tm, tn);
         pol.stamp(t, 2);
       }
+    }
+    if constexpr (Policy::kBulkEpilogue) {
+      if (lane == 0) ptx::bulk_wait<0>();   // stores still reading the staging buffers finish before the CTA leaves
     }
   }
   ptx::tc_fence_before();

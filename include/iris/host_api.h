@@ -38,6 +38,10 @@ enum IrisGemmOp {
   IRIS_GEMM_ALL_SCATTER = 6,    // GEMM then all-gather of C columns (rank r's columns at r*N)
   IRIS_GEMM_RS_TILES = 7,       // GEMM then sum over ranks; output [M, N], rank r writes only the
                                 // tiles it owns (contiguous tile blocks, last rank takes the remainder)
+  IRIS_GEMM_AR_ONE_SHOT = 8,    // all-reduce, one traversal: every rank sends its partial tiles to ALL ranks
+                                // (staging [2][W][M][N]) and every rank sums the W partials itself
+  IRIS_GEMM_AR_ATOMIC = 9,      // all-reduce by remote atomic adds of the partial tiles into every rank's
+                                // (pre-zeroed) output; 16-bit accumulation in memory, order not fixed
 };
 
 typedef struct IrisGemmDesc {
@@ -65,6 +69,17 @@ typedef struct IrisGemmDesc {
   int32_t K_local;        // AG_K: K per rank
   void* timeline;         // optional int64 [tiles + chunks][4]: per-tile timestamps in ns (0 start,
                           // 1 operands available, 2 stored; comm CTA 0 stamps slot tiles+c, col 3)
+  // Block-scaled fp8 inputs (in_dtype == IRIS_F8E4M3; 0 means "same as dtype"): A [.., K] and B [N, K]
+  // are e4m3 bytes (B K-major only), `dtype` is the 16-bit output format, lda / ldb count bytes.
+  // Scales are UE8M0 bytes (power-of-two factors) packed in 512-byte atoms of 128 rows x 4 K groups of
+  // 32 (row r at byte (r % 32) * 16 + (r / 32) * 4):
+  //   sf_a  [ceil(rows / 128)][K / 128] atoms over the rows of A this rank holds (its shard for AG_*)
+  //   sf_b  [ceil(N / bn)][K / 128][ceil(bn / 128)] atoms, rows counted from each column tile's first column
+  //   sf_inbox (AG_*): [2][W][chunks][K blocks per source] atoms of the gathered shards (heap)
+  int32_t in_dtype;
+  const void* sf_a;
+  const void* sf_b;
+  void* sf_inbox;
 } IrisGemmDesc;
 
 // Block-scaled fp8 (e4m3) GEMM: C = (A * scale_a) @ (B * scale_b)^T with A [M, K] and B [N, K]
@@ -88,6 +103,8 @@ int iris_gemm_fp8_launch(const IrisFp8GemmDesc* d, void* stream);
 int iris_gemm_workspace(const IrisGemmDesc* d, uint64_t* inbox_bytes, uint64_t* flags_bytes, uint64_t* staging_bytes,
                         int32_t* bn_out, int32_t* pair_out);
 int iris_gemm_launch(const IrisGemmDesc* d, void* stream);
+// Bytes of the scale inbox of an fp8 AG_* op (0 for every other op).
+uint64_t iris_gemm_sf_inbox_bytes(const IrisGemmDesc* d);
 
 #ifdef __cplusplus
 }

@@ -54,6 +54,12 @@ IRIS_D void red_add_bf16x8(void* mc_ptr, V4 v) {
                : "memory");
 }
 
+IRIS_D void red_add_f16x8(void* mc_ptr, V4 v) {
+  asm volatile("multimem.red.relaxed.sys.global.add.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_ptr), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 }  // namespace multimem
 }  // namespace iris
 #endif

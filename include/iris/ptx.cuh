@@ -191,6 +191,37 @@ IRIS_D void mma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Block-scaled fp8: D[tmem] (+)= (A * SFA) * (B * SFB), e4m3 inputs, one UE8M0 scale per row and 32
+// elements of K (kind::mxf8f6f4.block_scale, scale_vec::1X), fp32 accumulate. The scales sit in
+// TMEM at `sfa_tmem` / `sfb_tmem` (copied there with tmem_cp_sf); which of the four bytes of a
+// 32-bit TMEM cell this MMA uses is part of the instruction descriptor (make_idesc_mxf8).
+IRIS_D void mma_mxf8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                     uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+IRIS_D void mma_mxf8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                          uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// Shared memory -> TMEM copy of one scale-factor atom: 32 rows x 16 bytes (512 contiguous bytes,
+// described by `sdesc`, no swizzle) land in four TMEM columns starting at `taddr`, replicated to
+// the four 32-lane groups. Asynchronous, ordered with the tcgen05.mma the same thread issues after it.
+IRIS_D void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// cta_group::2 form: each CTA of the pair copies from its own shared memory into its own TMEM.
+IRIS_D void tmem_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 // Arrive on an mbarrier of this CTA once all tcgen05.mma issued so far by this thread finished.
 IRIS_D void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

@@ -64,6 +64,10 @@ class IrisGemmDesc(C.Structure):
         ("M_local", C.c_int32),
         ("K_local", C.c_int32),
         ("timeline", C.c_void_p),
+        ("in_dtype", C.c_int32),
+        ("sf_a", C.c_void_p),
+        ("sf_b", C.c_void_p),
+        ("sf_inbox", C.c_void_p),
     ]
 
 
@@ -75,6 +79,7 @@ if hasattr(torch, "float8_e4m3fn"):
     DTYPE_CODE[torch.float8_e4m3fn] = 5
 
 GEMM_LOCAL, GEMM_AG_M, GEMM_AG_K, GEMM_ALL_GATHER, GEMM_REDUCE_SCATTER, GEMM_ALL_REDUCE, GEMM_ALL_SCATTER, GEMM_RS_TILES = range(8)
+GEMM_AR_ONE_SHOT, GEMM_AR_ATOMIC = 8, 9
 
 
 def _load(path, builder):
@@ -102,6 +107,8 @@ def kernels() -> C.CDLL:
             lib.iris_gemm_workspace.argtypes = [C.POINTER(IrisGemmDesc), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
                                                 C.POINTER(C.c_uint64), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
             lib.iris_gemm_workspace.restype = C.c_int
+            lib.iris_gemm_sf_inbox_bytes.argtypes = [C.POINTER(IrisGemmDesc)]
+            lib.iris_gemm_sf_inbox_bytes.restype = C.c_uint64
             _kernels = lib
         return _kernels
 

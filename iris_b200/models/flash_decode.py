@@ -116,7 +116,11 @@ class FlashDecodeLayer:
         by_len = max(1, -(-max_len // 256))                     # at least 256 positions per split
         return max(1, min(self.max_splits, want, by_len))
 
-    def forward(self, q, k_cache, v_cache, global_kv_lens, block_table, out=None, return_lse: bool = False):
+    def forward(self, q, k_cache, v_cache, global_kv_lens, block_table, out=None, return_lse: bool = False,
+                local_only: bool = False):
+        """Decode one token per sequence. ``local_only=True`` stops after this rank's own KV shard and
+        returns its partial ``(out, lse)`` without talking to any peer (what the NCCL baseline gathers and
+        merges itself, reference: examples/benchmark/reference/flash_decode_rccl/flash_decode_layer_rccl.py:100-130)."""
         ctx = self.ctx
         B = q.shape[0]
         if B > self.max_batch:
@@ -125,10 +129,12 @@ class FlashDecodeLayer:
         kv_lens = global_kv_lens[ctx.get_rank()].contiguous()
         page = k_cache.shape[1]
         if ctx.is_cpu:
+            if local_only:
+                raise NotImplementedError("local_only decode is a GPU path")
             return self._forward_cpu(q, k_cache, v_cache, kv_lens, block_table)
         if out is None:
             out = torch.empty((B, self.Hq, self.D), dtype=q.dtype, device=q.device)
-        lse = torch.empty((B, self.Hq), dtype=torch.float32, device=q.device) if return_lse else None
+        lse = torch.empty((B, self.Hq), dtype=torch.float32, device=q.device) if (return_lse or local_only) else None
         d = IrisDecodeDesc()
         d.ctx = ctx.ctx_struct()
         d.q, d.k_cache, d.v_cache = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
@@ -142,12 +148,12 @@ class FlashDecodeLayer:
         d.splits = self.num_splits(B, block_table.shape[1] * page)
         d.sm_scale, d.soft_cap = self.sm_scale, self.soft_cap
         d.dtype = _lib.DTYPE_CODE[q.dtype]
-        d.exchange = 1
+        d.exchange = 2 if local_only else 1
         d.num_blocks = 0 if self.use_tma is False else k_cache.shape[0]     # > 0 lets the kernel fill its tiles by TMA
         if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous() and block_table.is_contiguous()):
             raise ValueError("flash decode takes contiguous q, caches and block table")
         _lib.check(self._lib().iris_flash_decode(C.byref(d), C.c_void_p(_lib.current_stream_ptr())), "flash decode launch", kernels=2)
-        return (out, lse) if return_lse else out
+        return (out, lse) if (return_lse or local_only) else out
 
     __call__ = forward
 
@@ -181,6 +187,13 @@ class FlashDecodeLayer:
             live = block_table[cols < used[:, None].to(block_table.device)]
             if live.numel() and (int(live.min()) < 0 or int(live.max()) >= blocks):
                 raise ValueError(f"block_table names a block outside the cache of {blocks} blocks")
+
+    @staticmethod
+    def merge_partials(outs: torch.Tensor, lses: torch.Tensor) -> torch.Tensor:
+        """Log-sum-exp merge of per-shard results: ``outs [W, B, Hq, D]``, ``lses [W, B, Hq]`` -> ``[B, Hq, D]``."""
+        w = torch.softmax(lses.float(), dim=0)
+        w = torch.nan_to_num(w, nan=0.0)                       # a sequence no shard holds: every lse is -inf
+        return (w[..., None] * outs.float()).sum(0).to(outs.dtype)
 
     def _forward_cpu(self, q, k_cache, v_cache, kv_lens, block_table):
         """CPU backend: same exchange layout through the shared-memory heap, math in PyTorch."""

@@ -29,11 +29,13 @@ from .. import _lib
 from ..host import artifacts as _artifacts
 from .config import FusedConfig
 from .gemm import fill_desc, matmul
-from .gemm_fp8 import dequant_matmul, matmul_fp8, quantize_1x128, quantize_128x128
+from .gemm_fp8 import (BlockScaled, dequant_matmul, matmul_fp8, matmul_fp8_blockscaled, pack_scales_a, pack_scales_b,
+                       quantize_1x128, quantize_128x128, quantize_activation, quantize_weight)
 from .workspace import FusedWorkspace
 
 __all__ = [
     "FusedConfig", "FusedWorkspace", "OpsNamespace", "matmul", "matmul_fp8", "quantize_1x128", "quantize_128x128", "dequant_matmul",
+    "BlockScaled", "quantize_activation", "quantize_weight", "matmul_fp8_blockscaled", "pack_scales_a", "pack_scales_b",
     "matmul_all_reduce", "matmul_all_reduce_preamble", "all_gather_matmul", "all_gather_matmul_preamble",
     "matmul_all_gather", "matmul_all_gather_preamble", "matmul_reduce_scatter", "matmul_reduce_scatter_preamble",
 ]
@@ -42,15 +44,52 @@ _FUSED_DTYPES = (torch.bfloat16, torch.float16)
 _DEFAULT_CONFIG = FusedConfig()      # what config=None means; never mutated
 
 
+def _is_fp8(*tensors) -> bool:
+    return all(isinstance(t, BlockScaled) for t in tensors)
+
+
 def _fusable(ctx, *tensors) -> bool:
-    return (not ctx.is_cpu) and all(t.dtype in _FUSED_DTYPES for t in tensors) and all(t.dim() == 2 for t in tensors)
+    if ctx.is_cpu:
+        return False
+    if _is_fp8(*tensors):
+        return tensors[0].kind == "activation" and tensors[-1].kind == "weight"
+    return all((not isinstance(t, BlockScaled)) and t.dtype in _FUSED_DTYPES and t.dim() == 2 for t in tensors)
+
+
+def _fp8_tile(config) -> int:
+    return 128 if config.tile_n() == 128 else 224
+
+
+def _lower_fp8(A, B, dtype):
+    """Block-scaled operands as plain matrices of ``dtype`` (the path of the CPU backend and of shapes
+    the tensor-core kernel cannot take): dequantised, then handled like 16-bit inputs."""
+    if isinstance(A, BlockScaled):
+        A = A.dequantize().to(dtype)
+    if isinstance(B, BlockScaled):
+        B = B.dequantize().to(dtype)
+    return A, B
 
 
 def _base_desc(ctx, op, M, N, K, A, B, out, config, bias_row=None, bias_col=None) -> tuple:
     d = _lib.IrisGemmDesc()
     d.op = op
     d.M, d.N, d.K = M, N, K
-    keep = fill_desc(d, A, B, out, bias_row=bias_row, bias_col=bias_col, bn=config.tile_n())
+    if _is_fp8(A, B):
+        # e4m3 operands, scales applied by the tensor core; the output tensor gives the 16-bit result format
+        if out.dtype not in _FUSED_DTYPES or out.stride(1) != 1:
+            raise TypeError("the output of an fp8 op is a row-major fp16 or bf16 tensor")
+        tile = _fp8_tile(config)
+        d.dtype, d.in_dtype, d.b_kmajor, d.bn = _lib.DTYPE_CODE[out.dtype], _lib.DTYPE_CODE[torch.float8_e4m3fn], 1, tile
+        d.A, d.lda = A.q.data_ptr(), A.q.stride(0)
+        d.B, d.ldb = B.q.data_ptr(), B.q.stride(0)
+        d.C, d.ldc = out.data_ptr(), out.stride(0)
+        sa, sb = A.sf(), B.sf(tile)
+        d.sf_a, d.sf_b = sa.data_ptr(), sb.data_ptr()
+        d.bias_row = bias_row.data_ptr() if bias_row is not None else None
+        d.bias_col = bias_col.data_ptr() if bias_col is not None else None
+        keep = (A.q, B.q, sa, sb)
+    else:
+        keep = fill_desc(d, A, B, out, bias_row=bias_row, bias_col=bias_col, bn=config.tile_n())
     d.group_m = config.group_size_m
     d.comm_ctas = config.comm_sms
     d.two_sm = 0 if config.two_sm is None else (2 if config.two_sm else 1)
@@ -81,6 +120,9 @@ def _make_workspace(ctx, operation, shape, dtype, variant, d) -> FusedWorkspace 
     if staging:
         ws.staging = ctx.heap.allocate(staging, torch.uint8)
         ws.aux_buffer = ws.staging
+    sf_inbox = int(_lib.kernels().iris_gemm_sf_inbox_bytes(C.byref(d)))
+    if sf_inbox:        # fp8 all-gather: the gathered shards' scale atoms
+        ws.extra["sf_inbox"] = ctx.heap.allocate(sf_inbox, torch.uint8)
     ws.prepared = True
     # arrival counters count communication CTAs: the number used at creation is part of the workspace
     ws.extra["comm_ctas"] = d.comm_ctas
@@ -151,7 +193,7 @@ def _refresh_bias(keep) -> None:
 
 
 def _ptr_key(*tensors):
-    return tuple((t.data_ptr(), t.stride(0)) if t is not None else None for t in tensors)
+    return tuple(None if t is None else (t.key() if isinstance(t, BlockScaled) else (t.data_ptr(), t.stride(0))) for t in tensors)
 
 
 def _launch(ctx, d, ws) -> None:
@@ -160,6 +202,8 @@ def _launch(ctx, d, ws) -> None:
     d.flags = ws.flags.data_ptr() if ws.flags is not None else None
     d.staging = ws.staging.data_ptr() if ws.staging is not None else None
     d.bn = ws.bn
+    sfi = ws.extra.get("sf_inbox")
+    d.sf_inbox = sfi.data_ptr() if sfi is not None else None
     d.comm_ctas = ws.extra.get("comm_ctas", d.comm_ctas)
     d.two_sm = ws.extra.get("two_sm", d.two_sm)
     tl = ws.extra.get("timeline")
@@ -232,7 +276,7 @@ def all_gather_matmul_preamble(shmem, A_sharded, B, config=None, shard_dim=1):
         return FusedWorkspace(operation="all_gather_matmul", variant="unfused", world_size=shmem.num_ranks, prepared=True)
     W = shmem.num_ranks
     shape = (A_sharded.shape[0], B.shape[1]) if shard_dim == 1 else (A_sharded.shape[0] * W, B.shape[1])
-    out = torch.empty(shape, dtype=A_sharded.dtype, device=A_sharded.device)
+    out = torch.empty(shape, dtype=torch.bfloat16 if isinstance(A_sharded, BlockScaled) else A_sharded.dtype, device=A_sharded.device)
     d, _ = _agm_desc(shmem, out, A_sharded, B, None, config, shard_dim)
     key = tuple(A_sharded.shape) + tuple(B.shape) + (shard_dim,)
     ws = _make_workspace(shmem, "all_gather_matmul", key, A_sharded.dtype, "fused", d)
@@ -262,6 +306,7 @@ def all_gather_matmul(shmem, output_tensor, A_sharded, B, bias=None, async_op=Fa
         ws = _auto_workspace(shmem, "all_gather_matmul", key, A_sharded.dtype, config,
                              lambda: all_gather_matmul_preamble(shmem, A_sharded, B, config, shard_dim), extra=B.stride(-1) == 1)
     if ws.variant == "unfused":
+        A_sharded, B = _lower_fp8(A_sharded, B, output_tensor.dtype)
         gathered = _unfused_gather(shmem, ws, A_sharded, shard_dim)
         output_tensor.copy_(_local_matmul(gathered, B, bias, bias_dim=0))
     else:
@@ -292,7 +337,7 @@ def matmul_all_gather_preamble(shmem, A, B, config=None, scatter_cols=False):
     W = shmem.num_ranks
     M, K = A.shape
     N = B.shape[1]
-    out = torch.empty((M * W, N) if not scatter_cols else (M, N * W), dtype=A.dtype, device=A.device)
+    out = torch.empty((M * W, N) if not scatter_cols else (M, N * W), dtype=torch.bfloat16 if isinstance(A, BlockScaled) else A.dtype, device=A.device)
     op = _lib.GEMM_ALL_SCATTER if scatter_cols else _lib.GEMM_ALL_GATHER
     d, _ = _base_desc(shmem, op, M, N, K, A, B, out, config)
     ws = _make_workspace(shmem, "matmul_all_gather", tuple(A.shape) + tuple(B.shape) + (scatter_cols,), A.dtype, "fused", d)
@@ -323,6 +368,7 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
         ws = _auto_workspace(shmem, "matmul_all_gather", key, A.dtype, config,
                              lambda: matmul_all_gather_preamble(shmem, A, B, config, scatter_cols), extra=B.stride(-1) == 1)
     if ws.variant == "unfused" or not shmem.is_symmetric(output_tensor):
+        A, B = _lower_fp8(A, B, output_tensor.dtype)
         local = _local_matmul(A, B, bias, bias_dim=0)
         part = _on_heap(shmem, ws, "part", local)
         if scatter_cols:
@@ -345,20 +391,47 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
 
 
 # ----------------------------------------------------------------------------- matmul_all_reduce
+# Variants (reference: iris/ops/matmul_all_reduce.py:120-144, FusedConfig.all_reduce_variant):
+#   two_shot  every tile has an owner rank; the others push their partial tile to it, the owner adds them to
+#             its own accumulators and sends the finished tile to every rank (the default for large outputs)
+#   one_shot  every rank sends its partial tiles to ALL ranks and sums the W partials itself: one NVLink
+#             traversal and no second hop, W times the traffic; for small outputs (latency bound)
+#   atomic    every rank adds its partial tiles into every rank's pre-zeroed output with remote atomics
+#             (in the switch with NVLS); 16-bit accumulation in memory, summation order not fixed
+#   auto      one_shot while the output is at most ONE_SHOT_MAX_BYTES, else two_shot
+# spinlock and ring have no fused kernel here and are refused (ctx.ccl.all_reduce has both).
+ONE_SHOT_MAX_BYTES = 4 << 20
+_AR_OPS = {"two_shot": _lib.GEMM_ALL_REDUCE, "one_shot": _lib.GEMM_AR_ONE_SHOT, "atomic": _lib.GEMM_AR_ATOMIC}
+
+
+def _ar_variant(config, M: int, N: int) -> str:
+    v = config.all_reduce_variant
+    if v == "auto":
+        return "one_shot" if M * N * 2 <= ONE_SHOT_MAX_BYTES else "two_shot"
+    if v not in _AR_OPS:
+        raise ValueError(f"matmul_all_reduce has no fused kernel for all_reduce_variant={v!r}; use two_shot, one_shot, atomic or auto "
+                         "(ctx.ccl.all_reduce implements ring and spinlock for a GEMM + collective pair)")
+    return v
+
+
 def matmul_all_reduce_preamble(shmem, C_out, A, B, config=None):
     config = config or _DEFAULT_CONFIG
-    if not _fusable(shmem, A, B) or not shmem.is_symmetric(C_out):
-        return FusedWorkspace(operation="matmul_all_reduce", variant="unfused", world_size=shmem.num_ranks, prepared=True)
     M, K = A.shape
     N = B.shape[1]
-    d, _ = _base_desc(shmem, _lib.GEMM_ALL_REDUCE, M, N, K, A, B, C_out, config)
-    ws = _make_workspace(shmem, "matmul_all_reduce", tuple(A.shape) + tuple(B.shape), A.dtype, "fused", d)
+    variant = _ar_variant(config, M, N)
+    if not _fusable(shmem, A, B) or not shmem.is_symmetric(C_out):
+        return FusedWorkspace(operation="matmul_all_reduce", variant="unfused", world_size=shmem.num_ranks, prepared=True)
+    d, _ = _base_desc(shmem, _AR_OPS[variant], M, N, K, A, B, C_out, config)
+    ws = _make_workspace(shmem, "matmul_all_reduce", tuple(A.shape) + tuple(B.shape) + (variant,), A.dtype, "fused", d)
+    if ws is not None:
+        ws.extra["all_reduce_variant"] = variant
     return ws or FusedWorkspace(operation="matmul_all_reduce", variant="unfused", world_size=shmem.num_ranks, prepared=True)
 
 
 def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, config=None, workspace=None):
     """``output = sum over ranks of (A_r @ B_r)`` (+ bias) on every rank
-    (reference: iris/ops/matmul_all_reduce.py:222-372). The bias, if any, is added once."""
+    (reference: iris/ops/matmul_all_reduce.py:222-372). The bias, if any, is added once.
+    ``config.all_reduce_variant`` picks the algorithm (see the table above this function)."""
     config = config or _DEFAULT_CONFIG
     W = shmem.num_ranks
     M, K = A.shape
@@ -368,7 +441,8 @@ def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, con
         raise ValueError(f"matmul_all_reduce: A has K = {K}, B has {B.shape[0]} rows")
     if tuple(output_tensor.shape) != (M, N):
         raise ValueError(f"matmul_all_reduce: output must be {(M, N)}, got {tuple(output_tensor.shape)}")
-    key = tuple(A.shape) + tuple(B.shape)
+    variant = _ar_variant(config, M, N)
+    key = tuple(A.shape) + tuple(B.shape) + (variant,)
     ws = workspace
     if ws is None or not (ws.variant == "unfused" or ws.matches("matmul_all_reduce", key, A.dtype, W, "fused")):
         ws = _auto_workspace(shmem, "matmul_all_reduce", key, A.dtype, config,
@@ -377,14 +451,19 @@ def matmul_all_reduce(shmem, output_tensor, A, B, bias=None, async_op=False, con
     # a bias must enter the sum exactly once: rank 0 adds it to its partial product
     b = bias if (bias is not None and shmem.cur_rank == 0) else None
     if ws.variant == "unfused":
+        A, B = _lower_fp8(A, B, output_tensor.dtype)
         part = _on_heap(shmem, ws, "part", _local_matmul(A, B, b, bias_dim=0))
         dst = output_tensor if shmem.is_symmetric(output_tensor) else _scratch(shmem, ws, "out", (M, N), A.dtype)
         shmem.ccl.all_reduce(dst, part)
         if dst is not output_tensor:
             output_tensor.copy_(dst)
     else:
-        d, keep = _cached_desc(ws, _ptr_key(output_tensor, A, B, b) + (id(shmem._ctx_epoch),),
-                               lambda: _with_bias(b, lambda b32: _base_desc(shmem, _lib.GEMM_ALL_REDUCE, M, N, K, A, B, output_tensor, config, bias_row=b32)))
+        if variant == "atomic":
+            # every rank's output starts at zero before any rank adds to it (as the reference's preamble does)
+            output_tensor.zero_()
+            shmem.barrier()
+        d, keep = _cached_desc(ws, _ptr_key(output_tensor, A, B, b) + (id(shmem._ctx_epoch), variant),
+                               lambda: _with_bias(b, lambda b32: _base_desc(shmem, _AR_OPS[variant], M, N, K, A, B, output_tensor, config, bias_row=b32)))
         _refresh_bias(keep)
         _launch(shmem, d, ws)
     _finish(shmem, async_op)
@@ -444,6 +523,7 @@ def matmul_reduce_scatter(shmem, output_tensor, A, B, bias=None, async_op=False,
     if ws.variant == "unfused":
         from ..ccl import Config
 
+        A, B = _lower_fp8(A, B, output_tensor.dtype)
         part = _on_heap(shmem, ws, "part", _local_matmul(A, B, b, bias_dim=0))
         if scatter_rows:
             dst = _scratch(shmem, ws, "out", want, A.dtype)

@@ -19,7 +19,7 @@ class FusedConfig:
     num_sms: int | None = None
     num_xcds: int = 1
     chunk_size: int = 1
-    all_reduce_variant: str = "two_shot"
+    all_reduce_variant: str = "auto"        # matmul_all_reduce: two_shot, one_shot, atomic, or auto (by output size)
     all_reduce_num_rings: int = 1
     comm_sms: int = 0
     use_multicast: bool = True

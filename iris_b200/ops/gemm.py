@@ -54,7 +54,19 @@ def matmul(A: torch.Tensor, B: torch.Tensor, bias: torch.Tensor | None = None, o
 
     ``two_sm`` selects the variant in which the two CTAs of a cluster share one 256-row tile
     (``tcgen05.mma.cta_group::2``): ``True`` whenever the shape allows, ``False`` never, ``None``
-    lets the plan pick by wave count."""
+    lets the plan pick by wave count.
+
+    Block-scaled e4m3 operands (``BlockScaled`` activation and weight, see ``gemm_fp8``) go to the
+    hardware-scaled kernel; the result is bf16 unless ``out`` says otherwise."""
+    from .gemm_fp8 import BlockScaled, blockscaled_tile_n, matmul_fp8_blockscaled
+
+    if isinstance(A, BlockScaled) or isinstance(B, BlockScaled):
+        if not (isinstance(A, BlockScaled) and isinstance(B, BlockScaled) and A.kind == "activation" and B.kind == "weight"):
+            raise TypeError("an fp8 product takes a BlockScaled activation and a BlockScaled weight")
+        if bias is not None:
+            raise ValueError("the block-scaled local GEMM takes no bias")
+        tile = blockscaled_tile_n(A.shape[0], B.shape[1], bn, two_sm)
+        return matmul_fp8_blockscaled(A.q, A.sf(), B.q, B.sf(tile), out=out, bn=bn, two_sm=two_sm)
     M, K = A.shape
     K2, N = B.shape
     if K != K2:

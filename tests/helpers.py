@@ -6,6 +6,7 @@ per GPU with the nccl backend. The child entry point is a module-level function
 """
 from __future__ import annotations
 
+import datetime
 import os
 import socket
 import sys
@@ -25,6 +26,7 @@ def free_port() -> int:
 
 
 def _entry(rank, world, port, backend, fn, args, errq, env):
+    reported = False
     try:
         os.environ.update(env)
         os.environ.update({"RANK": str(rank), "LOCAL_RANK": str(rank), "WORLD_SIZE": str(world),
@@ -35,11 +37,18 @@ def _entry(rank, world, port, backend, fn, args, errq, env):
 
         if backend == "nccl":
             torch.cuda.set_device(rank)
-            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+            # a collective that a failed peer never joins ends with an error after this long, not after NCCL's ten minutes
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                                    timeout=datetime.timedelta(seconds=float(os.environ.get("IRIS_TEST_PG_TIMEOUT_S", "180"))))
         else:
             dist.init_process_group("gloo", rank=rank, world_size=world)
         try:
             fn(rank, world, *args)
+        except BaseException:
+            # report first: the clean-up below can block when the peers are in a different state
+            errq.put((rank, traceback.format_exc()))
+            reported = True
+            raise
         finally:
             # Leave in order: unbind and unmap every heap this process created (a heap may be bound
             # to an NVLink multicast object, which must not outlive an abrupt exit), then the group.
@@ -49,12 +58,14 @@ def _entry(rank, world, port, backend, fn, args, errq, env):
                 close_all()
             except Exception:
                 pass
-            try:
-                dist.destroy_process_group()
-            except Exception:
-                pass
+            if not reported:
+                try:
+                    dist.destroy_process_group()
+                except Exception:
+                    pass
     except BaseException:
-        errq.put((rank, traceback.format_exc()))
+        if not reported:
+            errq.put((rank, traceback.format_exc()))
         raise
 
 

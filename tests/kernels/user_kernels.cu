@@ -59,7 +59,7 @@ __global__ void tile_kernel(DeviceContext ctx, int op, float* src, float* dst, i
   TileView t{tile_id / tiles_n, tile_id % tiles_n, bm, bn};
   TensorView<float> s = make_tensor_view(src, M, N, (int64_t)N);
   TensorView<float> d = make_tensor_view(dst, dst_M, dst_N, (int64_t)dst_N);
-  if (op == 2 || op == 3 || op == 7) {
+  if (op == 2 || op == 3 || op == 7 || op == 8) {
     __syncthreads();
     if (threadIdx.x == 0) { fence_sys(); st_release_sys(locks + tile_id, ready); }
   }
@@ -72,6 +72,7 @@ __global__ void tile_kernel(DeviceContext ctx, int op, float* src, float* dst, i
     case 5: tile::gather(ctx, t, s, d, arg); break;
     case 6: tile::all_to_all(ctx, t, s, d, arg); break;
     case 7: tile::reduce_scatter(ctx, t, tile_id, tiles_m * tiles_n, s, d, locks, ready); break;
+    case 8: tile::all_reduce_ring(ctx, t, tile_id, s, d, locks, ready); break;
   }
 }
 extern "C" int tile_collective(const IrisCtx* c, int op, float* src, float* dst, int32_t* locks, int M, int N, int dst_M,

@@ -23,6 +23,7 @@ class _Recorder:
         self.ccl, self.gemm = [], []
         self._ccl_t, self._gemm_t = ccl_desc_type, gemm_desc_type
         self.iris_gemm_workspace = real.iris_gemm_workspace
+        self.iris_gemm_sf_inbox_bytes = real.iris_gemm_sf_inbox_bytes
 
         def ccl_launch(op, d, stream):
             self.ccl.append((op, self._ccl_t.from_buffer_copy(d._obj)))
@@ -66,7 +67,8 @@ def _pretend_gpu(ctx):
 
 def _dry_run(rank, world):
     import iris_b200 as iris
-    from iris_b200 import _lib
+    from iris_b200 import _lib, ops
+    from iris_b200.ops import FusedConfig
     from iris_b200.ccl import Config
     from iris_b200.parallel import ColumnParallelLinear, GradientBuckets, RowParallelLinear, UlyssesExchange
 
@@ -174,8 +176,19 @@ def _dry_run(rank, world):
     bias = torch.ones(Ml * W)
     ws3 = ctx.ops.matmul_all_reduce(Yt, H, W2, bias=bias)
     g = rec.gemm[-1]
-    assert ws3.variant == "fused" and g.op == _lib.GEMM_ALL_REDUCE and g.C == Yt.data_ptr()
+    # the default variant is "auto": a small output takes the one-shot kernel, a large one the two-shot kernel
+    small = Ml * W * K * 2 <= ops.ONE_SHOT_MAX_BYTES
+    assert ws3.variant == "fused" and g.op == (_lib.GEMM_AR_ONE_SHOT if small else _lib.GEMM_ALL_REDUCE) and g.C == Yt.data_ptr()
     assert bool(g.bias_row) == (rank == 0)                                           # the bias enters the sum once
+    for name, code in (("two_shot", _lib.GEMM_ALL_REDUCE), ("one_shot", _lib.GEMM_AR_ONE_SHOT), ("atomic", _lib.GEMM_AR_ATOMIC)):
+        wv = ctx.ops.matmul_all_reduce(Yt, H, W2, config=FusedConfig(all_reduce_variant=name))
+        assert rec.gemm[-1].op == code and wv.extra["all_reduce_variant"] == name and rec.gemm[-1].staging == (wv.staging.data_ptr() if wv.staging is not None else None)
+    for name in ("ring", "spinlock"):                                                # no fused kernel: refused, not ignored
+        try:
+            ctx.ops.matmul_all_reduce(Yt, H, W2, config=FusedConfig(all_reduce_variant=name))
+            raise AssertionError("expected a ValueError")
+        except ValueError:
+            pass
     off_heap = torch.zeros(Ml * W, K, dtype=dt)
     n_before = len(rec.gemm)
     ctx.ops.matmul_all_reduce(off_heap, H, W2)                                       # output not on the heap: GEMM + collective
@@ -219,7 +232,7 @@ def _dry_run(rank, world):
     assert y.shape == (Ml, K) and [x.op for x in rec.gemm[n_before:]] == [_lib.GEMM_AG_M, _lib.GEMM_REDUCE_SCATTER]
     down2 = RowParallelLinear(ctx, N, K, dtype=dt, seed=2, sequence_parallel=False)
     y2 = down2(torch.zeros(Ml * W, N, dtype=dt))
-    assert ctx.is_symmetric(y2) and rec.gemm[-1].op == _lib.GEMM_ALL_REDUCE and rec.gemm[-1].C == y2.data_ptr()
+    assert ctx.is_symmetric(y2) and rec.gemm[-1].op in (_lib.GEMM_ALL_REDUCE, _lib.GEMM_AR_ONE_SHOT) and rec.gemm[-1].C == y2.data_ptr()
     model = torch.nn.Linear(32, 16)
     model(torch.ones(4, 32)).sum().backward()
     buckets = GradientBuckets(ctx, model.parameters())

@@ -163,7 +163,7 @@ def _ops(rank, world):
     for name in ("block_size_m", "block_size_n", "block_size_k", "group_size_m", "num_sms", "num_xcds", "chunk_size",
                  "all_reduce_variant", "all_reduce_num_rings"):
         assert hasattr(cfg, name), name
-    assert cfg.block_size_m == 128 and cfg.tile_n() == 0 and cfg.all_reduce_variant == "two_shot"
+    assert cfg.block_size_m == 128 and cfg.tile_n() == 0 and cfg.all_reduce_variant == "auto"
     assert FusedConfig(block_size_n=224).tile_n() == 224 and FusedConfig(block_size_n=64).tile_n() == 0
     cfg.validate(world)
     with pytest.raises(ValueError):
@@ -192,3 +192,59 @@ def test_owned_tile_range_partitions_the_tiles():
                 assert got == list(range(tiles))                      # contiguous blocks in rank order
                 sizes = [len(owned_tile_range(tiles, world, r)) for r in range(world)]
                 assert sizes[:-1] == [tiles // world] * (world - 1) and sizes[-1] == tiles - (world - 1) * (tiles // world)
+
+
+def _fp8_ops(rank, world):
+    """Block-scaled e4m3 operands through the four fused ops (dequantised on the CPU backend): each op
+    means what its 16-bit form means on the dequantised matrices."""
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.ops import BlockScaled, pack_scales_a, pack_scales_b, quantize_activation, quantize_weight
+
+    if not hasattr(torch, "float8_e4m3fn"):
+        return
+    ctx = iris.iris(1 << 27)
+    g = torch.Generator().manual_seed(7 + rank)
+    M, K, N = 32, 256, 24
+    x = quantize_activation(torch.randn(M, K, generator=g) * 3)
+    w = quantize_weight(torch.randn(N, K, generator=g) * 0.1)            # [N, K], used as the [K, N] matrix
+    assert x.shape == (M, K) and w.shape == (K, N) and x.kind == "activation" and w.kind == "weight"
+    assert torch.all(torch.log2(x.scale) == torch.round(torch.log2(x.scale)))                  # powers of two
+    assert x.sf().shape == (1, 2, 512) and w.sf(224).shape == (1, 2, 2, 512) and w.sf(128).shape == (1, 2, 1, 512)
+    # the atom layout: row r of a 128-row tile at byte (r % 32) * 16 + (r // 32) * 4, four equal bytes per block
+    e = (torch.log2(x.scale) + 127).to(torch.uint8)
+    for r, kb in ((0, 0), (17, 1), (31, 0)):
+        off = (r % 32) * 16 + (r // 32) * 4
+        assert torch.all(x.sf()[0, kb, off:off + 4] == e[r, kb])
+    xd, wd = x.dequantize(), w.dequantize()
+    tol = dict(atol=2e-2, rtol=2e-2)
+    parts_x = [torch.empty_like(xd) for _ in range(world)]
+    dist.all_gather(parts_x, xd)
+    # all_gather_matmul, rows sharded: every rank multiplies the gathered activations by ITS weight
+    out = ctx.zeros((M * world, N), dtype=torch.bfloat16)
+    ws = ctx.ops.all_gather_matmul(out, x, w, shard_dim=0)
+    assert ws.variant == "unfused"
+    assert torch.allclose(out.float(), torch.cat(parts_x, 0) @ wd, **tol)
+    # matmul_all_reduce / matmul_reduce_scatter: sum over ranks of the local products
+    local = xd @ wd
+    total = local.clone()
+    dist.all_reduce(total)
+    out2 = ctx.zeros((M, N), dtype=torch.bfloat16)
+    ctx.ops.matmul_all_reduce(out2, x, w)
+    assert torch.allclose(out2.float(), total, atol=0.2, rtol=3e-2)
+    out3 = ctx.zeros((M // world, N), dtype=torch.bfloat16)
+    ctx.ops.matmul_reduce_scatter(out3, x, w, scatter_rows=True)
+    assert torch.allclose(out3.float(), total[rank * (M // world):(rank + 1) * (M // world)], atol=0.2, rtol=3e-2)
+    # matmul_all_gather: every rank's product, stacked by rank
+    out4 = ctx.zeros((M * world, N), dtype=torch.bfloat16)
+    ctx.ops.matmul_all_gather(out4, x, w)
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local)
+    assert torch.allclose(out4.float(), torch.cat(parts, 0), **tol)
+    with pytest.raises((TypeError, ValueError)):
+        BlockScaled(x.q, x.scale[:, :1], "activation")
+
+
+def test_fp8_block_scaled_operands_through_the_fused_ops():
+    run_ranks(_fp8_ops, 2)

@@ -166,7 +166,7 @@ def _ops(rank, world, nvls):
     import torch.distributed as dist
 
     import iris_b200 as iris
-    from iris_b200.ops import owned_tile_range
+    from iris_b200.ops import FusedConfig, owned_tile_range
 
     ctx = iris.iris(4 << 30)
     W = world
@@ -218,6 +218,15 @@ def _ops(rank, world, nvls):
         for _ in range(3):
             ws4 = ctx.ops.matmul_all_reduce(C4, A4, B4, workspace=ws4)
         assert _maxerr(C4, tot) <= tol
+        # every variant of the all-reduce half, three calls each (the staging is double-buffered by call parity)
+        for variant in ("two_shot", "one_shot", "atomic"):
+            Cv = ctx.zeros((M, N), dtype=dtype)
+            wv = None
+            for _ in range(3):
+                wv = ctx.ops.matmul_all_reduce(Cv, A4, B4, workspace=wv, config=FusedConfig(all_reduce_variant=variant))
+            assert wv.variant == "fused" and wv.extra["all_reduce_variant"] == variant
+            # atomic: 16-bit accumulation in memory, one rounding per rank
+            assert _maxerr(Cv, tot) <= (tol * (1 + W / 4) if variant == "atomic" else tol), variant
         C5 = ctx.zeros((Ml, N), dtype=dtype)
         ws5 = None
         for _ in range(3):
@@ -241,6 +250,83 @@ def _ops(rank, world, nvls):
 @pytest.mark.parametrize("nvls", [False, True])
 def test_fused_ops_match_reference(nvls):
     run_ranks(_ops, _world(), args=(nvls,), backend="nccl", env={"IRIS_NVLS": "1" if nvls else "0"}, timeout=600)
+
+
+def _fp8_ops(rank, world, nvls):
+    """The fused ops on block-scaled e4m3 operands (scales applied by the tensor core, shards and their
+    scale atoms gathered inside the kernel) against fp32 products of the dequantised operands."""
+    import torch.distributed as dist
+
+    import iris_b200 as iris
+    from iris_b200.ops import quantize_activation, quantize_weight
+
+    ctx = iris.iris(4 << 30)
+    W = world
+    dt = torch.bfloat16
+
+    def rowerr(c, ref):
+        return ((c.float() - ref).abs().amax(dim=1) / ref.abs().amax(dim=1).clamp_min(1e-20)).max().item()
+
+    for Ml, N, K in ((256, 448, 1024), (128, 896, 512 * W)):
+        torch.manual_seed(21 + rank)
+        x = torch.randn(Ml, K, device="cuda") * torch.exp2(torch.randint(-4, 4, (Ml, 1), device="cuda").float())
+        w = torch.randn(N, K, device="cuda") * 0.05 * torch.exp2(torch.randint(-3, 3, (-(-N // 128), -(-K // 128)), device="cuda").float()) \
+            .repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+        xq, wq = quantize_activation(x), quantize_weight(w)
+        xd, wd = xq.dequantize(), wq.dequantize()
+        # all_gather_matmul, rows sharded
+        xall = torch.empty(W * Ml, K, device="cuda")
+        dist.all_gather_into_tensor(xall, xd)
+        ref = xall @ wd
+        C = ctx.zeros((W * Ml, N), dtype=dt)
+        ws = None
+        for _ in range(3):
+            ws = ctx.ops.all_gather_matmul(C, xq, wq, shard_dim=0, workspace=ws)
+        assert ws.variant == "fused" and ws.bn == 224
+        assert rowerr(C, ref) < 1.5e-2
+        # all_gather_matmul, K sharded: rank r holds columns [r K/W, (r+1) K/W) of the activations, weights replicated
+        torch.manual_seed(99)
+        wfull = quantize_weight(torch.randn(N, K, device="cuda") * 0.05)
+        torch.manual_seed(21 + rank)
+        xs = quantize_activation(torch.randn(W * Ml, K // W, device="cuda"))
+        parts = [torch.empty(W * Ml, K // W, device="cuda") for _ in range(W)]
+        dist.all_gather(parts, xs.dequantize())
+        ref2 = torch.cat(parts, 1) @ wfull.dequantize()
+        C2 = ctx.zeros((W * Ml, N), dtype=dt)
+        ws2 = None
+        for _ in range(2):
+            ws2 = ctx.ops.all_gather_matmul(C2, xs, wfull, workspace=ws2)
+        assert ws2.variant == "fused" and rowerr(C2, ref2) < 1.5e-2
+        # reduce ops: sum over ranks of the local products
+        M = W * Ml
+        x4 = quantize_activation(torch.randn(M, K, device="cuda"))
+        tot = x4.dequantize() @ wd
+        dist.all_reduce(tot)
+        C4 = ctx.zeros((M, N), dtype=dt)
+        C5 = ctx.zeros((Ml, N), dtype=dt)
+        w4 = w5 = None
+        for _ in range(3):
+            w4 = ctx.ops.matmul_all_reduce(C4, x4, wq, workspace=w4)
+            w5 = ctx.ops.matmul_reduce_scatter(C5, x4, wq, scatter_rows=True, workspace=w5)
+        assert w4.variant == "fused" and w5.variant == "fused"
+        tol = 0.03 * tot.abs().max().item()
+        assert _maxerr(C4, tot) <= tol and _maxerr(C5, tot[rank * Ml:(rank + 1) * Ml]) <= tol
+        # matmul_all_gather
+        loc = (xd @ wd).to(dt)
+        ref_ag = torch.empty(W * Ml, N, device="cuda", dtype=dt)
+        dist.all_gather_into_tensor(ref_ag, loc)
+        C3 = ctx.zeros((W * Ml, N), dtype=dt)
+        w3 = None
+        for _ in range(2):
+            w3 = ctx.ops.matmul_all_gather(C3, xq, wq, workspace=w3)
+        assert w3.variant == "fused" and rowerr(C3, ref_ag.float()) < 1.5e-2
+    ctx.check()
+    ctx.barrier()
+
+
+@pytest.mark.parametrize("nvls", [False, True])
+def test_fp8_fused_ops_match_dequantised_reference(nvls):
+    run_ranks(_fp8_ops, _world(), args=(nvls,), backend="nccl", env={"IRIS_NVLS": "1" if nvls else "0"}, timeout=600)
 
 
 def _decode(rank, world):
@@ -404,15 +490,15 @@ def _tiles(rank, world):
     tiles_n = N // bn
     tiles = (M // bm) * tiles_n
     ready = 0
-    for op in (0, 1, 2, 3, 7):                      # the reductions
+    for op in (0, 1, 2, 3, 7, 8):                   # the reductions (8 = ring order)
         dst = ctx.zeros((M, N), dtype=torch.float32)
         locks = ctx.zeros(tiles, dtype=torch.int32)
         ctx.barrier()
         ready = 1
         call(ctx, op, src, dst, locks, M, N, M, N, bm, bn, 0, ready)
         ctx.barrier()
-        if op in (0, 1, 2, 3):
-            if op == 3 or op == 2 or op in (0, 1):
+        if op in (0, 1, 2, 3, 8):
+            if op == 3 or op == 2 or op in (0, 1, 8):
                 assert torch.allclose(dst, total, atol=1e-4), op
         else:                                       # reduce_scatter: contiguous tile blocks, last rank takes the rest
             per = max(tiles // world, 1)

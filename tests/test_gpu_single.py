@@ -264,6 +264,117 @@ def test_fp8_block_scaled_gemm_matches_dequantised_product(M, N, K, out_dtype):
     assert (out.float() - x @ w.t()).abs().max().item() / ref.abs().max().item() < 8e-2
 
 
+def _distinct_scale_operands(M, N, K):
+    """Operands whose every quantisation block gets a different scale: row magnitudes, K-block
+    magnitudes and 128 x 128 weight-block magnitudes all differ by powers of two and more."""
+    kb, nb = -(-K // 128), -(-N // 128)
+    x = torch.randn(M, K, device="cuda")
+    x = x * torch.exp2(torch.randint(-6, 6, (M, 1), device="cuda").float()) * (1 + torch.rand(M, 1, device="cuda"))
+    x = x * torch.exp2(torch.randint(-3, 3, (1, kb), device="cuda").float()).repeat_interleave(128, 1)[:, :K]
+    w = torch.randn(N, K, device="cuda") * 0.05
+    w = w * torch.exp2(torch.randint(-4, 4, (nb, kb), device="cuda").float()).repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+    return x, w
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (200, 520, 336)])
+def test_fp8_scale_layout_with_distinct_scales_per_block(M, N, K):
+    """Pins the 1 x 128 / 128 x 128 scale layout of the software-promotion kernel: every block has its own
+    scale, so a scale applied to the wrong row, column block or K block shows up as a large error."""
+    from iris_b200.ops.gemm_fp8 import dequant_matmul, matmul_fp8, quantize_1x128, quantize_128x128
+
+    torch.manual_seed(5)
+    x, w = _distinct_scale_operands(M, N, K)
+    aq, asc = quantize_1x128(x)
+    bq, bsc = quantize_128x128(w)
+    assert asc.unique().numel() > M // 2 and bsc.unique().numel() >= min(bsc.numel(), 3)
+    out = matmul_fp8(aq, asc, bq, bsc)
+    ref = dequant_matmul(aq, asc, bq, bsc)
+    # row by row: rows differ by up to 2^12 in magnitude, a global maximum would hide the small ones
+    err = (out.float() - ref).abs().amax(dim=1) / ref.abs().amax(dim=1).clamp_min(1e-20)
+    assert err.max().item() < 1.5e-2
+
+
+@pytest.mark.parametrize("M,N,K,bn,two_sm", [(128, 224, 128, 0, None), (256, 448, 1024, 0, None), (200, 520, 336, 0, None),
+                                             (256, 256, 512, 128, None), (512, 896, 2048, 0, True), (1024, 1024, 7168, 0, None)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+def test_fp8_hardware_block_scaled_gemm(M, N, K, bn, two_sm, out_dtype):
+    """tcgen05.mma.kind::mxf8f6f4.block_scale with UE8M0 scales staged in TMEM: power-of-two scales,
+    distinct per block, against the fp32 product of the dequantised operands, row by row."""
+    from iris_b200.ops.gemm_fp8 import (blockscaled_tile_n, dequant_matmul, matmul_fp8_blockscaled, pack_scales_a, pack_scales_b,
+                                        quantize_1x128, quantize_128x128)
+
+    torch.manual_seed(6)
+    x, w = _distinct_scale_operands(M, N, K)
+    aq, asc = quantize_1x128(x, pow2=True)
+    bq, bsc = quantize_128x128(w, pow2=True)
+    tile = blockscaled_tile_n(M, N, bn, two_sm)
+    out = matmul_fp8_blockscaled(aq, pack_scales_a(asc), bq, pack_scales_b(bsc, N, tile), out_dtype=out_dtype, bn=bn, two_sm=two_sm)
+    ref = dequant_matmul(aq, asc, bq, bsc)
+    err = (out.float() - ref).abs().amax(dim=1) / ref.abs().amax(dim=1).clamp_min(1e-20)
+    assert err.max().item() < 1.5e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("M,K", [(256, 512), (200, 328), (1, 128)])
+def test_activation_quantiser_kernel(M, K, dtype):
+    """One-kernel activation quantiser: power-of-two 1 x 128 scales, e4m3 values within half a step of
+    x / scale, and scale atoms equal to the PyTorch packing of the scales it reports."""
+    from iris_b200.ops.gemm_fp8 import pack_scales_a, quantize_activation
+
+    torch.manual_seed(9)
+    x = (torch.randn(M, K, device="cuda") * torch.exp2(torch.randint(-8, 8, (M, 1), device="cuda").float())).to(dtype)
+    b = quantize_activation(x)
+    s = b.scale
+    assert tuple(b.q.shape) == (M, K) and tuple(s.shape) == (M, -(-K // 128))
+    assert torch.all(torch.log2(s) == torch.round(torch.log2(s)))
+    amax = torch.nn.functional.pad(x.float().abs(), (0, s.shape[1] * 128 - K)).view(M, -1, 128).amax(dim=2).clamp_min(1e-12)
+    assert torch.all(amax / s <= 448.0) and torch.all(amax / s > 448.0 / 2 - 1e-3)       # the smallest power of two that fits
+    back = b.dequantize()
+    step = s.repeat_interleave(128, dim=1)[:, :K] * 32.0                                  # e4m3 spacing at the top binade (256..448)
+    assert torch.all((back - x.float()).abs() <= step / 2 + 1e-30)
+    assert torch.equal(b.sf(), pack_scales_a(s))
+    again = quantize_activation(x, out=b)                                                 # buffers reused
+    assert again is b and torch.equal(again.sf(), pack_scales_a(s))
+
+
+def test_fp8_fused_ops_world1(ctx):
+    """The fused ops with block-scaled e4m3 operands (one rank: same kernels, no peers)."""
+    from iris_b200.ops import quantize_activation, quantize_weight
+
+    torch.manual_seed(2)
+    xs, wt = _distinct_scale_operands(384, 640, 512)
+    x, w = quantize_activation(xs), quantize_weight(wt)
+    ref = x.dequantize() @ w.dequantize()
+    for op, kw in (("all_gather_matmul", {"shard_dim": 0}), ("all_gather_matmul", {"shard_dim": 1}), ("matmul_all_gather", {}),
+                   ("matmul_all_reduce", {}), ("matmul_reduce_scatter", {"scatter_rows": True}), ("matmul_reduce_scatter", {})):
+        C = ctx.zeros((384, 640), dtype=torch.bfloat16)
+        ws = None
+        for _ in range(3):
+            ws = getattr(ctx.ops, op)(C, x, w, workspace=ws, **kw)
+        assert ws.variant == "fused" and ws.bn == 224, op
+        err = (C.float() - ref).abs().amax(dim=1) / ref.abs().amax(dim=1).clamp_min(1e-20)
+        assert err.max().item() < 1.5e-2, op
+    ctx.check()
+
+
+def test_fused_op_reads_a_bias_updated_in_place(ctx):
+    """A 16-bit bias is converted to fp32 for the kernel and the conversion is kept with the cached
+    descriptor: an in-place update of the bias (an optimizer step) must reach the next call."""
+    dt = torch.bfloat16
+    torch.manual_seed(3)
+    A = torch.randn(256, 256, device="cuda", dtype=dt)
+    B = torch.randn(256, 256, device="cuda", dtype=dt) * 0.05
+    bias = torch.randn(256, device="cuda", dtype=dt)
+    C = ctx.zeros((256, 256), dtype=dt)
+    ws = ctx.ops.matmul_all_reduce(C, A, B, bias=bias)
+    ref = A.float() @ B.float()
+    assert _rel_err(C, ref + bias.float()[:, None]) < 1e-2
+    bias.add_(5.0)
+    ctx.ops.matmul_all_reduce(C, A, B, bias=bias, workspace=ws)
+    assert _rel_err(C, ref + bias.float()[:, None]) < 1e-2
+    ctx.check()
+
+
 @pytest.mark.parametrize("page,use_tma", [(64, None), (16, None), (64, False), (48, None)])
 def test_flash_decode_ignores_positions_past_the_length(ctx, page, use_tma):
     """Cache rows past a sequence's length (same page or unused pages) hold NaN: both tile-fill paths
@@ -402,7 +513,7 @@ def test_user_kernels_functional_and_oo_api(ctx, user_module):
     assert int(counter.item()) == 256
 
 
-@pytest.mark.parametrize("op", [0, 1, 2, 3, 4, 5, 6, 7])
+@pytest.mark.parametrize("op", [0, 1, 2, 3, 4, 5, 6, 7, 8])
 def test_tile_collectives_world1(ctx, user_module, op):
     M, N, bm, bn = 100, 72, 32, 16
     torch.manual_seed(op)
