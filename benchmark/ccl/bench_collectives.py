@@ -9,6 +9,9 @@ bench_all_reduce_vllm.py).
 Sizes are bytes per rank; bus bandwidth follows the NCCL convention
 (all_reduce 2(W-1)/W, all_gather / reduce_scatter / all_to_all (W-1)/W of the full payload).
 Each point checks the result against a float64 host reduction before it is timed.
+``--axis_timing=back_to_back`` times a run of calls issued without a gap (one event pair around all of them)
+instead of one call at a time behind a barrier and an L2 flush: below about 1 MB the per-call protocol
+measures the launch skew between the ranks rather than the collective.
 """
 import os
 import sys
@@ -50,6 +53,7 @@ def _host_sum(inp, world):
 @bench.axis("dtype", [torch.bfloat16, torch.float32])
 @bench.axis("impl", ["iris", "nccl"])
 @bench.axis("variant", ["auto"])
+@bench.axis("timing", ["per_call"])
 @bench.axis("bytes", bench.power_of_two(10, 30))
 def all_reduce(state, ctx):
     W, dtype = ctx.get_num_ranks(), state["dtype"]
@@ -77,6 +81,7 @@ def all_reduce(state, ctx):
 @bench.axis("num_ranks", [2, 4, 8])
 @bench.axis("dtype", [torch.bfloat16])
 @bench.axis("impl", ["iris", "nccl"])
+@bench.axis("timing", ["per_call"])
 @bench.axis("bytes", bench.power_of_two(10, 30))
 def all_gather(state, ctx):
     W, dtype = ctx.get_num_ranks(), state["dtype"]
@@ -101,6 +106,7 @@ def all_gather(state, ctx):
 @bench.axis("num_ranks", [2, 4, 8])
 @bench.axis("dtype", [torch.bfloat16])
 @bench.axis("impl", ["iris", "nccl"])
+@bench.axis("timing", ["per_call"])
 @bench.axis("bytes", bench.power_of_two(10, 30))
 def reduce_scatter(state, ctx):
     W, dtype = ctx.get_num_ranks(), state["dtype"]
@@ -127,6 +133,7 @@ def reduce_scatter(state, ctx):
 @bench.axis("num_ranks", [2, 4, 8])
 @bench.axis("dtype", [torch.bfloat16])
 @bench.axis("impl", ["iris", "nccl"])
+@bench.axis("timing", ["per_call"])
 @bench.axis("bytes", bench.power_of_two(10, 30))
 def all_to_all(state, ctx):
     W, dtype = ctx.get_num_ranks(), state["dtype"]

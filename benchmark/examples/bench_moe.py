@@ -73,7 +73,7 @@ def moe_nccl(x, logits, wg, wu, wd, K, W, rank):
 
 @bench.register
 @bench.axis("num_ranks", [1, 2, 4, 8])
-@bench.axis("impl", ["iris", "nccl"])
+@bench.axis("impl", ["iris", "iris_fp8", "nccl"])
 @bench.axis("tokens", [4096])
 @bench.axis("hidden", [7168])
 @bench.axis("ffn", [2048])
@@ -87,13 +87,14 @@ def moe_layer(state, ctx):
     wg = (torch.randn(El, D, F, device="cuda") * 0.02).to(dt)
     wu = (torch.randn(El, D, F, device="cuda") * 0.02).to(dt)
     wd = (torch.randn(El, F, D, device="cuda") * 0.02).to(dt)
-    layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg, w_up=wu, w_down=wd, capacity_factor=2.0)
+    layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg, w_up=wu, w_down=wd, capacity_factor=2.0, fp8=state["impl"] == "iris_fp8")
     x = torch.randn(T, D, device="cuda", dtype=dt)
     logits = torch.randn(T, E, device="cuda")
     out = torch.empty_like(x)
     flops = 2 * T * K * (D * 2 * F + F * D)
     state.set_flops(flops)
-    state.set_roofline_us(flops / (PEAK_TFLOPS * 1e6))
+    # roofline: the FLOPs at the measured bf16 tensor throughput (fp8 rows: at twice that)
+    state.set_roofline_us(flops / (PEAK_TFLOPS * 1e6 * (2 if state["impl"] == "iris_fp8" else 1)))
     state.set_repeat(20)
     state.set_warmup(5)
     if state["impl"] == "nccl":

@@ -5,6 +5,7 @@
     python benchmark/profile_target.py decode    # 3 flash-decode steps, batch 8, 16384 keys, 64/8 heads
     python benchmark/profile_target.py fused     # world-size-1 all_gather_matmul + matmul_reduce_scatter
     python benchmark/profile_target.py moe       # one MoE layer pass, 1024 tokens, 8 experts
+    python benchmark/profile_target.py moe_fp8   # the same with e4m3 tokens, weights and hidden activations
     python benchmark/profile_target.py fp8       # 3 launches of the block-scaled fp8 GEMM 4096x4096x7168
     python benchmark/profile_target.py ring      # 3 ring-attention calls, world size 1, 4096 tokens, 32/8 heads
     python benchmark/profile_target.py fp8hw     # 3 launches of the hardware block-scaled fp8 GEMM 4096x3584x8192
@@ -118,14 +119,14 @@ def main():
         for _ in range(2):
             ctx.ops.all_gather_matmul(H, X, W1, shard_dim=0, async_op=True)
             ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True, async_op=True)
-    elif what == "moe":
+    elif what in ("moe", "moe_fp8"):
         from iris_b200.models import MoELayer
 
         T, D, F, E, K = 1024, 2048, 1024, 8, 2
         wg = (torch.randn(E, D, F, device="cuda") * 0.02).to(dt)
         wu = (torch.randn(E, D, F, device="cuda") * 0.02).to(dt)
         wd = (torch.randn(E, F, D, device="cuda") * 0.02).to(dt)
-        layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg, w_up=wu, w_down=wd)
+        layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg, w_up=wu, w_down=wd, fp8=what == "moe_fp8")
         x = torch.randn(T, D, device="cuda", dtype=dt)
         logits = torch.randn(T, E, device="cuda")
         for _ in range(2):

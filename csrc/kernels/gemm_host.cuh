@@ -70,6 +70,8 @@ struct Common {
   IRIS_D void store_chunk_local(int width, const uint8_t* smem, int row, int col) const {
     ptx::tma_store_2d(width == 64 ? &tmC : &tmC32, smem, col, row);
   }
+  static constexpr bool kSfaFromRows = false;
+  static constexpr bool kQuantOut = false;
   // defaults of the epilogue hooks a policy may leave out
   struct NoState {};
   template <class S> IRIS_D bool bulk_tile(S&) const { return false; }

@@ -401,10 +401,17 @@ struct AllGatherGemm : Common {
 // Staging and counters are double-buffered by call parity, as in AllGatherGemm.
 template <bool kReduce>
 struct ScatterGemmT : Common {
-  static constexpr bool kBulkEpilogue = kReduce;
+  static constexpr bool kBulkEpilogue = true;
   DeviceContext ctx;
   SyncBlock* sb;
   int mode;               // IrisGemmOp
+  // ALL_GATHER / ALL_SCATTER with communication CTAs ("workgroup specialised", the reference's
+  // examples/10_gemm_all_scatter_wg_specialization): the GEMM CTAs store each tile into THIS rank's
+  // copy of the output (tensor stores at row / column offset out_roff / out_coff) and publish a per-tile
+  // flag; the communication CTAs wait for the flag and forward the tile to every peer.
+  int wg_spec;
+  int out_roff, out_coff;
+  int n_comm_ctas;
   uint8_t* out;           // final output; heap pointer when peers write it (AG / AR / ALL_SCATTER)
   int64_t ld_out;
   uint8_t* staging;       // heap: [2][W][max_owned][128*bn] 16-bit
@@ -488,7 +495,11 @@ struct ScatterGemmT : Common {
   static constexpr bool kSwiGLU = false;
   IRIS_D int row_origin(State&, int tm) const { return tm * kBM; }
   IRIS_D void begin_tile(State& st, int tm, int tn, uint8_t*) const {
-    if (mode == IRIS_GEMM_AR_ONE_SHOT && st.buf < 0) st.buf = read_epoch(sb) & 1;
+    if ((mode == IRIS_GEMM_AR_ONE_SHOT || wg_spec) && st.buf < 0) {
+      const int e = read_epoch(sb);
+      st.buf = e & 1;
+      st.target = (e >> 1) + 1;
+    }
     if (!reducing()) return;
     if (st.buf < 0) {
       const int e = read_epoch(sb);
@@ -515,8 +526,11 @@ struct ScatterGemmT : Common {
   // A tile finished elsewhere always leaves as bulk stores into the owner's staging; a tile finished here
   // leaves through the output's tensor maps when it stays on this rank (reduce-scatter), and by rows
   // when every rank gets it (all-reduce: multimem / per-peer stores).
-  IRIS_D bool bulk_tile(State& st) const { return !st.mine || (c_bulk != 0 && mode != IRIS_GEMM_ALL_REDUCE); }
-  IRIS_D bool signals_tile(State& st) const { return !st.mine; }
+  IRIS_D bool bulk_tile(State& st) const {
+    if (!reducing()) return wg_spec != 0;
+    return !st.mine || (c_bulk != 0 && mode != IRIS_GEMM_ALL_REDUCE);
+  }
+  IRIS_D bool signals_tile(State& st) const { return reducing() ? !st.mine : wg_spec != 0; }
   // Staging slot layout (private to this kernel): [64-col chunk][quarter][32 rows][width cols],
   // 16-byte groups XOR-swizzled by row exactly as staged in shared memory by the epilogue.
   IRIS_D void add_partials(State& st, int quarter, int c32, int lane, uint32_t (&acc)[32]) const {
@@ -623,6 +637,10 @@ struct ScatterGemmT : Common {
   // A tile finished elsewhere: rows [32*quarter, +32) x columns [64*chunk, +width) go to the
   // owner's staging slot as one contiguous piece.
   IRIS_D void store_chunk(State& st, int quarter, int chunk, int width, const uint8_t* smem, int row, int col) const {
+    if (!reducing()) {            // workgroup-specialised gather / scatter: into this rank's own copy of the output
+      store_chunk_local(width, smem, row + out_roff, col + out_coff);
+      return;
+    }
     if (st.mine) {
       store_chunk_local(width, smem, mode == IRIS_GEMM_REDUCE_SCATTER ? row - ctx.rank * tiles_m_per_rank * kBM : row, col);
       return;
@@ -643,6 +661,11 @@ struct ScatterGemmT : Common {
           red_release_sys_add(ctx.remote(fl, r), 1);
         }
       }
+      return;
+    }
+    if (wg_spec && !reducing()) {   // the tile is in this rank's output (its stores have completed): tell the communication CTAs
+      __threadfence();
+      st_release_gpu(flags + (size_t)st.buf * max_owned + (tm * tiles_n + tn), st.target);
       return;
     }
     if (!reducing() || st.mine) return;
@@ -687,7 +710,74 @@ struct ScatterGemmT : Common {
       }
     }
   }
-  IRIS_D void comm_main(uint8_t*, int) const {}
+  // Communication CTAs of the workgroup-specialised gather / scatter: CTA j forwards the 128-row tiles
+  // j, j + n, ... in the order the GEMM CTAs finish them. For each it waits for the tile's flag (acquire),
+  // then every thread moves 16-byte pieces of the tile from this rank's output to the same place on every
+  // peer (one multimem.st with NVLS, else one store per peer), eight loads in flight per thread.
+  IRIS_D void comm_main(uint8_t*, int) const {
+    if (!wg_spec) return;
+    __shared__ int s_ok;
+    const int j = blockIdx.x - n_gemm_ctas;
+    const int epoch = read_epoch(sb);
+    const int buf = epoch & 1;
+    const int32_t target = (epoch >> 1) + 1;
+    const int units_per_row = bn / 8;
+    const int n_order = order_m * tiles_n;
+    for (int q = j; q < (n_order << pair); q += n_comm_ctas) {
+      // 128-row tiles in the order of the tile walk; a pair tile contributes its two halves one after the other
+      int om, tn;
+      swizzled_tile(q >> pair, order_m, tiles_n, group_m, om, tn);
+      const int tm = pair ? 2 * om + (q & 1) : om;
+      if (tm >= tiles_m) continue;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const int32_t* fl = flags + (size_t)buf * max_owned + (tm * tiles_n + tn);
+        bool ok = true;
+        const uint64_t t0 = now_ns();
+        unsigned n = 0;
+        while (ld_acquire_gpu(fl) - target < 0) {
+          if ((++n & 63u) == 0) {
+            if (now_ns() - t0 > ctx.timeout_ns) { ok = false; fail(kTimeoutFlag); break; }
+            backoff(64);
+          }
+        }
+        s_ok = ok ? 1 : 0;
+      }
+      __syncthreads();
+      if (!s_ok) return;
+      constexpr int kUnroll = 8;
+      for (int u0 = threadIdx.x; u0 < kBM * units_per_row; u0 += blockDim.x * kUnroll) {
+        uint4 v[kUnroll];
+        uint8_t* dst[kUnroll];
+#pragma unroll
+        for (int k = 0; k < kUnroll; ++k) {
+          const int u = u0 + k * blockDim.x;
+          dst[k] = nullptr;
+          if (u < kBM * units_per_row) {
+            const int r = u / units_per_row, row = tm * kBM + r, col = tn * bn + (u - r * units_per_row) * 8;
+            if (row < sh.M && col < sh.N) {
+              dst[k] = out + ((int64_t)(row + out_roff) * ld_out + col + out_coff) * 2;
+              v[k] = __ldcg((const uint4*)dst[k]);
+            }
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < kUnroll; ++k) {
+          if (!dst[k]) continue;
+          if (use_mc) {
+            multimem::st_v4(ctx.mc(dst[k]), multimem::V4{v[k].x, v[k].y, v[k].z, v[k].w});
+          } else {
+            for (int p = 1; p < ctx.world; ++p) {
+              int r = ctx.rank + p;
+              if (r >= ctx.world) r -= ctx.world;
+              *(uint4*)ctx.remote(dst[k], r) = v[k];
+            }
+          }
+        }
+      }
+    }
+    grid_exit_barrier(ctx, sb, epoch, 0);
+  }
   IRIS_D void post_main() const {
     const int epoch = read_epoch(sb);
     // Outputs written by peers (AG, all-scatter, AR) need the cross-rank round; RS_TILES takes it
@@ -829,6 +919,16 @@ struct Plan {
   int kb_per_src;
 };
 
+// Workgroup-specialised gather / scatter applies when this rank's block of the output is made of whole
+// store boxes (a tensor store that overlapped the next rank's block would race with that rank's data).
+bool wg_specialised(const IrisGemmDesc* d) {
+  const int W = d->ctx.world > 0 ? d->ctx.world : 1;
+  if (d->overlap != 1 || W < 2) return false;
+  if (d->op == IRIS_GEMM_ALL_GATHER) return d->M % kBM == 0;
+  if (d->op == IRIS_GEMM_ALL_SCATTER) return d->N % 64 == 0;
+  return false;
+}
+
 int make_plan(const IrisGemmDesc* d, Plan& p) {
   memset(&p, 0, sizeof(p));
   const int W = d->ctx.world > 0 ? d->ctx.world : 1;
@@ -848,6 +948,8 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
     spare += spare & 1;            // even, so that CTA pairs stay possible
     p.comm_ctas = spare;
   }
+  const bool wg = wg_specialised(d);
+  if (wg) p.comm_ctas = d->comm_ctas > 0 ? d->comm_ctas : 16;
   p.gemm_ctas = d->gemm_ctas > 0 ? d->gemm_ctas : sms - p.comm_ctas;
   if (p.gemm_ctas + p.comm_ctas > sms) return -4;  // every CTA must be resident: consumers wait on producers
   if (d->bn != 0 && d->bn != 256 && d->bn != 224 && d->bn != 128) return -5;
@@ -893,9 +995,9 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
     p.max_owned = p.tiles_m_per_rank * tiles_n;
   } else if (d->op == IRIS_GEMM_ALL_REDUCE) {
     p.max_owned = p.pair ? 2 * ceil_div((tiles_m / 2) * tiles_n, W) : ceil_div(tiles_m * tiles_n, W);
-  } else if (d->op == IRIS_GEMM_AR_ONE_SHOT) {
+  } else if (d->op == IRIS_GEMM_AR_ONE_SHOT || wg) {
     if (d->N % 8) return -3;
-    p.max_owned = tiles_m * tiles_n;            // one arrival counter per tile
+    p.max_owned = tiles_m * tiles_n;            // one arrival counter / flag per 128-row tile
   } else if (d->op == IRIS_GEMM_RS_TILES) {
     p.tiles_per_rank = (tiles_m * tiles_n) / W;
     if (p.tiles_per_rank == 0) p.tiles_per_rank = 1;
@@ -903,7 +1005,7 @@ int make_plan(const IrisGemmDesc* d, Plan& p) {
     if (p.max_owned < p.tiles_per_rank) p.max_owned = p.tiles_per_rank;
   }
   if (p.max_owned) {
-    p.staging_bytes = d->op == IRIS_GEMM_AR_ONE_SHOT ? 2ull * W * d->M * d->N * 2 : 2ull * W * p.max_owned * kBM * p.bn * 2;
+    p.staging_bytes = d->op == IRIS_GEMM_AR_ONE_SHOT ? 2ull * W * d->M * d->N * 2 : wg ? 0 : 2ull * W * p.max_owned * kBM * p.bn * 2;
     p.flags_bytes = 2ull * p.max_owned * 4;
   }
   return 0;
@@ -991,6 +1093,17 @@ extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
     pol.max_owned = p.max_owned; pol.tiles_m_per_rank = p.tiles_m_per_rank; pol.tiles_per_rank = p.tiles_per_rank;
     pol.use_mc = use_mc;
     pol.c_bulk = 0;
+    pol.wg_spec = 0; pol.out_roff = 0; pol.out_coff = 0; pol.n_comm_ctas = p.comm_ctas;
+    if (wg_specialised(d)) {
+      // this rank's block of the gathered output, as a tensor-store target
+      const bool rows = d->op == IRIS_GEMM_ALL_GATHER;
+      pol.out_roff = rows ? ctx.rank * d->M : 0;
+      pol.out_coff = rows ? 0 : ctx.rank * d->N;
+      pol.c_bulk = make_out_maps(&pol.tmC, &pol.tmC32, d->C, d->dtype, rows ? (uint64_t)ctx.world * d->M : (uint64_t)d->M,
+                                 rows ? (uint64_t)d->N : (uint64_t)ctx.world * d->N, d->ldc);
+      if (!pol.c_bulk || !d->flags) return -15;
+      pol.wg_spec = 1;
+    }
     if (d->op == IRIS_GEMM_REDUCE_SCATTER)
       pol.c_bulk = make_out_maps(&pol.tmC, &pol.tmC32, d->C, d->dtype, (uint64_t)p.tiles_m_per_rank * kBM, d->N, d->ldc);
     else if (d->op == IRIS_GEMM_RS_TILES)

@@ -172,10 +172,24 @@ __global__ void moe_clear_kernel(MoeDims dm, MoeMeta m) {
 // kStage 1: A = inbox rows (dispatch runs in the communication CTAs of the same kernel), B = fused
 // gate|up weight, SwiGLU epilogue into H. kStage 2: A = H, B = down weight, the epilogue sends
 // every row to its token's home rank.
-template <int kStage>
+// kFp8: block-scaled e4m3. Tokens travel as e4m3 rows plus one scale byte per 128 columns; the inbox rows of
+// a tile arrive one by one, so the producer warp puts the tile's scale atoms together from those bytes
+// (kSfaFromRows). Stage 1's SwiGLU epilogue writes H as e4m3 with one scale byte per row and 128 columns
+// (kQuantOut), which stage 2 reads the same way. Weights carry 128 x 128 block scales packed per expert.
+template <int kStage, bool kFp8 = false>
 struct GroupedGemm : Common {
   static constexpr bool kBulkEpilogue = false;
   static constexpr bool kSwiGLU = kStage == 1;
+  static constexpr bool kSfaFromRows = kFp8;
+  static constexpr bool kQuantOut = kFp8 && kStage == 1;
+  static constexpr int kEsz = kFp8 ? 1 : 2;        // bytes per element of the tokens / of H
+  const uint8_t* a_sf;     // fp8: scale bytes of this GEMM's A rows, [capacity][a_sf_ld] (inbox_sf or H_sf)
+  int a_sf_ld;
+  const uint8_t* x_sf;     // fp8 stage 1: scale bytes of this rank's tokens [T][a_sf_ld] (dispatch source)
+  uint8_t* inbox_sf;       // fp8 stage 1: heap [capacity][a_sf_ld]
+  uint8_t* h_sf;           // fp8 stage 1: [capacity][h_sf_ld] scale bytes of H
+  int h_sf_ld;
+  int sfb_per_expert;      // fp8: scale atoms of B per expert (tiles_n * kblocks * sfb_atoms)
   DeviceContext ctx;
   SyncBlock* sb;
   MoeDims dm;
@@ -194,6 +208,8 @@ struct GroupedGemm : Common {
     int key = -1;          // expert whose arrivals were confirmed
     int row0 = 0, rows_end = 0;
     unsigned long long* tab = nullptr;   // stage 2: destination row pointers of this warp's 32 rows
+    uint32_t sf_cur[4] = {0, 0, 0, 0};   // fp8 producer: scale bytes of rows lane + 32 a for K blocks [4 g, 4 g + 4)
+    uint32_t sf_nxt[4] = {0, 0, 0, 0};   //               and for the next four
   };
   IRIS_D int num_tiles() const { return meta.tile_prefix[dm.El] * tiles_n; }
   // tile -> (virtual m index = global 128-row tile counter, n tile); experts in order
@@ -216,10 +232,44 @@ struct GroupedGemm : Common {
         ptx::fence_proxy_async();
       }
     }
-    s.map = &tmA; s.x = kb * kBK; s.y = st.row0;
-    if (b_kmajor) { s.bk = kb * kBK; s.bn0 += st.j * n_per_expert; }
-    else s.bk = st.j * k_per_expert + kb * kBK;
+    s.map = &tmA; s.x = kb * bk; s.y = st.row0;
+    if (b_kmajor) { s.bk = kb * bk; s.bn0 += st.j * n_per_expert; }
+    else s.bk = st.j * k_per_expert + kb * bk;
+    s.sf_map = nullptr; s.sf_row = 0;
+    s.sfb_off = st.j * sfb_per_expert;
     return true;
+  }
+  // fp8: the scale atom of (128-row tile at st.row0, K block kb). Lane l owns rows l, l + 32, l + 64, l + 96:
+  // their scale bytes come four K blocks at a time (one 32-bit load per row, the following group prefetched),
+  // and the lane writes bytes [16 l, 16 l + 16) of the atom: for each of its rows the byte of this block, four times.
+  IRIS_D void sfa_fill(State& st, int, int kb, uint8_t* atom, int lane) const {
+    auto ld = [&](int a, int k) -> uint32_t {
+      const int row = min(st.row0 + lane + 32 * a, dm.capacity - 1);
+      return __ldcg((const uint32_t*)(a_sf + (size_t)row * a_sf_ld + k));
+    };
+    if (kb == 0) {
+#pragma unroll
+      for (int a = 0; a < 4; ++a) { st.sf_cur[a] = ld(a, 0); st.sf_nxt[a] = 4 < a_sf_ld ? ld(a, 4) : 0; }
+    } else if ((kb & 3) == 0) {
+#pragma unroll
+      for (int a = 0; a < 4; ++a) { st.sf_cur[a] = st.sf_nxt[a]; st.sf_nxt[a] = kb + 4 < a_sf_ld ? ld(a, kb + 4) : 0; }
+    }
+    const int sh8 = (kb & 3) * 8;
+    uint4 v;
+    v.x = ((st.sf_cur[0] >> sh8) & 0xffu) * 0x01010101u;
+    v.y = ((st.sf_cur[1] >> sh8) & 0xffu) * 0x01010101u;
+    v.z = ((st.sf_cur[2] >> sh8) & 0xffu) * 0x01010101u;
+    v.w = ((st.sf_cur[3] >> sh8) & 0xffu) * 0x01010101u;
+    *(uint4*)(atom + lane * 16) = v;
+  }
+  // fp8 stage 1: 32 e4m3 values of H, and the row's scale byte for the tile's 128 columns
+  IRIS_D void store_q32(State& st, int row, int col, uint4 a, uint4 b) const {
+    if (row >= st.rows_end || col >= dm.F) return;
+    uint4* p = (uint4*)(H + (size_t)row * dm.F + col);
+    p[0] = a; p[1] = b;
+  }
+  IRIS_D void store_row_scale(State& st, int row, int n_tile, uint32_t byte) const {
+    if (row < st.rows_end) h_sf[(size_t)row * h_sf_ld + n_tile] = (uint8_t)byte;
   }
   IRIS_D int row_origin(State& st, int) const { return st.row0; }
   IRIS_D void begin_tile(State& st, int tm, int, uint8_t* warp_scratch) const {
@@ -234,7 +284,7 @@ struct GroupedGemm : Common {
       if (row < st.rows_end) {
         const long long mt = meta.inbox_meta[row];
         const int src = (int)(mt >> 32), pair = (int)(mt & 0xffffffffll);
-        ptr = (unsigned long long)ctx.remote(comb + (size_t)pair * dm.D * 2, src);
+        ptr = (unsigned long long)ctx.remote(comb + (size_t)pair * dm.D * 2, src);      // the combine buffer stays 16-bit
       }
       __syncwarp();
       st.tab[lane] = ptr;
@@ -265,7 +315,7 @@ struct GroupedGemm : Common {
     const int c = blockIdx.x - n_gemm_ctas;
     const int W = ctx.world;
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
-    const uint32_t row_bytes = (uint32_t)dm.D * 2;
+    const uint32_t row_bytes = (uint32_t)dm.D * kEsz;
     const int pieces = (int)((row_bytes + kSlot - 1) / kSlot);      // pieces per row
     int nb = (smem_bytes - 1024) / kSlot;
     if (nb > 12) nb = 12;
@@ -293,6 +343,16 @@ struct GroupedGemm : Common {
       // routing records
       for (int i = threadIdx.x; i < n; i += blockDim.x)
         if (dst0 + i < dm.capacity) dst_meta[dst0 + i] = ((long long)ctx.rank << 32) | (long long)meta.sorted_pairs[lo + i];
+      if constexpr (kFp8) {       // and the rows' scale bytes, 16 at a time
+        uint8_t* dst_sf = ctx.remote(inbox_sf, r);
+        const int per_row = a_sf_ld / 16;
+        for (int u = threadIdx.x; u < n * per_row; u += blockDim.x) {
+          const int i = u / per_row, c16 = u - i * per_row;
+          if (dst0 + i >= dm.capacity) continue;
+          const int tok = meta.sorted_pairs[lo + i] / dm.K;
+          *(uint4*)(dst_sf + (size_t)(dst0 + i) * a_sf_ld + c16 * 16) = *(const uint4*)(x_sf + (size_t)tok * a_sf_ld + c16 * 16);
+        }
+      }
       if (threadIdx.x == 0) {
         const int total = n * pieces;
         auto src_of = [&](int q) -> const uint8_t* {
@@ -387,6 +447,16 @@ typedef struct IrisMoeDesc {
   int32_t* expert_rows; int32_t* expert_row0; int32_t* tile_prefix; int32_t* expected_cum; int32_t* arrived;
   void* inbox_meta;
   int32_t weights_kmajor;   // 1: w13 is [El, 2F, D] and w2 is [El, D, F] (each expert's weight transposed: K contiguous)
+  // Block-scaled e4m3 mode (fp8 != 0; weights_kmajor must be 1): x is the e4m3 form of the tokens [T, D] bytes,
+  // w13 / w2 are e4m3, inbox is [capacity, D] bytes, H is [capacity, F] bytes; comb and out stay bf16.
+  int32_t fp8;
+  int32_t sf_ld1;           // bytes per row of x_sf / inbox_sf: >= D / 128, multiple of 16
+  int32_t sf_ld2;           // bytes per row of H_sf: >= F / 128, multiple of 16
+  const void* x_sf;         // [T, sf_ld1] one UE8M0 byte per token and 128 columns
+  void* inbox_sf;           // heap [capacity, sf_ld1]
+  void* H_sf;               // [capacity, sf_ld2]
+  const void* w13_sf;       // scale atoms of w13: [El][2F / 256][D / 128][2][512]
+  const void* w2_sf;        // scale atoms of w2:  [El][ceil(D / 224)][F / 128][2][512]
 } IrisMoeDesc;
 
 int iris_moe_forward(const IrisMoeDesc* d, void* stream_) {
@@ -406,43 +476,80 @@ int iris_moe_forward(const IrisMoeDesc* d, void* stream_) {
   const int sms = sm_count();
   const int comm = ctx.world > 0 ? (d->comm_ctas > 0 ? d->comm_ctas : 16) : 0;
   const bool km = d->weights_kmajor != 0;
+  auto common = [&](auto& pol, int bn, int N, int Kdim, bool f8) {
+    pol.sh = Shape{d->capacity, N, Kdim};
+    pol.tiles_m = 0; pol.tiles_n = ceil_div(N, bn); pol.group_m = 1;
+    pol.bf16 = 1; pol.bn = bn; pol.fp8 = f8; pol.bk = f8 ? 128 : kBK; pol.kblocks = ceil_div(Kdim, pol.bk);
+    pol.sfb_atoms = f8 ? ceil_div(bn, 128) : 0; pol.c_bulk = 0;
+    pol.bias_row = nullptr; pol.bias_col = nullptr; pol.status = d->ctx.status; pol.timeline = nullptr;
+    pol.ctx = ctx; pol.dm = dm; pol.meta = m;
+    pol.inbox = (uint8_t*)d->inbox; pol.H = (uint8_t*)d->H; pol.comb = (uint8_t*)d->comb;
+    pol.b_kmajor = km;
+    pol.a_sf = nullptr; pol.a_sf_ld = 0; pol.x_sf = nullptr; pol.inbox_sf = nullptr; pol.h_sf = nullptr; pol.h_sf_ld = 0;
+    pol.sfb_per_expert = pol.tiles_n * pol.kblocks * pol.sfb_atoms;
+  };
+  if (d->fp8) {
+    if (!km || d->sf_ld1 % 16 || d->sf_ld2 % 16 || d->sf_ld1 * 128 < d->D || d->sf_ld2 * 128 < d->F || d->D % 128 || d->F % 128) return -3;
+    {
+      GroupedGemm<1, true> pol;
+      common(pol, 256, 2 * d->F, d->D, true);
+      int r = make_map(&pol.tmA, d->inbox, IRIS_F8E4M3, d->capacity, d->D, d->D, 128, kBM);
+      if (r) return r;
+      r = make_map(&pol.tmB, d->w13, IRIS_F8E4M3, (uint64_t)d->El * 2 * d->F, d->D, d->D, 128, 256);
+      if (r) return r;
+      r = make_sf_map(&pol.tmSFB, d->w13_sf, (uint64_t)d->El * pol.sfb_per_expert, pol.sfb_atoms);
+      if (r) return r;
+      pol.tmSFA = pol.tmSFB;      // unused: A's atoms are built from the rows' scale bytes
+      pol.n_gemm_ctas = sms - comm; pol.sb = nullptr;
+      pol.x = (const uint8_t*)d->x; pol.n_comm_ctas = comm; pol.k_per_expert = d->D; pol.n_per_expert = 2 * d->F;
+      pol.a_sf = (const uint8_t*)d->inbox_sf; pol.a_sf_ld = d->sf_ld1; pol.x_sf = (const uint8_t*)d->x_sf;
+      pol.inbox_sf = (uint8_t*)d->inbox_sf; pol.h_sf = (uint8_t*)d->H_sf; pol.h_sf_ld = d->sf_ld2;
+      r = launch<Config<256, true, 3, false, true, 1>>(pol, sms, s);
+      if (r) return r;
+    }
+    {
+      GroupedGemm<2, true> pol;
+      common(pol, 224, d->D, d->F, true);
+      int r = make_map(&pol.tmA, d->H, IRIS_F8E4M3, d->capacity, d->F, d->F, 128, kBM);
+      if (r) return r;
+      r = make_map(&pol.tmB, d->w2, IRIS_F8E4M3, (uint64_t)d->El * d->D, d->F, d->F, 128, 224);
+      if (r) return r;
+      r = make_sf_map(&pol.tmSFB, d->w2_sf, (uint64_t)d->El * pol.sfb_per_expert, pol.sfb_atoms);
+      if (r) return r;
+      pol.tmSFA = pol.tmSFB;
+      pol.n_gemm_ctas = sms; pol.sb = (SyncBlock*)d->sync_gemm2;
+      pol.x = nullptr; pol.n_comm_ctas = 0; pol.k_per_expert = d->F; pol.n_per_expert = d->D;
+      pol.a_sf = (const uint8_t*)d->H_sf; pol.a_sf_ld = d->sf_ld2;
+      r = launch<Config<224, true, 4, false, true, 2>>(pol, sms, s);
+      if (r) return r;
+    }
+  } else {
   {
     GroupedGemm<1> pol;
-    IrisGemmDesc gd;
-    memset(&gd, 0, sizeof(gd));
-    gd.dtype = IRIS_BF16;
-    pol.tmA = CUtensorMap{};
+    common(pol, 256, 2 * d->F, d->D, false);
     int r = make_map(&pol.tmA, d->inbox, IRIS_BF16, d->capacity, d->D, d->D, kBK, kBM);
     if (r) return r;
     if (km) r = make_map(&pol.tmB, d->w13, IRIS_BF16, (uint64_t)d->El * 2 * d->F, d->D, d->D, kBK, 256);
     else r = make_map(&pol.tmB, d->w13, IRIS_BF16, (uint64_t)d->El * d->D, 2 * d->F, 2 * d->F, 64, 64);
     if (r) return r;
-    pol.sh = Shape{d->capacity, 2 * d->F, d->D};
-    pol.tiles_m = 0; pol.tiles_n = (2 * d->F) / 256; pol.group_m = 1;
-    pol.n_gemm_ctas = sms - comm; pol.bf16 = 1; pol.bn = 256; pol.fp8 = 0; pol.bk = kBK; pol.kblocks = 0; pol.sfb_atoms = 0; pol.c_bulk = 0;
-    pol.bias_row = nullptr; pol.bias_col = nullptr; pol.status = d->ctx.status; pol.timeline = nullptr;
-    pol.ctx = ctx; pol.sb = nullptr; pol.dm = dm; pol.meta = m;
-    pol.x = (const uint8_t*)d->x; pol.inbox = (uint8_t*)d->inbox; pol.H = (uint8_t*)d->H; pol.comb = (uint8_t*)d->comb;
-    pol.n_comm_ctas = comm; pol.k_per_expert = d->D; pol.n_per_expert = km ? 2 * d->F : 0; pol.b_kmajor = km;
+    pol.n_gemm_ctas = sms - comm; pol.sb = nullptr;
+    pol.x = (const uint8_t*)d->x; pol.n_comm_ctas = comm; pol.k_per_expert = d->D; pol.n_per_expert = km ? 2 * d->F : 0;
     r = km ? launch<Config<256, true, 4>>(pol, sms, s) : launch<Config<256, false, 4>>(pol, sms, s);
     if (r) return r;
   }
   {
     GroupedGemm<2> pol;
+    common(pol, 256, d->D, d->F, false);
     int r = make_map(&pol.tmA, d->H, IRIS_BF16, d->capacity, d->F, d->F, kBK, kBM);
     if (r) return r;
     if (km) r = make_map(&pol.tmB, d->w2, IRIS_BF16, (uint64_t)d->El * d->D, d->F, d->F, kBK, 256);
     else r = make_map(&pol.tmB, d->w2, IRIS_BF16, (uint64_t)d->El * d->F, d->D, d->D, 64, 64);
     if (r) return r;
-    pol.sh = Shape{d->capacity, d->D, d->F};
-    pol.tiles_m = 0; pol.tiles_n = d->D / 256; pol.group_m = 1;
-    pol.n_gemm_ctas = sms; pol.bf16 = 1; pol.bn = 256; pol.fp8 = 0; pol.bk = kBK; pol.kblocks = 0; pol.sfb_atoms = 0; pol.c_bulk = 0;
-    pol.bias_row = nullptr; pol.bias_col = nullptr; pol.status = d->ctx.status; pol.timeline = nullptr;
-    pol.ctx = ctx; pol.sb = (SyncBlock*)d->sync_gemm2; pol.dm = dm; pol.meta = m;
-    pol.x = nullptr; pol.inbox = (uint8_t*)d->inbox; pol.H = (uint8_t*)d->H; pol.comb = (uint8_t*)d->comb;
-    pol.n_comm_ctas = 0; pol.k_per_expert = d->F; pol.n_per_expert = km ? d->D : 0; pol.b_kmajor = km;
+    pol.n_gemm_ctas = sms; pol.sb = (SyncBlock*)d->sync_gemm2;
+    pol.x = nullptr; pol.n_comm_ctas = 0; pol.k_per_expert = d->F; pol.n_per_expert = km ? d->D : 0;
     r = km ? launch<Config<256, true, 4>>(pol, sms, s) : launch<Config<256, false, 4>>(pol, sms, s);
     if (r) return r;
+  }
   }
   moe_reduce_kernel<<<d->T, 256, 0, s>>>((const __nv_bfloat16*)d->comb, d->topk_w, (__nv_bfloat16*)d->out, d->T, d->K, d->D);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;

@@ -5,6 +5,8 @@
 //   atoms  [ceil(M / 128), KB, 512] UE8M0 bytes in the layout tcgen05.cp copies into TMEM: row r of a
 //          128-row tile at byte (r % 32) * 16 + (r / 32) * 4, four equal bytes (the four 32-element K
 //          groups of the block share the scale).
+//   rows   [M, ld_rows] one UE8M0 byte per row and K block (optional): the form that travels with a row when
+//          rows are routed one by one (MoE dispatch); the consumer builds the atoms of its tiles from it.
 // The reference has no quantised path; this plays the role of the activation cast in front of its
 // 16-bit GEMMs (iris/ops/matmul_all_reduce.py:95-105 consumes 16-bit tiles directly).
 // One warp per (row, K block): four elements per lane, amax by shuffles, scale = 2^ceil(log2(amax / 448)).
@@ -53,7 +55,8 @@ __device__ __forceinline__ void load4<__half>(const __half* p, int n_valid, bool
 
 template <typename T>
 __global__ void __launch_bounds__(256) quantize_1x128_pow2_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q, int64_t ldq,
-                                                                   float* __restrict__ scale, uint8_t* __restrict__ atoms, int M, int K, int KB,
+                                                                   float* __restrict__ scale, uint8_t* __restrict__ atoms,
+                                                                   uint8_t* __restrict__ rows, int64_t ld_rows, int M, int K, int KB,
                                                                    int aligned) {
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -82,6 +85,7 @@ __global__ void __launch_bounds__(256) quantize_1x128_pow2_kernel(const T* __res
   else for (int i = 0; i < n_valid; ++i) dst[i] = (uint8_t)(packed >> (8 * i));
   if (lane == 0) {
     if (scale) scale[(int64_t)row * KB + kb] = s;
+    if (rows) rows[(int64_t)row * ld_rows + kb] = (uint8_t)(e + 127);
     if (atoms) {
       const uint32_t b = (uint32_t)(e + 127);
       const int tile = row >> 7, r = row & 127;
@@ -95,8 +99,8 @@ __global__ void __launch_bounds__(256) quantize_1x128_pow2_kernel(const T* __res
 // x: [M, K] of `dtype` (IRIS_F32 / IRIS_BF16 / IRIS_F16), row pitch ldx elements. q: [M, K] bytes, pitch ldq.
 // scale (may be null): [M, ceil(K / 128)] fp32. atoms (may be null): [ceil(M / 128), ceil(K / 128), 512] bytes;
 // rows past M inside the last 128-row tile are NOT written (pre-fill the buffer with 127 = scale 1 if M is ragged).
-extern "C" int iris_quantize_1x128_pow2(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t ldq, float* scale, void* atoms,
-                                        int32_t M, int32_t K, void* stream) {
+static int quantize_launch(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t ldq, float* scale, void* atoms, void* rows,
+                           int64_t ld_rows, int32_t M, int32_t K, void* stream) {
   if (M <= 0 || K <= 0) return 0;
   const int KB = (K + 127) / 128;
   const int64_t warps = (int64_t)M * KB;
@@ -106,12 +110,22 @@ extern "C" int iris_quantize_1x128_pow2(const void* x, int64_t ldx, int32_t dtyp
   const int esz = dtype == IRIS_F32 ? 4 : 2;
   const int aligned = (((uintptr_t)x % (4 * esz)) == 0 && (ldx * esz) % (4 * esz) == 0) ? 1 : 0;
   if (dtype == IRIS_F32)
-    quantize_1x128_pow2_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)x, ldx, (uint8_t*)q, ldq, scale, (uint8_t*)atoms, M, K, KB, aligned);
+    quantize_1x128_pow2_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)x, ldx, (uint8_t*)q, ldq, scale, (uint8_t*)atoms, (uint8_t*)rows, ld_rows, M, K, KB, aligned);
   else if (dtype == IRIS_BF16)
-    quantize_1x128_pow2_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, scale, (uint8_t*)atoms, M, K, KB, aligned);
+    quantize_1x128_pow2_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, scale, (uint8_t*)atoms, (uint8_t*)rows, ld_rows, M, K, KB, aligned);
   else if (dtype == IRIS_F16)
-    quantize_1x128_pow2_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>((const __half*)x, ldx, (uint8_t*)q, ldq, scale, (uint8_t*)atoms, M, K, KB, aligned);
+    quantize_1x128_pow2_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>((const __half*)x, ldx, (uint8_t*)q, ldq, scale, (uint8_t*)atoms, (uint8_t*)rows, ld_rows, M, K, KB, aligned);
   else
     return -2;
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int iris_quantize_1x128_pow2(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t ldq, float* scale, void* atoms,
+                                        int32_t M, int32_t K, void* stream) {
+  return quantize_launch(x, ldx, dtype, q, ldq, scale, atoms, nullptr, 0, M, K, stream);
+}
+// Same, writing one scale byte per row and K block into rows [M, ld_rows] (bytes past ceil(K / 128) of a row are left alone).
+extern "C" int iris_quantize_1x128_pow2_rows(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t ldq, void* rows, int64_t ld_rows,
+                                             int32_t M, int32_t K, void* stream) {
+  return quantize_launch(x, ldx, dtype, q, ldq, nullptr, nullptr, rows, ld_rows, M, K, stream);
 }

@@ -53,6 +53,19 @@ struct Heap {
   uint64_t mc_base = 0;
   uint64_t mc_size = 0;
   bool mc_bound = false;
+  // Growable VMM heaps (the reference's VMemAllocator, allocators/vmem_allocator.py:55-212): `reserve` bytes of
+  // address space are reserved for the own mapping and for every peer's window; the first segment is the
+  // heap created up front, later segments (on-demand growth, or an external allocation mapped in without a
+  // copy) are mapped behind it at the same offset on every rank.
+  struct Segment {
+    uint64_t offset = 0, size = 0;
+    CUmemGenericAllocationHandle handle = 0;
+    bool external = false;     // a retained handle of somebody else's allocation: released, never freed twice
+  };
+  uint64_t reserve = 0;        // 0: not growable (address space = mapped_size)
+  uint64_t first_size = 0;     // mapped size of the segment created with the heap
+  std::vector<Segment> segs;                               // own segments after the first
+  std::vector<std::vector<Segment>> peer_segs;             // per peer: its later segments mapped here
   std::mutex mu;
   std::string error;
 };
@@ -79,13 +92,15 @@ static bool vmm_prop(int device, bool fabric, CUmemAllocationProp& prop, uint64_
   return true;
 }
 
-static bool vmm_map(int device, CUmemGenericAllocationHandle h, uint64_t size, uint64_t& va, std::string& e) {
+// Reserve `reserve` (>= size) bytes of address space and map `h` at its start.
+static bool vmm_map(int device, CUmemGenericAllocationHandle h, uint64_t size, uint64_t& va, std::string& e, uint64_t reserve = 0) {
   const DriverApi& d = driver();
   CUdeviceptr p = 0;
-  CUresult r = d.cuMemAddressReserve(&p, size, 0, 0, 0);
+  if (reserve < size) reserve = size;
+  CUresult r = d.cuMemAddressReserve(&p, reserve, 0, 0, 0);
   if (r != CUDA_SUCCESS) { e = "cuMemAddressReserve: " + cu_error(r); return false; }
   r = d.cuMemMap(p, size, 0, h, 0);
-  if (r != CUDA_SUCCESS) { d.cuMemAddressFree(p, size); e = "cuMemMap: " + cu_error(r); return false; }
+  if (r != CUDA_SUCCESS) { d.cuMemAddressFree(p, reserve); e = "cuMemMap: " + cu_error(r); return false; }
   CUmemAccessDesc acc;
   memset(&acc, 0, sizeof(acc));
   acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
@@ -94,11 +109,25 @@ static bool vmm_map(int device, CUmemGenericAllocationHandle h, uint64_t size, u
   r = d.cuMemSetAccess(p, size, &acc, 1);
   if (r != CUDA_SUCCESS) {
     d.cuMemUnmap(p, size);
-    d.cuMemAddressFree(p, size);
+    d.cuMemAddressFree(p, reserve);
     e = "cuMemSetAccess: " + cu_error(r);
     return false;
   }
   va = (uint64_t)p;
+  return true;
+}
+// Map `h` at a fixed address inside an existing reservation.
+static bool vmm_map_at(int device, CUmemGenericAllocationHandle h, uint64_t va, uint64_t size, std::string& e) {
+  const DriverApi& d = driver();
+  CUresult r = d.cuMemMap((CUdeviceptr)va, size, 0, h, 0);
+  if (r != CUDA_SUCCESS) { e = "cuMemMap: " + cu_error(r); return false; }
+  CUmemAccessDesc acc;
+  memset(&acc, 0, sizeof(acc));
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = device;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  r = d.cuMemSetAccess((CUdeviceptr)va, size, &acc, 1);
+  if (r != CUDA_SUCCESS) { d.cuMemUnmap((CUdeviceptr)va, size); e = "cuMemSetAccess: " + cu_error(r); return false; }
   return true;
 }
 
@@ -196,8 +225,16 @@ int iris_rt_ipc_close_handle(uint64_t ptr) {
 }
 
 // ---------------------------------------------------------------------------------- heap
+static uint64_t g_next_reserve = 0;
+// The next VMM heap created by this process reserves `bytes` of address space per mapping, so that it
+// can grow (iris_heap_grow) or take in external allocations (iris_heap_import_external) up to that size.
+void iris_heap_set_next_reserve(uint64_t bytes) { g_next_reserve = bytes; }
+
 void* iris_heap_create(uint64_t size, int device, int rank, int world, int kind, int fabric, char* err, int errlen) {
   Heap* h = new Heap();
+  h->peer_segs.assign(world, {});
+  if (kind == kVmm && g_next_reserve > size) h->reserve = g_next_reserve;
+  g_next_reserve = 0;
   h->kind = kind;
   h->device = device;
   h->rank = rank;
@@ -251,7 +288,9 @@ void* iris_heap_create(uint64_t size, int device, int rank, int world, int kind,
       }
       r = d.cuMemCreate(&h->handle, h->mapped_size, &prop, 0);
       if (r != CUDA_SUCCESS) { set_err(err, errlen, "cuMemCreate: " + cu_error(r)); delete h; return nullptr; }
-      if (!vmm_map(device, h->handle, h->mapped_size, h->base, e)) {
+      if (h->reserve) h->reserve = round_up(h->reserve, gran) < h->mapped_size ? h->mapped_size : round_up(h->reserve, gran);
+      h->first_size = h->mapped_size;
+      if (!vmm_map(device, h->handle, h->mapped_size, h->base, e, h->reserve)) {
         d.cuMemRelease(h->handle);
         set_err(err, errlen, e);
         delete h;
@@ -338,10 +377,97 @@ int iris_heap_import_fd(void* hp, int peer, int fd, char* err, int errlen) {
   CUresult r = d.cuMemImportFromShareableHandle(&ph, (void*)(intptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
   if (r != CUDA_SUCCESS) { set_err(err, errlen, "cuMemImportFromShareableHandle: " + cu_error(r)); return -1; }
   uint64_t va = 0;
-  if (!vmm_map(h->device, ph, h->mapped_size, va, e)) { d.cuMemRelease(ph); set_err(err, errlen, e); return -1; }
+  const uint64_t first = h->first_size ? h->first_size : h->mapped_size;
+  if (!vmm_map(h->device, ph, first, va, e, h->reserve)) { d.cuMemRelease(ph); set_err(err, errlen, e); return -1; }
   h->peer_base[peer] = va;
   h->peer_kind[peer] = 1;
   h->peer_handle[peer] = ph;
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------- growth and external memory
+// All of these are collective by convention (every rank grows by the same amount at the same point of its
+// allocation sequence, as with every allocation on a symmetric heap); the exchange of the new segment's
+// descriptor is driven from Python over the fd mesh.
+static int add_own_segment(Heap* h, CUmemGenericAllocationHandle handle, uint64_t size, bool external, std::string& e) {
+  if (h->mapped_size + size > h->reserve) { e = "the heap's reserved address space is exhausted"; return -1; }
+  if (!vmm_map_at(h->device, handle, h->base + h->mapped_size, size, e)) return -1;
+  Heap::Segment sgm;
+  sgm.offset = h->mapped_size; sgm.size = size; sgm.handle = handle; sgm.external = external;
+  h->segs.push_back(sgm);
+  h->mapped_size += size;
+  h->size = h->mapped_size;
+  return (int)h->segs.size() - 1;
+}
+// Map `bytes` more (rounded up to the allocation granularity) behind the heap. Returns the segment index or -1.
+int iris_heap_grow(void* hp, uint64_t bytes, char* err, int errlen) {
+  Heap* h = (Heap*)hp;
+  std::lock_guard<std::mutex> g(h->mu);
+  std::string e;
+  if (h->kind != kVmm || !h->reserve) { set_err(err, errlen, "this heap was not created growable"); return -1; }
+  const DriverApi& d = driver();
+  ensure_context(h->device);
+  CUmemAllocationProp prop;
+  uint64_t gran = 0;
+  if (!vmm_prop(h->device, h->fabric, prop, gran, e)) { set_err(err, errlen, e); return -1; }
+  const uint64_t size = round_up(bytes, gran);
+  CUmemGenericAllocationHandle handle = 0;
+  CUresult r = d.cuMemCreate(&handle, size, &prop, 0);
+  if (r != CUDA_SUCCESS) { set_err(err, errlen, "cuMemCreate: " + cu_error(r)); return -1; }
+  const int idx = add_own_segment(h, handle, size, false, e);
+  if (idx < 0) { d.cuMemRelease(handle); set_err(err, errlen, e); return -1; }
+  d.cuMemsetD8_v2((CUdeviceptr)(h->base + h->segs[idx].offset), 0, size);
+  d.cuCtxSynchronize();
+  return idx;
+}
+// Map the allocation that contains `ptr` (memory created with cuMemCreate by someone else, e.g. a framework's
+// expandable segments) behind the heap WITHOUT copying it: the same physical memory then has a second address
+// inside the heap, at which peers can reach it. *inner = offset of `ptr` inside the new segment.
+int iris_heap_import_external(void* hp, uint64_t ptr, uint64_t* inner, char* err, int errlen) {
+  Heap* h = (Heap*)hp;
+  std::lock_guard<std::mutex> g(h->mu);
+  std::string e;
+  if (h->kind != kVmm || !h->reserve) { set_err(err, errlen, "this heap was not created growable"); return -1; }
+  const DriverApi& d = driver();
+  ensure_context(h->device);
+  CUmemGenericAllocationHandle handle = 0;
+  CUresult r = d.cuMemRetainAllocationHandle(&handle, (void*)(uintptr_t)ptr);
+  if (r != CUDA_SUCCESS) { set_err(err, errlen, "cuMemRetainAllocationHandle (memory not created with cuMemCreate?): " + cu_error(r)); return -1; }
+  CUdeviceptr abase = 0;
+  size_t asize = 0;
+  r = d.cuMemGetAddressRange_v2(&abase, &asize, (CUdeviceptr)ptr);
+  if (r != CUDA_SUCCESS) { d.cuMemRelease(handle); set_err(err, errlen, "cuMemGetAddressRange: " + cu_error(r)); return -1; }
+  const int idx = add_own_segment(h, handle, (uint64_t)asize, true, e);
+  if (idx < 0) { d.cuMemRelease(handle); set_err(err, errlen, e); return -1; }
+  if (inner) *inner = ptr - (uint64_t)abase;
+  return idx;
+}
+int iris_heap_num_segments(void* hp) { return (int)((Heap*)hp)->segs.size(); }
+uint64_t iris_heap_segment_offset(void* hp, int seg) { return ((Heap*)hp)->segs[seg].offset; }
+uint64_t iris_heap_segment_size(void* hp, int seg) { return ((Heap*)hp)->segs[seg].size; }
+uint64_t iris_heap_reserved(void* hp) { return ((Heap*)hp)->reserve; }
+int iris_heap_segment_export_fd(void* hp, int seg, char* err, int errlen) {
+  Heap* h = (Heap*)hp;
+  int fd = -1;
+  CUresult r = driver().cuMemExportToShareableHandle(&fd, h->segs[seg].handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+  if (r != CUDA_SUCCESS) { set_err(err, errlen, "cuMemExportToShareableHandle(segment): " + cu_error(r)); return -1; }
+  return fd;
+}
+// Map a peer's segment (received as a file descriptor) at the same offset of that peer's window.
+int iris_heap_segment_import_fd(void* hp, int peer, int fd, uint64_t offset, uint64_t size, char* err, int errlen) {
+  Heap* h = (Heap*)hp;
+  std::string e;
+  if (h->kind != kVmm || !h->reserve || h->peer_kind[peer] != 1) { set_err(err, errlen, "no growable window for this peer"); return -1; }
+  if (offset + size > h->reserve) { set_err(err, errlen, "segment beyond the reserved window"); return -1; }
+  const DriverApi& d = driver();
+  ensure_context(h->device);
+  CUmemGenericAllocationHandle ph = 0;
+  CUresult r = d.cuMemImportFromShareableHandle(&ph, (void*)(intptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+  if (r != CUDA_SUCCESS) { set_err(err, errlen, "cuMemImportFromShareableHandle(segment): " + cu_error(r)); return -1; }
+  if (!vmm_map_at(h->device, ph, h->peer_base[peer] + offset, size, e)) { d.cuMemRelease(ph); set_err(err, errlen, e); return -1; }
+  Heap::Segment sgm;
+  sgm.offset = offset; sgm.size = size; sgm.handle = ph;
+  h->peer_segs[peer].push_back(sgm);
   return 0;
 }
 int iris_heap_import_blob(void* hp, int peer, const uint8_t* in64, char* err, int errlen) {
@@ -480,19 +606,29 @@ int iris_heap_destroy(void* hp) {
     if (d.cuMulticastUnbind(h->mc_handle, dev, 0, h->mc_size) != CUDA_SUCCESS) ++failures;
   }
   if (h->mc_handle && d.cuMemRelease(h->mc_handle) != CUDA_SUCCESS) ++failures;
+  const uint64_t first = h->first_size ? h->first_size : h->mapped_size;      // size of the segment created with the heap
+  const uint64_t window = h->reserve ? h->reserve : first;                    // address space per mapping
   for (int r = 0; r < h->world; ++r) {
     if (r == h->rank) continue;
     if (h->peer_kind[r] == 1) {
-      if (d.cuMemUnmap((CUdeviceptr)h->peer_base[r], h->mapped_size) != CUDA_SUCCESS) ++failures;
-      if (d.cuMemAddressFree((CUdeviceptr)h->peer_base[r], h->mapped_size) != CUDA_SUCCESS) ++failures;
+      for (auto& sg : h->peer_segs[r]) {
+        if (d.cuMemUnmap((CUdeviceptr)(h->peer_base[r] + sg.offset), sg.size) != CUDA_SUCCESS) ++failures;
+        if (d.cuMemRelease(sg.handle) != CUDA_SUCCESS) ++failures;
+      }
+      if (d.cuMemUnmap((CUdeviceptr)h->peer_base[r], first) != CUDA_SUCCESS) ++failures;
+      if (d.cuMemAddressFree((CUdeviceptr)h->peer_base[r], window) != CUDA_SUCCESS) ++failures;
       if (d.cuMemRelease(h->peer_handle[r]) != CUDA_SUCCESS) ++failures;
     } else if (h->peer_kind[r] == 2) {
       if (d.cuIpcCloseMemHandle((CUdeviceptr)h->peer_base[r]) != CUDA_SUCCESS) ++failures;
     }
   }
   if (h->kind == kVmm) {
-    if (d.cuMemUnmap((CUdeviceptr)h->base, h->mapped_size) != CUDA_SUCCESS) ++failures;
-    if (d.cuMemAddressFree((CUdeviceptr)h->base, h->mapped_size) != CUDA_SUCCESS) ++failures;
+    for (auto& sg : h->segs) {
+      if (d.cuMemUnmap((CUdeviceptr)(h->base + sg.offset), sg.size) != CUDA_SUCCESS) ++failures;
+      if (d.cuMemRelease(sg.handle) != CUDA_SUCCESS) ++failures;
+    }
+    if (d.cuMemUnmap((CUdeviceptr)h->base, first) != CUDA_SUCCESS) ++failures;
+    if (d.cuMemAddressFree((CUdeviceptr)h->base, window) != CUDA_SUCCESS) ++failures;
     if (d.cuMemRelease(h->handle) != CUDA_SUCCESS) ++failures;
   } else {
     if (d.cuMemFree_v2((CUdeviceptr)h->base) != CUDA_SUCCESS) ++failures;

@@ -18,6 +18,7 @@
 #include "../ptx.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 namespace iris {
 namespace gemm {
@@ -43,8 +44,11 @@ constexpr uint64_t kPipeTimeoutNs = 4000000000ull;
 // four bytes = the four K groups); the MMA thread copies them to TMEM (tcgen05.cp) in front of the
 // block's MMAs. The two accumulator buffers are packed BN columns apart and the scales use 16
 // columns behind them, so BN is at most 240.
-template <int BN_, bool kBKMajor_, int kStages_, bool kPair_ = false, bool kFp8_ = false>
+template <int BN_, bool kBKMajor_, int kStages_, bool kPair_ = false, bool kFp8_ = false, int kAccBufs_ = 2>
 struct Config {
+  static constexpr int kAccBufs = kAccBufs_;                             // accumulator buffers in TMEM: 2 (the epilogue of a tile overlaps
+                                                                        // the next tile's main loop) or 1 (a 256-wide fp8 tile: two would not
+                                                                        // leave room for the scale cells)
   static constexpr int BN = BN_;
   static constexpr bool kBKMajor = kBKMajor_;
   static constexpr int kStages = kStages_;
@@ -60,7 +64,7 @@ struct Config {
   static constexpr int kSfbAtoms = kFp8_ ? (BN_ + 127) / 128 : 0;       // scale atoms of B per stage (every CTA of a pair holds all of them)
   static constexpr int kSfBytes = kFp8_ ? (1 + kSfbAtoms) * 512 : 0;    // scale bytes per stage
   static constexpr int kAccCols = kFp8_ ? BN_ : 256;                    // column pitch of an accumulator buffer
-  static constexpr int kSfaCol = 2 * kAccCols;                          // TMEM columns of the scales (fp8 only): A 4, then B 4 per atom;
+  static constexpr int kSfaCol = kAccBufs_ * kAccCols;                        // TMEM columns of the scales (fp8 only): A 4, then B 4 per atom;
   static constexpr int kSfbCol = kSfaCol + 4;                           // two such sets, used by alternate K blocks, so that the copy
   static constexpr int kSfSetCols = 4 + 4 * kSfbAtoms;                  // for block kb + 1 does not wait for the MMAs of block kb
   static constexpr int kTmemCols = 512;
@@ -72,7 +76,8 @@ struct Config {
   static_assert(BN_ % 32 == 0 && BN_ >= 32 && BN_ <= 256, "BN must be a multiple of 32 up to 256");
   static_assert(!kPair_ || kBCols % 16 == 0, "a pair splits B into two halves of whole 16-column groups");
   static_assert(kStageBytes % 1024 == 0, "stages keep the 1024-byte alignment of the 128-byte swizzle");
-  static_assert(!kFp8_ || (kBKMajor_ && 2 * BN_ + 2 * (4 + 4 * kSfbAtoms) <= 512), "fp8: K-major B, and accumulators plus scales must fit TMEM");
+  static_assert(kAccBufs_ == 1 || kAccBufs_ == 2, "one or two accumulator buffers");
+  static_assert(!kFp8_ || (kBKMajor_ && kAccBufs_ * BN_ + 2 * (4 + 4 * kSfbAtoms) <= 512), "fp8: K-major B, and accumulators plus scales must fit TMEM");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
@@ -119,6 +124,7 @@ struct ASource {
   // fp8 only: where the scale atom of this (128-row tile, K block) is: row of a [atoms, 128 x u32] map
   const CUtensorMap* sf_map;
   int sf_row;
+  int sfb_off;   // added to the row of B's scale atoms (grouped GEMMs: the group's first atom)
 };
 
 // GROUP_M swizzled tile order (same idea as the reference's GROUP_SIZE_M, all_reduce.py:182-187).
@@ -154,6 +160,11 @@ struct Pipeline {
 //        [gate 128 | up 128]; emit silu(gate) * up, 128 columns per 256-wide tile)
 //   void store16(State&, int row, int col, uint4 v) const; (8 consecutive outputs of one row)
 //   float row_bias(int row) const;  float col_bias(int col) const;  bool has_bias() const;
+//   static constexpr bool kSfaFromRows;  void sfa_fill(State&, int m_tile, int kb, uint8_t* atom, int lane) const;
+//        (fp8: the producer warp builds A's 512-byte scale atom itself, lane l writing bytes [16 l, 16 l + 16))
+//   static constexpr bool kQuantOut;  void store_q32(State&, int row, int col, uint4, uint4) const;
+//        void store_row_scale(State&, int row, int n_tile, uint32_t ue8m0) const;
+//        (SwiGLU epilogue that writes e4m3 values, 32 per call, and one scale byte per row and tile)
 //   static constexpr bool kBulkEpilogue;                   (true: tiles may leave through store_chunk)
 //   bool bulk_tile(State&) const;                          (this tile leaves in 64-column chunks staged in
 //        shared memory in the 128-byte-swizzle layout, each stored by ONE asynchronous bulk / tensor store)
@@ -257,9 +268,20 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
       for (int kb = 0; kb < k_blocks; ++kb) {
         ASource as;
         as.bn0 = tn * Cfg::BN;
+        as.sfb_off = 0;
         if (!pol.a_source(st, tm, kb, as)) { ok = false; break; }
         if (kb == 0 && lane == 0) pol.stamp(t, 1);
         if (!ptx::mbar_wait<kPair>(&pipe.empty[s], ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
+        if constexpr (Cfg::kFp8 && Policy::kSfaFromRows) {
+          // A's scale atom is put together here from one scale byte per row (rows that arrived one by one,
+          // e.g. dispatched tokens, have no ready-made atom): lane l writes the 16 bytes of rows l, l + 32,
+          // l + 64, l + 96. Generic-proxy stores, made visible to tcgen05.cp by the proxy fence; the arrive of
+          // lane 0 below (after the warp barrier) publishes them together with the TMA bytes.
+          static_assert(!kPair, "scale atoms built from rows: single-CTA tiles only");
+          pol.sfa_fill(st, tm, kb, sf_base + s * Cfg::kSfBytes, lane);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+        }
         if (lane == 0) {
           uint8_t* sa = stage_base + s * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
@@ -275,7 +297,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
                 ptx::tma_load_2d_pair(sb + j * 8192, pol.b_map(), &pipe.full[s], n0 + j * 64, as.bk);
             }
           } else {
-            ptx::mbar_expect_tx(&pipe.full[s], Cfg::kStageBytes + Cfg::kSfBytes);
+            ptx::mbar_expect_tx(&pipe.full[s], Cfg::kStageBytes + Cfg::kSfBytes - ((Cfg::kFp8 && Policy::kSfaFromRows) ? 512 : 0));
             ptx::tma_load_2d(sa, as.map, &pipe.full[s], as.x, as.y);
             if constexpr (Cfg::kBKMajor) {
               ptx::tma_load_2d(sb, pol.b_map(), &pipe.full[s], as.bk, as.bn0);
@@ -289,12 +311,12 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
             // scale atoms: this tile's 128 rows of A, and all of the tile's columns of B (each
             // CTA of a pair keeps the whole of B's scales: its MMA half multiplies every column)
             uint8_t* ssf = sf_base + s * Cfg::kSfBytes;
-            const int brow = pol.b_sf_row(tn, as.bk / Cfg::kBKElems);   // B's K block: not kb when A is gathered along K
+            const int brow = pol.b_sf_row(tn, as.bk / Cfg::kBKElems) + as.sfb_off;   // B's K block: not kb when A is gathered along K
             if constexpr (kPair) {
               ptx::tma_load_2d_pair(ssf, as.sf_map, &pipe.full[s], 0, as.sf_row);
               ptx::tma_load_2d_pair(ssf + 512, pol.sfb_map(), &pipe.full[s], 0, brow);
             } else {
-              ptx::tma_load_2d(ssf, as.sf_map, &pipe.full[s], 0, as.sf_row);
+              if constexpr (!Policy::kSfaFromRows) ptx::tma_load_2d(ssf, as.sf_map, &pipe.full[s], 0, as.sf_row);
               ptx::tma_load_2d(ssf + 512, pol.sfb_map(), &pipe.full[s], 0, brow);
             }
           }
@@ -311,8 +333,8 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
     int it = 0;
     bool ok = leader;      // the even CTA of a pair issues for both
     for (int t = first; t < num_tiles && ok; t += step, ++it) {
-      const int buf = it & 1;
-      const uint32_t acc_ph = (it >> 1) & 1;
+      const int buf = Cfg::kAccBufs == 2 ? (it & 1) : 0;
+      const uint32_t acc_ph = Cfg::kAccBufs == 2 ? ((it >> 1) & 1) : (it & 1);
       if (!ptx::mbar_wait<kPair>(&pipe.tmem_empty[buf], acc_ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); break; }
       ptx::tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * Cfg::kAccCols;
@@ -375,8 +397,8 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
     typename Policy::State est;
     int it = 0;
     for (int t = first; t < num_tiles; t += step, ++it) {
-      const int buf = it & 1;
-      const uint32_t acc_ph = (it >> 1) & 1;
+      const int buf = Cfg::kAccBufs == 2 ? (it & 1) : 0;
+      const uint32_t acc_ph = Cfg::kAccBufs == 2 ? ((it >> 1) & 1) : (it & 1);
       int tm, tn;
       pol.tile(t, tm, tn);
       if constexpr (kPair) tm = 2 * tm + (int)cta;
@@ -464,7 +486,55 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
           if (lane == 0) ptx::bulk_wait_read<0>();   // earlier bulk stores may still read the staging
           __syncwarp();
         }
-        if constexpr (Policy::kSwiGLU) {
+        if constexpr (Policy::kSwiGLU && Policy::kQuantOut) {
+          // SwiGLU whose output feeds a block-scaled fp8 GEMM: the tile's 128 outputs of a row are exactly one
+          // 1 x 128 quantisation block. Pass 1 finds the row's amax, pass 2 (TMEM is read again, which is
+          // cheaper than keeping 128 values) writes e4m3 values; the row's scale leaves as one UE8M0 byte.
+          static_assert(Cfg::BN == 256, "the SwiGLU epilogue pairs columns c and c + 128 of a 256-wide tile");
+          float amax = 0.f;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t g[32], u[32];
+            ptx::tmem_ld_32x32(t_addr + c * 32, g);
+            ptx::tmem_ld_32x32(t_addr + 128 + c * 32, u);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+              amax = fmaxf(amax, fabsf(gv / (1.f + __expf(-gv)) * uv));
+            }
+          }
+          int e8 = (int)ceilf(log2f(fmaxf(amax, 1e-12f) * (1.0f / 448.0f)));
+          e8 = max(-127, min(127, e8));
+          const float inv = exp2f((float)-e8);
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t g[32], u[32];
+            ptx::tmem_ld_32x32(t_addr + c * 32, g);
+            ptx::tmem_ld_32x32(t_addr + 128 + c * 32, u);
+            ptx::tmem_ld_wait();
+            if (c == 3) {
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) release_acc(buf);
+            }
+            uint32_t q[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float h[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float gv = __uint_as_float(g[4 * j + k]), uv = __uint_as_float(u[4 * j + k]);
+                h[k] = gv / (1.f + __expf(-gv)) * uv * inv;
+              }
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(h[0], h[1]), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(h[2], h[3]), __NV_SATFINITE, __NV_E4M3);
+              q[j] = lo | (hi << 16);
+            }
+            pol.store_q32(est, row0 + lane, tn * 128 + c * 32, make_uint4(q[0], q[1], q[2], q[3]), make_uint4(q[4], q[5], q[6], q[7]));
+          }
+          pol.store_row_scale(est, row0 + lane, tn, (uint32_t)(e8 + 127));
+        } else if constexpr (Policy::kSwiGLU) {
           static_assert(!Policy::kSwiGLU || Cfg::BN == 256, "the SwiGLU epilogue pairs columns c and c + 128 of a 256-wide tile");
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {

@@ -80,6 +80,11 @@ typedef struct IrisGemmDesc {
   const void* sf_a;
   const void* sf_b;
   void* sf_inbox;
+  // ALL_GATHER / ALL_SCATTER: how the collective half overlaps the GEMM. 0: every epilogue warp stores its
+  // fragment to all ranks itself ("fused sequential"); 1: the GEMM CTAs write the tile to this rank's own
+  // output and raise a per-tile flag, `comm_ctas` communication CTAs of the same kernel wait for the flags
+  // and forward the tiles to the peers ("workgroup specialised"; flags: [2][128-row tiles x column tiles]).
+  int32_t overlap;
 } IrisGemmDesc;
 
 // Block-scaled fp8 (e4m3) GEMM: C = (A * scale_a) @ (B * scale_b)^T with A [M, K] and B [N, K]

@@ -68,6 +68,7 @@ class IrisGemmDesc(C.Structure):
         ("sf_a", C.c_void_p),
         ("sf_b", C.c_void_p),
         ("sf_inbox", C.c_void_p),
+        ("overlap", C.c_int32),
     ]
 
 

@@ -73,6 +73,7 @@ class State:
         self._baseline_fn = None
         self._baseline_preamble_fn = None
         self.n_warmup, self.n_repeat = n_warmup, n_repeat
+        self.timing = "per_call"
 
     def __getitem__(self, key):
         return self._params[key]
@@ -102,6 +103,15 @@ class State:
 
     def set_repeat(self, n: int) -> None:
         self.n_repeat = int(n)
+
+    def set_timing(self, mode: str) -> None:
+        """``"per_call"``: every timed call is preceded by a barrier, the preamble and an L2 flush (the
+        reference's do_bench protocol; below about 1 MB it mostly measures launch skew between the ranks).
+        ``"back_to_back"``: one pair of CUDA events around ``n_repeat`` calls issued without a gap after one
+        barrier: the steady-state time per call, caches warm."""
+        if mode not in ("per_call", "back_to_back"):
+            raise ValueError("timing is 'per_call' or 'back_to_back'")
+        self.timing = mode
 
     def exec(self, fn: Callable, preamble_fn: Callable | None = None) -> None:
         self._exec_fn, self._preamble_fn = fn, preamble_fn

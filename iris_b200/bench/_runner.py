@@ -120,6 +120,24 @@ def run_benchmarks(ctx, benchmarks, overrides, skips, n_warmup, n_repeat) -> lis
 
     from ..host.platform import do_bench
 
+    def timed(state, fn, preamble):
+        """Milliseconds per call on this rank, as a list (one entry per timed call, or one mean)."""
+        if state.timing == "back_to_back" and not ctx.is_cpu:
+            pre = preamble or (lambda: None)
+            pre()
+            for _ in range(max(state.n_warmup, 1)):
+                fn()
+            ctx.barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(state.n_repeat):
+                fn()
+            e.record()
+            torch.cuda.synchronize()
+            return [s.elapsed_time(e) / state.n_repeat]
+        return do_bench(fn, barrier_fn=ctx.barrier, preamble_fn=preamble or (lambda: None), n_warmup=state.n_warmup,
+                        n_repeat=state.n_repeat, return_mode="all")
+
     results = []
     world = ctx.get_num_ranks()
     # the heap is a bump allocator: take what outlives a point (the collectives' sync block) first,
@@ -141,8 +159,9 @@ def run_benchmarks(ctx, benchmarks, overrides, skips, n_warmup, n_repeat) -> lis
             if state._exec_fn is None:
                 results.append(Result(bdef.name, params, 0.0, [], skipped=True, skip_reason="no exec() registered", world_size=world))
                 continue
-            times = do_bench(state._exec_fn, barrier_fn=ctx.barrier, preamble_fn=state._preamble_fn or (lambda: None),
-                             n_warmup=state.n_warmup, n_repeat=state.n_repeat, return_mode="all")
+            if "timing" in params:
+                state.set_timing(params["timing"])
+            times = timed(state, state._exec_fn, state._preamble_fn)
             mean_ms = sum(times) / len(times)
             t = torch.tensor([mean_ms], dtype=torch.float64, device=ctx.device if not ctx.is_cpu else "cpu")
             if world > 1:
@@ -158,8 +177,7 @@ def run_benchmarks(ctx, benchmarks, overrides, skips, n_warmup, n_repeat) -> lis
                 r.roofline_us = state._roofline_us
                 r.roofline_frac = state._roofline_us / (ms * 1e3)
             if state._baseline_fn is not None:
-                base = do_bench(state._baseline_fn, barrier_fn=ctx.barrier, preamble_fn=state._baseline_preamble_fn or (lambda: None),
-                                n_warmup=state.n_warmup, n_repeat=state.n_repeat, return_mode="all")
+                base = timed(state, state._baseline_fn, state._baseline_preamble_fn)
                 tb = torch.tensor([sum(base) / len(base)], dtype=torch.float64, device=ctx.device if not ctx.is_cpu else "cpu")
                 if world > 1:
                     dist.all_reduce(tb, op=dist.ReduceOp.MAX)

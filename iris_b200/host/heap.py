@@ -73,6 +73,15 @@ def _rt():
         "iris_heap_mc_attach": (i32, [vp, i32, i32, cp, i32]),
         "iris_heap_mc_bind": (i32, [vp, cp, i32]),
         "iris_heap_destroy": (i32, [vp]),
+        "iris_heap_set_next_reserve": (None, [u64]),
+        "iris_heap_grow": (i32, [vp, u64, cp, i32]),
+        "iris_heap_import_external": (i32, [vp, u64, C.POINTER(C.c_uint64), cp, i32]),
+        "iris_heap_num_segments": (i32, [vp]),
+        "iris_heap_segment_offset": (u64, [vp, i32]),
+        "iris_heap_segment_size": (u64, [vp, i32]),
+        "iris_heap_reserved": (u64, [vp]),
+        "iris_heap_segment_export_fd": (i32, [vp, i32, cp, i32]),
+        "iris_heap_segment_import_fd": (i32, [vp, i32, i32, u64, u64, cp, i32]),
         "iris_fdmesh_create": (vp, [cp, cp, i32]),
         "iris_fdmesh_send": (i32, [vp, cp, i32, i32, i32, u64, cp, i32]),
         "iris_fdmesh_recv": (i32, [vp, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(u64), cp, i32]),
@@ -179,6 +188,17 @@ class SymmetricHeap:
             raise ValueError(f"unknown allocator_type {allocator_type!r} (torch, vmem, ipc, cpu)")
         self.allocator_type = allocator_type
         self.device = torch.device("cpu") if (kinds == [KIND_CPU] or fake) else torch.device("cuda", device_id)
+        # allocator_type="vmem" (the reference's VMemAllocator, allocators/vmem_allocator.py:37-344): address
+        # space for the whole heap is reserved, physical memory is mapped on demand (first IRIS_VMEM_INITIAL
+        # bytes, default 64 MiB; later segments as allocations need them) and an external allocation can be
+        # mapped in without a copy. Such a heap is not bound to a multicast object.
+        self.reserve = 0
+        if allocator_type == "vmem" and kinds == [KIND_VMM]:
+            self.reserve = self.heap_size
+            initial = int(os.environ.get("IRIS_VMEM_INITIAL", str(64 << 20)))
+            self._initial_size = max(min(self.heap_size, initial), 1 << 20)
+            if enable_multicast is None:
+                enable_multicast = False
 
         last_error = None
         for kind in kinds:
@@ -216,7 +236,11 @@ class SymmetricHeap:
         if kind != KIND_CPU and self.device.type == "cuda":
             torch.cuda.set_device(self.device_id)
             torch.zeros(1, device=f"cuda:{self.device_id}")  # make sure the primary context exists
-        h = rt.iris_heap_create(self.heap_size, self.device_id, self.cur_rank, self.num_ranks, kind, 0, err, _ERRLEN)
+        create_size = self.heap_size
+        if self.reserve and kind == KIND_VMM:
+            rt.iris_heap_set_next_reserve(self.reserve)
+            create_size = self._initial_size
+        h = rt.iris_heap_create(create_size, self.device_id, self.cur_rank, self.num_ranks, kind, 0, err, _ERRLEN)
         if not h:
             raise RuntimeError(err.value.decode())
         self._handle = h
@@ -301,6 +325,18 @@ class SymmetricHeap:
         elem = torch.empty((), dtype=dtype).element_size()
         nbytes = int(num_elements) * elem
         off = _rt().iris_heap_alloc(self._handle, nbytes, alignment)
+        if off < 0 and self.reserve:
+            # growable heap: map more physical memory behind what is mapped (collective: every rank reaches this
+            # point of its allocation sequence with the same request), then allocate again
+            used = _rt().iris_heap_offset(self._handle)
+            mapped = _rt().iris_heap_mapped_size(self._handle)
+            start = -(-used // alignment) * alignment
+            need = start + max(nbytes, alignment) - mapped
+            chunk = int(os.environ.get("IRIS_VMEM_CHUNK", str(64 << 20)))
+            grow = max(need, min(chunk, self.reserve - mapped))
+            if mapped + need <= self.reserve and grow > 0:
+                self._add_segment(lambda err: _rt().iris_heap_grow(self._handle, int(grow), err, _ERRLEN))
+                off = _rt().iris_heap_alloc(self._handle, nbytes, alignment)
         if off < 0:
             used = _rt().iris_heap_offset(self._handle)
             raise MemoryError(f"Heap out of memory: requested {nbytes} bytes, {self.heap_size - used} of {self.heap_size} free")
@@ -337,10 +373,84 @@ class SymmetricHeap:
             return True
         return self.owns_ptr(tensor.data_ptr(), tensor.numel() * tensor.element_size() if tensor.is_contiguous() else 0)
 
+    # ------------------------------------------------------------------ segments (growable heaps)
+    def _add_segment(self, make) -> int:
+        """Create one more segment of this rank's heap with ``make(err) -> index`` and map every peer's new
+        segment at the same offset of that peer's window (collective; descriptors travel over the fd mesh)."""
+        rt = _rt()
+        err = C.create_string_buffer(_ERRLEN)
+        seg = make(err)
+        ok = seg >= 0
+        msg = err.value.decode() if not ok else ""
+        off = rt.iris_heap_segment_offset(self._handle, seg) if ok else 0
+        size = rt.iris_heap_segment_size(self._handle, seg) if ok else 0
+        # every rank must have got the same segment, or the heaps stop being symmetric
+        seen = D.distributed_allgather(np.array([1 if ok else 0, off, size], dtype=np.int64), self.group).reshape(-1, 3)
+        if not all(int(r[0]) for r in seen):
+            raise RuntimeError(f"a rank could not add a heap segment: {msg or 'see the other ranks'}")
+        if len({(int(r[1]), int(r[2])) for r in seen}) != 1:
+            raise RuntimeError(f"heap segments differ between ranks (offset, size): {[(int(r[1]), int(r[2])) for r in seen]}")
+        if self.num_ranks > 1:
+            mesh = FdMesh(self.cur_rank, self.num_ranks, self.group)
+            fd = rt.iris_heap_segment_export_fd(self._handle, seg, err, _ERRLEN)
+            try:
+                if fd < 0:
+                    raise RuntimeError(err.value.decode())
+                for p in range(self.num_ranks):
+                    if p != self.cur_rank:
+                        mesh.send(p, fd, _TAG_HEAP)
+                for _ in range(self.num_ranks - 1):
+                    pfd, src, tag, _ = mesh.recv()
+                    if tag != _TAG_HEAP or pfd < 0:
+                        raise RuntimeError(f"unexpected message (tag {tag}) while exchanging segment handles")
+                    rc = rt.iris_heap_segment_import_fd(self._handle, src, pfd, off, size, err, _ERRLEN)
+                    rt.iris_close_fd(pfd)
+                    if rc != 0:
+                        raise RuntimeError(f"mapping rank {src}'s segment: {err.value.decode()}")
+            finally:
+                if fd >= 0:
+                    rt.iris_close_fd(fd)
+                mesh.close()
+            dist.barrier(group=self.group)
+        self.heap_size = max(self.heap_size, rt.iris_heap_mapped_size(self._handle)) if not self.reserve else self.heap_size
+        return seg
+
+    def import_external_tensor(self, tensor: torch.Tensor) -> torch.Tensor:
+        """Map the allocation behind ``tensor`` into the heap WITHOUT copying (collective) and return the view of
+        ``tensor`` at its heap address: peers reach it like any heap tensor, and both views alias the same memory
+        (reference: allocators/vmem_allocator.py:241-317). Needs a growable heap (``allocator_type="vmem"``) and
+        memory that was created with the driver's virtual-memory API and may be shared through a file descriptor;
+        anything else (``cudaMalloc``'d pools) raises ``RuntimeError`` and ``as_symmetric`` falls back to a copy.
+        Every rank must import an allocation of the same size."""
+        if not self.reserve:
+            raise RuntimeError("import_external_tensor needs a growable heap (allocator_type='vmem')")
+        rt = _rt()
+        inner = C.c_uint64(0)
+        seg = self._add_segment(lambda err: rt.iris_heap_import_external(self._handle, tensor.data_ptr(), C.byref(inner), err, _ERRLEN))
+        off = rt.iris_heap_segment_offset(self._handle, seg)
+        size = rt.iris_heap_segment_size(self._handle, seg)
+        rt.iris_heap_set_offset(self._handle, off + size)           # later allocations come after the imported segment
+        span = (tensor.untyped_storage().nbytes() - tensor.storage_offset() * tensor.element_size()) // tensor.element_size()
+        flat = tensor_from_ptr(self.base + off + inner.value, max(span, tensor.numel()), tensor.dtype, self.device, keepalive=(self, tensor))
+        return flat.as_strided(tensor.shape, tensor.stride())
+
     def as_symmetric(self, tensor: torch.Tensor) -> torch.Tensor:
-        """Return a tensor on the heap with ``tensor``'s contents (the tensor itself if already there)."""
+        """Return a tensor on the heap with ``tensor``'s contents (the tensor itself if already there). On a
+        growable heap the tensor's own memory is mapped into the heap when the driver allows it (no copy);
+        otherwise the contents are copied into a fresh heap allocation."""
         if self.is_symmetric(tensor):
             return tensor
+        if self.reserve and tensor.device.type == self.device.type and os.environ.get("IRIS_VMEM_IMPORT", "1") != "0":
+            # all ranks decide together: an import that one rank cannot do must not leave the others in the exchange
+            can = 1
+            try:
+                from .platform import mem_retain_allocation_handle, mem_release
+                mem_release(mem_retain_allocation_handle(tensor.data_ptr()))
+            except Exception:
+                can = 0
+            votes = D.distributed_allgather(np.array([can], dtype=np.int64), self.group)
+            if int(votes.min()) == 1:
+                return self.import_external_tensor(tensor)
         flat = self.allocate(tensor.numel(), tensor.dtype)
         out = flat.view(tensor.shape) if tensor.is_contiguous() else flat.view(tensor.shape)
         out.copy_(tensor)

@@ -223,6 +223,14 @@ def mem_import_from_shareable_handle(fd: int) -> int:
     return h.value
 
 
+def mem_retain_allocation_handle(ptr: int) -> int:
+    """Handle of the VMM allocation mapped at ``ptr`` (retained: ``mem_release`` it). Raises for memory that
+    was not created with the virtual-memory API (``cudaMalloc``'d pools)."""
+    h = C.c_uint64(0)
+    gpu_try(_rt().iris_rt_mem_retain_handle(int(ptr), C.byref(h)), "cuMemRetainAllocationHandle")
+    return h.value
+
+
 def export_dmabuf_handle(ptr: int, size: int = 0) -> int:
     """File descriptor for the allocation mapped at ``ptr`` (the reference exports a DMA-BUF of an
     address range; here the range must be a VMM mapping, whose allocation handle is exported)."""

@@ -7,8 +7,11 @@ the expert FFNs as grouped GEMMs and returns the weighted sum of the k expert ou
 order. On a GPU the whole pass is the launch sequence of ``csrc/kernels/moe.cu`` on the current
 stream, with the dispatch fused into the first grouped GEMM and the combine fused into the second
 one's epilogue; the reference pipeline with its host barriers and Python-side metadata is
-examples/31_expert_sharded_moe/moe.py:195-328. Weights are bf16 here (the fp8 block-scaled variant
-is not built yet). ``reference_moe`` is the unsharded fp32 PyTorch statement of the layer.
+examples/31_expert_sharded_moe/moe.py:195-328. Weights are bf16, or (``fp8=True``) e4m3 with
+128 x 128 power-of-two block scales: then the tokens are quantised to e4m3 with 1 x 128 scales before
+the dispatch (half the bytes on the wire), both grouped GEMMs run on the tensor core's block-scaled
+path, and the SwiGLU epilogue re-quantises the hidden activations for the down projection; the
+combine and the output stay bf16. ``reference_moe`` is the unsharded fp32 PyTorch statement of the layer.
 """
 from __future__ import annotations
 
@@ -33,6 +36,8 @@ class IrisMoeDesc(C.Structure):
         ("expert_rows", C.c_void_p), ("expert_row0", C.c_void_p), ("tile_prefix", C.c_void_p), ("expected_cum", C.c_void_p),
         ("arrived", C.c_void_p), ("inbox_meta", C.c_void_p),
         ("weights_kmajor", C.c_int32),
+        ("fp8", C.c_int32), ("sf_ld1", C.c_int32), ("sf_ld2", C.c_int32),
+        ("x_sf", C.c_void_p), ("inbox_sf", C.c_void_p), ("H_sf", C.c_void_p), ("w13_sf", C.c_void_p), ("w2_sf", C.c_void_p),
     ]
 
 
@@ -70,7 +75,7 @@ def fuse_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
 class MoELayer:
     def __init__(self, ctx, hidden: int, ffn: int, num_experts: int, top_k: int, max_tokens: int,
                  w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, capacity_factor: float | None = None,
-                 comm_sms: int = 16):
+                 comm_sms: int = 16, fp8: bool = False):
         W = ctx.get_num_ranks()
         if num_experts % W:
             raise ValueError("num_experts must be a multiple of the number of ranks")
@@ -79,6 +84,7 @@ class MoELayer:
             raise ValueError("expected local expert weights [E/W, hidden, ffn] (gate, up) and [E/W, ffn, hidden] (down)")
         self.ctx, self.D, self.F, self.E, self.El, self.K, self.T = ctx, hidden, ffn, num_experts, El, top_k, max_tokens
         self.comm_sms = comm_sms
+        self.fp8 = bool(fp8)
         self.w_gate, self.w_up, self.w_down = w_gate, w_up, w_down
         if ctx.is_cpu:
             return
@@ -92,14 +98,18 @@ class MoELayer:
         cap = W * pairs if capacity_factor is None else min(W * pairs, int(capacity_factor * pairs))
         self.capacity = max(128, -(-cap // 128) * 128)
         i32 = torch.int32
-        self.inbox = ctx.heap.allocate(self.capacity * hidden, torch.bfloat16).view(self.capacity, hidden)
+        if self.fp8:
+            self._init_fp8(dev)
+        else:
+            self.inbox = ctx.heap.allocate(self.capacity * hidden, torch.bfloat16).view(self.capacity, hidden)
         self.inbox_meta = ctx.zeros(self.capacity, dtype=torch.int64)
         self.comb = ctx.heap.allocate(pairs * hidden, torch.bfloat16).view(pairs, hidden)
         self.counts_all = ctx.zeros((W, num_experts), dtype=i32)
         self.arrived = ctx.zeros(El, dtype=i32)
         self.sync_meta = ctx.zeros(80, dtype=i32)
         self.sync_gemm2 = ctx.zeros(80, dtype=i32)
-        self.H = torch.zeros(self.capacity, ffn, dtype=torch.bfloat16, device=dev)
+        if not self.fp8:
+            self.H = torch.zeros(self.capacity, ffn, dtype=torch.bfloat16, device=dev)
         self.topk_idx = torch.zeros(max_tokens, top_k, dtype=i32, device=dev)
         self.topk_w = torch.zeros(max_tokens, top_k, dtype=torch.float32, device=dev)
         z = lambda n: torch.zeros(n, dtype=i32, device=dev)  # noqa: E731
@@ -107,6 +117,46 @@ class MoELayer:
         self.sorted_pairs = z(pairs)
         self.expert_rows, self.expert_row0, self.tile_prefix, self.expected_cum = z(El), z(El + 1), z(El + 1), z(El)
         ctx.barrier()
+
+    def _init_fp8(self, dev) -> None:
+        """Quantise the expert weights (e4m3, 128 x 128 power-of-two block scales, scale atoms packed for the
+        tile widths of the two grouped GEMMs: 256 for gate|up, 224 for down) and allocate the e4m3 buffers."""
+        from ..ops.gemm_fp8 import pack_scales_b, quantize_128x128
+
+        ctx, El, D, F = self.ctx, self.El, self.D, self.F
+        if D % 128 or F % 128:
+            raise ValueError("the fp8 MoE needs hidden and ffn to be multiples of 128")
+        q13, s13 = quantize_128x128(self.w13.reshape(El * 2 * F, D).float(), pow2=True)
+        self.w13_q = q13.view(El, 2 * F, D)
+        self.w13_scale = s13                                                     # [El * 2F / 128, D / 128]
+        self.w13_sf = pack_scales_b(s13, El * 2 * F, 256)                        # experts start on tile boundaries (2F % 256 == 0)
+        q2, s2 = quantize_128x128(self.w2.reshape(El * D, F).float(), pow2=True)
+        self.w2_q = q2.view(El, D, F)
+        self.w2_scale = s2                                                       # [El * D / 128, F / 128]
+        per = D // 128
+        self.w2_sf = torch.stack([pack_scales_b(s2[j * per:(j + 1) * per], D, 224) for j in range(El)]).contiguous()
+        self.sf_ld1 = -(-(D // 128) // 16) * 16
+        self.sf_ld2 = -(-(F // 128) // 16) * 16
+        u8 = torch.uint8
+        self.inbox = ctx.heap.allocate(self.capacity * D, u8).view(self.capacity, D)
+        self.inbox_sf = ctx.heap.allocate(self.capacity * self.sf_ld1, u8).view(self.capacity, self.sf_ld1)
+        self.inbox_sf.fill_(127)
+        self.H = torch.zeros(self.capacity, F, dtype=u8, device=dev)
+        self.H_sf = torch.full((self.capacity, self.sf_ld2), 127, dtype=u8, device=dev)
+        self.xq = torch.zeros(self.T, D, dtype=u8, device=dev)
+        self.x_sf = torch.full((self.T, self.sf_ld1), 127, dtype=u8, device=dev)
+        del self.w13, self.w2
+
+    def _quantise_tokens(self, x) -> None:
+        lib = _lib.kernels()
+        if not getattr(lib, "_iris_quant_rows_typed", False):
+            lib.iris_quantize_1x128_pow2_rows.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                                          C.c_int32, C.c_int32, C.c_void_p]
+            lib.iris_quantize_1x128_pow2_rows.restype = C.c_int
+            lib._iris_quant_rows_typed = True
+        _lib.check(lib.iris_quantize_1x128_pow2_rows(C.c_void_p(x.data_ptr()), x.stride(0), _lib.DTYPE_CODE[x.dtype], C.c_void_p(self.xq.data_ptr()),
+                                                     self.xq.stride(0), C.c_void_p(self.x_sf.data_ptr()), self.sf_ld1, x.shape[0], self.D,
+                                                     C.c_void_p(_lib.current_stream_ptr())), "token quantiser launch", kernels=1)
 
     def _lib(self):
         lib = _lib.kernels()
@@ -133,7 +183,15 @@ class MoELayer:
         d = IrisMoeDesc()
         d.ctx = ctx.ctx_struct()
         d.T, d.K, d.E, d.El, d.D, d.F, d.capacity, d.comm_ctas = T, self.K, self.E, self.El, self.D, self.F, self.capacity, self.comm_sms
-        d.x, d.logits, d.w13, d.w2, d.out = x.data_ptr(), logits.data_ptr(), self.w13.data_ptr(), self.w2.data_ptr(), out.data_ptr()
+        if self.fp8:
+            self._quantise_tokens(x)
+            d.fp8, d.sf_ld1, d.sf_ld2 = 1, self.sf_ld1, self.sf_ld2
+            d.x, d.w13, d.w2 = self.xq.data_ptr(), self.w13_q.data_ptr(), self.w2_q.data_ptr()
+            d.x_sf, d.inbox_sf, d.H_sf = self.x_sf.data_ptr(), self.inbox_sf.data_ptr(), self.H_sf.data_ptr()
+            d.w13_sf, d.w2_sf = self.w13_sf.data_ptr(), self.w2_sf.data_ptr()
+        else:
+            d.x, d.w13, d.w2 = x.data_ptr(), self.w13.data_ptr(), self.w2.data_ptr()
+        d.logits, d.out = logits.data_ptr(), out.data_ptr()
         d.inbox, d.H, d.comb = self.inbox.data_ptr(), self.H.data_ptr(), self.comb.data_ptr()
         d.sync_meta, d.sync_gemm2 = self.sync_meta.data_ptr(), self.sync_gemm2.data_ptr()
         for name in ("topk_idx", "topk_w", "counts_local", "counts_all", "cursor", "list_off", "sorted_pairs", "my_off",

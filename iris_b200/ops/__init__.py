@@ -94,6 +94,7 @@ def _base_desc(ctx, op, M, N, K, A, B, out, config, bias_row=None, bias_col=None
     d.comm_ctas = config.comm_sms
     d.two_sm = 0 if config.two_sm is None else (2 if config.two_sm else 1)
     d.use_mc = 1 if (config.use_multicast and ctx.has_multicast()) else 0
+    d.overlap = 1 if config.overlap in ("wg_specialized", "producer_consumer") else 0
     d.ctx = ctx.ctx_struct()
     return d, keep
 
@@ -137,7 +138,7 @@ def _auto_workspace(ctx, operation, key, dtype, config, make, extra=None):
     dtype, tile configuration) and kept on the context, so a loop that calls an op without passing
     the returned workspace back does not allocate heap memory (and run a barrier) on every call."""
     cache = ctx.__dict__.setdefault("_ops_workspaces", {})
-    ck = (operation, tuple(key), dtype, config.tile_n(), config.two_sm, config.comm_sms, config.use_multicast, extra)
+    ck = (operation, tuple(key), dtype, config.tile_n(), config.two_sm, config.comm_sms, config.use_multicast, config.overlap, extra)
     ws = cache.get(ck)
     if ws is None:
         ws = cache[ck] = make()
@@ -332,7 +333,7 @@ def _unfused_gather(ctx, ws, A_sharded, shard_dim):
 # ----------------------------------------------------------------------------- matmul_all_gather
 def matmul_all_gather_preamble(shmem, A, B, config=None, scatter_cols=False):
     config = config or _DEFAULT_CONFIG
-    if not _fusable(shmem, A, B):
+    if not _fusable(shmem, A, B) or config.overlap == "bulk_synchronous":
         return FusedWorkspace(operation="matmul_all_gather", variant="unfused", world_size=shmem.num_ranks, prepared=True)
     W = shmem.num_ranks
     M, K = A.shape
@@ -341,6 +342,8 @@ def matmul_all_gather_preamble(shmem, A, B, config=None, scatter_cols=False):
     op = _lib.GEMM_ALL_SCATTER if scatter_cols else _lib.GEMM_ALL_GATHER
     d, _ = _base_desc(shmem, op, M, N, K, A, B, out, config)
     ws = _make_workspace(shmem, "matmul_all_gather", tuple(A.shape) + tuple(B.shape) + (scatter_cols,), A.dtype, "fused", d)
+    if ws is not None:
+        ws.extra["overlap"] = "wg_specialized" if d.overlap else "fused"
     return ws or FusedWorkspace(operation="matmul_all_gather", variant="unfused", world_size=W, prepared=True)
 
 
@@ -351,6 +354,11 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
     With ``scatter_cols`` the local result is ``(M, N_local)`` and lands in columns
     ``[r*N_local, (r+1)*N_local)`` of every rank's ``(M, W*N_local)`` output: the "GEMM +
     all-scatter" layout of the reference's examples/07_gemm_all_scatter.
+
+    ``config.overlap`` selects the overlap pattern (``FusedConfig``): ``"fused"`` (default),
+    ``"wg_specialized"`` (communication CTAs inside the kernel; ``"producer_consumer"`` is accepted as a
+    synonym: its two-kernel form, two kernels that wait on one another on one GPU, is not built) or
+    ``"bulk_synchronous"`` (GEMM, then ``ctx.ccl.all_gather``).
     """
     config = config or _DEFAULT_CONFIG
     W = shmem.num_ranks
@@ -364,6 +372,11 @@ def matmul_all_gather(shmem, output_tensor, A, B, bias=None, async_op=False, con
         raise ValueError(f"matmul_all_gather: output must be {want}, got {tuple(output_tensor.shape)}")
     key = tuple(A.shape) + tuple(B.shape) + (scatter_cols,)
     ws = workspace
+    want_overlap = "wg_specialized" if config.overlap in ("wg_specialized", "producer_consumer") else config.overlap
+    if ws is not None and ws.variant == "fused" and ws.extra.get("overlap", "fused") != want_overlap:
+        ws = None            # the flags of the workgroup-specialised form belong to its own workspace
+    if ws is not None and (ws.variant == "unfused") != (config.overlap == "bulk_synchronous") and _fusable(shmem, A, B):
+        ws = None
     if ws is None or not (ws.variant == "unfused" or ws.matches("matmul_all_gather", key, A.dtype, W, "fused")):
         ws = _auto_workspace(shmem, "matmul_all_gather", key, A.dtype, config,
                              lambda: matmul_all_gather_preamble(shmem, A, B, config, scatter_cols), extra=B.stride(-1) == 1)

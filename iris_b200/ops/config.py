@@ -24,6 +24,13 @@ class FusedConfig:
     comm_sms: int = 0
     use_multicast: bool = True
     two_sm: bool | None = None      # CTA pairs on 256-row tiles (tcgen05 cta_group::2); None = the plan decides
+    # matmul_all_gather (GEMM + all-gather / all-scatter): how the collective overlaps the GEMM, after the
+    # reference's taxonomy (docs/conceptual/taxonomy.md; examples 07, 10, 11, 12):
+    #   "fused"             every epilogue warp stores its fragment to all ranks (fused sequential, example 07)
+    #   "wg_specialized"    comm_sms communication CTAs of the same kernel forward finished tiles (example 10;
+    #                       also what stands in for the two-kernel producer / consumer of example 11 here)
+    #   "bulk_synchronous"  GEMM kernel, then the all-gather kernel (example 12)
+    overlap: str = "fused"
     allow_tf32: bool = True
 
     def __post_init__(self):
@@ -31,6 +38,8 @@ class FusedConfig:
             raise ValueError("block sizes must be positive")
         if self.group_size_m <= 0:
             raise ValueError("group_size_m must be positive")
+        if self.overlap not in ("fused", "wg_specialized", "producer_consumer", "bulk_synchronous"):
+            raise ValueError(f"unknown overlap pattern {self.overlap!r}")
         if self.all_reduce_variant not in ("atomic", "ring", "one_shot", "two_shot", "spinlock", "auto"):
             raise ValueError(f"unknown all_reduce_variant {self.all_reduce_variant!r}")
 

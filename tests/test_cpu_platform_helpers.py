@@ -326,3 +326,64 @@ def _context_on_vmm_heap(rank, world):
 
 def test_context_on_the_vmm_heap_of_the_host_memory_driver():
     run_ranks(_context_on_vmm_heap, 3, env={"IRIS_FAKE_DRIVER_DEVICES": "4"}, timeout=120.0)
+
+
+def _vmm_growth(rank, world):
+    """A growable heap (allocator_type="vmem"): address space for the whole heap, physical memory mapped on
+    demand, every rank's new segment mapped at the same offset of its window in every peer; and an external
+    allocation taken into the heap without a copy. Reference: tests/unittests/test_vmem_allocator.py,
+    test_vmem_segmented_export_import.py, test_vmem_imported_tensor_rma.py (on GPUs there)."""
+    import torch.distributed as dist
+
+    from iris_b200.host import platform as hip
+    from iris_b200.host.heap import SymmetricHeap, _rt
+    from iris_b200.host.tensor_utils import tensor_from_ptr
+
+    heap = SymmetricHeap(32 << 20, 0, rank, world, allocator_type="vmem")
+    rt = _rt()
+    assert heap.reserve == 32 << 20 and heap.mc_base == 0
+    first = rt.iris_heap_mapped_size(heap._handle)
+    assert first <= 4 << 20                                                    # IRIS_VMEM_INITIAL, rounded to the granularity
+    a = heap.allocate(256 << 10, torch.float32)                               # 1 MB: inside the first segment
+    assert rt.iris_heap_num_segments(heap._handle) == 0
+    b = heap.allocate(2 << 20, torch.float32)                                 # 8 MB: needs more than is mapped
+    assert rt.iris_heap_num_segments(heap._handle) >= 1 and rt.iris_heap_mapped_size(heap._handle) > first
+    assert heap.is_symmetric(b) and heap.offset_of(b) >= heap.offset_of(a) + a.numel() * 4
+    a.fill_(float(rank + 1))
+    b.fill_(float(10 * (rank + 1)))
+    dist.barrier()
+    for r in range(world):                                                     # both segments of every peer, through this rank's windows
+        assert float(heap.peer_view(a, r)[-1]) == r + 1 and float(heap.peer_view(b, r)[-1]) == 10 * (r + 1)
+    dist.barrier()
+    # an allocation made outside the heap with the driver's virtual-memory API ...
+    gran = hip.get_allocation_granularity(0)
+    h = hip.mem_create(gran, 0)
+    va = hip.mem_address_reserve(gran)
+    hip.mem_map(va, gran, 0, h)
+    hip.mem_set_access(va, gran, 0)
+    ext = tensor_from_ptr(va, 1024, torch.int32, heap.device)
+    ext.copy_(torch.arange(1024, dtype=torch.int32) + 1000 * rank)
+    # ... becomes part of the heap without a copy: same memory, second address
+    sym = heap.as_symmetric(ext)
+    assert heap.is_symmetric(sym) and sym.data_ptr() != ext.data_ptr()
+    assert torch.equal(sym, ext)
+    ext[0] = -7
+    assert int(sym[0]) == -7                                                   # aliases, not copies
+    dist.barrier()
+    nxt = (rank + 1) % world
+    assert int(heap.peer_view(sym, nxt)[1]) == 1 + 1000 * nxt and int(heap.peer_view(sym, nxt)[0]) == -7
+    c = heap.allocate(16, torch.float32)                                       # later allocations come after the imported segment
+    assert heap.offset_of(c) >= heap.offset_of(sym) + sym.numel() * 4
+    with pytest.raises(MemoryError):
+        heap.allocate(40 << 20, torch.uint8)                                   # beyond the reserved address space
+    dist.barrier()
+    del a, b, c, sym, ext
+    heap.close()
+    hip.mem_unmap(va, gran)
+    hip.mem_address_free(va, gran)
+    hip.mem_release(h)
+
+
+def test_growable_vmm_heap_and_zero_copy_import_on_the_host_memory_driver():
+    run_ranks(_vmm_growth, 2, env={"IRIS_FAKE_DRIVER_DEVICES": "2", "IRIS_VMEM_INITIAL": str(2 << 20), "IRIS_VMEM_CHUNK": str(4 << 20)},
+              timeout=120.0)

@@ -429,6 +429,39 @@ def test_moe_layer_world1(ctx, T, E, K):
     ctx.check()
 
 
+@pytest.mark.parametrize("T,E,K,D,F", [(64, 8, 2, 256, 128), (200, 16, 4, 512, 256), (128, 4, 2, 1024, 512)])
+def test_moe_layer_fp8_world1(ctx, T, E, K, D, F):
+    """Block-scaled e4m3 MoE (tokens and hidden activations quantised 1 x 128, weights 128 x 128, scales applied by
+    the tensor core) against the fp32 layer evaluated on the SAME quantised weights: what remains is the
+    quantisation of the tokens and of the hidden activations."""
+    from iris_b200.models import MoELayer, reference_moe
+    from iris_b200.ops.gemm_fp8 import dequantize, quantize_128x128
+
+    torch.manual_seed(4)
+    dt = torch.bfloat16
+    wg = (torch.randn(E, D, F, device="cuda") * 0.05).to(dt)
+    wu = (torch.randn(E, D, F, device="cuda") * 0.05).to(dt)
+    wd = (torch.randn(E, F, D, device="cuda") * 0.05).to(dt)
+    layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg, w_up=wu, w_down=wd, fp8=True)
+
+    def deq(w):      # [E, in, out] -> the values the layer's e4m3 weights stand for
+        out = []
+        for e in range(E):
+            q, s = quantize_128x128(w[e].t().contiguous().float(), pow2=True)       # stored [out, in]
+            out.append(dequantize(q, s, 128).t())
+        return torch.stack(out)
+
+    wgd, wud, wdd = deq(wg), deq(wu), deq(wd)
+    for it in range(2):
+        x = torch.randn(T, D, device="cuda", dtype=dt)
+        logits = torch.randn(T, E, device="cuda")
+        out = layer(x, logits)
+        ref = reference_moe(x, logits, wgd, wud, wdd, K)
+        err = (out.float() - ref).abs().max().item()
+        assert err < 6e-2 * max(ref.abs().max().item(), 1.0), (it, err)
+    ctx.check()
+
+
 def test_router_matches_torch_topk(ctx):
     from iris_b200.models import MoELayer, route
 
