@@ -504,7 +504,7 @@ int iris_moe_forward(const IrisMoeDesc* d, void* stream_) {
       pol.x = (const uint8_t*)d->x; pol.n_comm_ctas = comm; pol.k_per_expert = d->D; pol.n_per_expert = 2 * d->F;
       pol.a_sf = (const uint8_t*)d->inbox_sf; pol.a_sf_ld = d->sf_ld1; pol.x_sf = (const uint8_t*)d->x_sf;
       pol.inbox_sf = (uint8_t*)d->inbox_sf; pol.h_sf = (uint8_t*)d->H_sf; pol.h_sf_ld = d->sf_ld2;
-      r = launch<Config<256, true, 3, false, true, 1>>(pol, sms, s);
+      r = launch<Config<256, true, 4, false, true, 1, 0>>(pol, sms, s);
       if (r) return r;
     }
     {

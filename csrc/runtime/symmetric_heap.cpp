@@ -275,8 +275,9 @@ void* iris_heap_create(uint64_t size, int device, int rank, int world, int kind,
       if (!vmm_prop(device, h->fabric, prop, gran, e)) { set_err(err, errlen, e); delete h; return nullptr; }
       h->mapped_size = round_up(size, gran);
       // a heap that may later be bound to an NVLS multicast object must also be a multiple of
-      // the multicast granularity
-      if (world > 1 && !h->fabric) {
+      // the multicast granularity (hundreds of MB where the driver recommends so); a growable heap is never
+      // bound to one and keeps its small first segment
+      if (world > 1 && !h->fabric && !h->reserve) {
         CUmulticastObjectProp mp;
         memset(&mp, 0, sizeof(mp));
         mp.numDevices = world;
@@ -290,6 +291,7 @@ void* iris_heap_create(uint64_t size, int device, int rank, int world, int kind,
       if (r != CUDA_SUCCESS) { set_err(err, errlen, "cuMemCreate: " + cu_error(r)); delete h; return nullptr; }
       if (h->reserve) h->reserve = round_up(h->reserve, gran) < h->mapped_size ? h->mapped_size : round_up(h->reserve, gran);
       h->first_size = h->mapped_size;
+      if (h->reserve) h->size = h->mapped_size;        // a growable heap allocates from everything that is mapped
       if (!vmm_map(device, h->handle, h->mapped_size, h->base, e, h->reserve)) {
         d.cuMemRelease(h->handle);
         set_err(err, errlen, e);

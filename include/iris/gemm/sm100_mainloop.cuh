@@ -44,8 +44,9 @@ constexpr uint64_t kPipeTimeoutNs = 4000000000ull;
 // four bytes = the four K groups); the MMA thread copies them to TMEM (tcgen05.cp) in front of the
 // block's MMAs. The two accumulator buffers are packed BN columns apart and the scales use 16
 // columns behind them, so BN is at most 240.
-template <int BN_, bool kBKMajor_, int kStages_, bool kPair_ = false, bool kFp8_ = false, int kAccBufs_ = 2>
+template <int BN_, bool kBKMajor_, int kStages_, bool kPair_ = false, bool kFp8_ = false, int kAccBufs_ = 2, int kEpiStage_ = 8192>
 struct Config {
+  static constexpr int kEpiStageBytes = kEpiStage_;                     // staging per epilogue warp: 8 KB, or 0 for an epilogue that stores from registers
   static constexpr int kAccBufs = kAccBufs_;                             // accumulator buffers in TMEM: 2 (the epilogue of a tile overlaps
                                                                         // the next tile's main loop) or 1 (a 256-wide fp8 tile: two would not
                                                                         // leave room for the scale cells)
@@ -68,7 +69,7 @@ struct Config {
   static constexpr int kSfbCol = kSfaCol + 4;                           // two such sets, used by alternate K blocks, so that the copy
   static constexpr int kSfSetCols = 4 + 4 * kSfbAtoms;                  // for block kb + 1 does not wait for the MMAs of block kb
   static constexpr int kTmemCols = 512;
-  static constexpr int kEpiWarpBytes = 2 * 4096 + 256;                  // per warp: 8 KB of staging (two 32-row x 64-col chunks,
+  static constexpr int kEpiWarpBytes = kEpiStage_ + 256;                 // per warp: 8 KB of staging (two 32-row x 64-col chunks,
                                                                         // or one 32-row x 128-col round) + 256 B of policy scratch
                                                                         // (all staging first, 1024-byte aligned, then the scratch)
   static constexpr int kEpiBytes = kEpiWarps * kEpiWarpBytes;
@@ -210,7 +211,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
   // epilogue staging: 8 KB per warp, 1024-byte aligned (tensor stores apply the hardware swizzle to
   // absolute shared-memory addresses), then 256 bytes of policy scratch per warp, then the scales
   uint8_t* epi_base = smem + Cfg::kStages * Cfg::kStageBytes;
-  uint8_t* scratch_base = epi_base + kEpiWarps * 8192;
+  uint8_t* scratch_base = epi_base + kEpiWarps * Cfg::kEpiStageBytes;
   uint8_t* sf_base = scratch_base + kEpiWarps * 256;               // fp8: per stage one scale atom of A, then B's
   uint64_t* bars = (uint64_t*)(sf_base + Cfg::kStages * Cfg::kSfBytes);
   Pipeline pipe{bars, bars + Cfg::kStages, bars + 2 * Cfg::kStages, bars + 2 * Cfg::kStages + 2};
@@ -390,7 +391,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    uint8_t* my_epi = epi_base + (warp - 2) * 8192;
+    uint8_t* my_epi = epi_base + (warp - 2) * Cfg::kEpiStageBytes;
     uint32_t chunk_seq = 0;   // bulk epilogue: chunks issued by this warp (selects the staging half)
     const bool bf16 = pol.is_bf16();
     const bool has_bias = pol.has_bias();
@@ -488,26 +489,13 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         }
         if constexpr (Policy::kSwiGLU && Policy::kQuantOut) {
           // SwiGLU whose output feeds a block-scaled fp8 GEMM: the tile's 128 outputs of a row are exactly one
-          // 1 x 128 quantisation block. Pass 1 finds the row's amax, pass 2 (TMEM is read again, which is
-          // cheaper than keeping 128 values) writes e4m3 values; the row's scale leaves as one UE8M0 byte.
+          // 1 x 128 quantisation block. The outputs are computed once and kept as bf16 pairs in registers while
+          // the row's amax is found (the accumulator buffer is released as soon as TMEM has been read), then
+          // written as e4m3 values; the row's scale leaves as one UE8M0 byte.
           static_assert(Cfg::BN == 256, "the SwiGLU epilogue pairs columns c and c + 128 of a 256-wide tile");
           float amax = 0.f;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t g[32], u[32];
-            ptx::tmem_ld_32x32(t_addr + c * 32, g);
-            ptx::tmem_ld_32x32(t_addr + 128 + c * 32, u);
-            ptx::tmem_ld_wait();
+          uint32_t hreg[64];      // the row's 128 outputs as bf16 pairs: kept so that TMEM is read (and released) once
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
-              amax = fmaxf(amax, fabsf(gv / (1.f + __expf(-gv)) * uv));
-            }
-          }
-          int e8 = (int)ceilf(log2f(fmaxf(amax, 1e-12f) * (1.0f / 448.0f)));
-          e8 = max(-127, min(127, e8));
-          const float inv = exp2f((float)-e8);
-#pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t g[32], u[32];
             ptx::tmem_ld_32x32(t_addr + c * 32, g);
@@ -518,17 +506,28 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
               __syncwarp();
               if (lane == 0) release_acc(buf);
             }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float g0 = __uint_as_float(g[2 * j]), u0 = __uint_as_float(u[2 * j]);
+              const float g1 = __uint_as_float(g[2 * j + 1]), u1 = __uint_as_float(u[2 * j + 1]);
+              const float h0 = g0 / (1.f + __expf(-g0)) * u0, h1 = g1 / (1.f + __expf(-g1)) * u1;
+              amax = fmaxf(amax, fmaxf(fabsf(h0), fabsf(h1)));
+              const __nv_bfloat162 hb = __floats2bfloat162_rn(h0, h1);
+              hreg[c * 16 + j] = *(const uint32_t*)&hb;
+            }
+          }
+          int e8 = (int)ceilf(log2f(fmaxf(amax, 1e-12f) * (1.0f / 448.0f)));
+          e8 = max(-127, min(127, e8));
+          const float inv = exp2f((float)-e8);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
             uint32_t q[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              float h[4];
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const float gv = __uint_as_float(g[4 * j + k]), uv = __uint_as_float(u[4 * j + k]);
-                h[k] = gv / (1.f + __expf(-gv)) * uv * inv;
-              }
-              const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(h[0], h[1]), __NV_SATFINITE, __NV_E4M3);
-              const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(h[2], h[3]), __NV_SATFINITE, __NV_E4M3);
+              const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&hreg[c * 16 + 2 * j]);
+              const float2 b = __bfloat1622float2(*(const __nv_bfloat162*)&hreg[c * 16 + 2 * j + 1]);
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a.x * inv, a.y * inv), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(b.x * inv, b.y * inv), __NV_SATFINITE, __NV_E4M3);
               q[j] = lo | (hi << 16);
             }
             pol.store_q32(est, row0 + lane, tn * 128 + c * 32, make_uint4(q[0], q[1], q[2], q[3]), make_uint4(q[4], q[5], q[6], q[7]));

@@ -72,6 +72,62 @@ def test_rma_between_gpus():
     run_ranks(_rma, _world(), backend="nccl")
 
 
+def _vmem(rank, world):
+    """allocator_type="vmem" on real GPUs: physical memory mapped on demand behind a reserved address range,
+    every new segment exported to and mapped by every peer, and an allocation made outside the heap with the
+    virtual-memory API taken in without a copy (reference: tests/unittests/test_vmem_allocator.py,
+    test_vmem_segmented_export_import.py, test_vmem_imported_tensor_rma.py)."""
+    import iris_b200 as iris
+    from iris_b200.host import platform as hip
+    from iris_b200.host.heap import _rt
+    from iris_b200.host.tensor_utils import tensor_from_ptr
+
+    ctx = iris.iris(256 << 20, allocator_type="vmem")
+    heap, rt = ctx.heap, _rt()
+    assert heap.reserve == 256 << 20 and not ctx.has_multicast()
+    first = rt.iris_heap_mapped_size(heap._handle)
+    a = ctx.zeros(1 << 20, dtype=torch.float32)                    # 4 MB
+    b = ctx.zeros(8 << 20, dtype=torch.float32)                    # 32 MB: beyond the 16 MB mapped at first
+    assert rt.iris_heap_num_segments(heap._handle) >= 1 and rt.iris_heap_mapped_size(heap._handle) > first
+    a.fill_(float(rank + 1))
+    b.fill_(float(10 * (rank + 1)))
+    ctx.barrier()
+    peer = (rank + 1) % world
+    assert float(ctx.rma.load(a[-4:], from_rank=peer)[0]) == peer + 1
+    assert float(ctx.rma.load(b[-4:], from_rank=peer)[0]) == 10 * (peer + 1)        # the grown segment, read from the peer
+    out, inp = ctx.zeros((64, 256), dtype=torch.float32), ctx.full((64, 256), float(rank + 1))
+    ctx.ccl.all_reduce(out, inp)                                    # collectives on a heap without a multicast window
+    assert torch.all(out == sum(range(1, world + 1)))
+    # external VMM allocation -> part of the heap, no copy
+    dev = ctx.gpu_id
+    gran = hip.get_allocation_granularity(dev)
+    h = hip.mem_create(gran, dev)
+    va = hip.mem_address_reserve(gran)
+    hip.mem_map(va, gran, 0, h)
+    hip.mem_set_access(va, gran, dev)
+    ext = tensor_from_ptr(va, 4096, torch.int32, ctx.get_device())
+    ext.copy_(torch.arange(4096, dtype=torch.int32, device=ctx.get_device()) + 1000 * rank)
+    sym = ctx.as_symmetric(ext)
+    assert ctx.is_symmetric(sym) and sym.data_ptr() != ext.data_ptr() and torch.equal(sym, ext)
+    ext[0] = -7
+    torch.cuda.synchronize()
+    assert int(sym[0]) == -7                                        # the same memory under a second address
+    ctx.barrier()
+    got = ctx.rma.load(sym[:8], from_rank=peer).cpu()
+    assert int(got[0]) == -7 and int(got[1]) == 1 + 1000 * peer     # and peers reach it like any heap tensor
+    ctx.barrier()
+    ctx.check()
+    del a, b, sym, ext, out, inp
+    ctx.close()
+    hip.mem_unmap(va, gran)
+    hip.mem_address_free(va, gran)
+    hip.mem_release(h)
+
+
+def test_growable_vmem_heap_and_zero_copy_import_between_gpus():
+    run_ranks(_vmem, _world(), backend="nccl", env={"IRIS_VMEM_INITIAL": str(16 << 20)}, timeout=300)
+
+
 def _ccl(rank, world, nvls):
     import torch.distributed as dist
 
