@@ -807,8 +807,8 @@ struct ScatterGemmT : Common {
 // `pair_ok`). The estimate is waves x tile width x a per-shape factor. Under the power cap a
 // partly idle last wave costs little (the busy SMs clock higher; measured: 6.05 waves of 256-wide
 // pair tiles beat 6.92 waves of 224-wide ones), so the wave count is the fractional one, at least
-// one. Factors are measured: a pair tile saves 4 to 7 % (B leaves L2 once per pair), a 128-wide
-// tile costs about 12 % more.
+// one. Factors are measured: a pair tile saves about 11 % (B leaves L2 once per pair and every
+// stage holds less, so more K blocks are in flight), a 128-wide tile costs about 12 % more.
 void choose_tile(int M, int N, int ctas, int bn_fixed, int pair_mode, bool pair_ok, int& bn_out, int& pair_out) {
   const int cand[3] = {256, 224, 128};
   double best = 1e30;
@@ -825,8 +825,9 @@ void choose_tile(int M, int N, int ctas, int bn_fixed, int pair_mode, bool pair_
       const int slots = ctas >> pr;
       const double frac = (double)tiles / slots;
       const double waves = frac < 1.0 ? 1.0 : frac;
-      // (a 224-wide pair tile measured 2 to 12 % slower per flop than a 256-wide one: its B halves are 112 wide)
-      const double cost = waves * bn * (bn == 128 ? 1.12 : 1.0) * (pr ? (bn == 224 ? 1.05 : 0.95) : 1.0);
+      // (measured with every configuration interleaved under the same power state: a pair tile costs 0.89 of a
+      // single one per flop at either width; a single 224-wide tile 1.05 of a single 256-wide one)
+      const double cost = waves * bn * (bn == 128 ? 1.12 : 1.0) * (pr ? 0.89 : (bn == 224 ? 1.05 : 1.0));
       if (cost < best - 1e-9) { best = cost; bn_out = bn; pair_out = pr; }
     }
   }
@@ -870,10 +871,13 @@ bool is_fp8(const IrisGemmDesc* d) { return d->in_dtype == IRIS_F8E4M3; }
 
 // `sf_a_atoms`: scale atoms behind d->sf_a (rows of A this call reads directly, in 128-row tiles, times
 // the K blocks of those rows).
+__device__ long long g_dbg_rec[512];
 int fill_common(Common& c, const IrisGemmDesc* d, int bn, int pair, int gemm_ctas, const void* A, uint64_t a_rows,
                 uint64_t a_cols, int64_t lda) {
   if (d->dtype != IRIS_BF16 && d->dtype != IRIS_F16) return -2;
   const bool f8 = is_fp8(d);
+  { const char* e = getenv("IRIS_GEMM_DBG"); c.dbg = e ? atoi(e) : 0;
+    if (getenv("IRIS_GEMM_REC")) { void* p = nullptr; cudaGetSymbolAddress(&p, g_dbg_rec); c.dbg_buf = (long long*)p; } }
   if (d->in_dtype != 0 && !f8 && d->in_dtype != d->dtype) return -2;
   if (d->N % 8 || d->K % (f8 ? 16 : 8)) return -3;
   const int in_dt = f8 ? IRIS_F8E4M3 : d->dtype;
@@ -1122,3 +1126,5 @@ extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
   if (r) return r;
   return dispatch(pol, p.bn, d->b_kmajor != 0, grid, stream);
 }
+
+extern "C" int iris_gemm_dbg_read(long long* host, int n) { return (int)cudaMemcpyFromSymbol(host, g_dbg_rec, n * sizeof(long long)); }

@@ -254,6 +254,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
     else ptx::mbar_arrive_cluster(&pipe.tmem_empty[buf], 0);
   };
 
+  const uint32_t stage0 = ptx::smem_u32(stage_base), sf0 = ptx::smem_u32(sf_base);
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) ptx::prefetch_tmap(pol.b_map());
@@ -270,65 +271,69 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         ASource as;
         as.bn0 = tn * Cfg::BN;
         as.sfb_off = 0;
-        if (!pol.a_source(st, tm, kb, as)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, pol.a_source(st, tm, kb, as))) { ok = false; break; }
         if (kb == 0 && lane == 0) pol.stamp(t, 1);
-        if (!ptx::mbar_wait<kPair>(&pipe.empty[s], ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait<kPair>(&pipe.empty[s], ph ^ 1, kPipeTimeoutNs))) { pol.fail(kTimeoutPipeline); ok = false; break; }
         if constexpr (Cfg::kFp8 && Policy::kSfaFromRows) {
           // A's scale atom is put together here from one scale byte per row (rows that arrived one by one,
           // e.g. dispatched tokens, have no ready-made atom): lane l writes the 16 bytes of rows l, l + 32,
-          // l + 64, l + 96. Generic-proxy stores, made visible to tcgen05.cp by the proxy fence; the arrive of
-          // lane 0 below (after the warp barrier) publishes them together with the TMA bytes.
+          // l + 64, l + 96. Generic-proxy stores, made visible to tcgen05.cp by the proxy fence; the arrive
+          // below (after the warp barrier) publishes them together with the TMA bytes.
           static_assert(!kPair, "scale atoms built from rows: single-CTA tiles only");
           pol.sfa_fill(st, tm, kb, sf_base + s * Cfg::kSfBytes, lane);
           ptx::fence_proxy_async_smem();
           __syncwarp();
         }
-        if (lane == 0) {
-          uint8_t* sa = stage_base + s * Cfg::kStageBytes;
-          uint8_t* sb = sa + Cfg::kABytes;
-          if constexpr (kPair) {
-            if (leader) ptx::mbar_expect_tx(&pipe.full[s], 2 * (Cfg::kStageBytes + Cfg::kSfBytes));
-            const int n0 = as.bn0 + (int)cta * Cfg::kBCols;
-            ptx::tma_load_2d_pair(sa, as.map, &pipe.full[s], as.x, as.y);
-            if constexpr (Cfg::kBKMajor) {
-              ptx::tma_load_2d_pair(sb, pol.b_map(), &pipe.full[s], as.bk, n0);
-            } else {
-#pragma unroll
-              for (int j = 0; j < Cfg::kBBoxes; ++j)
-                ptx::tma_load_2d_pair(sb + j * 8192, pol.b_map(), &pipe.full[s], n0 + j * 64, as.bk);
-            }
+        // the warp stays converged and every instruction elects its issuing lane (see the MMA issuer)
+        const uint32_t sa = stage0 + s * Cfg::kStageBytes;
+        const uint32_t sb = sa + Cfg::kABytes;
+        if constexpr (kPair) {
+          if (leader) ptx::mbar_expect_tx_elect(&pipe.full[s], 2 * (Cfg::kStageBytes + Cfg::kSfBytes));
+          const int n0 = as.bn0 + (int)cta * Cfg::kBCols;
+          ptx::tma_load_2d_pair_elect(sa, as.map, &pipe.full[s], as.x, as.y);
+          if constexpr (Cfg::kBKMajor) {
+            ptx::tma_load_2d_pair_elect(sb, pol.b_map(), &pipe.full[s], as.bk, n0);
           } else {
-            ptx::mbar_expect_tx(&pipe.full[s], Cfg::kStageBytes + Cfg::kSfBytes - ((Cfg::kFp8 && Policy::kSfaFromRows) ? 512 : 0));
-            ptx::tma_load_2d(sa, as.map, &pipe.full[s], as.x, as.y);
-            if constexpr (Cfg::kBKMajor) {
-              ptx::tma_load_2d(sb, pol.b_map(), &pipe.full[s], as.bk, as.bn0);
-            } else {
 #pragma unroll
-              for (int j = 0; j < Cfg::kBBoxes; ++j)
-                ptx::tma_load_2d(sb + j * 8192, pol.b_map(), &pipe.full[s], as.bn0 + j * 64, as.bk);
-            }
+            for (int j = 0; j < Cfg::kBBoxes; ++j)
+              ptx::tma_load_2d_pair_elect(sb + j * 8192, pol.b_map(), &pipe.full[s], n0 + j * 64, as.bk);
           }
-          if constexpr (Cfg::kFp8) {
-            // scale atoms: this tile's 128 rows of A, and all of the tile's columns of B (each
-            // CTA of a pair keeps the whole of B's scales: its MMA half multiplies every column)
-            uint8_t* ssf = sf_base + s * Cfg::kSfBytes;
-            const int brow = pol.b_sf_row(tn, as.bk / Cfg::kBKElems) + as.sfb_off;   // B's K block: not kb when A is gathered along K
-            if constexpr (kPair) {
-              ptx::tma_load_2d_pair(ssf, as.sf_map, &pipe.full[s], 0, as.sf_row);
-              ptx::tma_load_2d_pair(ssf + 512, pol.sfb_map(), &pipe.full[s], 0, brow);
-            } else {
-              if constexpr (!Policy::kSfaFromRows) ptx::tma_load_2d(ssf, as.sf_map, &pipe.full[s], 0, as.sf_row);
-              ptx::tma_load_2d(ssf + 512, pol.sfb_map(), &pipe.full[s], 0, brow);
-            }
+        } else {
+          ptx::mbar_expect_tx_elect(&pipe.full[s], Cfg::kStageBytes + Cfg::kSfBytes - ((Cfg::kFp8 && Policy::kSfaFromRows) ? 512 : 0));
+          ptx::tma_load_2d_elect(sa, as.map, &pipe.full[s], as.x, as.y);
+          if constexpr (Cfg::kBKMajor) {
+            ptx::tma_load_2d_elect(sb, pol.b_map(), &pipe.full[s], as.bk, as.bn0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < Cfg::kBBoxes; ++j)
+              ptx::tma_load_2d_elect(sb + j * 8192, pol.b_map(), &pipe.full[s], as.bn0 + j * 64, as.bk);
           }
         }
-        __syncwarp();
+        if constexpr (Cfg::kFp8) {
+          // scale atoms: this tile's 128 rows of A, and all of the tile's columns of B (each
+          // CTA of a pair keeps the whole of B's scales: its MMA half multiplies every column)
+          const uint32_t ssf = sf0 + s * Cfg::kSfBytes;
+          const int brow = pol.b_sf_row(tn, as.bk / Cfg::kBKElems) + as.sfb_off;   // B's K block: not kb when A is gathered along K
+          if constexpr (kPair) {
+            ptx::tma_load_2d_pair_elect(ssf, as.sf_map, &pipe.full[s], 0, as.sf_row);
+            ptx::tma_load_2d_pair_elect(ssf + 512, pol.sfb_map(), &pipe.full[s], 0, brow);
+          } else {
+            if constexpr (!Policy::kSfaFromRows) ptx::tma_load_2d_elect(ssf, as.sf_map, &pipe.full[s], 0, as.sf_row);
+            ptx::tma_load_2d_elect(ssf + 512, pol.sfb_map(), &pipe.full[s], 0, brow);
+          }
+        }
         if (++s == Cfg::kStages) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    // The warp stays converged: every lane computes the (warp-uniform) descriptors and each tensor-core
+    // instruction elects the lane that issues it. Issued from inside `if (lane == 0)` every instruction
+    // cost this warp 100 to 150 cycles, more than a fifth of a K block's MMA time.
     const uint32_t idesc = make_idesc(Cfg::BN, pol.is_bf16(), !Cfg::kBKMajor, kPair ? 2 * kBM : kBM);
+    // warp reductions and votes give the compiler values it knows to be the same in every lane (the TMEM
+    // base comes out of shared memory, the waits return per lane), which keeps the loop state uniform
+    const uint32_t tmem_u = __reduce_or_sync(0xffffffffu, tmem_base);
     int s = 0;
     uint32_t ph = 0;
     int it = 0;
@@ -336,55 +341,58 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
     for (int t = first; t < num_tiles && ok; t += step, ++it) {
       const int buf = Cfg::kAccBufs == 2 ? (it & 1) : 0;
       const uint32_t acc_ph = Cfg::kAccBufs == 2 ? ((it >> 1) & 1) : (it & 1);
-      if (!ptx::mbar_wait<kPair>(&pipe.tmem_empty[buf], acc_ph ^ 1, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); break; }
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait<kPair>(&pipe.tmem_empty[buf], acc_ph ^ 1, kPipeTimeoutNs))) { pol.fail(kTimeoutPipeline); break; }
       ptx::tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * Cfg::kAccCols;
+      const uint32_t d_tmem = tmem_u + buf * Cfg::kAccCols;
       for (int kb = 0; kb < k_blocks; ++kb) {
-        if (!ptx::mbar_wait<kPair>(&pipe.full[s], ph, kPipeTimeoutNs)) { pol.fail(kTimeoutPipeline); ok = false; break; }
+        const bool rec = pol.dbg_buf != nullptr && blockIdx.x == 0 && lane == 0 && it < 2 && kb < 64;
+        long long* recp = rec ? pol.dbg_buf + (it * 64 + kb) * 3 : nullptr;
+        if (rec) recp[0] = clock64();
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait<kPair>(&pipe.full[s], ph, kPipeTimeoutNs))) { pol.fail(kTimeoutPipeline); ok = false; break; }
         ptx::tc_fence_after();
-        if (lane == 0) {
-          const uint32_t sa = ptx::smem_u32(stage_base + s * Cfg::kStageBytes);
-          const uint32_t sb = sa + Cfg::kABytes;
-          if constexpr (Cfg::kFp8) {
-            // this block's scales: shared memory -> TMEM, in front of the MMAs that use them (the
-            // copies and the MMAs of one thread execute in issue order, so the cells are rewritten
-            // only after the previous block's MMAs have read them)
-            const uint32_t ssf = ptx::smem_u32(sf_base + s * Cfg::kSfBytes);
-            const uint32_t t_sfa = tmem_base + Cfg::kSfaCol + (kb & 1) * Cfg::kSfSetCols, t_sfb = t_sfa + 4;
-            if constexpr (kPair) {
-              ptx::tmem_cp_sf_pair(t_sfa, desc_sf(ssf));
+        if (rec) recp[1] = clock64();
+        const uint32_t sa = stage0 + s * Cfg::kStageBytes;
+        const uint32_t sb = sa + Cfg::kABytes;
+        if constexpr (Cfg::kFp8) {
+          // this block's scales: shared memory -> TMEM, in front of the MMAs that use them (the
+          // copies and the MMAs of one thread execute in issue order, so the cells are rewritten
+          // only after the previous block's MMAs have read them)
+          const uint32_t ssf = sf0 + s * Cfg::kSfBytes;
+          const uint32_t t_sfa = tmem_u + Cfg::kSfaCol + (kb & 1) * Cfg::kSfSetCols, t_sfb = t_sfa + 4;
+          if (pol.dbg == 1 && kb >= 2) {
+          } else if constexpr (kPair) {
+            ptx::tmem_cp_sf_pair_elect(t_sfa, desc_sf(ssf));
 #pragma unroll
-              for (int j = 0; j < Cfg::kSfbAtoms; ++j) ptx::tmem_cp_sf_pair(t_sfb + 4 * j, desc_sf(ssf + 512 + 512 * j));
-            } else {
-              ptx::tmem_cp_sf(t_sfa, desc_sf(ssf));
-#pragma unroll
-              for (int j = 0; j < Cfg::kSfbAtoms; ++j) ptx::tmem_cp_sf(t_sfb + 4 * j, desc_sf(ssf + 512 + 512 * j));
-            }
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {     // four MMAs of K 32, each with its own scale byte
-              const uint64_t ad = desc_kmajor(sa + k * 32), bd = desc_kmajor(sb + k * 32);
-              const uint32_t id8 = make_idesc_mxf8(Cfg::BN, kPair ? 2 * kBM : kBM, (uint32_t)k);
-              if constexpr (kPair) ptx::mma_mxf8_pair(d_tmem, ad, bd, id8, (kb | k) != 0, t_sfa, t_sfb);
-              else ptx::mma_mxf8(d_tmem, ad, bd, id8, (kb | k) != 0, t_sfa, t_sfb);
-            }
+            for (int j = 0; j < Cfg::kSfbAtoms; ++j) ptx::tmem_cp_sf_pair_elect(t_sfb + 4 * j, desc_sf(ssf + 512 + 512 * j));
           } else {
+            ptx::tmem_cp_sf_elect(t_sfa, desc_sf(ssf));
 #pragma unroll
-            for (int k = 0; k < kBK / kUmmaK; ++k) {
-              uint64_t ad = desc_kmajor(sa + k * (kUmmaK * 2));
-              uint64_t bd = Cfg::kBKMajor ? desc_kmajor(sb + k * (kUmmaK * 2)) : desc_mnmajor(sb + k * (kUmmaK * 128));
-              if constexpr (kPair) ptx::mma_f16_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
-              else ptx::mma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
-            }
+            for (int j = 0; j < Cfg::kSfbAtoms; ++j) ptx::tmem_cp_sf_elect(t_sfb + 4 * j, desc_sf(ssf + 512 + 512 * j));
           }
-          if constexpr (kPair) {
-            ptx::mma_commit_pair(&pipe.empty[s], 3);
-            if (kb == k_blocks - 1) ptx::mma_commit_pair(&pipe.tmem_full[buf], 3);
-          } else {
-            ptx::mma_commit(&pipe.empty[s]);
-            if (kb == k_blocks - 1) ptx::mma_commit(&pipe.tmem_full[buf]);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {     // four MMAs of K 32, each with its own scale byte
+            const uint64_t ad = desc_kmajor(sa + k * 32), bd = desc_kmajor(sb + k * 32);
+            const uint32_t id8 = make_idesc_mxf8(Cfg::BN, kPair ? 2 * kBM : kBM, (uint32_t)k);
+            if constexpr (kPair) ptx::mma_mxf8_pair_elect(d_tmem, ad, bd, id8, (kb | k) != 0, t_sfa, t_sfb);
+            else ptx::mma_mxf8_elect(d_tmem, ad, bd, id8, (kb | k) != 0, t_sfa, t_sfb);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t ad = desc_kmajor(sa + k * (kUmmaK * 2));
+            const uint64_t bd = Cfg::kBKMajor ? desc_kmajor(sb + k * (kUmmaK * 2)) : desc_mnmajor(sb + k * (kUmmaK * 128));
+            if constexpr (kPair) ptx::mma_f16_pair_elect(d_tmem, ad, bd, idesc, (kb | k) != 0);
+            else ptx::mma_f16_elect(d_tmem, ad, bd, idesc, (kb | k) != 0);
           }
         }
-        __syncwarp();
+        if constexpr (kPair) {
+          ptx::mma_commit_pair_elect(&pipe.empty[s], 3);
+          if (kb == k_blocks - 1) ptx::mma_commit_pair_elect(&pipe.tmem_full[buf], 3);
+        } else {
+          ptx::mma_commit_elect(&pipe.empty[s]);
+          if (kb == k_blocks - 1) ptx::mma_commit_elect(&pipe.tmem_full[buf]);
+        }
+        if (rec) recp[2] = clock64();
         if (++s == Cfg::kStages) { s = 0; ph ^= 1; }
       }
     }

@@ -76,6 +76,29 @@ IRIS_D bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe of a phase (try_wait may suspend the thread for a while when the phase is open).
+template <bool kCluster = false>
+IRIS_D uint32_t mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  if constexpr (kCluster) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+  }
+  return ok;
+}
 // Bounded wait. Returns false when `timeout_ns` elapsed without the phase completing; the
 // caller records a status and leaves its loop (no trap, no endless spin).
 template <bool kCluster = false>
@@ -235,6 +258,78 @@ IRIS_D void mma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
       "h"(cta_mask)
       : "memory");
 }
+
+// ---- Forms for a warp that stays converged while one of its lanes issues -------------------------------
+// Every lane executes the statement with the same (warp-uniform) operands; `elect.sync` picks the one
+// lane whose instruction is issued. The warp must be converged at the call. Descriptors and addresses
+// computed outside a divergent branch live in uniform registers, where the tensor-core and TMA
+// instructions take them from. Issued from inside `if (lane == 0)`, or predicated on a per-lane
+// register, each instruction cost the issuing warp 60 to 150 cycles; in this form about 25.
+#define IRIS_ELECT ".reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+IRIS_D void mma_f16_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t" IRIS_ELECT "setp.ne.b32 p, %4, 0;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+IRIS_D void mma_f16_pair_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t" IRIS_ELECT "setp.ne.b32 p, %4, 0;\n\t"
+               "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+IRIS_D void mma_mxf8_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                           uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile("{\n\t.reg .pred p;\n\t" IRIS_ELECT "setp.ne.b32 p, %4, 0;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+               : "memory");
+}
+IRIS_D void mma_mxf8_pair_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                                uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile("{\n\t.reg .pred p;\n\t" IRIS_ELECT "setp.ne.b32 p, %4, 0;\n\t"
+               "@q tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+               : "memory");
+}
+IRIS_D void tmem_cp_sf_elect(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("{\n\t" IRIS_ELECT "@q tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+IRIS_D void tmem_cp_sf_pair_elect(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("{\n\t" IRIS_ELECT "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+IRIS_D void mma_commit_elect(uint64_t* bar) {
+  asm volatile("{\n\t" IRIS_ELECT "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+IRIS_D void mma_commit_pair_elect(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("{\n\t" IRIS_ELECT
+               "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}" ::"r"(
+                   smem_u32(bar)),
+               "h"(cta_mask)
+               : "memory");
+}
+IRIS_D void mbar_expect_tx_elect(uint64_t* bar, uint32_t bytes) {
+  asm volatile("{\n\t" IRIS_ELECT "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+IRIS_D void tma_load_2d_elect(uint32_t smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y) {
+  asm volatile("{\n\t" IRIS_ELECT
+               "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}" ::"r"(
+                   smem_dst),
+               "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y)
+               : "memory");
+}
+IRIS_D void tma_load_2d_pair_elect(uint32_t smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y) {
+  uint32_t bar_addr = smem_u32(bar) & 0xFEFFFFFFu;
+  asm volatile("{\n\t" IRIS_ELECT
+               "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}" ::"r"(
+                   smem_dst),
+               "l"(m), "r"(bar_addr), "r"(x), "r"(y)
+               : "memory");
+}
+#undef IRIS_ELECT
 
 // TMEM -> registers: this warp's 32 lanes x 32 consecutive fp32 columns (thread i gets lane i).
 IRIS_D void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
