@@ -144,14 +144,13 @@ __global__ void __launch_bounds__(kThreads8, 1) gemm_fp8_kernel(const __grid_con
       int tm, tn;
       swizzled_tile(t, a.tiles_m, a.tiles_n, a.group_m, tm, tn);
       for (int kb = 0; kb < k_blocks; ++kb) {
-        if (!ptx::mbar_wait(&empty[s], ph ^ 1, kPipeTimeoutNs)) { fail(); ok = false; break; }
-        if (lane == 0) {
-          uint8_t* sa = stage_base + s * kStageBytes8;
-          ptx::mbar_expect_tx(&full[s], kStageBytes8);
-          ptx::tma_load_2d(sa, &a.tmA, &full[s], kb * kBK8, tm * kBM);
-          ptx::tma_load_2d(sa + kABytes8, &a.tmB, &full[s], kb * kBK8, tn * kBN8);
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&empty[s], ph ^ 1, kPipeTimeoutNs))) { fail(); ok = false; break; }
+        {   // converged warp: each instruction elects its issuing lane, operands stay warp-uniform
+          const uint32_t sa = ptx::smem_u32(stage_base + s * kStageBytes8);
+          ptx::mbar_expect_tx_elect(&full[s], kStageBytes8);
+          ptx::tma_load_2d_elect(sa, &a.tmA, &full[s], kb * kBK8, tm * kBM);
+          ptx::tma_load_2d_elect(sa + kABytes8, &a.tmB, &full[s], kb * kBK8, tn * kBN8);
         }
-        __syncwarp();
         if (++s == kStages8) { s = 0; ph ^= 1; }
       }
     }
@@ -162,23 +161,23 @@ __global__ void __launch_bounds__(kThreads8, 1) gemm_fp8_kernel(const __grid_con
     uint32_t ph = 0;
     uint32_t blk = 0;      // K blocks issued so far by this CTA: selects the TMEM buffer and its phase
     bool ok = true;
+    const uint32_t tmem_u = __reduce_or_sync(0xffffffffu, tmem_base);   // the same value, known to be warp-uniform
     for (int t = first; t < num_tiles && ok; t += step) {
       for (int kb = 0; kb < k_blocks; ++kb, ++blk) {
         const int buf = blk & 1;
-        if (!ptx::mbar_wait(&acc_empty[buf], ((blk >> 1) & 1) ^ 1, kPipeTimeoutNs)) { fail(); ok = false; break; }
-        if (!ptx::mbar_wait(&full[s], ph, kPipeTimeoutNs)) { fail(); ok = false; break; }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&acc_empty[buf], ((blk >> 1) & 1) ^ 1, kPipeTimeoutNs))) { fail(); ok = false; break; }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&full[s], ph, kPipeTimeoutNs))) { fail(); ok = false; break; }
         ptx::tc_fence_after();
-        if (lane == 0) {
+        {
           const uint32_t sa = ptx::smem_u32(stage_base + s * kStageBytes8);
           const uint32_t sb = sa + kABytes8;
-          const uint32_t d_tmem = tmem_base + buf * 256;
+          const uint32_t d_tmem = tmem_u + buf * 256;
 #pragma unroll
           for (int k = 0; k < kBK8 / 32; ++k)
-            ptx::mma_f8(d_tmem, desc_kmajor(sa + k * 32), desc_kmajor(sb + k * 32), idesc, k != 0);
-          ptx::mma_commit(&empty[s]);
-          ptx::mma_commit(&acc_full[buf]);
+            ptx::mma_f8_elect(d_tmem, desc_kmajor(sa + k * 32), desc_kmajor(sb + k * 32), idesc, k != 0);
+          ptx::mma_commit_elect(&empty[s]);
+          ptx::mma_commit_elect(&acc_full[buf]);
         }
-        __syncwarp();
         if (++s == kStages8) { s = 0; ph ^= 1; }
       }
     }

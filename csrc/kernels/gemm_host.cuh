@@ -22,8 +22,6 @@ static_assert(sizeof(IrisCtx) == sizeof(DeviceContext), "IrisCtx must mirror iri
 namespace {
 
 struct Common {
-  int dbg = 0;
-  long long* dbg_buf = nullptr;
   CUtensorMap tmA;
   CUtensorMap tmB;
   Shape sh;

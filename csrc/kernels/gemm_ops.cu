@@ -871,13 +871,10 @@ bool is_fp8(const IrisGemmDesc* d) { return d->in_dtype == IRIS_F8E4M3; }
 
 // `sf_a_atoms`: scale atoms behind d->sf_a (rows of A this call reads directly, in 128-row tiles, times
 // the K blocks of those rows).
-__device__ long long g_dbg_rec[512];
 int fill_common(Common& c, const IrisGemmDesc* d, int bn, int pair, int gemm_ctas, const void* A, uint64_t a_rows,
                 uint64_t a_cols, int64_t lda) {
   if (d->dtype != IRIS_BF16 && d->dtype != IRIS_F16) return -2;
   const bool f8 = is_fp8(d);
-  { const char* e = getenv("IRIS_GEMM_DBG"); c.dbg = e ? atoi(e) : 0;
-    if (getenv("IRIS_GEMM_REC")) { void* p = nullptr; cudaGetSymbolAddress(&p, g_dbg_rec); c.dbg_buf = (long long*)p; } }
   if (d->in_dtype != 0 && !f8 && d->in_dtype != d->dtype) return -2;
   if (d->N % 8 || d->K % (f8 ? 16 : 8)) return -3;
   const int in_dt = f8 ? IRIS_F8E4M3 : d->dtype;
@@ -1126,5 +1123,3 @@ extern "C" int iris_gemm_launch(const IrisGemmDesc* d, void* stream_) {
   if (r) return r;
   return dispatch(pol, p.bn, d->b_kmajor != 0, grid, stream);
 }
-
-extern "C" int iris_gemm_dbg_read(long long* host, int n) { return (int)cudaMemcpyFromSymbol(host, g_dbg_rec, n * sizeof(long long)); }

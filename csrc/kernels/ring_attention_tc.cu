@@ -75,6 +75,14 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uin
       "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same for a converged warp: every lane executes it with warp-uniform operands and one elected lane issues.
+__device__ __forceinline__ void mma_f16_ts_elect(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\telect.sync _|q, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -220,10 +228,10 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
         }
         const int st = n_tile % kKvStages;
         const uint32_t ph = ((n_tile / kKvStages) & 1) ^ 1;
-        if (!ptx::mbar_wait(&k_empty[st], ph, kWaitNs) || !ptx::mbar_wait(&v_empty[st], ph, kWaitNs)) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&k_empty[st], ph, kWaitNs) && ptx::mbar_wait(&v_empty[st], ph, kWaitNs))) {
           ctx.fail(kTimeoutPipeline); ok = false; break;
         }
-        if (lane == 0) {
+        {   // converged warp, one elected lane per instruction
           const bool own = w.origin == r;
           const CUtensorMap* mk = own ? &g.tmKown : &g.tmKbuf;
           const CUtensorMap* mv = own ? &g.tmVown : &g.tmVbuf;
@@ -231,19 +239,18 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
           const int rowk = own ? 0 : ((par * W + w.origin) * 2) * a.S;
           const int rowv = own ? 0 : rowk + a.S;
           const int pos0 = w.t * kTK;
-          uint8_t* kd = k_s + st * kTile;
-          uint8_t* vd = v_s + st * kTile;
-          ptx::mbar_expect_tx(&k_full[st], kTile);
-          ptx::tma_load_2d(kd, mk, &k_full[st], kvh * kD, rowk + pos0);
-          ptx::tma_load_2d(kd + kHalf, mk, &k_full[st], kvh * kD + 64, rowk + pos0);
-          ptx::mbar_expect_tx(&v_full[st], kTile);
+          const uint32_t kd = ptx::smem_u32(k_s + st * kTile);
+          const uint32_t vd = ptx::smem_u32(v_s + st * kTile);
+          ptx::mbar_expect_tx_elect(&k_full[st], kTile);
+          ptx::tma_load_2d_elect(kd, mk, &k_full[st], kvh * kD, rowk + pos0);
+          ptx::tma_load_2d_elect(kd + kHalf, mk, &k_full[st], kvh * kD + 64, rowk + pos0);
+          ptx::mbar_expect_tx_elect(&v_full[st], kTile);
 #pragma unroll
           for (int kh = 0; kh < 2; ++kh)
 #pragma unroll
             for (int nb = 0; nb < 2; ++nb)
-              ptx::tma_load_2d(vd + kh * kHalf + nb * 8192, mv, &v_full[st], kvh * kD + nb * 64, rowv + pos0 + kh * 64);
+              ptx::tma_load_2d_elect(vd + kh * kHalf + nb * 8192, mv, &v_full[st], kvh * kD + nb * 64, rowv + pos0 + kh * 64);
         }
-        __syncwarp();
         ++n_tile;
       }
     }
@@ -253,44 +260,46 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
     const uint32_t idesc_o = make_idesc(kD, !kFp16, true);       // B = V tile, [keys, d] row-major
     uint32_t n_item = 0, n_s = 0, n_pv = 0;     // items, S tiles and P V tiles issued so far
     bool ok = true;
+    // The warp stays converged: every lane computes the warp-uniform operands and each tensor-core instruction
+    // elects its issuing lane (issued from inside `if (lane == 0)` they cost about 100 cycles apiece). Votes and
+    // the warp reduction make the loop state and the TMEM base uniform for the compiler too.
+    const uint32_t tmem_u = __reduce_or_sync(0xffffffffu, tmem_base);
     // The S buffer of tile j also holds P of tile j (its first 64 columns) until the P V MMA of
     // tile j has read it; S of tile j + 2 is issued after that MMA and the tensor pipe runs MMAs in
     // issue order, so no barrier guards the reuse of the buffer.
     auto issue_s = [&]() -> bool {
       const int sb = n_s & 1, st = n_s % kKvStages;
-      if (!ptx::mbar_wait(&k_full[st], (n_s / kKvStages) & 1, kWaitNs)) return false;
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&k_full[st], (n_s / kKvStages) & 1, kWaitNs))) return false;
       ptx::tc_fence_after();
-      if (lane == 0) {
+      {
         const uint32_t kb = ptx::smem_u32(k_s + st * kTile);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {        // 16 of the 128 head dimensions per step: 8 columns of Q in TMEM
           const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
-          mma_f16_ts(tmem_base + sb * 128, tmem_base + 384 + k * 8, desc_kmajor(kb + off), idesc_s, k != 0);
+          mma_f16_ts_elect(tmem_u + sb * 128, tmem_u + 384 + k * 8, desc_kmajor(kb + off), idesc_s, k != 0);
         }
-        ptx::mma_commit(&k_empty[st]);
-        ptx::mma_commit(&s_full[sb]);
+        ptx::mma_commit_elect(&k_empty[st]);
+        ptx::mma_commit_elect(&s_full[sb]);
       }
-      __syncwarp();
       ++n_s;
       return true;
     };
     auto issue_pv = [&](bool first_of_item) -> bool {
       const int sb = n_pv & 1, st = n_pv % kKvStages;
-      if (!ptx::mbar_wait(&p_full[sb], (n_pv >> 1) & 1, kWaitNs)) return false;
-      if (!ptx::mbar_wait(&v_full[st], (n_pv / kKvStages) & 1, kWaitNs)) return false;
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&p_full[sb], (n_pv >> 1) & 1, kWaitNs))) return false;
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&v_full[st], (n_pv / kKvStages) & 1, kWaitNs))) return false;
       ptx::tc_fence_after();
-      if (lane == 0) {
+      {
         const uint32_t vb = ptx::smem_u32(v_s + st * kTile);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t boff = (k >> 2) * kHalf + (k & 3) * 2048;        // V: 64-key halves, 16 keys = 2048 B
           // P: 16 keys = 8 columns of 16-bit pairs at the start of the tile's S buffer
-          mma_f16_ts(tmem_base + 256, tmem_base + sb * 128 + k * 8, desc_mnmajor(vb + boff), idesc_o, !(first_of_item && k == 0));
+          mma_f16_ts_elect(tmem_u + 256, tmem_u + sb * 128 + k * 8, desc_mnmajor(vb + boff), idesc_o, !(first_of_item && k == 0));
         }
-        ptx::mma_commit(&v_empty[st]);
-        ptx::mma_commit(&o_ready[sb]);
+        ptx::mma_commit_elect(&v_empty[st]);
+        ptx::mma_commit_elect(&o_ready[sb]);
       }
-      __syncwarp();
       ++n_pv;
       return true;
     };
@@ -301,14 +310,13 @@ __device__ void attn_main_tc(const TcArgs& g, uint8_t* smem_raw, int call) {
         TileWalk w(a, qt);
         while (w.next()) ++n;
       }
-      if (!ptx::mbar_wait(q_full, n_item & 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); break; }
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(q_full, n_item & 1, kWaitNs))) { ctx.fail(kTimeoutPipeline); break; }
       if (!issue_s()) { ctx.fail(kTimeoutPipeline); break; }
       for (int j = 0; j < n; ++j) {
         if (j + 1 < n && !issue_s()) { ctx.fail(kTimeoutPipeline); ok = false; break; }
-        if (j + 1 == n && lane == 0) ptx::mma_commit(q_free);       // every S MMA of the item is issued
-        __syncwarp();
+        if (j + 1 == n) ptx::mma_commit_elect(q_free);       // every S MMA of the item is issued
         // the previous item's O must have been read out before this item's first P V overwrites it
-        if (j == 0 && !ptx::mbar_wait(o_free, (n_item & 1) ^ 1, kWaitNs)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
+        if (j == 0 && !__all_sync(0xffffffffu, ptx::mbar_wait(o_free, (n_item & 1) ^ 1, kWaitNs))) { ctx.fail(kTimeoutPipeline); ok = false; break; }
         if (!issue_pv(j == 0)) { ctx.fail(kTimeoutPipeline); ok = false; break; }
       }
     }

@@ -345,12 +345,8 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
       ptx::tc_fence_after();
       const uint32_t d_tmem = tmem_u + buf * Cfg::kAccCols;
       for (int kb = 0; kb < k_blocks; ++kb) {
-        const bool rec = pol.dbg_buf != nullptr && blockIdx.x == 0 && lane == 0 && it < 2 && kb < 64;
-        long long* recp = rec ? pol.dbg_buf + (it * 64 + kb) * 3 : nullptr;
-        if (rec) recp[0] = clock64();
         if (!__all_sync(0xffffffffu, ptx::mbar_wait<kPair>(&pipe.full[s], ph, kPipeTimeoutNs))) { pol.fail(kTimeoutPipeline); ok = false; break; }
         ptx::tc_fence_after();
-        if (rec) recp[1] = clock64();
         const uint32_t sa = stage0 + s * Cfg::kStageBytes;
         const uint32_t sb = sa + Cfg::kABytes;
         if constexpr (Cfg::kFp8) {
@@ -359,8 +355,7 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
           // only after the previous block's MMAs have read them)
           const uint32_t ssf = sf0 + s * Cfg::kSfBytes;
           const uint32_t t_sfa = tmem_u + Cfg::kSfaCol + (kb & 1) * Cfg::kSfSetCols, t_sfb = t_sfa + 4;
-          if (pol.dbg == 1 && kb >= 2) {
-          } else if constexpr (kPair) {
+          if constexpr (kPair) {
             ptx::tmem_cp_sf_pair_elect(t_sfa, desc_sf(ssf));
 #pragma unroll
             for (int j = 0; j < Cfg::kSfbAtoms; ++j) ptx::tmem_cp_sf_pair_elect(t_sfb + 4 * j, desc_sf(ssf + 512 + 512 * j));
@@ -392,7 +387,6 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
           ptx::mma_commit_elect(&pipe.empty[s]);
           if (kb == k_blocks - 1) ptx::mma_commit_elect(&pipe.tmem_full[buf]);
         }
-        if (rec) recp[2] = clock64();
         if (++s == Cfg::kStages) { s = 0; ph ^= 1; }
       }
     }

@@ -272,6 +272,12 @@ IRIS_D void mma_f16_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint3
                "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
                : "memory");
 }
+IRIS_D void mma_f8_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t" IRIS_ELECT "setp.ne.b32 p, %4, 0;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
 IRIS_D void mma_f16_pair_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\t" IRIS_ELECT "setp.ne.b32 p, %4, 0;\n\t"
                "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),

@@ -156,6 +156,11 @@ def run_benchmarks(ctx, benchmarks, overrides, skips, n_warmup, n_repeat) -> lis
             except SkipCombination as s:
                 results.append(Result(bdef.name, params, 0.0, [], skipped=True, skip_reason=s.reason, world_size=world))
                 continue
+            except MemoryError as e:
+                # the symmetric heap is too small for this point: every rank runs the same allocation sequence
+                # and fails alike, so the sweep goes on with the next point (--heap_size raises the limit)
+                results.append(Result(bdef.name, params, 0.0, [], skipped=True, skip_reason=f"heap too small ({e})"[:120], world_size=world))
+                continue
             if state._exec_fn is None:
                 results.append(Result(bdef.name, params, 0.0, [], skipped=True, skip_reason="no exec() registered", world_size=world))
                 continue
