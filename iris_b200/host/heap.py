@@ -240,46 +240,72 @@ class SymmetricHeap:
         if self.reserve and kind == KIND_VMM:
             rt.iris_heap_set_next_reserve(self.reserve)
             create_size = self._initial_size
+        # Every step that can fail on one rank only is followed by a vote, so that all ranks leave this backend
+        # together (a rank that went on alone to the next backend would sit in a different exchange than its peers).
+        def agree(ok: bool, what: str, msg: str = "") -> None:
+            if self.num_ranks == 1:
+                if not ok:
+                    raise RuntimeError(msg or what)
+                return
+            oks = D.distributed_allgather(np.array([1 if ok else 0], dtype=np.int64), self.group).flatten()
+            if not all(int(o) for o in oks):
+                bad = [r for r, o in enumerate(oks) if not int(o)]
+                raise RuntimeError(f"{what} failed on rank(s) {bad}" + (f": {msg}" if msg else ""))
+
         h = rt.iris_heap_create(create_size, self.device_id, self.cur_rank, self.num_ranks, kind, 0, err, _ERRLEN)
-        if not h:
-            raise RuntimeError(err.value.decode())
-        self._handle = h
-        self.kind = kind
-        self.base = rt.iris_heap_base(h)
+        msg = "" if h else err.value.decode()
+        fd, blob = -1, None
+        if h:
+            self._handle = h
+            self.kind = kind
+            self.base = rt.iris_heap_base(h)
+            if self.num_ranks > 1:
+                if kind in (KIND_VMM, KIND_CPU):
+                    fd = rt.iris_heap_export_fd(h, err, _ERRLEN)
+                    if fd < 0:
+                        msg = err.value.decode()
+                else:
+                    blob = C.create_string_buffer(64)
+                    if rt.iris_heap_export_blob(h, blob, err, _ERRLEN) != 0:
+                        msg, blob = err.value.decode(), None
+        local_ok = bool(h) and (self.num_ranks == 1 or fd >= 0 or blob is not None)
+        try:
+            agree(local_ok, "creating / exporting the heap", msg)
+        except RuntimeError:
+            if fd >= 0:
+                rt.iris_close_fd(fd)
+            raise
         if self.num_ranks == 1:
             return
+        msg = ""
         if kind in (KIND_VMM, KIND_CPU):
             if self._mesh is None:
                 self._mesh = FdMesh(self.cur_rank, self.num_ranks, self.group)
-            fd = rt.iris_heap_export_fd(h, err, _ERRLEN)
-            if fd < 0:
-                raise RuntimeError(err.value.decode())
-            ok = True
             try:
                 for p in range(self.num_ranks):
                     if p != self.cur_rank:
                         self._mesh.send(p, fd, _TAG_HEAP)
-                for _ in range(self.num_ranks - 1):
+                for _ in range(self.num_ranks - 1):      # every message is taken off the mesh even after a failure
                     pfd, src, tag, _ = self._mesh.recv()
                     if tag != _TAG_HEAP or pfd < 0:
-                        raise RuntimeError(f"unexpected message (tag {tag}) while exchanging heap handles")
+                        msg = msg or f"unexpected message (tag {tag}) while exchanging heap handles"
+                        continue
                     rc = rt.iris_heap_import_fd(h, src, pfd, err, _ERRLEN)
                     rt.iris_close_fd(pfd)
                     if rc != 0:
-                        raise RuntimeError(f"mapping rank {src}'s heap: {err.value.decode()}")
+                        msg = msg or f"mapping rank {src}'s heap: {err.value.decode()}"
+            except Exception as e:  # a broken mesh: still vote below, the peers must not wait for this rank
+                msg = msg or f"{type(e).__name__}: {e}"
             finally:
                 rt.iris_close_fd(fd)
-            del ok
         else:
-            blob = C.create_string_buffer(64)
-            if rt.iris_heap_export_blob(h, blob, err, _ERRLEN) != 0:
-                raise RuntimeError(err.value.decode())
             blobs = D.distributed_allgather(np.frombuffer(blob.raw, dtype=np.uint8).copy(), self.group)
             for p in range(self.num_ranks):
                 if p == self.cur_rank:
                     continue
                 if rt.iris_heap_import_blob(h, p, blobs[p].tobytes(), err, _ERRLEN) != 0:
-                    raise RuntimeError(f"opening rank {p}'s IPC handle: {err.value.decode()}")
+                    msg = msg or f"opening rank {p}'s IPC handle: {err.value.decode()}"
+        agree(not msg, "mapping the peers' heaps", msg)
 
     def _setup_multicast(self) -> None:
         """Bind the heap to an NVLS multicast object; on any failure continue without it."""

@@ -278,14 +278,14 @@ def test_heap_creation_cleans_up_after_an_injected_driver_failure():
             dist.destroy_process_group()
 
 
-def _peer_import_fails(rank, world):
+def _peer_import_fails(rank, world, fail_at=6):
     from iris_b200.host.heap import KIND_VMM, SymmetricHeap, _rt
 
     rt = _rt()
     rt.iris_rt_install_fake_driver(2)
     baseline = rt.iris_rt_fake_live_objects()
     if rank == 1:
-        rt.iris_rt_fake_fail_after(6)            # its own region comes up (5 calls); importing the peer's handle fails
+        rt.iris_rt_fake_fail_after(fail_at)      # 6: its own region comes up (5 calls), importing the peer's handle fails; 1: its own region fails
     with pytest.raises(RuntimeError, match="could not create a symmetric heap on every rank"):
         SymmetricHeap(4 << 20, 0, rank, world, allocator_type="vmem", enable_multicast=False)
     rt.iris_rt_fake_fail_after(0)
@@ -306,3 +306,9 @@ def _peer_import_fails(rank, world):
 
 def test_a_failed_peer_import_fails_the_heap_on_every_rank():
     run_ranks(_peer_import_fails, 2, env={"IRIS_FAKE_DRIVER_DEVICES": "2"}, timeout=120)
+
+
+def test_a_rank_that_cannot_create_its_region_fails_the_heap_on_every_rank():
+    """The ranks vote after creating and exporting, before any handle is exchanged: the rank whose region came
+    up does not wait for a descriptor that will never arrive, and every rank leaves the backend together."""
+    run_ranks(_peer_import_fails, 2, args=(1,), env={"IRIS_FAKE_DRIVER_DEVICES": "2"}, timeout=120)
