@@ -492,31 +492,37 @@ IRIS_D void gemm_cta_main(const Policy& pol, uint8_t* smem_raw) {
         if constexpr (Policy::kSwiGLU && Policy::kQuantOut) {
           // SwiGLU whose output feeds a block-scaled fp8 GEMM: the tile's 128 outputs of a row are exactly one
           // 1 x 128 quantisation block. The outputs are computed once and kept as bf16 pairs in registers while
-          // the row's amax is found (the accumulator buffer is released as soon as TMEM has been read), then
-          // written as e4m3 values; the row's scale leaves as one UE8M0 byte.
+          // the row's amax is found, then written as e4m3 values; the row's scale leaves as one UE8M0 byte.
           static_assert(Cfg::BN == 256, "the SwiGLU epilogue pairs columns c and c + 128 of a 256-wide tile");
           float amax = 0.f;
-          uint32_t hreg[64];      // the row's 128 outputs as bf16 pairs: kept so that TMEM is read (and released) once
+          // gate and up values leave TMEM as bf16 pairs (128 registers) and the accumulator buffer is released
+          // before any SiLU is computed: with one accumulator buffer the next tile's MMAs wait for this release
+          uint32_t hreg[64], ureg[64];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t g[32], u[32];
-            ptx::tmem_ld_32x32(t_addr + c * 32, g);
-            ptx::tmem_ld_32x32(t_addr + 128 + c * 32, u);
+          for (int c = 0; c < 8; ++c) {        // chunks 0..3: gate columns, 4..7: up columns (32 at a time)
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(t_addr + c * 32, r);
             ptx::tmem_ld_wait();
-            if (c == 3) {
+            if (c == 7) {
               ptx::tc_fence_before();
               __syncwarp();
               if (lane == 0) release_acc(buf);
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const float g0 = __uint_as_float(g[2 * j]), u0 = __uint_as_float(u[2 * j]);
-              const float g1 = __uint_as_float(g[2 * j + 1]), u1 = __uint_as_float(u[2 * j + 1]);
-              const float h0 = g0 / (1.f + __expf(-g0)) * u0, h1 = g1 / (1.f + __expf(-g1)) * u1;
-              amax = fmaxf(amax, fmaxf(fabsf(h0), fabsf(h1)));
-              const __nv_bfloat162 hb = __floats2bfloat162_rn(h0, h1);
-              hreg[c * 16 + j] = *(const uint32_t*)&hb;
+              const __nv_bfloat162 pb = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+              if (c < 4) hreg[c * 16 + j] = *(const uint32_t*)&pb;
+              else ureg[(c - 4) * 16 + j] = *(const uint32_t*)&pb;
             }
+          }
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            const float2 gf = __bfloat1622float2(*(const __nv_bfloat162*)&hreg[j]);
+            const float2 uf = __bfloat1622float2(*(const __nv_bfloat162*)&ureg[j]);
+            const float h0 = gf.x / (1.f + __expf(-gf.x)) * uf.x, h1 = gf.y / (1.f + __expf(-gf.y)) * uf.y;
+            amax = fmaxf(amax, fmaxf(fabsf(h0), fabsf(h1)));
+            const __nv_bfloat162 hb = __floats2bfloat162_rn(h0, h1);
+            hreg[j] = *(const uint32_t*)&hb;
           }
           int e8 = (int)ceilf(log2f(fmaxf(amax, 1e-12f) * (1.0f / 448.0f)));
           e8 = max(-127, min(127, e8));
