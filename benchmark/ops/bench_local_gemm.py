@@ -5,8 +5,9 @@ tensor-parallel MLP benchmark.
 
     python benchmark/ops/bench_local_gemm.py [--iters 20]
 
-Timing: CUDA events around `iters` back-to-back launches after 3 warm-up launches; operands
-(A + B + C >= 170 MB) are larger than L2.
+Timing: all configurations and cuBLAS take turns (`iters` back-to-back launches each, eight rounds, medians), so
+that they run under the same power state; the SM clock is read through NVML while each burst runs and
+time x clock is printed next to the time. Operands (A + B + C >= 170 MB) are larger than L2.
 """
 import argparse
 import os
@@ -33,34 +34,68 @@ def check(M, N, K, dtype, kmajor, two_sm, bias=False, bn=0):
     return ok
 
 
-def bench(M, N, K, kmajor, iters):
+class _Clock:
+    """SM clock through NVML, read while the GPU works (None when NVML is not there)."""
+
+    def __init__(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+            self.nv = pynvml
+        except Exception:
+            self.h = None
+
+    def mhz(self):
+        return self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM) if self.h is not None else None
+
+
+def bench(M, N, K, kmajor, iters, rounds=8):
+    """Every configuration and cuBLAS in turn (A, B, C, ..., A, B, C, ...), `iters` launches at a time, `rounds`
+    times: under the power cap all of them then see the same clocks. Reported: median time, TFLOP/s and
+    time x SM MHz (thousands of SM cycles per GEMM, which takes the clock out of the comparison)."""
+    import statistics
+
     dt = torch.bfloat16
     A = torch.randn(M, K, device="cuda", dtype=dt)
     B = torch.randn(N, K, device="cuda", dtype=dt).t() if kmajor else torch.randn(K, N, device="cuda", dtype=dt)
     C = torch.empty(M, N, device="cuda", dtype=dt)
-    cols = []
-    for name, fn in (("pair bn256", lambda: matmul(A, B, out=C, two_sm=True, bn=256)),
-                     ("pair bn224", lambda: matmul(A, B, out=C, two_sm=True, bn=224)),
-                     ("plan", lambda: matmul(A, B, out=C)),
-                     ("single CTA", lambda: matmul(A, B, out=C, two_sm=False)),
-                     ("cuBLAS", lambda: torch.matmul(A, B, out=C))):
+    cfgs = (("pair bn256", lambda: matmul(A, B, out=C, two_sm=True, bn=256)),
+            ("pair bn224", lambda: matmul(A, B, out=C, two_sm=True, bn=224)),
+            ("plan", lambda: matmul(A, B, out=C)),
+            ("single CTA", lambda: matmul(A, B, out=C, two_sm=False)),
+            ("cuBLAS", lambda: torch.matmul(A, B, out=C)))
+    clock = _Clock()
+    for _, fn in cfgs:
         for _ in range(3):
             fn()
-        torch.cuda.synchronize()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        for _ in range(iters):
-            fn()
-        e.record()
-        torch.cuda.synchronize()
-        ms = s.elapsed_time(e) / iters
-        cols.append(f"{name} {ms:.3f} ms {2 * M * N * K / ms / 1e9:.0f} TF")
+    torch.cuda.synchronize()
+    times = {n: [] for n, _ in cfgs}
+    clocks = {n: [] for n, _ in cfgs}
+    for _ in range(rounds):
+        for name, fn in cfgs:
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(iters):
+                fn()
+            e.record()
+            mhz = clock.mhz()           # read while the launches above are still running
+            torch.cuda.synchronize()
+            times[name].append(s.elapsed_time(e) / iters)
+            if mhz:
+                clocks[name].append(mhz)
+    cols = []
+    for name, _ in cfgs:
+        ms = statistics.median(times[name])
+        mhz = statistics.median(clocks[name]) if clocks[name] else None
+        cyc = f", {mhz:.0f} MHz, {ms * mhz:.0f} kcycles" if mhz else ""
+        cols.append(f"{name} {ms:.3f} ms {2 * M * N * K / ms / 1e9:.0f} TF{cyc}")
     print(f"M={M} N={N} K={K} B{'^T' if kmajor else ''}: " + " | ".join(cols), flush=True)
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     torch.manual_seed(0)
     ok = check(256, 256, 64, torch.bfloat16, True, True)
