@@ -11,6 +11,8 @@
     python benchmark/profile_target.py fp8hw     # 3 launches of the hardware block-scaled fp8 GEMM 4096x3584x8192
     python benchmark/profile_target.py ar        # world-size-1 matmul_all_reduce (two_shot, one_shot) and matmul_all_gather
     python benchmark/profile_target.py ccl       # world-size-1 all_reduce / all_gather / reduce_scatter kernels, 256 MB
+    python benchmark/profile_target.py moe_full  # two passes of the benchmark-size MoE layer (4096 tokens, hidden 7168, 32 experts, top-8):
+    python benchmark/profile_target.py moe_fp8_full   # for a launch list (`--metrics gpu__time_duration.sum`, one pass) only, about 6 GB held
 
 The fused ops and collectives run here with ONE rank: the same kernel templates as on several GPUs
 (policy code, epilogues, flag protocol) with no peer to wait for, which is the form a replaying
@@ -68,7 +70,7 @@ def main():
             matmul(a, b, out=out)
         torch.cuda.synchronize()
         return
-    ctx = ctx_world1()
+    ctx = ctx_world1(8 << 30 if what.endswith("_full") else 2 << 30)
     if what == "ar":
         from iris_b200.ops import FusedConfig
 
@@ -119,14 +121,15 @@ def main():
         for _ in range(2):
             ctx.ops.all_gather_matmul(H, X, W1, shard_dim=0, async_op=True)
             ctx.ops.matmul_reduce_scatter(Y, H, W2, scatter_rows=True, async_op=True)
-    elif what in ("moe", "moe_fp8"):
+    elif what in ("moe", "moe_fp8", "moe_full", "moe_fp8_full"):
         from iris_b200.models import MoELayer
 
-        T, D, F, E, K = 1024, 2048, 1024, 8, 2
+        T, D, F, E, K = (4096, 7168, 2048, 32, 8) if what.endswith("_full") else (1024, 2048, 1024, 8, 2)
         wg = (torch.randn(E, D, F, device="cuda") * 0.02).to(dt)
         wu = (torch.randn(E, D, F, device="cuda") * 0.02).to(dt)
         wd = (torch.randn(E, F, D, device="cuda") * 0.02).to(dt)
-        layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg, w_up=wu, w_down=wd, fp8=what == "moe_fp8")
+        layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg, w_up=wu, w_down=wd, fp8="fp8" in what,
+                         **({"capacity_factor": 2.0} if what.endswith("_full") else {}))
         x = torch.randn(T, D, device="cuda", dtype=dt)
         logits = torch.randn(T, E, device="cuda")
         for _ in range(2):
