@@ -33,8 +33,14 @@ if __name__ == "__main__":
     C = ctx.zeros((M, W * N), dtype=dt)
     ctx.ops.matmul_all_gather(C, A, B, scatter_cols=True)
     assert (C.float() - torch.cat(parts, dim=1)).abs().max().item() < tol
-    # the bulk-synchronous form of the same result: GEMM, then the collective
-    from iris_b200.ops import matmul
+    # the same result under each selectable overlap pattern (examples 07 / 10 / 11 / 12 of the reference):
+    # epilogue stores, communication CTAs forwarding finished tiles, GEMM kernel followed by the collective
+    from iris_b200.ops import FusedConfig, matmul
+    for pattern in ("fused", "wg_specialized", "producer_consumer", "bulk_synchronous"):
+        Cp = ctx.zeros((M, W * N), dtype=dt)
+        ctx.ops.matmul_all_gather(Cp, A, B, scatter_cols=True, config=FusedConfig(overlap=pattern))
+        assert (Cp.float() - torch.cat(parts, dim=1)).abs().max().item() < tol, pattern
+    # the bulk-synchronous form by hand: GEMM, then the collective
     loc = ctx.as_symmetric((matmul(A, B) if A.is_cuda else (A @ B)).contiguous())
     rows = ctx.zeros((W * M, N), dtype=dt)
     ctx.ccl.all_gather(rows, loc)
@@ -44,6 +50,11 @@ if __name__ == "__main__":
     C2 = ctx.zeros((M, N), dtype=dt)
     ctx.ops.matmul_all_reduce(C2, A, B)
     assert (C2.float() - total).abs().max().item() < tol
+    # every all-reduce variant (examples 08: atomics, 09 / 21: one shot; two_shot: owner reduces, then broadcasts)
+    for variant in ("two_shot", "one_shot", "atomic"):
+        Cv = ctx.zeros((M, N), dtype=dt)
+        ctx.ops.matmul_all_reduce(Cv, A, B, config=FusedConfig(all_reduce_variant=variant))
+        assert (Cv.float() - total).abs().max().item() < tol, variant
     if M % (128 * W) == 0:
         C3 = ctx.zeros((M // W, N), dtype=dt)
         ctx.ops.matmul_reduce_scatter(C3, A, B, scatter_rows=True)
