@@ -76,29 +76,6 @@ IRIS_D bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Non-blocking probe of a phase (try_wait may suspend the thread for a while when the phase is open).
-template <bool kCluster = false>
-IRIS_D uint32_t mbar_test_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  if constexpr (kCluster) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-  }
-  return ok;
-}
 // Bounded wait. Returns false when `timeout_ns` elapsed without the phase completing; the
 // caller records a status and leaves its loop (no trap, no endless spin).
 template <bool kCluster = false>
@@ -191,6 +168,8 @@ IRIS_D void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
 IRIS_D void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 IRIS_D void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// The forms from here to mma_commit_pair are for ONE thread that issues on its own (the warp has diverged, or the
+// operands are per-thread values anyway). The warp-specialised loops use the *_elect forms further down.
 // D[tmem] (+)= A[smem desc] * B[smem desc]; bf16/fp16 inputs (kind::f16), fp32 accumulate.
 IRIS_D void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
