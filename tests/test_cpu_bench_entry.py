@@ -204,3 +204,35 @@ if __name__ == "__main__":
     assert proc.returncode != 0
     assert "benchmark workers failed" in proc.stderr and "result mismatch on this rank" in proc.stderr
     assert time.time() - t0 < 120
+
+
+def test_runner_skips_a_point_that_exhausts_the_heap_and_goes_on(tmp_path):
+    """A sweep point that asks the symmetric heap for more than it has is reported as skipped (all ranks run the
+    same allocation sequence and fail alike); the points after it still run and the results are written."""
+    script = tmp_path / "bench_big.py"
+    script.write_text(f'''import sys
+sys.path.insert(0, {ROOT!r})
+import torch
+import iris_b200.bench as bench
+
+
+@bench.register
+@bench.axis("num_ranks", [2])
+@bench.axis("mb", [1, 64, 2])
+def grows(state, ctx):
+    buf = ctx.zeros(state["mb"] << 20, dtype=torch.uint8)
+    state.exec(lambda: buf.add_(1))
+
+
+if __name__ == "__main__":
+    bench.main()
+''')
+    out = tmp_path / "big.json"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    proc = subprocess.run([sys.executable, str(script), "--heap_size", str(16 << 20), "--n_warmup", "1", "--n_repeat", "1",
+                           "--benchmark_format", "json", "--benchmark_out", str(out)], env=env, capture_output=True, text=True, timeout=240)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    res = json.loads(out.read_text())["results"]
+    assert [r["params"]["mb"] for r in res] == ["1", "64", "2"]
+    assert [bool(r["skipped"]) for r in res] == [False, True, False]
+    assert "heap too small" in res[1]["skip_reason"]
