@@ -204,6 +204,15 @@ class MoELayer:
 
     __call__ = forward
 
+    @staticmethod
+    def _cpu_fake_quant(t: torch.Tensor, weight: bool = False) -> torch.Tensor:
+        """Round ``t`` the way the e4m3 path stores it: rows in 1 x 128 blocks (activations) or 128 x 128 blocks
+        (a weight given as [out, in]), power-of-two scales."""
+        from ..ops.gemm_fp8 import dequantize, quantize_1x128, quantize_128x128
+
+        q, sc = (quantize_128x128 if weight else quantize_1x128)(t.float(), pow2=True)
+        return dequantize(q, sc, 128 if weight else 1)
+
     def _forward_cpu(self, x, logits):
         """CPU backend: gather every rank's tokens, apply the local experts, sum over ranks."""
         ctx = self.ctx
@@ -220,13 +229,18 @@ class MoELayer:
         ctx.ccl.all_gather(ls, l_loc)
         idx, w = route(ls, self.K)
         part.zero_()
+        # fp8 mode: the same roundings as the e4m3 kernels (tokens and hidden activations in 1 x 128 blocks,
+        # weights in 128 x 128 blocks, power-of-two scales), applied here as quantise + dequantise in fp32
+        q8 = self._cpu_fake_quant if self.fp8 and hasattr(torch, "float8_e4m3fn") else (lambda t, weight=False: t)
+        xs_q = q8(xs)
         for j in range(self.El):
             e = me * self.El + j
             tok, slot = torch.nonzero(idx == e, as_tuple=True)
             if tok.numel() == 0:
                 continue
-            h = xs[tok]
-            y = (torch.nn.functional.silu(h @ self.w_gate[j].float()) * (h @ self.w_up[j].float())) @ self.w_down[j].float()
-            part.index_add_(0, tok, y * w[tok, slot][:, None])
+            h = xs_q[tok]
+            wg, wu, wd = (q8(m.float().t().contiguous(), weight=True).t() for m in (self.w_gate[j], self.w_up[j], self.w_down[j]))
+            hid = q8(torch.nn.functional.silu(h @ wg) * (h @ wu))
+            part.index_add_(0, tok, (hid @ wd) * w[tok, slot][:, None])
         ctx.ccl.all_reduce(tot, part)
         return tot[me * T:(me + 1) * T].to(x.dtype)

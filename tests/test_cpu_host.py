@@ -357,6 +357,48 @@ def test_moe_cpu_world2():
     run_ranks(_moe_cpu, 2)
 
 
+def _moe_cpu_fp8(rank, world):
+    """``fp8=True`` on the CPU backend applies the roundings of the e4m3 kernels (tokens and hidden activations in
+    1 x 128 blocks, weights in 128 x 128 blocks, power-of-two scales): the result equals a reference built from
+    the rounded operands and differs from the unrounded layer by a quantisation error, not by nothing."""
+    import iris_b200 as iris
+    from iris_b200.models import MoELayer, reference_moe
+    from iris_b200.models.moe import route
+
+    if not hasattr(torch, "float8_e4m3fn"):
+        return
+    ctx = iris.iris(1 << 26)
+    T, D, F, K = 12, 256, 128, 2
+    E = 2 * world
+    torch.manual_seed(5)
+    wg, wu, wd = torch.randn(E, D, F) * 0.1, torch.randn(E, D, F) * 0.1, torch.randn(E, F, D) * 0.1
+    sl = slice(rank * 2, rank * 2 + 2)
+    layer = MoELayer(ctx, D, F, E, K, max_tokens=T, w_gate=wg[sl], w_up=wu[sl], w_down=wd[sl], fp8=True)
+    torch.manual_seed(60 + rank)
+    x, logits = torch.randn(T, D), torch.randn(T, E)
+    out = layer(x, logits)
+    fq = MoELayer._cpu_fake_quant
+    wq = lambda w: torch.stack([fq(m.t().contiguous(), weight=True).t() for m in w])          # noqa: E731
+    xq = fq(x)
+    assert not torch.equal(xq, x) and torch.allclose(xq, x, atol=0.3, rtol=0.07)                # e4m3: 3 mantissa bits
+    idx, wts = route(logits, K)
+    ref = torch.zeros(T, D)
+    for t in range(T):
+        for k in range(K):
+            e = int(idx[t, k])
+            h = fq((torch.nn.functional.silu(xq[t:t + 1] @ wq(wg)[e]) * (xq[t:t + 1] @ wq(wu)[e])))
+            ref[t] += (h @ wq(wd)[e])[0] * wts[t, k]
+    assert torch.allclose(out, ref, atol=1e-3, rtol=1e-3)
+    plain = reference_moe(x, logits, wg, wu, wd, K)
+    err = (out - plain).abs().max().item() / plain.abs().max().item()
+    assert 1e-4 < err < 0.15
+    ctx.barrier()
+
+
+def test_moe_cpu_fp8_mode_applies_the_e4m3_roundings():
+    run_ranks(_moe_cpu_fp8, 2)
+
+
 def test_fuse_gate_up_layout():
     from iris_b200.models import fuse_gate_up
 
