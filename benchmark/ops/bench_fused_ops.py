@@ -26,6 +26,18 @@ def _roof(flops, link_bytes):
     return max(flops / (PEAK_TFLOPS * 1e6), link_bytes / (LINK_GBPS * 1e3))
 
 
+def _record_error(state, got, ref):
+    """Counter `max_rel_err` of a benchmark point: largest deviation of a sample of the fused result from an fp32
+    PyTorch product, over the reference's largest magnitude (bf16 rounding gives a few 1e-3). Never raises:
+    a benchmark reports, the tests assert."""
+    try:
+        torch.cuda.synchronize()
+        err = (got.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-12)
+        state.add_counter("max_rel_err", round(err, 6))
+    except Exception:  # noqa: BLE001
+        state.add_counter("max_rel_err", -1.0)
+
+
 @bench.register
 @bench.axis("num_ranks", [1, 2, 4, 8])
 @bench.axis("impl", ["iris", "nccl"])
@@ -55,6 +67,8 @@ def all_gather_matmul(state, ctx):
         state.exec(base)
         return
     ws = ctx.ops.all_gather_matmul(C, A, B, shard_dim=0)
+    r, n = ctx.get_rank(), min(64, M // W)
+    _record_error(state, C[r * (M // W):r * (M // W) + n], A[:n].float() @ B.float())       # this rank's own rows of the gathered product
     state.exec(lambda: ctx.ops.all_gather_matmul(C, A, B, shard_dim=0, workspace=ws, async_op=True))
 
 
@@ -91,10 +105,22 @@ def matmul_reduce(state, ctx):
     if rs:
         C = ctx.zeros((M // W, N), dtype=dt)
         ws = ctx.ops.matmul_reduce_scatter(C, A, B, scatter_rows=True)
+        r, n = ctx.get_rank(), min(64, M // W)
+        ref = torch.zeros(W, n, N, device="cuda")                # row sample of every rank's block, summed over ranks
+        for o in range(W):
+            ref[o] = A[o * (M // W):o * (M // W) + n].float() @ B.float()
+        if W > 1:
+            dist.all_reduce(ref)
+        _record_error(state, C[:n], ref[r])
         state.exec(lambda: ctx.ops.matmul_reduce_scatter(C, A, B, scatter_rows=True, workspace=ws, async_op=True))
     else:
         C = ctx.zeros((M, N), dtype=dt)
         ws = ctx.ops.matmul_all_reduce(C, A, B)
+        n = min(64, M)
+        ref = A[:n].float() @ B.float()
+        if W > 1:
+            dist.all_reduce(ref)
+        _record_error(state, C[:n], ref)
         state.exec(lambda: ctx.ops.matmul_all_reduce(C, A, B, workspace=ws, async_op=True))
 
 
@@ -125,6 +151,8 @@ def matmul_all_gather(state, ctx):
         state.exec(base)
         return
     ws = ctx.ops.matmul_all_gather(C, A, B)
+    r, n = ctx.get_rank(), min(64, M)
+    _record_error(state, C[r * M:r * M + n], A[:n].float() @ B.float())
     state.exec(lambda: ctx.ops.matmul_all_gather(C, A, B, workspace=ws, async_op=True))
 
 
