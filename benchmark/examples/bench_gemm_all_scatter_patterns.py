@@ -41,9 +41,12 @@ LINK_GBPS = 770.0
 def gemm_all_scatter(state, ctx):
     W, M, N, K = ctx.get_num_ranks(), state["M"], state["N"], state["K"]
     dt = getattr(torch, state["dtype"]) if isinstance(state["dtype"], str) else state["dtype"]
+    dev = ctx.get_device()
+    if dev.type != "cuda":
+        dt = torch.float32                                                # gloo ranks: the host fallbacks
     Nl = N // W
-    A = torch.randn(M, K, device="cuda", dtype=dt)
-    B = (torch.randn(Nl, K, device="cuda", dtype=dt) * 0.02).t()          # weight stored (out, in)
+    A = torch.randn(M, K, device=dev, dtype=dt)
+    B = (torch.randn(Nl, K, device=dev, dtype=dt) * 0.02).t()             # weight stored (out, in)
     C = ctx.zeros((M, N), dtype=dt)
     flops_rank = 2.0 * M * Nl * K
     link = (W - 1) * M * Nl * 2
@@ -54,8 +57,8 @@ def gemm_all_scatter(state, ctx):
     state.set_warmup(5)
     pattern = state["pattern"]
     if pattern == "nccl":
-        loc = torch.empty(M, Nl, device="cuda", dtype=dt)
-        parts = torch.empty(W, M, Nl, device="cuda", dtype=dt)
+        loc = torch.empty(M, Nl, device=dev, dtype=dt)
+        parts = torch.empty(W, M, Nl, device=dev, dtype=dt)
 
         def base():
             torch.matmul(A, B, out=loc)
@@ -69,6 +72,14 @@ def gemm_all_scatter(state, ctx):
         return
     cfg = FusedConfig(overlap=pattern, comm_sms=state["comm_sms"] if pattern == "wg_specialized" else 0)
     ws = ctx.ops.matmul_all_gather(C, A, B, scatter_cols=True, config=cfg)
+    try:   # deviation of a row sample of this rank's column block from an fp32 product (a counter: benchmarks report, tests assert)
+        n, r = min(64, M), ctx.get_rank()
+        ref = A[:n].float() @ B.float()
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        state.add_counter("max_rel_err", round((C[:n, r * Nl:(r + 1) * Nl].float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-12), 6))
+    except Exception:  # noqa: BLE001
+        state.add_counter("max_rel_err", -1.0)
     state.exec(lambda: ctx.ops.matmul_all_gather(C, A, B, scatter_cols=True, config=cfg, workspace=ws, async_op=True))
 
 

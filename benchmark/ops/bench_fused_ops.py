@@ -31,7 +31,8 @@ def _record_error(state, got, ref):
     PyTorch product, over the reference's largest magnitude (bf16 rounding gives a few 1e-3). Never raises:
     a benchmark reports, the tests assert."""
     try:
-        torch.cuda.synchronize()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
         err = (got.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-12)
         state.add_counter("max_rel_err", round(err, 6))
     except Exception:  # noqa: BLE001
@@ -46,16 +47,16 @@ def _record_error(state, got, ref):
 @bench.axis("K", [8192])
 def all_gather_matmul(state, ctx):
     W, M, N, K = ctx.get_num_ranks(), state["M"], state["N"], state["K"]
-    dt = torch.bfloat16
-    A = torch.randn(M // W, K, device="cuda", dtype=dt)
-    B = torch.randn(K, N, device="cuda", dtype=dt) * 0.02
+    dt = torch.bfloat16 if ctx.get_device().type == "cuda" else torch.float32          # gloo ranks: the host fallbacks, fp32
+    A = torch.randn(M // W, K, device=ctx.get_device(), dtype=dt)
+    B = torch.randn(K, N, device=ctx.get_device(), dtype=dt) * 0.02
     C = ctx.zeros((M, N), dtype=dt)
     state.set_flops(2 * M * N * K)
     state.set_bytes((W - 1) * (M // W) * K * 2)
     state.set_roofline_us(_roof(2 * M * N * K, (W - 1) * (M // W) * K * 2))
     if state["impl"] == "nccl":
-        Aall = torch.empty(M, K, device="cuda", dtype=dt)
-        Cr = torch.empty(M, N, device="cuda", dtype=dt)
+        Aall = torch.empty(M, K, device=ctx.get_device(), dtype=dt)
+        Cr = torch.empty(M, N, device=ctx.get_device(), dtype=dt)
 
         def base():
             if W > 1:
@@ -84,16 +85,16 @@ def matmul_reduce(state, ctx):
     rs = state["op"] == "reduce_scatter"
     if rs and M % (128 * W):
         state.skip("row reduce-scatter needs M to be a multiple of 128 * ranks")
-    dt = torch.bfloat16
-    A = torch.randn(M, K, device="cuda", dtype=dt)
-    B = torch.randn(K, N, device="cuda", dtype=dt) * 0.02
+    dt = torch.bfloat16 if ctx.get_device().type == "cuda" else torch.float32          # gloo ranks: the host fallbacks, fp32
+    A = torch.randn(M, K, device=ctx.get_device(), dtype=dt)
+    B = torch.randn(K, N, device=ctx.get_device(), dtype=dt) * 0.02
     link = (W - 1) / W * M * N * 2 * (1 if rs else 2)
     state.set_flops(2 * M * N * K)
     state.set_bytes(int(link))
     state.set_roofline_us(_roof(2 * M * N * K, link))
     if state["impl"] == "nccl":
-        P = torch.empty(M, N, device="cuda", dtype=dt)
-        R = torch.empty(M // W, N, device="cuda", dtype=dt) if rs else None
+        P = torch.empty(M, N, device=ctx.get_device(), dtype=dt)
+        R = torch.empty(M // W, N, device=ctx.get_device(), dtype=dt) if rs else None
 
         def base():
             torch.matmul(A, B, out=P)
@@ -106,7 +107,7 @@ def matmul_reduce(state, ctx):
         C = ctx.zeros((M // W, N), dtype=dt)
         ws = ctx.ops.matmul_reduce_scatter(C, A, B, scatter_rows=True)
         r, n = ctx.get_rank(), min(64, M // W)
-        ref = torch.zeros(W, n, N, device="cuda")                # row sample of every rank's block, summed over ranks
+        ref = torch.zeros(W, n, N, device=ctx.get_device())                # row sample of every rank's block, summed over ranks
         for o in range(W):
             ref[o] = A[o * (M // W):o * (M // W) + n].float() @ B.float()
         if W > 1:
@@ -132,16 +133,16 @@ def matmul_reduce(state, ctx):
 @bench.axis("K", [8192])
 def matmul_all_gather(state, ctx):
     W, M, N, K = ctx.get_num_ranks(), state["M"], state["N"], state["K"]
-    dt = torch.bfloat16
-    A = torch.randn(M, K, device="cuda", dtype=dt)
-    B = torch.randn(K, N, device="cuda", dtype=dt) * 0.02
+    dt = torch.bfloat16 if ctx.get_device().type == "cuda" else torch.float32          # gloo ranks: the host fallbacks, fp32
+    A = torch.randn(M, K, device=ctx.get_device(), dtype=dt)
+    B = torch.randn(K, N, device=ctx.get_device(), dtype=dt) * 0.02
     C = ctx.zeros((W * M, N), dtype=dt)
     state.set_flops(2 * M * N * K)
     state.set_bytes((W - 1) * M * N * 2)
     state.set_roofline_us(_roof(2 * M * N * K, (W - 1) * M * N * 2))
     if state["impl"] == "nccl":
-        loc = torch.empty(M, N, device="cuda", dtype=dt)
-        full = torch.empty(W * M, N, device="cuda", dtype=dt)
+        loc = torch.empty(M, N, device=ctx.get_device(), dtype=dt)
+        full = torch.empty(W * M, N, device=ctx.get_device(), dtype=dt)
 
         def base():
             torch.matmul(A, B, out=loc)

@@ -236,3 +236,33 @@ if __name__ == "__main__":
     assert [r["params"]["mb"] for r in res] == ["1", "64", "2"]
     assert [bool(r["skipped"]) for r in res] == [False, True, False]
     assert "heap too small" in res[1]["skip_reason"]
+
+
+def test_fused_ops_benchmark_on_the_cpu_backend(tmp_path):
+    """The fused-ops sweep on two gloo ranks (host fallbacks, fp32): every point is timed and carries the deviation of
+    a row sample from an fp32 product, which is rounding noise there."""
+    out = tmp_path / "fused.json"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, os.path.join(ROOT, "benchmark", "ops", "bench_fused_ops.py"), "--axis_num_ranks=2", "--axis_impl=iris",
+           "--axis_M=256", "--axis_N=64", "--axis_K=128", "--n_warmup", "1", "--n_repeat", "2", "--benchmark_format", "json",
+           "--benchmark_out", str(out)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    res = json.loads(out.read_text())["results"]
+    assert {r["benchmark"] for r in res} == {"all_gather_matmul", "matmul_reduce", "matmul_all_gather"}
+    assert len(res) == 4 and all(not r["skipped"] and r["gpu_time_ms"] > 0 for r in res)
+    assert all(0 <= r["counters"]["max_rel_err"] < 1e-4 for r in res)
+
+
+def test_overlap_pattern_benchmark_on_the_cpu_backend(tmp_path):
+    """GEMM + all-scatter under every overlap pattern on two gloo ranks: all patterns give the same, correct result."""
+    out = tmp_path / "patterns.json"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, os.path.join(ROOT, "benchmark", "examples", "bench_gemm_all_scatter_patterns.py"), "--axis_num_ranks=2",
+           "--axis_pattern=bulk_synchronous,fused,wg_specialized", "--axis_M=128", "--axis_N=128", "--axis_K=64", "--n_warmup", "1",
+           "--n_repeat", "2", "--benchmark_format", "json", "--benchmark_out", str(out)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    res = json.loads(out.read_text())["results"]
+    assert [r["params"]["pattern"] for r in res] == ["bulk_synchronous", "fused", "wg_specialized"]
+    assert all(not r["skipped"] and r["gpu_time_ms"] > 0 and 0 <= r["counters"]["max_rel_err"] < 1e-4 for r in res)
