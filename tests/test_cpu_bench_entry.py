@@ -266,3 +266,22 @@ def test_overlap_pattern_benchmark_on_the_cpu_backend(tmp_path):
     res = json.loads(out.read_text())["results"]
     assert [r["params"]["pattern"] for r in res] == ["bulk_synchronous", "fused", "wg_specialized"]
     assert all(not r["skipped"] and r["gpu_time_ms"] > 0 and 0 <= r["counters"]["max_rel_err"] < 1e-4 for r in res)
+
+
+def test_moe_benchmark_on_the_cpu_backend(tmp_path):
+    """The MoE sweep on two gloo ranks: the layer's host path agrees with the stock PyTorch form of the benchmark (all-to-all,
+    per-expert GEMM loop, weighted index_add) exactly in fp32, and within the e4m3 quantisation error in fp8 mode."""
+    out = tmp_path / "moe.json"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, os.path.join(ROOT, "benchmark", "examples", "bench_moe.py"), "--axis_num_ranks=2", "--axis_tokens=16",
+           "--axis_hidden=256", "--axis_ffn=128", "--axis_experts_per_rank=2", "--axis_top_k=2", "--n_warmup", "1", "--n_repeat", "2",
+           "--benchmark_format", "json", "--benchmark_out", str(out)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    res = {r["params"]["impl"]: r for r in json.loads(out.read_text())["results"]}
+    assert set(res) == {"iris", "iris_fp8", "nccl"} and all(not r["skipped"] and r["gpu_time_ms"] > 0 for r in res.values())
+    assert res["iris"]["counters"]["max_rel_err_vs_unfused"] < 1e-5
+    import torch
+
+    if hasattr(torch, "float8_e4m3fn"):
+        assert 1e-4 < res["iris_fp8"]["counters"]["max_rel_err_vs_unfused"] < 0.15
