@@ -285,3 +285,20 @@ def test_moe_benchmark_on_the_cpu_backend(tmp_path):
 
     if hasattr(torch, "float8_e4m3fn"):
         assert 1e-4 < res["iris_fp8"]["counters"]["max_rel_err_vs_unfused"] < 0.15
+
+
+@pytest.mark.parametrize("script,args,points", [
+    ("benchmark/examples/bench_ring_attention.py", ["--axis_seq_per_rank=256"], 3),       # not causal, causal, causal zigzag
+    ("benchmark/examples/bench_flash_decode.py", ["--axis_batch=2", "--axis_total_kv=2048,4096"], 2),
+])
+def test_attention_benchmarks_on_the_cpu_backend(tmp_path, script, args, points):
+    """Ring attention and distributed flash decode sweeps on two gloo ranks: every timed point carries the deviation of a
+    sample of the layer's output from fp32 attention over the keys of all ranks."""
+    out = tmp_path / "attn.json"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, os.path.join(ROOT, script), "--axis_num_ranks=2", "--axis_impl=iris", *args, "--n_warmup", "1", "--n_repeat", "2",
+           "--benchmark_format", "json", "--benchmark_out", str(out)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    timed = [r for r in json.loads(out.read_text())["results"] if not r["skipped"]]
+    assert len(timed) == points and all(r["gpu_time_ms"] > 0 and 0 <= r["counters"]["max_rel_err"] < 1e-4 for r in timed)
