@@ -48,7 +48,7 @@ def flash_decode(state, ctx):
     kv_bytes = 2 * B * L * Hkv * D * 2
     state.set_bytes(kv_bytes)
     state.set_roofline_us(kv_bytes / (HBM_GBPS * 1e3))
-    state.set_repeat(30)
+    state.set_repeat(min(state.n_repeat, 30))            # fewer repeats than the default, never more than asked for
     if state["impl"] == "nccl":
         po = torch.empty(B, Hq, D, device=dev, dtype=dt)
         g_o = torch.empty(W, B, Hq, D, device=dev, dtype=dt)

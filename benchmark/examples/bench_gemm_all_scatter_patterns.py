@@ -53,8 +53,8 @@ def gemm_all_scatter(state, ctx):
     state.set_flops(flops_rank * W)                                      # aggregate over ranks: every rank does flops_rank in the same time
     state.set_bytes(link)
     state.set_roofline_us(max(flops_rank / (PEAK_TFLOPS * 1e6), link / (LINK_GBPS * 1e3)))
-    state.set_repeat(20)
-    state.set_warmup(5)
+    state.set_repeat(min(state.n_repeat, 20))            # long kernels: fewer repeats than the default, never more than asked for
+    state.set_warmup(min(state.n_warmup, 5))
     pattern = state["pattern"]
     if pattern == "nccl":
         loc = torch.empty(M, Nl, device=dev, dtype=dt)

@@ -96,8 +96,8 @@ def moe_layer(state, ctx):
     state.set_flops(flops)
     # roofline: the FLOPs at the measured bf16 tensor throughput (fp8 rows: at twice that)
     state.set_roofline_us(flops / (PEAK_TFLOPS * 1e6 * (2 if state["impl"] == "iris_fp8" else 1)))
-    state.set_repeat(20)
-    state.set_warmup(5)
+    state.set_repeat(min(state.n_repeat, 20))            # long kernels: fewer repeats than the default, never more than asked for
+    state.set_warmup(min(state.n_warmup, 5))
     rank = ctx.get_rank()
     if state["impl"] == "nccl":
         state.exec(lambda: out.copy_(moe_nccl(x, logits, wg, wu, wd, K, W, rank)))

@@ -44,8 +44,8 @@ def ring_attention(state, ctx):
     flops = 4.0 * S * (W * S) * Hq * D * (0.5 if causal else 1.0)
     state.set_flops(flops)
     state.set_roofline_us(flops / (PEAK_TFLOPS * 1e6))
-    state.set_repeat(20)
-    state.set_warmup(5)
+    state.set_repeat(min(state.n_repeat, 20))            # long kernels: fewer repeats than the default, never more than asked for
+    state.set_warmup(min(state.n_warmup, 5))
     if state["impl"] == "nccl":
         if state["layout"] != "contiguous":
             state.skip("the NCCL baseline gathers a contiguous sequence")

@@ -274,7 +274,7 @@ def test_moe_benchmark_on_the_cpu_backend(tmp_path):
     out = tmp_path / "moe.json"
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
     cmd = [sys.executable, os.path.join(ROOT, "benchmark", "examples", "bench_moe.py"), "--axis_num_ranks=2", "--axis_tokens=16",
-           "--axis_hidden=256", "--axis_ffn=128", "--axis_experts_per_rank=2", "--axis_top_k=2", "--n_warmup", "1", "--n_repeat", "2",
+           "--axis_hidden=128", "--axis_ffn=128", "--axis_experts_per_rank=2", "--axis_top_k=2", "--n_warmup", "1", "--n_repeat", "1",
            "--benchmark_format", "json", "--benchmark_out", str(out)]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0, proc.stderr[-3000:]
